@@ -1,0 +1,105 @@
+"""ctypes binding of ``liblfm25_b200.so`` (the C ABI declared in ``include/lfm25_b200.h``).
+
+The library is the product; there is no fallback.  If it has not been built, importing this
+module raises, and every op refuses to run.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIBRARY_PATH = os.path.join(HERE, "liblfm25_b200.so")
+
+
+class Lfm25Error(RuntimeError):
+    """An entry point returned a negative status; ``code`` is the LFM25_ERR_* value."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[{code}] {message}")
+        self.code = code
+        self.message = message
+
+
+OK = 0
+ERR_INVALID_ARGUMENT = -1
+ERR_BUFFER_TOO_SMALL = -2
+ERR_UNSUPPORTED = -3
+ERR_OVERFLOW = -4
+ERR_CUDA = -5
+ERR_NULL_POINTER = -6
+
+
+class Slice(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("len", ctypes.c_size_t)]
+
+
+def _launch_struct(name, slices_and_sizes):
+    fields = []
+    for field in slices_and_sizes:
+        if isinstance(field, tuple):
+            fields.append(field)
+        elif field.startswith("#"):
+            fields.append((field[1:], ctypes.c_size_t))
+        else:
+            fields.append((field, Slice))
+    return type(name, (ctypes.Structure,), {"_fields_": fields})
+
+
+KvCacheWriteLaunch = _launch_struct("KvCacheWriteLaunch", [
+    "#page_size", "key", "value", "key_cache", "value_cache", "slot_mapping", "#num_tokens", "#num_pages"])
+QkPostprocessLaunch = _launch_struct("QkPostprocessLaunch", [
+    "#page_size", "query", "key", "value", "query_norm", "key_norm", "inv_freq", "position_ids",
+    "slot_mapping", "key_cache", "value_cache", "#num_tokens", "#num_pages", ("eps", ctypes.c_float)])
+PagedAttentionLaunch = _launch_struct("PagedAttentionLaunch", [
+    "#page_size", "query", "key_cache", "value_cache", "block_table", "position_ids", "output",
+    "#num_tokens", "#num_pages"])
+FastRaggedAttentionLaunch = _launch_struct("FastRaggedAttentionLaunch", [
+    "#page_size", "query", "key_cache", "value_cache", "block_tables", "request_slots", "position_ids",
+    "output", "#num_tokens", "#num_pages", "#block_table_stride"])
+SplitKRaggedAttentionLaunch = _launch_struct("SplitKRaggedAttentionLaunch", [
+    "#page_size", "query", "key_cache", "value_cache", "block_tables", "request_slots", "position_ids",
+    "partials", "output", "#num_tokens", "#num_pages", "#block_table_stride", "#num_splits"])
+
+# name -> (restype, argtypes); every symbol that include/lfm25_b200.h declares
+_P = ctypes.POINTER
+_size = ctypes.c_size_t
+_stream = ctypes.c_void_p
+PROTOTYPES = {
+    "lfm25_last_error": (ctypes.c_char_p, []),
+    "lfm25_version": (ctypes.c_char_p, []),
+    "lfm25_device_status": (ctypes.c_int32, [_stream, _P(ctypes.c_uint32)]),
+    "lfm25_kv_cache_write_lfm2_bf16": (ctypes.c_int32, [_stream, _P(KvCacheWriteLaunch)]),
+    "lfm25_qk_norm_rope_kv_write_decode": (ctypes.c_int32, [_stream, _P(QkPostprocessLaunch)]),
+    "lfm25_paged_attention_fast_lfm2_bf16": (ctypes.c_int32, [_stream, _P(PagedAttentionLaunch)]),
+    "lfm25_paged_ragged_attention_fast_lfm2_bf16": (ctypes.c_int32, [_stream, _P(FastRaggedAttentionLaunch)]),
+    "lfm25_paged_ragged_attention_splitk_lfm2_bf16": (ctypes.c_int32, [_stream, _P(SplitKRaggedAttentionLaunch)]),
+    "lfm25_splitk_workspace_elements": (_size, [_size]),
+    "lfm25_splitk_decode_splits": (_size, [_size, _size, _size]),
+    "lfm25_quantize_bf16_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, ctypes.c_float]),
+    "lfm25_silu_mul_packed_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
+    "lfm25_silu_mul_packed_bf16_to_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size, ctypes.c_float]),
+}
+
+_library = None
+
+
+def library() -> ctypes.CDLL:
+    global _library
+    if _library is None:
+        if not os.path.exists(LIBRARY_PATH):
+            raise ImportError(
+                f"{LIBRARY_PATH} is missing: build it with `python lfm25-inference_b200/build.py`. "
+                "There is no CPU or PyTorch fallback for this library.")
+        handle = ctypes.CDLL(LIBRARY_PATH)
+        for name, (restype, argtypes) in PROTOTYPES.items():
+            function = getattr(handle, name)
+            function.restype = restype
+            function.argtypes = argtypes
+        _library = handle
+    return _library
+
+
+def check(code: int) -> None:
+    if code != OK:
+        raise Lfm25Error(code, library().lfm25_last_error().decode())

@@ -1,0 +1,48 @@
+"""Build recipe of the CUDA library (stands in for the reference's build.rs, which compiles its
+kernels with nvcc at build time).  Produces ``liblfm25_b200.so`` next to this file, for sm_100a only.
+
+    python lfm25-inference_b200/build.py [--force] [--verbose]
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+OUTPUT = os.path.join(HERE, "liblfm25_b200.so")
+SOURCES = ["api.cu", "attention.cu", "kv_cache.cu", "fp8_elementwise.cu"]
+HEADERS = ["common.cuh", "kernels.h", os.path.join("..", "..", "include", "lfm25_b200.h")]
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared", "-cudart", "static",
+]
+
+
+def _stale() -> bool:
+    if not os.path.exists(OUTPUT):
+        return True
+    built = os.path.getmtime(OUTPUT)
+    inputs = [os.path.join(CSRC, name) for name in SOURCES + HEADERS] + [os.path.abspath(__file__)]
+    return any(os.path.getmtime(path) > built for path in inputs)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not _stale():
+        return OUTPUT
+    nvcc = os.environ.get("NVCC", "nvcc")
+    flags = [flag for flag in NVCC_FLAGS if flag != "--use_fast_math=false"]
+    if verbose:
+        flags += ["-Xptxas", "-v"]
+    command = [nvcc, *flags, "-o", OUTPUT, *[os.path.join(CSRC, name) for name in SOURCES]]
+    result = subprocess.run(command, capture_output=True, text=True)
+    if verbose or result.returncode != 0:
+        sys.stderr.write(result.stdout + result.stderr)
+    if result.returncode != 0:
+        raise RuntimeError("nvcc failed building liblfm25_b200.so")
+    return OUTPUT
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

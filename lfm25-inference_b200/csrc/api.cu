@@ -1,0 +1,399 @@
+// extern "C" boundary of the library: host-side validation (the reference wrappers' `ensure!`
+// checks, in the same order) followed by the kernel launch.  Nothing is launched on error.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <cmath>
+#include <limits>
+
+#include "../../include/lfm25_b200.h"
+#include "common.cuh"
+#include "kernels.h"
+
+namespace {
+
+thread_local char g_last_error[256] = "";
+
+int32_t fail(int32_t code, const char* format, ...) {
+    va_list arguments;
+    va_start(arguments, format);
+    vsnprintf(g_last_error, sizeof g_last_error, format, arguments);
+    va_end(arguments);
+    return code;
+}
+
+#define LFM25_ENSURE(condition, code, ...) \
+    do {                                   \
+        if (!(condition)) {                \
+            return fail(code, __VA_ARGS__); \
+        }                                  \
+    } while (0)
+
+bool checked_mul(size_t a, size_t b, size_t* out) {
+    if (a != 0 && b > std::numeric_limits<size_t>::max() / a) {
+        return false;
+    }
+    *out = a * b;
+    return true;
+}
+
+// pages * 8 * page_size * 64 elements
+bool cache_elements(size_t num_pages, size_t page_size, size_t* out) {
+    size_t value = 0;
+    return checked_mul(num_pages, 8, &value) && checked_mul(value, page_size, &value) &&
+           checked_mul(value, 64, out);
+}
+
+int32_t cuda_result(cudaError_t status, const char* what) {
+    if (status == cudaSuccess) {
+        return LFM25_OK;
+    }
+    return fail(LFM25_ERR_CUDA, "%s: %s", what, cudaGetErrorString(status));
+}
+
+// Device status words shared by all kernels with bounded waits.
+__device__ unsigned int g_device_status[4];
+
+unsigned int* device_status_pointer() {
+    // One address per device; looked up on first use with that device current.
+    static thread_local int cached_device = -1;
+    static thread_local unsigned int* cached_pointer = nullptr;
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess) {
+        return nullptr;
+    }
+    if (device != cached_device) {
+        void* pointer = nullptr;
+        if (cudaGetSymbolAddress(&pointer, g_device_status) != cudaSuccess) {
+            return nullptr;
+        }
+        cached_pointer = static_cast<unsigned int*>(pointer);
+        cached_device = device;
+    }
+    return cached_pointer;
+}
+
+// Checks shared by the three attention entry points that take block tables per request
+// (src/cuda/kernels/attention_async_fast.rs:215-282).
+int32_t validate_ragged_common(size_t page_size, const lfm25_slice& query, const lfm25_slice& key_cache,
+                               const lfm25_slice& value_cache, const lfm25_slice& block_tables,
+                               const lfm25_slice* request_slots, const lfm25_slice& position_ids,
+                               const lfm25_slice& output, size_t num_tokens, size_t num_pages,
+                               size_t block_table_stride) {
+    LFM25_ENSURE(num_tokens > 0, LFM25_ERR_INVALID_ARGUMENT, "fast-exp ragged attention requires tokens");
+    LFM25_ENSURE(num_pages > 0, LFM25_ERR_INVALID_ARGUMENT, "fast-exp ragged attention requires cache pages");
+    LFM25_ENSURE(page_size == 16 || page_size == 32, LFM25_ERR_INVALID_ARGUMENT,
+                 "unsupported fast-exp ragged page size %zu", page_size);
+    LFM25_ENSURE(page_size == 16, LFM25_ERR_UNSUPPORTED, "page size 32 is not built; use 16");
+    LFM25_ENSURE(block_table_stride > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "fast-exp ragged block table stride must be positive");
+    LFM25_ENSURE(block_tables.len >= block_table_stride, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "fast-exp ragged block tables too small");
+    LFM25_ENSURE(block_tables.len % block_table_stride == 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "fast-exp ragged block tables not row aligned");
+    LFM25_ENSURE(request_slots == nullptr || request_slots->len >= num_tokens, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "fast-exp ragged request slots too small");
+    LFM25_ENSURE(position_ids.len >= num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "fast-exp ragged positions too small");
+    size_t q_required = 0;
+    LFM25_ENSURE(checked_mul(num_tokens, 32 * 64, &q_required), LFM25_ERR_OVERFLOW,
+                 "fast-exp ragged query size overflow");
+    size_t cache_required = 0;
+    LFM25_ENSURE(cache_elements(num_pages, page_size, &cache_required), LFM25_ERR_OVERFLOW,
+                 "fast-exp ragged cache size overflow");
+    LFM25_ENSURE(query.len >= q_required, LFM25_ERR_BUFFER_TOO_SMALL, "fast-exp ragged query storage too small");
+    LFM25_ENSURE(output.len >= q_required, LFM25_ERR_BUFFER_TOO_SMALL, "fast-exp ragged output storage too small");
+    LFM25_ENSURE(key_cache.len >= cache_required, LFM25_ERR_BUFFER_TOO_SMALL, "fast-exp ragged K cache too small");
+    LFM25_ENSURE(value_cache.len >= cache_required, LFM25_ERR_BUFFER_TOO_SMALL, "fast-exp ragged V cache too small");
+    LFM25_ENSURE(query.ptr && output.ptr && key_cache.ptr && value_cache.ptr && block_tables.ptr &&
+                     (request_slots == nullptr || request_slots->ptr) && position_ids.ptr,
+                 LFM25_ERR_NULL_POINTER, "fast-exp ragged attention received a null device pointer");
+    // Limits of this implementation's 32-bit grid and TMA row coordinates.
+    LFM25_ENSURE(num_tokens <= (1u << 24), LFM25_ERR_INVALID_ARGUMENT, "attention grid size exceeds u32");
+    LFM25_ENSURE(num_pages <= (1u << 24), LFM25_ERR_INVALID_ARGUMENT, "attention page pool exceeds 2^24 pages");
+    LFM25_ENSURE((reinterpret_cast<uintptr_t>(key_cache.ptr) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(value_cache.ptr) & 15) == 0,
+                 LFM25_ERR_INVALID_ARGUMENT, "KV cache must be 16-byte aligned");
+    return LFM25_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* lfm25_last_error(void) { return g_last_error; }
+
+const char* lfm25_version(void) { return "lfm25_b200 0.1 sm_100a"; }
+
+int32_t lfm25_device_status(void* stream, uint32_t out[4]) {
+    LFM25_ENSURE(out != nullptr, LFM25_ERR_NULL_POINTER, "device status output is null");
+    unsigned int* pointer = device_status_pointer();
+    LFM25_ENSURE(pointer != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+    cudaError_t status = cudaMemcpyAsync(out, pointer, 4 * sizeof(uint32_t), cudaMemcpyDeviceToHost, cuda_stream);
+    if (status == cudaSuccess) {
+        status = cudaMemsetAsync(pointer, 0, 4 * sizeof(uint32_t), cuda_stream);
+    }
+    if (status == cudaSuccess) {
+        status = cudaStreamSynchronize(cuda_stream);
+    }
+    return cuda_result(status, "device status read failed");
+}
+
+int32_t lfm25_kv_cache_write_lfm2_bf16(void* stream, const lfm25_kv_cache_write_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "KV cache write launch is null");
+    const lfm25_kv_cache_write_launch& l = *launch;
+    LFM25_ENSURE(l.num_tokens > 0, LFM25_ERR_INVALID_ARGUMENT, "KV cache write requires at least one token");
+    LFM25_ENSURE(l.num_pages > 0, LFM25_ERR_INVALID_ARGUMENT, "KV cache requires at least one page");
+    size_t required = 0;
+    LFM25_ENSURE(checked_mul(l.num_tokens, 8 * 64, &required), LFM25_ERR_OVERFLOW, "KV input size overflow");
+    size_t cache_required = 0;
+    LFM25_ENSURE(cache_elements(l.num_pages, l.page_size, &cache_required), LFM25_ERR_OVERFLOW,
+                 "KV cache size overflow");
+    LFM25_ENSURE(l.key.len >= required, LFM25_ERR_BUFFER_TOO_SMALL, "K storage too small");
+    LFM25_ENSURE(l.value.len >= required, LFM25_ERR_BUFFER_TOO_SMALL, "V storage too small");
+    LFM25_ENSURE(l.key_cache.len >= cache_required, LFM25_ERR_BUFFER_TOO_SMALL, "K cache storage too small");
+    LFM25_ENSURE(l.value_cache.len >= cache_required, LFM25_ERR_BUFFER_TOO_SMALL, "V cache storage too small");
+    LFM25_ENSURE(l.slot_mapping.len >= l.num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "slot mapping storage too small");
+    LFM25_ENSURE(l.page_size == 16 || l.page_size == 32, LFM25_ERR_INVALID_ARGUMENT, "unsupported KV page size %zu",
+                 l.page_size);
+    LFM25_ENSURE(l.page_size == 16, LFM25_ERR_UNSUPPORTED, "page size 32 is not built; use 16");
+    LFM25_ENSURE(l.key.ptr && l.value.ptr && l.key_cache.ptr && l.value_cache.ptr && l.slot_mapping.ptr,
+                 LFM25_ERR_NULL_POINTER, "KV cache write received a null device pointer");
+    LFM25_ENSURE(l.num_tokens <= 0x7fffffffu, LFM25_ERR_INVALID_ARGUMENT, "KV cache write grid size exceeds u32");
+    LFM25_ENSURE(((reinterpret_cast<uintptr_t>(l.key.ptr) | reinterpret_cast<uintptr_t>(l.value.ptr) |
+                   reinterpret_cast<uintptr_t>(l.key_cache.ptr) | reinterpret_cast<uintptr_t>(l.value_cache.ptr)) &
+                  15) == 0,
+                 LFM25_ERR_INVALID_ARGUMENT, "KV cache write buffers must be 16-byte aligned");
+    return cuda_result(
+        lfm25::launch_kv_cache_write(static_cast<cudaStream_t>(stream), l.key.ptr, l.value.ptr, l.key_cache.ptr,
+                                     l.value_cache.ptr, static_cast<const int64_t*>(l.slot_mapping.ptr), l.num_tokens,
+                                     l.num_pages),
+        "KV cache write launch failed");
+}
+
+int32_t lfm25_qk_norm_rope_kv_write_decode(void* stream, const lfm25_qk_postprocess_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "fused QK postprocess launch is null");
+    const lfm25_qk_postprocess_launch& l = *launch;
+    LFM25_ENSURE(l.num_tokens > 0, LFM25_ERR_INVALID_ARGUMENT, "fused QK postprocess requires tokens");
+    LFM25_ENSURE(l.num_pages > 0, LFM25_ERR_INVALID_ARGUMENT, "fused QK postprocess requires cache pages");
+    size_t q_required = 0;
+    LFM25_ENSURE(checked_mul(l.num_tokens, 32 * 64, &q_required), LFM25_ERR_OVERFLOW, "fused Q storage overflow");
+    size_t kv_required = 0;
+    LFM25_ENSURE(checked_mul(l.num_tokens, 8 * 64, &kv_required), LFM25_ERR_OVERFLOW, "fused KV storage overflow");
+    size_t cache_required = 0;
+    LFM25_ENSURE(cache_elements(l.num_pages, l.page_size, &cache_required), LFM25_ERR_OVERFLOW,
+                 "fused cache storage overflow");
+    LFM25_ENSURE(l.query.len >= q_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused Q storage too small");
+    LFM25_ENSURE(l.key.len >= kv_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused K storage too small");
+    LFM25_ENSURE(l.value.len >= kv_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused V storage too small");
+    LFM25_ENSURE(l.query_norm.len >= 64, LFM25_ERR_BUFFER_TOO_SMALL, "query norm weight too small");
+    LFM25_ENSURE(l.key_norm.len >= 64, LFM25_ERR_BUFFER_TOO_SMALL, "key norm weight too small");
+    LFM25_ENSURE(l.inv_freq.len >= 32, LFM25_ERR_BUFFER_TOO_SMALL, "RoPE frequency storage too small");
+    LFM25_ENSURE(l.position_ids.len >= l.num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "position storage too small");
+    LFM25_ENSURE(l.slot_mapping.len >= l.num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "slot mapping storage too small");
+    LFM25_ENSURE(l.key_cache.len >= cache_required, LFM25_ERR_BUFFER_TOO_SMALL, "K cache storage too small");
+    LFM25_ENSURE(l.value_cache.len >= cache_required, LFM25_ERR_BUFFER_TOO_SMALL, "V cache storage too small");
+    LFM25_ENSURE(l.page_size == 16 || l.page_size == 32, LFM25_ERR_INVALID_ARGUMENT,
+                 "unsupported fused QK page size %zu", l.page_size);
+    LFM25_ENSURE(l.page_size == 16, LFM25_ERR_UNSUPPORTED, "page size 32 is not built; use 16");
+    LFM25_ENSURE(l.num_tokens <= 0x7fffffffu, LFM25_ERR_INVALID_ARGUMENT, "fused QK grid size exceeds u32");
+    LFM25_ENSURE(l.query.ptr && l.key.ptr && l.value.ptr && l.query_norm.ptr && l.key_norm.ptr && l.inv_freq.ptr &&
+                     l.position_ids.ptr && l.slot_mapping.ptr && l.key_cache.ptr && l.value_cache.ptr,
+                 LFM25_ERR_NULL_POINTER, "fused QK postprocess received a null device pointer");
+    lfm25::QkPostprocessArgs args;
+    args.query = l.query.ptr;
+    args.key = l.key.ptr;
+    args.value = l.value.ptr;
+    args.query_norm = l.query_norm.ptr;
+    args.key_norm = l.key_norm.ptr;
+    args.inv_freq = static_cast<const float*>(l.inv_freq.ptr);
+    args.position_ids = static_cast<const uint32_t*>(l.position_ids.ptr);
+    args.slot_mapping = static_cast<const int64_t*>(l.slot_mapping.ptr);
+    args.key_cache = l.key_cache.ptr;
+    args.value_cache = l.value_cache.ptr;
+    args.num_tokens = l.num_tokens;
+    args.num_pages = l.num_pages;
+    args.eps = l.eps;
+    return cuda_result(lfm25::launch_qk_norm_rope_kv_write_decode(static_cast<cudaStream_t>(stream), args),
+                       "fused QK postprocess launch failed");
+}
+
+int32_t lfm25_paged_attention_fast_lfm2_bf16(void* stream, const lfm25_paged_attention_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "fast-exp attention launch is null");
+    const lfm25_paged_attention_launch& l = *launch;
+    LFM25_ENSURE(l.num_tokens > 0, LFM25_ERR_INVALID_ARGUMENT, "fast-exp attention requires tokens");
+    LFM25_ENSURE(l.num_pages > 0, LFM25_ERR_INVALID_ARGUMENT, "fast-exp attention requires cache pages");
+    LFM25_ENSURE(l.block_table.len > 0, LFM25_ERR_INVALID_ARGUMENT, "fast-exp attention block table is empty");
+    // One sequence is the ragged form with a single row that every token reads.
+    const int32_t status = validate_ragged_common(l.page_size, l.query, l.key_cache, l.value_cache, l.block_table,
+                                                  nullptr, l.position_ids, l.output, l.num_tokens, l.num_pages,
+                                                  l.block_table.len);
+    if (status != LFM25_OK) {
+        return status;
+    }
+    lfm25::AttentionLaunch args = {};
+    args.query = l.query.ptr;
+    args.key_cache = l.key_cache.ptr;
+    args.value_cache = l.value_cache.ptr;
+    args.block_tables = static_cast<const uint32_t*>(l.block_table.ptr);
+    args.request_slots = nullptr;
+    args.position_ids = static_cast<const uint32_t*>(l.position_ids.ptr);
+    args.output = l.output.ptr;
+    args.partials = nullptr;
+    args.status = device_status_pointer();
+    args.num_tokens = l.num_tokens;
+    args.num_pages = l.num_pages;
+    args.block_table_stride = l.block_table.len;
+    args.block_table_rows = 1;
+    args.num_splits = 1;
+    LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
+                       "fast-exp attention launch failed");
+}
+
+int32_t lfm25_paged_ragged_attention_fast_lfm2_bf16(void* stream, const lfm25_fast_ragged_attention_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "fast-exp ragged attention launch is null");
+    const lfm25_fast_ragged_attention_launch& l = *launch;
+    const int32_t status =
+        validate_ragged_common(l.page_size, l.query, l.key_cache, l.value_cache, l.block_tables, &l.request_slots,
+                               l.position_ids, l.output, l.num_tokens, l.num_pages, l.block_table_stride);
+    if (status != LFM25_OK) {
+        return status;
+    }
+    lfm25::AttentionLaunch args = {};
+    args.query = l.query.ptr;
+    args.key_cache = l.key_cache.ptr;
+    args.value_cache = l.value_cache.ptr;
+    args.block_tables = static_cast<const uint32_t*>(l.block_tables.ptr);
+    args.request_slots = static_cast<const uint32_t*>(l.request_slots.ptr);
+    args.position_ids = static_cast<const uint32_t*>(l.position_ids.ptr);
+    args.output = l.output.ptr;
+    args.partials = nullptr;
+    args.status = device_status_pointer();
+    args.num_tokens = l.num_tokens;
+    args.num_pages = l.num_pages;
+    args.block_table_stride = l.block_table_stride;
+    args.block_table_rows = l.block_tables.len / l.block_table_stride;
+    args.num_splits = 1;
+    LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
+                       "fast-exp ragged attention launch failed");
+}
+
+int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream,
+                                                      const lfm25_splitk_ragged_attention_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "split-K ragged attention launch is null");
+    const lfm25_splitk_ragged_attention_launch& l = *launch;
+    const int32_t status =
+        validate_ragged_common(l.page_size, l.query, l.key_cache, l.value_cache, l.block_tables, &l.request_slots,
+                               l.position_ids, l.output, l.num_tokens, l.num_pages, l.block_table_stride);
+    if (status != LFM25_OK) {
+        return status;
+    }
+    LFM25_ENSURE(l.num_splits >= 2 && l.num_splits <= 8, LFM25_ERR_INVALID_ARGUMENT,
+                 "split-K ragged attention requires 2..=8 splits");
+    size_t partial_required = 0;
+    LFM25_ENSURE(checked_mul(l.num_tokens, 32, &partial_required) &&
+                     checked_mul(partial_required, l.num_splits, &partial_required) &&
+                     checked_mul(partial_required, 66, &partial_required),
+                 LFM25_ERR_OVERFLOW, "split-K partial workspace size overflow");
+    LFM25_ENSURE(l.partials.len >= partial_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "split-K partial workspace too small: need %zu, have %zu", partial_required, l.partials.len);
+    LFM25_ENSURE(l.partials.ptr != nullptr, LFM25_ERR_NULL_POINTER, "split-K partial workspace is null");
+    lfm25::AttentionLaunch args = {};
+    args.query = l.query.ptr;
+    args.key_cache = l.key_cache.ptr;
+    args.value_cache = l.value_cache.ptr;
+    args.block_tables = static_cast<const uint32_t*>(l.block_tables.ptr);
+    args.request_slots = static_cast<const uint32_t*>(l.request_slots.ptr);
+    args.position_ids = static_cast<const uint32_t*>(l.position_ids.ptr);
+    args.output = l.output.ptr;
+    args.partials = static_cast<float*>(l.partials.ptr);
+    args.status = device_status_pointer();
+    args.num_tokens = l.num_tokens;
+    args.num_pages = l.num_pages;
+    args.block_table_stride = l.block_table_stride;
+    args.block_table_rows = l.block_tables.len / l.block_table_stride;
+    args.num_splits = static_cast<uint32_t>(l.num_splits);
+    LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
+                       "split-K ragged attention launch failed");
+}
+
+size_t lfm25_splitk_workspace_elements(size_t maximum_tokens) {
+    size_t value = 0;
+    if (!checked_mul(maximum_tokens, 32, &value) || !checked_mul(value, 8, &value) ||
+        !checked_mul(value, 66, &value)) {
+        return 0;
+    }
+    return value;
+}
+
+size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_tokens, size_t page_size) {
+    if (num_tokens == 0 || page_size != 16) {
+        return 1;
+    }
+    // A B200 keeps 148 SMs x 3 CTAs = 444 (token, KV head, split) items resident.  Split until
+    // about two waves of items exist, but never below 8 pages (128 tokens) per split.
+    const size_t pages = (maximum_context_tokens + page_size - 1) / page_size;
+    const size_t base_items = num_tokens * 8;
+    size_t splits = 1;
+    while (splits < 8 && base_items * splits < 888 && pages / (splits * 2) >= 8) {
+        splits *= 2;
+    }
+    return splits;
+}
+
+int32_t lfm25_quantize_bf16_e4m3(void* stream, lfm25_slice input, lfm25_slice output, size_t numel, float scale) {
+    LFM25_ENSURE(numel > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 quantization requires at least one element");
+    LFM25_ENSURE(input.len >= numel, LFM25_ERR_BUFFER_TOO_SMALL, "FP8 quantization input storage too small");
+    LFM25_ENSURE(output.len >= numel, LFM25_ERR_BUFFER_TOO_SMALL, "FP8 quantization output storage too small");
+    LFM25_ENSURE(std::isfinite(scale) && scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT, "invalid FP8 quantization scale");
+    LFM25_ENSURE(input.ptr && output.ptr, LFM25_ERR_NULL_POINTER, "FP8 quantization received a null device pointer");
+    return cuda_result(
+        lfm25::launch_quantize_bf16_e4m3(static_cast<cudaStream_t>(stream), input.ptr, output.ptr, numel, scale),
+        "FP8 quantization launch failed");
+}
+
+int32_t lfm25_silu_mul_packed_bf16(void* stream, lfm25_slice packed, lfm25_slice out, size_t rows,
+                                   size_t intermediate_size) {
+    LFM25_ENSURE(rows > 0 && intermediate_size > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "packed silu_mul requires non-empty dimensions");
+    size_t output_elements = 0;
+    LFM25_ENSURE(checked_mul(rows, intermediate_size, &output_elements), LFM25_ERR_OVERFLOW,
+                 "packed silu_mul output size overflow");
+    size_t packed_elements = 0;
+    LFM25_ENSURE(checked_mul(output_elements, 2, &packed_elements), LFM25_ERR_OVERFLOW,
+                 "packed silu_mul input size overflow");
+    LFM25_ENSURE(packed.len >= packed_elements, LFM25_ERR_BUFFER_TOO_SMALL, "packed silu_mul input storage too small");
+    LFM25_ENSURE(out.len >= output_elements, LFM25_ERR_BUFFER_TOO_SMALL, "packed silu_mul output storage too small");
+    LFM25_ENSURE(packed.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "packed silu_mul received a null device pointer");
+    return cuda_result(lfm25::launch_silu_mul_packed_bf16(static_cast<cudaStream_t>(stream), packed.ptr, out.ptr,
+                                                          rows, intermediate_size),
+                       "packed silu_mul launch failed");
+}
+
+int32_t lfm25_silu_mul_packed_bf16_to_e4m3(void* stream, lfm25_slice packed, lfm25_slice out, size_t rows,
+                                           size_t intermediate_size, float scale) {
+    LFM25_ENSURE(rows > 0 && intermediate_size > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "packed silu_mul FP8 fusion requires non-empty dimensions");
+    LFM25_ENSURE(std::isfinite(scale) && scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                 "packed silu_mul FP8 fusion requires a finite positive scale");
+    size_t output_elements = 0;
+    LFM25_ENSURE(checked_mul(rows, intermediate_size, &output_elements), LFM25_ERR_OVERFLOW,
+                 "packed silu_mul FP8 output size overflow");
+    size_t packed_elements = 0;
+    LFM25_ENSURE(checked_mul(output_elements, 2, &packed_elements), LFM25_ERR_OVERFLOW,
+                 "packed silu_mul FP8 input size overflow");
+    LFM25_ENSURE(packed.len >= packed_elements, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "packed silu_mul FP8 input storage too small");
+    LFM25_ENSURE(out.len >= output_elements, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "packed silu_mul FP8 output storage too small");
+    LFM25_ENSURE(packed.ptr && out.ptr, LFM25_ERR_NULL_POINTER,
+                 "packed silu_mul FP8 fusion received a null device pointer");
+    return cuda_result(lfm25::launch_silu_mul_packed_bf16_to_e4m3(static_cast<cudaStream_t>(stream), packed.ptr,
+                                                                  out.ptr, rows, intermediate_size, scale),
+                       "packed silu_mul FP8 fusion launch failed");
+}
+
+}  // extern "C"

@@ -1,0 +1,453 @@
+// Ragged paged GQA decode attention for sm_100a.
+//
+// Replaces the reference's kernels/attention_async_fast.cu (unsplit :72-205, split-K :211-358,
+// merge :362-419).  The arithmetic contract is the same -- per token t and query head q,
+// O = softmax(0.125 * Q K^T) V over keys 0..=position[t] of KV head q/4, found through
+// block_tables[request_slots[t]] -- but the execution model is new:
+//
+//  * one CTA per (token, KV head[, split]); its 4 warps take the pages of the range
+//    round-robin and each warp runs an independent online-softmax stream;
+//  * every physical page (16 tokens x 64 dims of K and of V, 2 KiB each) is fetched ONCE per
+//    KV head by a TMA tile copy (128-byte swizzle, mbarrier completion, no multicast) into a
+//    per-warp ring of shared-memory stages, and is shared by the 4 grouped query heads, which
+//    occupy rows 0..3 of the M=16 operand of mma.sync.m16n8k16 (bf16 in, fp32 accumulate);
+//  * softmax runs on the accumulator fragments with quad shuffles; the 4 warps are combined
+//    through shared memory with the exact log-sum-exp identity, which is also the split-K
+//    record format of the reference ((max, denominator, acc[64]) per (token, head, split)).
+//
+// HBM traffic per CTA is the K/V pages of its range (valid or not, the last page is read whole),
+// 512 B of Q, and either 512 B of output or 4 x 264 B of partial records.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lfm25 {
+
+namespace {
+
+constexpr uint32_t kWarps = 4;
+constexpr uint32_t kThreads = kWarps * 32;
+constexpr uint32_t kStages = 4;                        // ring depth per warp
+constexpr uint32_t kStageBytes = 2 * kPageTileBytes;   // K tile then V tile
+constexpr uint32_t kRingBytes = kStages * kStageBytes; // per warp
+constexpr uint32_t kMergeFloats = kWarps * kQPerKv * kPartialStride;
+constexpr uint32_t kSmemBytes = kWarps * kRingBytes + kMergeFloats * 4 + kWarps * kStages * 8 + 16;
+constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;     // room to align the rings to 1 KiB
+
+struct AttentionParams {
+    const __nv_bfloat16* query;
+    const uint32_t* block_tables;
+    const uint32_t* request_slots;  // nullptr: every token uses block-table row 0
+    const uint32_t* position_ids;
+    __nv_bfloat16* output;
+    float* partials;
+    unsigned int* status;
+    uint64_t block_table_stride;
+    uint64_t block_table_rows;
+    uint32_t num_tokens;
+    uint32_t num_pages;
+    uint32_t num_splits;  // 1: write normalised output; >1: write split records
+};
+
+__global__ void __launch_bounds__(kThreads, 3)
+ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
+                               const __grid_constant__ CUtensorMap value_map, const AttentionParams p) {
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+
+    // ---- which (token, KV head, split) this CTA owns; every early exit is CTA-uniform ----
+    const uint32_t splits = p.num_splits;
+    const uint32_t split = blockIdx.x % splits;
+    const uint32_t item = blockIdx.x / splits;
+    const uint32_t token = item / kKvHeads;
+    const uint32_t kv_head = item % kKvHeads;
+    if (token >= p.num_tokens) {
+        return;
+    }
+    uint64_t table_row = 0;
+    if (p.request_slots != nullptr) {
+        table_row = p.request_slots[token];
+        if (table_row >= p.block_table_rows) {
+            return;
+        }
+    }
+    const uint32_t position = p.position_ids[token];
+    if (static_cast<uint64_t>(position) >= p.block_table_stride * kPageSize) {
+        return;
+    }
+    const uint32_t* __restrict__ table = p.block_tables + table_row * p.block_table_stride;
+    const uint32_t total_pages = position / kPageSize + 1;
+    uint32_t first_page = 0;
+    uint32_t end_page = total_pages;
+    if (splits > 1) {
+        first_page = static_cast<uint32_t>(static_cast<uint64_t>(total_pages) * split / splits);
+        end_page = static_cast<uint32_t>(static_cast<uint64_t>(total_pages) * (split + 1) / splits);
+    }
+    const uint32_t range_pages = end_page - first_page;
+    // warp w owns pages first_page + w + 4*i
+    const uint32_t my_pages = range_pages > warp ? (range_pages - warp + kWarps - 1) / kWarps : 0;
+
+    // ---- shared memory carve-up ----
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const uint32_t ring = smem_u32(smem) + warp * kRingBytes;
+    float* merge = reinterpret_cast<float*>(smem + kWarps * kRingBytes);
+    const uint32_t bars = smem_u32(smem + kWarps * kRingBytes + kMergeFloats * 4) + warp * kStages * 8;
+    uint32_t* bad_flag = reinterpret_cast<uint32_t*>(smem + kWarps * kRingBytes + kMergeFloats * 4 + kWarps * kStages * 8);
+
+    if (threadIdx.x == 0) {
+        *bad_flag = 0;
+    }
+    if (lane == 0) {
+        for (uint32_t stage = 0; stage < kStages; ++stage) {
+            mbar_init(bars + stage * 8, 1);
+        }
+        fence_barrier_init();
+        fence_proxy_async_smem();
+    }
+    __syncthreads();
+
+    // ---- producer state (lane 0 only): issue TMA for this warp's pages, kStages ahead ----
+    const int32_t head_row = static_cast<int32_t>(kv_head * kPageSize);
+    uint32_t bad = 0;
+    uint32_t next_entry = 0;
+    auto table_entry = [&](uint32_t iteration) -> uint32_t {
+        return __ldg(table + first_page + warp + iteration * kWarps);
+    };
+    auto issue = [&](uint32_t stage, uint32_t entry) {
+        if (entry >= p.num_pages) {
+            // An unassigned or out-of-range page: keep the pipeline uniform by reading page 0,
+            // and discard this CTA's result at the end (the reference CTA returns silently).
+            bad = 1;
+            entry = 0;
+        }
+        const int32_t row = static_cast<int32_t>(entry) * static_cast<int32_t>(kKvHeads * kPageSize) + head_row;
+        const uint32_t bar = bars + stage * 8;
+        const uint32_t dst = ring + stage * kStageBytes;
+        mbar_arrive_expect_tx(bar, kStageBytes);
+        tma_load_2d(dst, &key_map, bar, 0, row);
+        tma_load_2d(dst + kPageTileBytes, &value_map, bar, 0, row);
+    };
+    if (lane == 0) {
+        const uint32_t prologue = my_pages < kStages ? my_pages : kStages;
+        uint32_t entries[kStages];
+#pragma unroll
+        for (uint32_t stage = 0; stage < kStages; ++stage) {
+            entries[stage] = stage < prologue ? table_entry(stage) : 0;
+        }
+#pragma unroll
+        for (uint32_t stage = 0; stage < kStages; ++stage) {
+            if (stage < prologue) {
+                issue(stage, entries[stage]);
+            }
+        }
+        if (my_pages > kStages) {
+            next_entry = table_entry(kStages);
+        }
+    }
+
+    // ---- query fragments: heads of this KV group in rows 0..3 of the A operand ----
+    const uint32_t group = lane >> 2;   // accumulator row
+    const uint32_t quad = lane & 3;     // column pair within a quad
+    uint32_t qa[4][2];
+#pragma unroll
+    for (uint32_t ks = 0; ks < 4; ++ks) {
+        qa[ks][0] = 0;
+        qa[ks][1] = 0;
+    }
+    if (group < kQPerKv) {
+        const __nv_bfloat16* q_row = p.query + (static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + group) * kHeadDim;
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks) {
+            qa[ks][0] = *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + quad * 2);
+            qa[ks][1] = *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 8 + quad * 2);
+        }
+    }
+
+    constexpr float kScaleLog2 = kAttnScale * kLog2e;
+    float running_max = -INFINITY;  // in units of the raw dot product
+    float running_sum = 0.0f;       // this thread's share; reduced over the quad at the end
+    float acc[8][4];
+#pragma unroll
+    for (uint32_t nt = 0; nt < 8; ++nt) {
+        acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+    }
+
+    // ldmatrix row/chunk of this lane: matrix = lane / 8, row inside the matrix = lane % 8
+    const uint32_t ld_matrix = lane >> 3;
+    const uint32_t ld_row = lane & 7;
+    const uint32_t k_token = ((ld_matrix >> 1) << 3) + ld_row;  // K: matrices 2,3 are tokens 8..15
+    const uint32_t k_chunk = ld_matrix & 1;                     //    matrices 1,3 are the upper 8 dims
+    const uint32_t v_token = ((ld_matrix & 1) << 3) + ld_row;   // V: matrices 1,3 are tokens 8..15
+    const uint32_t v_chunk = ld_matrix >> 1;                    //    matrices 2,3 are the next 8 dims
+
+    bool timed_out = false;
+    uint32_t failed_iteration = 0;
+    for (uint32_t iteration = 0; iteration < my_pages; ++iteration) {
+        const uint32_t stage = iteration % kStages;
+        const uint32_t parity = (iteration / kStages) & 1;
+        const uint32_t bar = bars + stage * 8;
+        const bool ready = mbar_wait_bounded(bar, parity);
+        if (!__all_sync(0xffffffffu, ready)) {
+            timed_out = true;
+            failed_iteration = iteration;
+            break;
+        }
+        const uint32_t k_base = ring + stage * kStageBytes;
+        const uint32_t v_base = k_base + kPageTileBytes;
+        const uint32_t page = first_page + warp + iteration * kWarps;
+        const uint32_t valid = (page + 1 == total_pages) ? (position - page * kPageSize + 1) : kPageSize;
+
+        // S[head, token] = Q K^T over this page: 2 token tiles x 4 dim steps
+        float s[2][4];
+#pragma unroll
+        for (uint32_t nt = 0; nt < 2; ++nt) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+        }
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks) {
+            uint32_t b0, b1, b2, b3;
+            const uint32_t chunk = ks * 2 + k_chunk;
+            ldmatrix_x4(k_base + k_token * 128 + ((chunk ^ ld_row) << 4), b0, b1, b2, b3);
+            mma_bf16_16816(s[0], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+            mma_bf16_16816(s[1], qa[ks][0], 0u, qa[ks][1], 0u, b2, b3);
+        }
+
+        if (valid < kPageSize) {
+            // Last page of the sequence: tokens beyond the position do not exist.  Mask their
+            // scores and clear their V rows so that stale bits (even NaN patterns) cannot leak.
+#pragma unroll
+            for (uint32_t nt = 0; nt < 2; ++nt) {
+                const uint32_t token_in_page = nt * 8 + quad * 2;
+                if (token_in_page >= valid) s[nt][0] = -INFINITY;
+                if (token_in_page + 1 >= valid) s[nt][1] = -INFINITY;
+            }
+            for (uint32_t row = valid; row < kPageSize; ++row) {
+                asm volatile("st.shared.u32 [%0], %1;" ::"r"(v_base + row * 128 + lane * 4), "r"(0u) : "memory");
+            }
+            __syncwarp();
+        }
+
+        // online softmax on rows 0..3 (rows 4..7 carry zeros and are ignored later)
+        float page_max = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        page_max = fmaxf(page_max, __shfl_xor_sync(0xffffffffu, page_max, 1));
+        page_max = fmaxf(page_max, __shfl_xor_sync(0xffffffffu, page_max, 2));
+        const float new_max = fmaxf(running_max, page_max);
+        const float rescale = fast_exp2((running_max - new_max) * kScaleLog2);
+        const float offset = -new_max * kScaleLog2;
+        const uint32_t pa0 = pack_bf16x2(fast_exp2(fmaf(s[0][0], kScaleLog2, offset)),
+                                         fast_exp2(fmaf(s[0][1], kScaleLog2, offset)));
+        const uint32_t pa2 = pack_bf16x2(fast_exp2(fmaf(s[1][0], kScaleLog2, offset)),
+                                         fast_exp2(fmaf(s[1][1], kScaleLog2, offset)));
+        // The denominator sums the same bf16-rounded weights that multiply V, so that the
+        // result stays an exact convex combination of the V rows.
+        const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa0));
+        const float2 w2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa2));
+        running_sum = fmaf(running_sum, rescale, (w0.x + w0.y) + (w2.x + w2.y));
+        running_max = new_max;
+#pragma unroll
+        for (uint32_t nt = 0; nt < 8; ++nt) {
+            acc[nt][0] *= rescale;
+            acc[nt][1] *= rescale;
+        }
+
+        // O[head, dim] += P V: 8 dim tiles, one 16-token step
+#pragma unroll
+        for (uint32_t pair = 0; pair < 4; ++pair) {
+            uint32_t b0, b1, b2, b3;
+            const uint32_t chunk = pair * 2 + v_chunk;
+            ldmatrix_x4_trans(v_base + v_token * 128 + ((chunk ^ ld_row) << 4), b0, b1, b2, b3);
+            mma_bf16_16816(acc[pair * 2], pa0, 0u, pa2, 0u, b0, b1);
+            mma_bf16_16816(acc[pair * 2 + 1], pa0, 0u, pa2, 0u, b2, b3);
+        }
+
+        // refill this stage with the page kStages ahead
+        __syncwarp();
+        if (lane == 0 && iteration + kStages < my_pages) {
+            fence_proxy_async_smem();
+            issue(stage, next_entry);
+            if (iteration + kStages + 1 < my_pages) {
+                next_entry = table_entry(iteration + kStages + 1);
+            }
+        }
+    }
+
+    if (timed_out) {
+        // Give the copies still in flight a second, bounded chance to land before this CTA's
+        // shared memory is released, then report and discard the result.
+        for (uint32_t pending = failed_iteration; pending < my_pages && pending < failed_iteration + kStages;
+             ++pending) {
+            (void)mbar_wait_bounded(bars + (pending % kStages) * 8, (pending / kStages) & 1);
+        }
+        if (lane == 0) {
+            record_wait_timeout(p.status, kTagAttention, blockIdx.x);
+            bad = 1;
+        }
+    }
+    if (lane == 0 && bad) {
+        atomicOr(bad_flag, 1u);
+    }
+
+    // ---- per-warp state -> shared memory (heads 0..3 live in lanes 0..15) ----
+    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
+    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
+    if (group < kQPerKv) {
+        float* record = merge + (warp * kQPerKv + group) * kPartialStride;
+        if (quad == 0) {
+            record[0] = running_max * kAttnScale;  // maximum of the scaled scores; -inf if no page
+            record[1] = running_sum;
+        }
+#pragma unroll
+        for (uint32_t nt = 0; nt < 8; ++nt) {
+            *reinterpret_cast<float2*>(record + 2 + nt * 8 + quad * 2) = make_float2(acc[nt][0], acc[nt][1]);
+        }
+    }
+    __syncthreads();
+    if (*bad_flag != 0) {
+        return;
+    }
+
+    // ---- combine the 4 warps: thread = (head, dims lane and lane + 32) ----
+    const uint32_t head = warp;
+    float maximum = -INFINITY;
+#pragma unroll
+    for (uint32_t w = 0; w < kWarps; ++w) {
+        maximum = fmaxf(maximum, merge[(w * kQPerKv + head) * kPartialStride]);
+    }
+    float denominator = 0.0f;
+    float out0 = 0.0f;
+    float out1 = 0.0f;
+#pragma unroll
+    for (uint32_t w = 0; w < kWarps; ++w) {
+        const float* record = merge + (w * kQPerKv + head) * kPartialStride;
+        const float part_sum = record[1];
+        const float scale = part_sum == 0.0f ? 0.0f : fast_exp2((record[0] - maximum) * kLog2e);
+        denominator = fmaf(part_sum, scale, denominator);
+        out0 = fmaf(record[2 + lane], scale, out0);
+        out1 = fmaf(record[2 + lane + 32], scale, out1);
+    }
+    const size_t q_index = static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + head;
+    if (splits == 1) {
+        __nv_bfloat16* out_row = p.output + q_index * kHeadDim;
+        out_row[lane] = __float2bfloat16_rn(out0 / denominator);
+        out_row[lane + 32] = __float2bfloat16_rn(out1 / denominator);
+    } else {
+        float* record = p.partials + (q_index * splits + split) * kPartialStride;
+        if (lane == 0) {
+            record[0] = maximum;
+            record[1] = denominator;
+        }
+        record[2 + lane] = out0;
+        record[2 + lane + 32] = out1;
+    }
+}
+
+// Merge of split records, one CTA per (token, KV head), thread = (head, dims lane, lane+32).
+// Same identity as kernels/attention_async_fast.cu:362-419 of the reference.
+__global__ void __launch_bounds__(kThreads)
+merge_splitk_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ output, uint32_t num_tokens,
+                    uint32_t num_splits) {
+    const uint32_t token = blockIdx.x / kKvHeads;
+    const uint32_t kv_head = blockIdx.x % kKvHeads;
+    if (token >= num_tokens) {
+        return;
+    }
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t head = threadIdx.x >> 5;
+    const size_t q_index = static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + head;
+    const float* records = partials + q_index * num_splits * kPartialStride;
+    float maximum = -INFINITY;
+    for (uint32_t split = 0; split < num_splits; ++split) {
+        maximum = fmaxf(maximum, records[split * kPartialStride]);
+    }
+    float denominator = 0.0f;
+    float out0 = 0.0f;
+    float out1 = 0.0f;
+    for (uint32_t split = 0; split < num_splits; ++split) {
+        const float* record = records + split * kPartialStride;
+        const float part_sum = record[1];
+        const float scale = part_sum == 0.0f ? 0.0f : fast_exp2((record[0] - maximum) * kLog2e);
+        denominator = fmaf(part_sum, scale, denominator);
+        out0 = fmaf(record[2 + lane], scale, out0);
+        out1 = fmaf(record[2 + lane + 32], scale, out1);
+    }
+    __nv_bfloat16* out_row = output + q_index * kHeadDim;
+    out_row[lane] = __float2bfloat16_rn(out0 / denominator);
+    out_row[lane + 32] = __float2bfloat16_rn(out1 / denominator);
+}
+
+// ---- tensor maps over the arena: rows = pages * 8 heads * 16 tokens, 64 bf16 per row ----
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_entry() {
+    static EncodeTiledFn entry = [] {
+        void* pointer = nullptr;
+        cudaDriverEntryPointQueryResult query = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &query) != cudaSuccess ||
+            query != cudaDriverEntryPointSuccess) {
+            pointer = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(pointer);
+    }();
+    return entry;
+}
+
+bool make_page_map(CUtensorMap* map, const void* cache, uint64_t num_pages) {
+    EncodeTiledFn encode = encode_tiled_entry();
+    if (encode == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[2] = {kHeadDim, num_pages * kKvHeads * kPageSize};
+    const cuuint64_t strides[1] = {kHeadDim * 2};
+    const cuuint32_t box[2] = {kHeadDim, kPageSize};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box,
+                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionLaunch& launch) {
+    CUtensorMap key_map;
+    CUtensorMap value_map;
+    if (!make_page_map(&key_map, launch.key_cache, launch.num_pages) ||
+        !make_page_map(&value_map, launch.value_cache, launch.num_pages)) {
+        return cudaErrorInvalidValue;
+    }
+    static cudaError_t attribute_status = cudaFuncSetAttribute(
+        ragged_decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemAlloc));
+    if (attribute_status != cudaSuccess) {
+        return attribute_status;
+    }
+    AttentionParams params;
+    params.query = static_cast<const __nv_bfloat16*>(launch.query);
+    params.block_tables = launch.block_tables;
+    params.request_slots = launch.request_slots;
+    params.position_ids = launch.position_ids;
+    params.output = static_cast<__nv_bfloat16*>(launch.output);
+    params.partials = launch.partials;
+    params.status = launch.status;
+    params.block_table_stride = launch.block_table_stride;
+    params.block_table_rows = launch.block_table_rows;
+    params.num_tokens = static_cast<uint32_t>(launch.num_tokens);
+    params.num_pages = static_cast<uint32_t>(launch.num_pages);
+    params.num_splits = launch.num_splits;
+    const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
+    ragged_decode_attention_kernel<<<static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream>>>(
+        key_map, value_map, params);
+    cudaError_t status = cudaGetLastError();
+    if (status != cudaSuccess || launch.num_splits == 1) {
+        return status;
+    }
+    merge_splitk_kernel<<<static_cast<unsigned int>(launch.num_tokens * kKvHeads), kThreads, 0, stream>>>(
+        launch.partials, static_cast<__nv_bfloat16*>(launch.output), static_cast<uint32_t>(launch.num_tokens),
+        launch.num_splits);
+    return cudaGetLastError();
+}
+
+}  // namespace lfm25

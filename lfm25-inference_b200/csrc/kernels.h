@@ -1,0 +1,57 @@
+// Host-side launch functions of the CUDA kernels (internal to the library; the public
+// boundary is include/lfm25_b200.h).  Arguments are already validated by the callers in api.cu.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace lfm25 {
+
+struct AttentionLaunch {
+    const void* query;            // bf16 [T,32,64]
+    const void* key_cache;        // bf16 [pages,8,16,64]
+    const void* value_cache;
+    const uint32_t* block_tables; // [rows, stride]
+    const uint32_t* request_slots;// [T] or nullptr (row 0)
+    const uint32_t* position_ids; // [T]
+    void* output;                 // bf16 [T,32,64]
+    float* partials;              // f32 [T,32,S,66] when num_splits > 1
+    unsigned int* status;
+    size_t num_tokens;
+    size_t num_pages;
+    size_t block_table_stride;
+    size_t block_table_rows;
+    uint32_t num_splits;          // 1 = unsplit
+};
+cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionLaunch& launch);
+
+cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const void* value, void* key_cache,
+                                  void* value_cache, const int64_t* slot_mapping, size_t num_tokens,
+                                  size_t num_pages);
+
+struct QkPostprocessArgs {
+    void* query;
+    const void* key;
+    const void* value;
+    const void* query_norm;
+    const void* key_norm;
+    const float* inv_freq;
+    const uint32_t* position_ids;
+    const int64_t* slot_mapping;
+    void* key_cache;
+    void* value_cache;
+    size_t num_tokens;
+    size_t num_pages;
+    float eps;
+};
+cudaError_t launch_qk_norm_rope_kv_write_decode(cudaStream_t stream, const QkPostprocessArgs& args);
+
+cudaError_t launch_quantize_bf16_e4m3(cudaStream_t stream, const void* input, void* output, size_t numel,
+                                      float scale);
+cudaError_t launch_silu_mul_packed_bf16(cudaStream_t stream, const void* packed, void* out, size_t rows,
+                                        size_t intermediate);
+cudaError_t launch_silu_mul_packed_bf16_to_e4m3(cudaStream_t stream, const void* packed, void* out, size_t rows,
+                                                size_t intermediate, float scale);
+
+}  // namespace lfm25

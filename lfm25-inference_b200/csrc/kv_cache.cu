@@ -1,0 +1,157 @@
+// Paged KV append kernels for sm_100a.
+//
+// raw append      : replaces kernels/kv_cache.cu:30-120 of the reference (bit copy of K and V
+//                   [T,8,64] into the arena [pages,8,16,64] at slot_mapping[t]).
+// fused post-proc : replaces kernels/qk_postprocess.cu:44-151 (Q RMSNorm + RoPE in place,
+//                   K RMSNorm + RoPE written straight into the arena, V copied).
+//
+// Both are latency-bound (a few KiB per token); they exist to be bit-exact and cheap to launch.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lfm25 {
+
+namespace {
+
+// One CTA per token, 128 threads, 16 bytes per thread: threads 0..63 move K, 64..127 move V.
+// A token's K (8 heads x 128 B) is contiguous in the source and lands as 8 runs of 128 B.
+__global__ void __launch_bounds__(128)
+kv_cache_write_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value, uint4* __restrict__ key_cache,
+                      uint4* __restrict__ value_cache, const int64_t* __restrict__ slot_mapping, size_t num_tokens,
+                      size_t num_pages) {
+    const size_t token = blockIdx.x;
+    if (token >= num_tokens) {
+        return;
+    }
+    const int64_t slot = slot_mapping[token];
+    if (slot < 0) {
+        return;
+    }
+    const size_t page = static_cast<size_t>(slot) / kPageSize;
+    const size_t offset = static_cast<size_t>(slot) % kPageSize;
+    if (page >= num_pages) {
+        return;
+    }
+    const uint32_t vector = threadIdx.x & 63;      // 16-byte vector inside the token: 8 per head
+    const uint32_t head = vector >> 3;
+    const uint32_t piece = vector & 7;
+    const size_t source = token * 64 + vector;
+    const size_t destination = ((page * kKvHeads + head) * kPageSize + offset) * 8 + piece;
+    if (threadIdx.x < 64) {
+        key_cache[destination] = key[source];
+    } else {
+        value_cache[destination] = value[source];
+    }
+}
+
+// Sum over the 32 lanes in the association order of a shuffle-down tree read at lane 0
+// (16, 8, 4, 2, 1).  The xor butterfly adds the same pairs at every level, and addition is
+// commutative, so every lane ends with exactly the bits lane 0 of the tree would hold.
+__device__ __forceinline__ float warp_tree_sum(float value) {
+#pragma unroll
+    for (uint32_t delta = 16; delta > 0; delta >>= 1) {
+        value += __shfl_xor_sync(0xffffffffu, value, delta);
+    }
+    return value;
+}
+
+// RMSNorm + RoPE of one 64-wide head held as (dim lane, dim lane+32) per lane.  The rounding
+// points are the reference's (kernels/qk_postprocess.cu:21-30,104-112): normalise -> bf16 ->
+// bf16 multiply by the weight -> fp32 rotation with fmaf -> bf16.
+__device__ __forceinline__ void norm_rope(float raw0, float raw1, __nv_bfloat16 weight0, __nv_bfloat16 weight1,
+                                          float sin_value, float cos_value, float eps, __nv_bfloat16& out0,
+                                          __nv_bfloat16& out1) {
+    const float sum = warp_tree_sum(fmaf(raw0, raw0, raw1 * raw1));
+    const float inv_rms = __frsqrt_rn(sum * (1.0f / 64.0f) + eps);
+    const float x0 = __bfloat162float(__hmul(__float2bfloat16_rn(raw0 * inv_rms), weight0));
+    const float x1 = __bfloat162float(__hmul(__float2bfloat16_rn(raw1 * inv_rms), weight1));
+    out0 = __float2bfloat16_rn(fmaf(-x1, sin_value, x0 * cos_value));
+    out1 = __float2bfloat16_rn(fmaf(x0, sin_value, x1 * cos_value));
+}
+
+// One CTA per token, 10 warps: warps 0..7 each take 4 query heads, warps 8..9 each take 4 KV
+// heads (K normalised + rotated into the arena, V copied).  Every warp evaluates the 32 RoPE
+// coefficients of the token itself (one sincosf per lane), so the CTA needs no barrier.
+constexpr uint32_t kPostWarps = 10;
+__global__ void __launch_bounds__(kPostWarps * 32)
+qk_norm_rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ query, const __nv_bfloat16* __restrict__ key,
+                                    const __nv_bfloat16* __restrict__ value,
+                                    const __nv_bfloat16* __restrict__ query_norm,
+                                    const __nv_bfloat16* __restrict__ key_norm, const float* __restrict__ inv_freq,
+                                    const uint32_t* __restrict__ position_ids,
+                                    const int64_t* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ key_cache,
+                                    __nv_bfloat16* __restrict__ value_cache, size_t num_tokens, size_t num_pages,
+                                    float eps) {
+    const size_t token = blockIdx.x;
+    if (token >= num_tokens) {
+        return;
+    }
+    const int64_t slot = slot_mapping[token];
+    if (slot < 0) {
+        return;
+    }
+    const size_t page = static_cast<size_t>(slot) / kPageSize;
+    const size_t offset = static_cast<size_t>(slot) % kPageSize;
+    if (page >= num_pages) {
+        return;
+    }
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = threadIdx.x >> 5;
+    float sin_value;
+    float cos_value;
+    sincosf(static_cast<float>(position_ids[token]) * inv_freq[lane], &sin_value, &cos_value);
+
+    if (warp < 8) {
+        const __nv_bfloat16 weight0 = query_norm[lane];
+        const __nv_bfloat16 weight1 = query_norm[lane + kHalfDim];
+#pragma unroll
+        for (uint32_t index = 0; index < 4; ++index) {
+            __nv_bfloat16* row = query + (token * kQHeads + warp * 4 + index) * kHeadDim;
+            __nv_bfloat16 out0, out1;
+            norm_rope(__bfloat162float(row[lane]), __bfloat162float(row[lane + kHalfDim]), weight0, weight1,
+                      sin_value, cos_value, eps, out0, out1);
+            row[lane] = out0;
+            row[lane + kHalfDim] = out1;
+        }
+    } else {
+        const __nv_bfloat16 weight0 = key_norm[lane];
+        const __nv_bfloat16 weight1 = key_norm[lane + kHalfDim];
+#pragma unroll
+        for (uint32_t index = 0; index < 4; ++index) {
+            const uint32_t head = (warp - 8) * 4 + index;
+            const size_t source = (token * kKvHeads + head) * kHeadDim;
+            const size_t destination = ((page * kKvHeads + head) * kPageSize + offset) * kHeadDim;
+            __nv_bfloat16 out0, out1;
+            norm_rope(__bfloat162float(key[source + lane]), __bfloat162float(key[source + lane + kHalfDim]), weight0,
+                      weight1, sin_value, cos_value, eps, out0, out1);
+            key_cache[destination + lane] = out0;
+            key_cache[destination + lane + kHalfDim] = out1;
+            // V: 128 bytes per head, 4 bytes per lane
+            reinterpret_cast<uint32_t*>(value_cache + destination)[lane] =
+                reinterpret_cast<const uint32_t*>(value + source)[lane];
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const void* value, void* key_cache,
+                                  void* value_cache, const int64_t* slot_mapping, size_t num_tokens,
+                                  size_t num_pages) {
+    kv_cache_write_kernel<<<static_cast<unsigned int>(num_tokens), 128, 0, stream>>>(
+        static_cast<const uint4*>(key), static_cast<const uint4*>(value), static_cast<uint4*>(key_cache),
+        static_cast<uint4*>(value_cache), slot_mapping, num_tokens, num_pages);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_qk_norm_rope_kv_write_decode(cudaStream_t stream, const QkPostprocessArgs& args) {
+    qk_norm_rope_kv_write_decode_kernel<<<static_cast<unsigned int>(args.num_tokens), kPostWarps * 32, 0, stream>>>(
+        static_cast<__nv_bfloat16*>(args.query), static_cast<const __nv_bfloat16*>(args.key),
+        static_cast<const __nv_bfloat16*>(args.value), static_cast<const __nv_bfloat16*>(args.query_norm),
+        static_cast<const __nv_bfloat16*>(args.key_norm), args.inv_freq, args.position_ids, args.slot_mapping,
+        static_cast<__nv_bfloat16*>(args.key_cache), static_cast<__nv_bfloat16*>(args.value_cache), args.num_tokens,
+        args.num_pages, args.eps);
+    return cudaGetLastError();
+}
+
+}  // namespace lfm25

@@ -1,0 +1,192 @@
+"""Op surface of the decode path, named and shaped after the reference's ``src/ops`` functions.
+
+Every function takes CUDA ``torch`` tensors as plain device buffers (torch is only the owner of the
+memory and of the stream), checks ranks and shapes the way the reference's op layer does before any
+launch, and then calls the C ABI on the current stream.  ``*_into`` variants write into caller-owned
+outputs; nothing here allocates device memory except the convenience wrappers that return a tensor.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from . import _abi
+from ._abi import Lfm25Error, Slice, check, library
+
+SPLITK_MAX_SPLITS = 8
+SPLITK_PARTIAL_STRIDE = 66
+
+
+def _slice(tensor: torch.Tensor) -> Slice:
+    if not tensor.is_cuda:
+        raise Lfm25Error(_abi.ERR_INVALID_ARGUMENT, "tensor is not on a CUDA device")
+    if not tensor.is_contiguous():
+        raise Lfm25Error(_abi.ERR_INVALID_ARGUMENT, "tensor storage must be contiguous")
+    return Slice(tensor.data_ptr(), tensor.numel())
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ensure(condition: bool, message: str) -> None:
+    if not condition:
+        raise Lfm25Error(_abi.ERR_INVALID_ARGUMENT, message)
+
+
+@dataclass
+class PagedKvArena:
+    """Physical K and V store of one attention layer: two bf16 tensors [num_pages, 8, page_size, 64],
+    zero-filled at creation (reference: src/cache/arena.rs:13-30)."""
+
+    key: torch.Tensor
+    value: torch.Tensor
+    page_size: int = 16
+
+    @classmethod
+    def new(cls, num_pages: int, page_size: int = 16, device="cuda") -> "PagedKvArena":
+        _ensure(num_pages > 0, "paged KV arena requires pages")
+        shape = (num_pages, 8, page_size, 64)
+        return cls(torch.zeros(shape, dtype=torch.bfloat16, device=device),
+                   torch.zeros(shape, dtype=torch.bfloat16, device=device), page_size)
+
+    @property
+    def num_pages(self) -> int:
+        return self.key.shape[0]
+
+    def write_lfm2(self, key: torch.Tensor, value: torch.Tensor, physical_slots: torch.Tensor) -> None:
+        """Raw append (reference: src/cache/arena.rs:52-86)."""
+        _ensure(key.dim() == 3 and tuple(key.shape[1:]) == (8, 64), "KV write key must have shape [N,8,64]")
+        _ensure(value.shape == key.shape, "KV write key/value shape mismatch")
+        _ensure(physical_slots.numel() == key.shape[0], "KV write slot count mismatch")
+        kv_cache_write_lfm2_bf16(key, value, self.key, self.value, physical_slots, self.page_size)
+
+
+@dataclass
+class FastRaggedAttentionInput:
+    """Reference: src/ops/attention_async_fast.rs:15-22."""
+
+    query: torch.Tensor
+    arena: PagedKvArena
+    block_tables: torch.Tensor
+    block_table_stride: int
+    request_slots: torch.Tensor
+    position_ids: torch.Tensor
+
+
+# ------------------------------------------------------------------------------- KV append
+
+
+def kv_cache_write_lfm2_bf16(key, value, key_cache, value_cache, slot_mapping, page_size: int = 16) -> None:
+    launch = _abi.KvCacheWriteLaunch(page_size, _slice(key), _slice(value), _slice(key_cache), _slice(value_cache),
+                                     _slice(slot_mapping), key.shape[0] if key.dim() else 0, key_cache.shape[0])
+    check(library().lfm25_kv_cache_write_lfm2_bf16(_stream(), launch))
+
+
+def qk_norm_rope_kv_write_arena_decode_bf16(query, key, value, query_norm, key_norm, inv_freq, position_ids,
+                                            slot_mapping, arena: PagedKvArena, eps: float) -> None:
+    """Reference: src/ops/qk_postprocess.rs:107-116 (shape checks :32-105)."""
+    _ensure(query.dim() == 3 and tuple(query.shape[1:]) == (32, 64), "fused QK query must have shape [N,32,64]")
+    num_tokens = query.shape[0]
+    _ensure(tuple(key.shape) == (num_tokens, 8, 64), "fused QK key must have shape [N,8,64]")
+    _ensure(tuple(value.shape) == (num_tokens, 8, 64), "fused QK value must have shape [N,8,64]")
+    _ensure(position_ids.numel() == num_tokens, "fused QK position count mismatch")
+    _ensure(slot_mapping.numel() == num_tokens, "fused QK slot count mismatch")
+    launch = _abi.QkPostprocessLaunch(arena.page_size, _slice(query), _slice(key), _slice(value), _slice(query_norm),
+                                      _slice(key_norm), _slice(inv_freq), _slice(position_ids), _slice(slot_mapping),
+                                      _slice(arena.key), _slice(arena.value), num_tokens, arena.num_pages, eps)
+    check(library().lfm25_qk_norm_rope_kv_write_decode(_stream(), launch))
+
+
+# ------------------------------------------------------------------------------- attention
+
+
+def splitk_workspace_elements(maximum_tokens: int) -> int:
+    return int(library().lfm25_splitk_workspace_elements(maximum_tokens))
+
+
+def splitk_decode_splits(num_tokens: int, maximum_context_tokens: int, page_size: int = 16) -> int:
+    return int(library().lfm25_splitk_decode_splits(num_tokens, maximum_context_tokens, page_size))
+
+
+def paged_attention_fast_lfm2_bf16_into(query, key_cache, value_cache, block_table, position_ids, output,
+                                        page_size: int = 16) -> None:
+    """One sequence (reference: src/ops/attention_async_fast.rs:49-83)."""
+    _ensure(query.dim() == 3 and tuple(query.shape[1:]) == (32, 64), "fast LFM2 query must have shape [N,32,64]")
+    _ensure(position_ids.numel() == query.shape[0], "fast attention position count mismatch")
+    launch = _abi.PagedAttentionLaunch(page_size, _slice(query), _slice(key_cache), _slice(value_cache),
+                                       _slice(block_table), _slice(position_ids), _slice(output), query.shape[0],
+                                       key_cache.shape[0])
+    check(library().lfm25_paged_attention_fast_lfm2_bf16(_stream(), launch))
+
+
+def _validate_ragged_input(inputs: FastRaggedAttentionInput) -> int:
+    _ensure(inputs.query.dim() == 3 and tuple(inputs.query.shape[1:]) == (32, 64),
+            "fast ragged LFM2 query must have shape [N,32,64]")
+    _ensure(inputs.block_tables.dim() == 2, "fast block tables must be rank 2")
+    _ensure(inputs.block_tables.shape[1] == inputs.block_table_stride, "fast block table stride/shape mismatch")
+    num_tokens = inputs.query.shape[0]
+    _ensure(inputs.request_slots.numel() == num_tokens, "fast ragged request slot count mismatch")
+    _ensure(inputs.position_ids.numel() == num_tokens, "fast ragged position count mismatch")
+    return num_tokens
+
+
+def paged_ragged_attention_fast_lfm2_bf16_into(inputs: FastRaggedAttentionInput, output: torch.Tensor) -> None:
+    """Reference: src/ops/attention_async_fast.rs:123-152."""
+    num_tokens = _validate_ragged_input(inputs)
+    launch = _abi.FastRaggedAttentionLaunch(
+        inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
+        _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(output),
+        num_tokens, inputs.arena.num_pages, inputs.block_table_stride)
+    check(library().lfm25_paged_ragged_attention_fast_lfm2_bf16(_stream(), launch))
+
+
+def paged_ragged_attention_fast_lfm2_bf16(inputs: FastRaggedAttentionInput) -> torch.Tensor:
+    output = torch.empty((inputs.query.shape[0], 32, 64), dtype=torch.bfloat16, device=inputs.query.device)
+    paged_ragged_attention_fast_lfm2_bf16_into(inputs, output)
+    return output
+
+
+def paged_ragged_attention_splitk_lfm2_bf16_into(inputs: FastRaggedAttentionInput, partials: torch.Tensor,
+                                                 num_splits: int, output: torch.Tensor) -> None:
+    """Reference: src/ops/attention_async_fast.rs:154-197."""
+    _ensure(2 <= num_splits <= SPLITK_MAX_SPLITS, f"split-K attention requires 2..={SPLITK_MAX_SPLITS} splits")
+    num_tokens = _validate_ragged_input(inputs)
+    launch = _abi.SplitKRaggedAttentionLaunch(
+        inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
+        _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(partials),
+        _slice(output), num_tokens, inputs.arena.num_pages, inputs.block_table_stride, num_splits)
+    check(library().lfm25_paged_ragged_attention_splitk_lfm2_bf16(_stream(), launch))
+
+
+# ------------------------------------------------------------------------------- FP8 producers
+
+
+def quantize_bf16_e4m3_into(values: torch.Tensor, output: torch.Tensor, scale: float) -> None:
+    check(library().lfm25_quantize_bf16_e4m3(_stream(), _slice(values), _slice(output), values.numel(), scale))
+
+
+def silu_mul_packed_bf16_into(packed: torch.Tensor, output: torch.Tensor) -> None:
+    """Reference: src/ops/silu_mul.rs (packed [rows, 2I] -> [rows, I])."""
+    _ensure(packed.dim() >= 1 and packed.shape[-1] % 2 == 0, "packed silu_mul input must have an even last dimension")
+    intermediate = packed.shape[-1] // 2
+    rows = packed.numel() // packed.shape[-1] if packed.numel() else 0
+    check(library().lfm25_silu_mul_packed_bf16(_stream(), _slice(packed), _slice(output), rows, intermediate))
+
+
+def silu_mul_packed_bf16_to_e4m3_into(packed: torch.Tensor, output: torch.Tensor, scale: float) -> None:
+    """Reference: src/ops/silu_mul.rs:65-100."""
+    _ensure(packed.dim() >= 1 and packed.shape[-1] % 2 == 0, "packed silu_mul input must have an even last dimension")
+    intermediate = packed.shape[-1] // 2
+    rows = packed.numel() // packed.shape[-1] if packed.numel() else 0
+    check(library().lfm25_silu_mul_packed_bf16_to_e4m3(_stream(), _slice(packed), _slice(output), rows, intermediate,
+                                                       scale))
+
+
+def device_status() -> tuple[int, int, int, int]:
+    """(waits that ran out since the last read, kernel tag, detail, reserved); clears the words."""
+    import ctypes
+    out = (ctypes.c_uint32 * 4)()
+    check(library().lfm25_device_status(_stream(), out))
+    return tuple(int(word) for word in out)

@@ -1,0 +1,136 @@
+"""Launcher for the reference's own CUDA kernels (``oracle/_ref/*.cubin``).  TEST INFRASTRUCTURE ONLY.
+
+``make -C oracle ref`` compiles the reference project's unmodified ``kernels/*.cu`` for sm_100a.  This
+module loads those images with the CUDA driver API and launches them with the grid and block sizes of
+the reference's Rust wrappers, so that the new kernels can be compared with the reference's results
+on the same device buffers (and timed next to them).  It needs a GPU; nothing in the product imports it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_REF = os.path.join(_HERE, "_ref")
+_BLOCK = 256
+
+_driver = None
+_modules: dict[str, ctypes.c_void_p] = {}
+_functions: dict[tuple[str, str], ctypes.c_void_p] = {}
+
+
+def available() -> bool:
+    return os.path.exists(os.path.join(_REF, "attention_async_fast.cubin"))
+
+
+def _cuda():
+    global _driver
+    if _driver is None:
+        _driver = ctypes.CDLL("libcuda.so.1")
+        _driver.cuLaunchKernel.argtypes = [ctypes.c_void_p] + [ctypes.c_uint] * 6 + [
+            ctypes.c_uint, ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+    return _driver
+
+
+def _check(code: int, what: str) -> None:
+    if code != 0:
+        raise RuntimeError(f"{what} failed with CUDA driver error {code}")
+
+
+def _function(module: str, name: str) -> ctypes.c_void_p:
+    key = (module, name)
+    if key not in _functions:
+        torch.zeros(1, device="cuda")  # makes the primary context current
+        if module not in _modules:
+            with open(os.path.join(_REF, module + ".cubin"), "rb") as handle:
+                image = handle.read()
+            loaded = ctypes.c_void_p()
+            _check(_cuda().cuModuleLoadData(ctypes.byref(loaded), image), f"cuModuleLoadData({module})")
+            _modules[module] = loaded
+        function = ctypes.c_void_p()
+        _check(_cuda().cuModuleGetFunction(ctypes.byref(function), _modules[module], name.encode()),
+               f"cuModuleGetFunction({name})")
+        _functions[key] = function
+    return _functions[key]
+
+
+def _launch(module: str, name: str, blocks: int, arguments: list, block: int = _BLOCK) -> None:
+    function = _function(module, name)
+    holders = []
+    for argument in arguments:
+        if isinstance(argument, torch.Tensor):
+            holders.append(ctypes.c_void_p(argument.data_ptr()))
+        else:
+            holders.append(argument)
+    pointers = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.pointer(h), ctypes.c_void_p) for h in holders])
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _check(_cuda().cuLaunchKernel(function, blocks, 1, 1, block, 1, 1, 0, stream, pointers, None),
+           f"cuLaunchKernel({name})")
+
+
+_sz = ctypes.c_size_t
+
+
+def kv_cache_write(key, value, key_cache, value_cache, slot_mapping) -> None:
+    tokens = key.shape[0]
+    _launch("kv_cache", "kv_cache_write_lfm2_bf16_ps16", tokens,
+            [key, value, key_cache, value_cache, slot_mapping, _sz(tokens), _sz(key_cache.shape[0])])
+
+
+def qk_norm_rope_kv_write_decode(query, key, value, query_norm, key_norm, inv_freq, position_ids, slot_mapping,
+                                 key_cache, value_cache, eps: float) -> None:
+    tokens = query.shape[0]
+    _launch("qk_postprocess", "qk_norm_rope_kv_write_decode_ps16", tokens,
+            [query, key, value, query_norm, key_norm, inv_freq, position_ids, slot_mapping, key_cache, value_cache,
+             _sz(tokens), _sz(key_cache.shape[0]), ctypes.c_float(eps)])
+
+
+def paged_ragged_attention_precise(query, key_cache, value_cache, block_tables, request_slots, position_ids,
+                                   output) -> None:
+    """The reference's own test oracle: kernels/attention.cu `paged_ragged_gqa_lfm2_bf16_ps16`."""
+    tokens = query.shape[0]
+    stride = block_tables.shape[1]
+    _launch("attention", "paged_ragged_gqa_lfm2_bf16_ps16", tokens * 8,
+            [query, key_cache, value_cache, block_tables, request_slots, position_ids, output, _sz(tokens),
+             _sz(key_cache.shape[0]), _sz(stride), _sz(stride)])
+
+
+def paged_ragged_attention_fast(query, key_cache, value_cache, block_tables, request_slots, position_ids,
+                                output) -> None:
+    tokens = query.shape[0]
+    rows, stride = block_tables.shape
+    _launch("attention_async_fast", "paged_ragged_gqa_lfm2_bf16_async_fast_ps16", tokens * 8,
+            [query, key_cache, value_cache, block_tables, request_slots, position_ids, output, _sz(tokens),
+             _sz(key_cache.shape[0]), _sz(stride), _sz(rows)])
+
+
+def paged_ragged_attention_splitk(query, key_cache, value_cache, block_tables, request_slots, position_ids,
+                                  partials, output, num_splits: int) -> None:
+    tokens = query.shape[0]
+    rows, stride = block_tables.shape
+    _launch("attention_async_fast", "paged_ragged_gqa_lfm2_bf16_splitk_ps16", tokens * 8 * num_splits,
+            [query, key_cache, value_cache, block_tables, request_slots, position_ids, partials, _sz(tokens),
+             _sz(key_cache.shape[0]), _sz(stride), _sz(rows), ctypes.c_uint32(num_splits)])
+    _launch("attention_async_fast", "merge_ragged_gqa_lfm2_bf16_splitk", tokens * 8,
+            [partials, output, _sz(tokens), ctypes.c_uint32(num_splits)])
+
+
+def quantize_bf16_e4m3(values, output, scale: float) -> None:
+    numel = values.numel()
+    blocks = max(1, min((numel // 2 + _BLOCK - 1) // _BLOCK, 65535))
+    _launch("fp8_quantize", "quantize_bf16_e4m3", blocks, [values, output, _sz(numel), ctypes.c_float(scale)])
+
+
+def silu_mul_packed_bf16(packed, output) -> None:
+    rows, width = packed.shape
+    blocks = max(1, min((rows * width // 4 + _BLOCK - 1) // _BLOCK, 65535))
+    _launch("silu_mul", "silu_mul_packed_bf16", blocks, [packed, output, _sz(rows), _sz(width // 2)])
+
+
+def silu_mul_packed_bf16_to_e4m3(packed, output, scale: float) -> None:
+    rows, width = packed.shape
+    blocks = max(1, min((rows * width // 4 + _BLOCK - 1) // _BLOCK, 65535))
+    _launch("silu_mul", "silu_mul_packed_bf16_to_e4m3", blocks,
+            [packed, output, _sz(rows), _sz(width // 2), ctypes.c_float(scale)])
