@@ -183,6 +183,28 @@ int32_t lfm25_silu_mul_packed_bf16(void* stream, lfm25_slice packed, lfm25_slice
 int32_t lfm25_silu_mul_packed_bf16_to_e4m3(void* stream, lfm25_slice packed, lfm25_slice out, size_t rows,
                                            size_t intermediate_size, float scale);
 
+/* ------------------------------------------------------------------------------------------
+ * FP8 (E4M3) linear
+ * ------------------------------------------------------------------------------------------ */
+
+#define LFM25_FP8_SCALE_TENSORWIDE 0 /* Fp8ScaleMode::Tensorwide */
+#define LFM25_FP8_SCALE_BLOCK32 1    /* Fp8ScaleMode::Block32 (research-only in the reference): not built */
+
+/* Replaces Fp8LinearConfig (src/cuda/blaslt/mod.rs:21-28). */
+typedef struct lfm25_fp8_linear_config {
+    size_t m;
+    size_t n;
+    size_t k;
+    uint32_t scale_mode;
+    float output_scale; /* d_x * d_w, applied to the fp32 sum before rounding to bf16 */
+} lfm25_fp8_linear_config;
+
+/* Replaces BlasLt::linear_fp8_scaled (src/cuda/blaslt/mod.rs:212-298, cuBLASLt descriptor
+ * src/cuda/blaslt/fp8.rs:312-353): out[M,N] = bf16(output_scale * x[M,K] * weight[N,K]^T), E4M3 codes in,
+ * fp32 accumulation.  No plan cache and no workspace are needed. */
+int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
+                                const lfm25_fp8_linear_config* config);
+
 #ifdef __cplusplus
 }
 #endif

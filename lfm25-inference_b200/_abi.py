@@ -61,10 +61,22 @@ SplitKRaggedAttentionLaunch = _launch_struct("SplitKRaggedAttentionLaunch", [
     "#page_size", "query", "key_cache", "value_cache", "block_tables", "request_slots", "position_ids",
     "partials", "output", "#num_tokens", "#num_pages", "#block_table_stride", "#num_splits"])
 
-# name -> (restype, argtypes); every symbol that include/lfm25_b200.h declares
+
+
 _P = ctypes.POINTER
 _size = ctypes.c_size_t
 _stream = ctypes.c_void_p
+
+
+class Fp8LinearConfig(ctypes.Structure):
+    _fields_ = [("m", ctypes.c_size_t), ("n", ctypes.c_size_t), ("k", ctypes.c_size_t),
+                ("scale_mode", ctypes.c_uint32), ("output_scale", ctypes.c_float)]
+
+
+FP8_SCALE_TENSORWIDE = 0
+FP8_SCALE_BLOCK32 = 1
+
+# name -> (restype, argtypes); every symbol that include/lfm25_b200.h declares
 PROTOTYPES = {
     "lfm25_last_error": (ctypes.c_char_p, []),
     "lfm25_version": (ctypes.c_char_p, []),
@@ -79,6 +91,7 @@ PROTOTYPES = {
     "lfm25_quantize_bf16_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, ctypes.c_float]),
     "lfm25_silu_mul_packed_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
     "lfm25_silu_mul_packed_bf16_to_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size, ctypes.c_float]),
+    "lfm25_linear_fp8_scaled": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _P(Fp8LinearConfig)]),
 }
 
 _library = None

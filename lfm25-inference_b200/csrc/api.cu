@@ -396,4 +396,50 @@ int32_t lfm25_silu_mul_packed_bf16_to_e4m3(void* stream, lfm25_slice packed, lfm
                        "packed silu_mul FP8 fusion launch failed");
 }
 
+int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
+                                const lfm25_fp8_linear_config* config) {
+    LFM25_ENSURE(config != nullptr, LFM25_ERR_NULL_POINTER, "FP8 linear config is null");
+    const size_t m = config->m;
+    const size_t n = config->n;
+    const size_t k = config->k;
+    LFM25_ENSURE(m > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul M must be > 0");
+    LFM25_ENSURE(n > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul N must be > 0");
+    LFM25_ENSURE(k > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul K must be > 0");
+    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE || config->scale_mode == LFM25_FP8_SCALE_BLOCK32,
+                 LFM25_ERR_INVALID_ARGUMENT, "unknown FP8 scale mode %u", config->scale_mode);
+    LFM25_ENSURE(config->scale_mode != LFM25_FP8_SCALE_BLOCK32 || k % 32 == 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "MXFP8 matmul K must be divisible by 32, got %zu", k);
+    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE, LFM25_ERR_UNSUPPORTED,
+                 "Block32 (MXFP8) scaling is not built; use the tensor-wide mode");
+    LFM25_ENSURE(std::isfinite(config->output_scale) && config->output_scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                 "FP8 output scale must be finite and positive");
+    size_t x_required = 0;
+    size_t weight_required = 0;
+    size_t out_required = 0;
+    LFM25_ENSURE(checked_mul(m, k, &x_required), LFM25_ERR_OVERFLOW, "FP8 linear input size overflow");
+    LFM25_ENSURE(checked_mul(n, k, &weight_required), LFM25_ERR_OVERFLOW, "FP8 linear weight size overflow");
+    LFM25_ENSURE(checked_mul(m, n, &out_required), LFM25_ERR_OVERFLOW, "FP8 linear output size overflow");
+    LFM25_ENSURE(x.len >= x_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "FP8 linear input storage too small: required=%zu, actual=%zu", x_required, x.len);
+    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "FP8 linear weight storage too small: required=%zu, actual=%zu", weight_required, weight.len);
+    LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "FP8 linear output storage too small: required=%zu, actual=%zu", out_required, out.len);
+    LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER,
+                 "FP8 linear received a null device pointer");
+    LFM25_ENSURE(m <= 0x7fffffffu && n <= 0x7fffffffu && k <= 0x7fffffffu, LFM25_ERR_INVALID_ARGUMENT,
+                 "FP8 linear dimension exceeds i32");
+    cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+    const bool aligned =
+        ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr)) & 15) == 0;
+    if (aligned && lfm25::fp8_gemm_stream_supports(m, n, k)) {
+        return cuda_result(
+            lfm25::launch_fp8_gemm_stream(cuda_stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale),
+            "FP8 linear launch failed");
+    }
+    return cuda_result(
+        lfm25::launch_fp8_gemm_generic(cuda_stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale),
+        "FP8 linear launch failed");
+}
+
 }  // extern "C"

@@ -419,7 +419,8 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
         !make_page_map(&value_map, launch.value_cache, launch.num_pages)) {
         return cudaErrorInvalidValue;
     }
-    static cudaError_t attribute_status = cudaFuncSetAttribute(
+    // per launch: the attribute belongs to the current device's copy of the kernel
+    const cudaError_t attribute_status = cudaFuncSetAttribute(
         ragged_decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemAlloc));
     if (attribute_status != cudaSuccess) {
         return attribute_status;

@@ -76,16 +76,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for a phase of an mbarrier with an iteration limit.  Returns false when the limit is
-// reached (the caller records the failure and unwinds); it never spins without bound.
-constexpr uint32_t kWaitLimit = 1u << 22;
+// Waits for a phase of an mbarrier for at most about one second of wall time.  Returns false when
+// the limit is reached (the caller records the failure and unwinds); it never spins without bound.
+constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    return now;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-    for (uint32_t spin = 0; spin < kWaitLimit; ++spin) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const uint64_t start = global_timer_ns();
+    for (;;) {
+#pragma unroll 1
+        for (uint32_t spin = 0; spin < 64; ++spin) {
+            if (mbar_try_wait(bar, parity)) {
+                return true;
+            }
+        }
+        if (global_timer_ns() - start > kWaitLimitNs) {
+            return false;
         }
     }
-    return false;
 }
 
 // ------------------------------------------------------------------ TMA (no multicast anywhere)

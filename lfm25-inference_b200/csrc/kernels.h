@@ -54,4 +54,11 @@ cudaError_t launch_silu_mul_packed_bf16(cudaStream_t stream, const void* packed,
 cudaError_t launch_silu_mul_packed_bf16_to_e4m3(cudaStream_t stream, const void* packed, void* out, size_t rows,
                                                 size_t intermediate, float scale);
 
+// FP8 linear: Y[M,N] = bf16(alpha * Xq[M,K] * Wq[N,K]^T)
+bool fp8_gemm_stream_supports(size_t m, size_t n, size_t k);
+cudaError_t launch_fp8_gemm_stream(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                   size_t n, size_t k, float alpha);
+cudaError_t launch_fp8_gemm_generic(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                    size_t n, size_t k, float alpha);
+
 }  // namespace lfm25

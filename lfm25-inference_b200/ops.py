@@ -184,6 +184,37 @@ def silu_mul_packed_bf16_to_e4m3_into(packed: torch.Tensor, output: torch.Tensor
                                                        scale))
 
 
+def linear_fp8_scaled_into(x_codes: torch.Tensor, weight_codes: torch.Tensor, output: torch.Tensor,
+                           output_scale: float, scale_mode: int = _abi.FP8_SCALE_TENSORWIDE) -> None:
+    """out[M,N] = bf16(output_scale * x[M,K] @ weight[N,K]^T) on E4M3 codes
+    (reference: src/model/decode_executor.rs:35-76 -> src/cuda/blaslt/mod.rs:212-298)."""
+    _ensure(x_codes.dim() == 2, f"persistent prequantized FP8 linear requires rank-2 input, got {tuple(x_codes.shape)}")
+    _ensure(weight_codes.dim() == 2, "persistent prequantized FP8 weight must be rank 2")
+    m, k = x_codes.shape
+    n = weight_codes.shape[0]
+    _ensure(m > 0 and k > 0 and n > 0, "persistent FP8 linear is empty")
+    _ensure(weight_codes.shape[1] == k,
+            f"persistent prequantized FP8 K mismatch: input K={k}, weight={tuple(weight_codes.shape)}")
+    config = _abi.Fp8LinearConfig(m, n, k, scale_mode, output_scale)
+    check(library().lfm25_linear_fp8_scaled(_stream(), _slice(x_codes), _slice(weight_codes), _slice(output), config))
+
+
+def linear_fp8_e4m3(x: torch.Tensor, weight_codes: torch.Tensor, activation_scale, weight_scale) -> torch.Tensor:
+    """Quantise a bf16 activation with its static scale, then the FP8 linear
+    (reference: src/ops/linear.rs:29-77).  Scales are (quantize_multiplier, dequantize_multiplier) pairs."""
+    _ensure(x.dim() >= 1, "FP8 linear input must have rank >= 1")
+    _ensure(weight_codes.dim() == 2, "FP8 linear weight must have rank 2")
+    _ensure(x.numel() > 0 and weight_codes.numel() > 0, "FP8 linear does not support empty tensors")
+    k = x.shape[-1]
+    _ensure(weight_codes.shape[1] == k, "FP8 linear K mismatch")
+    rows = x.numel() // k
+    codes = torch.empty((rows, k), dtype=torch.uint8, device=x.device)
+    quantize_bf16_e4m3_into(x, codes, activation_scale[0])
+    output = torch.empty((*x.shape[:-1], weight_codes.shape[0]), dtype=torch.bfloat16, device=x.device)
+    linear_fp8_scaled_into(codes, weight_codes, output.view(rows, -1), activation_scale[1] * weight_scale[1])
+    return output
+
+
 def device_status() -> tuple[int, int, int, int]:
     """(waits that ran out since the last read, kernel tag, detail, reserved); clears the words."""
     import ctypes

@@ -108,6 +108,24 @@ def test_fp8_producer_validation():
     assert call(fused, None, fake(16), fake(8), 1, 8, float("nan"))[0] == _abi.ERR_INVALID_ARGUMENT
 
 
+def test_fp8_linear_validation():
+    library = _abi.library()
+    linear = library.lfm25_linear_fp8_scaled
+
+    def launch(m=2, n=16, k=128, mode=0, scale=1.0, x=256, w=2048, out=32):
+        return call(linear, None, fake(x), fake(w), fake(out), _abi.Fp8LinearConfig(m, n, k, mode, scale))
+
+    assert launch(m=0) == (_abi.ERR_INVALID_ARGUMENT, "FP8 matmul M must be > 0")
+    assert launch(n=0)[0] == _abi.ERR_INVALID_ARGUMENT and launch(k=0)[0] == _abi.ERR_INVALID_ARGUMENT
+    assert launch(scale=float("inf")) == (_abi.ERR_INVALID_ARGUMENT, "FP8 output scale must be finite and positive")
+    assert launch(mode=1)[0] == _abi.ERR_UNSUPPORTED
+    assert launch(mode=1, k=100)[0] == _abi.ERR_INVALID_ARGUMENT      # MXFP8 wants K % 32 == 0
+    assert launch(mode=7)[0] == _abi.ERR_INVALID_ARGUMENT
+    assert launch(x=255) == (_abi.ERR_BUFFER_TOO_SMALL, "FP8 linear input storage too small: required=256, actual=255")
+    assert launch(w=2047)[0] == _abi.ERR_BUFFER_TOO_SMALL and launch(out=31)[0] == _abi.ERR_BUFFER_TOO_SMALL
+    assert launch(m=2 ** 40, n=2 ** 40)[0] == _abi.ERR_OVERFLOW
+
+
 def test_workspace_and_split_policy():
     library = _abi.library()
     # src/ops/attention_async_fast.rs:203-207  splitk_workspace_is_bounded_for_serving_capacity
