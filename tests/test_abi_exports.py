@@ -135,7 +135,8 @@ def test_workspace_and_split_policy():
     assert splits(0, 8192, 16) == 1            # src/ops/splitk_policy.rs:20-22
     assert splits(1, 100, 16) == 1             # short contexts never split
     assert splits(1, 8192, 16) == 8            # one long sequence: as many splits as allowed
-    assert splits(64, 8192, 16) == 2           # 512 items already: one doubling reaches two waves
+    assert splits(64, 8192, 16) == 4           # 512 items: two doublings reach four waves of resident CTAs
+    assert splits(128, 4096, 16) == 2
     assert splits(256, 8192, 16) == 1          # enough items without splitting
     assert splits(4, 8192, 32) == 1            # page size 32 is not built
     for tokens in (1, 2, 8, 16, 32, 64, 128):
