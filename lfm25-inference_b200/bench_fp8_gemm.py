@@ -1,0 +1,105 @@
+"""Sweep of the E4M3 decode GEMMs: packed Gate/Up 2048->16384, Down 8192->2048, LM head 2048->65536 at
+M in {1, 8, 32, 128, 256}; weights ~ N(0, 0.02) and activations ~ N(0, 1) quantised per tensor (amax / 448).
+
+    python lfm25-inference_b200/bench_fp8_gemm.py [--iterations 200] [--ms 1 8 32 128 256] [--no-cublaslt]
+
+For every point one JSON line: microseconds per launch with HBM-cold weights (the launches rotate over a ring
+of distinct weight copies of at least 512 MB, larger than L2) and with L2-warm weights (one copy), the
+algorithmic bytes and flops, the achieved GB/s against the measured HBM copy peak, and -- next to it -- cuBLASLt's
+FP8 GEMM on the same buffers through torch._scaled_mm (what the reference runtime calls for these sites).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+SHAPES = [("gate_up", 16384, 2048), ("down", 2048, 8192), ("lm_head", 65536, 2048)]
+RING_BYTES = 512 << 20
+
+
+def time_launches(function, count):
+    start = torch.cuda.Event(enable_timing=True)
+    stop = torch.cuda.Event(enable_timing=True)
+    for index in range(5):
+        function(index)
+    torch.cuda.synchronize()
+    start.record()
+    for index in range(count):
+        function(index)
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e3 / count
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--iterations", type=int, default=200)
+    parser.add_argument("--ms", type=int, nargs="+", default=[1, 8, 32, 128, 256])
+    parser.add_argument("--no-cublaslt", action="store_true")
+    arguments = parser.parse_args()
+    entry.load_package()
+    from lfm25_inference_b200 import ops
+
+    device = torch.device("cuda:0")
+    peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    hbm_peak = json.load(open(peak_path))["hbm_gbs"] if os.path.exists(peak_path) else 6650.0
+    generator = torch.Generator(device=device).manual_seed(2)
+    for name, n, k in SHAPES:
+        copies = max(2, (RING_BYTES + n * k - 1) // (n * k))
+        weight = torch.randn((n, k), generator=generator, device=device) * 0.02
+        w_amax = float(weight.abs().max())
+        codes = (weight * (448.0 / w_amax)).clamp(-448, 448).to(torch.float8_e4m3fn).view(torch.uint8)
+        ring = [codes.clone() for _ in range(copies)]
+        del weight
+        for m in arguments.ms:
+            x = torch.randn((m, k), generator=generator, device=device, dtype=torch.bfloat16)
+            x_amax = float(x.float().abs().max())
+            x_codes = torch.empty((m, k), dtype=torch.uint8, device=device)
+            ops.quantize_bf16_e4m3_into(x, x_codes, 448.0 / x_amax)
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+            scale = (x_amax / 448.0) * (w_amax / 448.0)
+
+            def ours(index, ring=ring, out=out, x_codes=x_codes):
+                ops.linear_fp8_scaled_into(x_codes, ring[index % len(ring)], out, scale)
+
+            def ours_with_quantise(index, ring=ring, out=out, x_codes=x_codes, x=x):
+                ops.quantize_bf16_e4m3_into(x, x_codes, 448.0 / x_amax)
+                ops.linear_fp8_scaled_into(x_codes, ring[index % len(ring)], out, scale)
+
+            cold = time_launches(ours, arguments.iterations)
+            warm = time_launches(lambda index: ours(0), arguments.iterations)
+            with_quantise = time_launches(ours_with_quantise, arguments.iterations)
+            bytes_moved = n * k + m * k + 2 * m * n
+            line = {"shape": name, "m": m, "n": n, "k": k, "us_cold": cold, "us_l2_warm": warm,
+                    "us_cold_with_quantise": with_quantise, "bytes": bytes_moved, "flops": 2 * m * n * k,
+                    "gbs_cold": bytes_moved / cold / 1e3, "hbm_frac_cold": bytes_moved / cold / 1e3 / hbm_peak,
+                    "tflops_cold": 2 * m * n * k / cold / 1e6, "weight_copies": copies}
+            if not arguments.no_cublaslt:
+                try:
+                    one = torch.ones((), device=device)
+                    a8 = x_codes.view(torch.float8_e4m3fn)
+                    ring8 = [w.view(torch.float8_e4m3fn).t() for w in ring]
+
+                    def cublaslt(index):
+                        torch._scaled_mm(a8, ring8[index % len(ring8)], scale_a=one, scale_b=one,
+                                         out_dtype=torch.bfloat16)
+
+                    line["cublaslt_us_cold"] = time_launches(cublaslt, arguments.iterations)
+                    line["cublaslt_us_l2_warm"] = time_launches(lambda index: cublaslt(0), arguments.iterations)
+                    line["speedup_vs_cublaslt_cold"] = line["cublaslt_us_cold"] / cold
+                except Exception as error:  # shape rules of torch._scaled_mm differ between releases
+                    line["cublaslt_error"] = str(error)[:120]
+            print(json.dumps(line), flush=True)
+        del ring
+
+
+if __name__ == "__main__":
+    main()
