@@ -156,6 +156,21 @@ typedef struct lfm25_splitk_ragged_attention_launch {
 } lfm25_splitk_ragged_attention_launch;
 int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream, const lfm25_splitk_ragged_attention_launch* launch);
 
+/* Split-K decode attention for hosts that must not allocate device memory after start-up (an engine that
+ * gave all free memory to its KV pool, a loop that cannot afford cudaMalloc's device synchronisation, an
+ * embedder whose own allocator is the only one allowed).  Same inputs, outputs and results as
+ * lfm25_paged_ragged_attention_splitk_lfm2_bf16, but the split records go to an array compiled into the
+ * library (8,650,752 bytes per device, held until exit) instead of a caller workspace.  Limits: at most 128
+ * tokens per call (more is rejected with LFM25_ERR_INVALID_ARGUMENT), 2..=8 splits.  The first call on a
+ * device looks up the array's device address; make that call before any stream capture begins.  All calls
+ * share the one array and it keeps whatever the last call wrote, so calls must not overlap on the GPU: keep
+ * them ordered on one stream.  Nothing needs clearing between calls: each call writes every record it later
+ * reads.  This entry point has no counterpart in the reference, whose split-K path always takes a
+ * caller-allocated `partials` tensor. */
+int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(void* stream,
+                                                             const lfm25_fast_ragged_attention_launch* launch,
+                                                             size_t num_splits);
+
 /* Replaces splitk_workspace_elements (src/ops/attention_async_fast.rs:24-30):
  * maximum_tokens * 32 * 8 * 66 f32 elements; 0 on overflow. */
 size_t lfm25_splitk_workspace_elements(size_t maximum_tokens);

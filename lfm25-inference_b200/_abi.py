@@ -86,6 +86,8 @@ PROTOTYPES = {
     "lfm25_paged_attention_fast_lfm2_bf16": (ctypes.c_int32, [_stream, _P(PagedAttentionLaunch)]),
     "lfm25_paged_ragged_attention_fast_lfm2_bf16": (ctypes.c_int32, [_stream, _P(FastRaggedAttentionLaunch)]),
     "lfm25_paged_ragged_attention_splitk_lfm2_bf16": (ctypes.c_int32, [_stream, _P(SplitKRaggedAttentionLaunch)]),
+    "lfm25_paged_ragged_attention_splitk_static_lfm2_bf16": (
+        ctypes.c_int32, [_stream, _P(FastRaggedAttentionLaunch), _size]),
     "lfm25_splitk_workspace_elements": (_size, [_size]),
     "lfm25_splitk_decode_splits": (_size, [_size, _size, _size]),
     "lfm25_quantize_bf16_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, ctypes.c_float]),

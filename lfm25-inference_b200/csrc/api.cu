@@ -118,6 +118,10 @@ int32_t validate_ragged_common(size_t page_size, const lfm25_slice& query, const
 
 }  // namespace
 
+namespace lfm25 {
+int32_t report_error(int32_t code, const char* message) { return fail(code, "%s", message); }
+}  // namespace lfm25
+
 extern "C" {
 
 const char* lfm25_last_error(void) { return g_last_error; }

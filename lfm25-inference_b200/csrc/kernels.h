@@ -61,4 +61,7 @@ cudaError_t launch_fp8_gemm_stream(cudaStream_t stream, const void* x, const voi
 cudaError_t launch_fp8_gemm_generic(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
                                     size_t n, size_t k, float alpha);
 
+// Stores `message` as the calling thread's last error (what lfm25_last_error() returns) and returns `code`.
+int32_t report_error(int32_t code, const char* message);
+
 }  // namespace lfm25

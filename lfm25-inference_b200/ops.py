@@ -160,6 +160,19 @@ def paged_ragged_attention_splitk_lfm2_bf16_into(inputs: FastRaggedAttentionInpu
     check(library().lfm25_paged_ragged_attention_splitk_lfm2_bf16(_stream(), launch))
 
 
+def paged_ragged_attention_splitk_static_lfm2_bf16_into(inputs: FastRaggedAttentionInput, num_splits: int,
+                                                        output: torch.Tensor) -> None:
+    """Split-K attention without a caller workspace, for hosts that may not allocate device memory while
+    serving: the records go to a fixed array inside the library (at most 128 tokens per call; calls share the
+    array, so they must stay ordered on one stream).  No counterpart in the reference."""
+    num_tokens = _validate_ragged_input(inputs)
+    launch = _abi.FastRaggedAttentionLaunch(
+        inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
+        _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(output),
+        num_tokens, inputs.arena.num_pages, inputs.block_table_stride)
+    check(library().lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(_stream(), launch, num_splits))
+
+
 # ------------------------------------------------------------------------------- FP8 producers
 
 
