@@ -216,9 +216,163 @@ typedef struct lfm25_fp8_linear_config {
 
 /* Replaces BlasLt::linear_fp8_scaled (src/cuda/blaslt/mod.rs:212-298, cuBLASLt descriptor
  * src/cuda/blaslt/fp8.rs:312-353): out[M,N] = bf16(output_scale * x[M,K] * weight[N,K]^T), E4M3 codes in,
- * fp32 accumulation.  No plan cache and no workspace are needed. */
+ * fp32 accumulation.  No plan cache and no workspace are needed.  Kernel choice: M <= 8 weight-streaming
+ * mma.sync kernel, 9..256 tcgen05/TMEM kernel, other shapes a generic kernel; the environment variable
+ * LFM25_FP8_GEMM_PATH=stream|umma|generic overrides it for measurements. */
 int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                 const lfm25_fp8_linear_config* config);
+
+/* Replaces the `BlasLt` object (src/cuda/blaslt/mod.rs:30-70): bound to one stream, owns the 32 MiB device
+ * workspace that cuBLASLt uses for the BF16 linears, allocated once at creation.  The FP8 linear through the
+ * handle is the stateless one on the handle's stream. */
+typedef struct lfm25_blaslt lfm25_blaslt;
+int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out);
+void lfm25_blaslt_destroy(lfm25_blaslt* handle);
+/* Rebinds the handle to another stream (the reference binds at construction only; work already enqueued on the
+ * old stream that uses the workspace must have been ordered before new work by the caller). */
+int32_t lfm25_blaslt_set_stream(lfm25_blaslt* handle, void* stream);
+size_t lfm25_blaslt_workspace_size(const lfm25_blaslt* handle); /* BlasLt::workspace_size */
+int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
+                                       const lfm25_fp8_linear_config* config);
+/* Replaces BlasLt::linear_bf16 (src/cuda/blaslt/mod.rs:113-186): out[M,N] = x[M,K] * weight[N,K]^T in bf16 with
+ * fp32 accumulation, through cuBLASLt (opened lazily; plans cached per shape), as the reference does for the
+ * sites that are not promoted to FP8. */
+int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out, size_t m,
+                                 size_t n, size_t k);
+
+/* ------------------------------------------------------------------------------------------
+ * Remaining ops of the decode step
+ * ------------------------------------------------------------------------------------------ */
+
+/* Replaces EmbeddingKernels::launch (kernels/embedding.cu:65): out[t,:] = weight[token_ids[t],:]; an id >= vocab
+ * leaves the row untouched. */
+int32_t lfm25_embedding_bf16(void* stream, lfm25_slice token_ids, lfm25_slice weight, lfm25_slice out,
+                             size_t num_tokens, size_t vocab_size, size_t hidden_size);
+/* Replaces rms_norm_bf16 (kernels/rms_norm.cu:342): out = bf16(bf16(x * inv_rms) * weight), hidden_size even. */
+int32_t lfm25_rms_norm_bf16(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out, size_t rows,
+                            size_t hidden_size, float eps);
+/* Replaces residual_rms_norm_bf16 (kernels/rms_norm.cu:364-463): residual_out = bf16(residual + update);
+ * normalized_out = bf16(float(residual_out) * inv_rms * weight), the variance taken from the unrounded sums. */
+int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
+                                     lfm25_slice residual_out, lfm25_slice normalized_out, size_t rows,
+                                     size_t hidden_size, float eps);
+/* Replaces short_conv_segmented_lfm2_bf16 (kernels/short_conv.cu:100-143) for decode (one token per segment):
+ * projected [T, 3*hidden] = (b | c | x), weight [hidden, 3], states [request_slots, hidden, 2] updated in place. */
+int32_t lfm25_short_conv_decode_bf16(void* stream, lfm25_slice projected, lfm25_slice weight, lfm25_slice states,
+                                     lfm25_slice request_slots, lfm25_slice output, size_t num_tokens,
+                                     size_t hidden_size, size_t num_request_slots);
+/* Replaces argmax_rows_bf16 and its atomic variant (kernels/sampling.cu:53-217): greedy argmax per row with the
+ * legacy tie order (smaller column % 256, then smaller column / 256; NaN and -inf never win; +-0 equal). */
+int32_t lfm25_argmax_rows_bf16(void* stream, lfm25_slice logits, lfm25_slice sampled, size_t rows, size_t vocab_size);
+
+/* ------------------------------------------------------------------------------------------
+ * Decode step: device-resident batch metadata and the executor
+ * ------------------------------------------------------------------------------------------ */
+
+/* Device-resident step metadata (the tensors of GpuBatch, src/scheduler/batch.rs:126-140).  One token per
+ * sequence.  `positions[t]` is the index of the token being decoded (= context length before it). */
+typedef struct lfm25_decode_batch {
+    uint32_t* token_ids;           /* u32 [num_tokens] */
+    uint32_t* positions;           /* u32 [num_tokens] */
+    const uint32_t* request_slots; /* u32 [num_tokens] block-table / conv-state row of each token */
+    int64_t* physical_slots;       /* i64 [num_tokens], written by the step */
+    const uint32_t* block_tables;  /* u32 [block_table_rows, block_table_stride] */
+    size_t block_table_stride;
+    size_t block_table_rows;
+    size_t num_tokens;
+    size_t max_context_tokens;     /* upper bound used to choose the number of KV splits */
+} lfm25_decode_batch;
+
+/* Replaces BatchModelCache::prepare_tokens + GpuBatch::update_step/update_segments + scatter_batch_metadata
+ * (src/model/lfm2_base.rs:322-388, src/scheduler/batch.rs:142-260, kernels/metadata.cu:12-69) for pure decode:
+ * physical_slots[t] = block_tables[slot][pos/16]*16 + pos%16 (or -1 when not mapped), computed on the device.
+ * With advance != 0 every sequence first moves on by one token: token_ids[t] = sampled[t], positions[t] += 1.
+ * No host loop, no H2D copy, no synchronisation. */
+int32_t lfm25_decode_step_metadata(void* stream, const lfm25_decode_batch* batch, lfm25_slice sampled,
+                                   size_t num_pages, uint32_t advance);
+
+/* One linear site: BF16 weights, and/or E4M3 weights with their static scales (Fp8LinearWeight of the reference:
+ * activation_scale = (448/c_x, c_x/448), weight_scale dequantize = c_w/448).  data == NULL: site not promoted. */
+typedef struct lfm25_fp8_site {
+    const void* data; /* u8 [n, k] */
+    float activation_quantize;
+    float activation_dequantize;
+    float weight_dequantize;
+} lfm25_fp8_site;
+typedef struct lfm25_linear_weights {
+    const void* bf16; /* bf16 [n, k], may be NULL when the FP8 copy is the only one resident */
+    lfm25_fp8_site fp8;
+    size_t n;
+    size_t k;
+} lfm25_linear_weights;
+
+/* One decoder layer with its cache (LayerWeights + BatchLayerCache of the reference). */
+typedef struct lfm25_layer {
+    uint32_t is_attention;
+    const void* operator_norm; /* bf16 [2048] */
+    const void* ffn_norm;      /* bf16 [2048] */
+    lfm25_linear_weights conv_input;  /* [6144, 2048] */
+    const void* conv_kernel;          /* bf16 [2048, 3] */
+    lfm25_linear_weights conv_output; /* [2048, 2048] */
+    void* conv_state;                 /* bf16 [request_slots, 2048, 2] */
+    lfm25_linear_weights query;       /* [2048, 2048] */
+    lfm25_linear_weights key;         /* [512, 2048] */
+    lfm25_linear_weights value;       /* [512, 2048] */
+    lfm25_linear_weights output;      /* [2048, 2048] */
+    const void* query_norm;           /* bf16 [64] */
+    const void* key_norm;             /* bf16 [64] */
+    void* key_cache;                  /* bf16 [num_pages, 8, 16, 64] */
+    void* value_cache;
+    lfm25_linear_weights gate_up;     /* [16384, 2048], rows packed gate | up */
+    lfm25_linear_weights down;        /* [2048, 8192] */
+} lfm25_layer;
+
+typedef struct lfm25_model {
+    uint32_t num_layers;
+    const lfm25_layer* layers;
+    const void* embedding;      /* bf16 [65536, 2048]; tied LM head */
+    lfm25_fp8_site lm_head_fp8; /* u8 [65536, 2048] when promoted */
+    const void* final_norm;     /* bf16 [2048] */
+    const float* inv_freq;      /* f32 [32] */
+    float norm_eps;
+    size_t num_pages;
+    size_t num_request_slots;
+} lfm25_model;
+
+/* Replaces DecodeExecutor (src/model/decode_executor.rs): persistent scratch for up to maximum_tokens (<= 256)
+ * tokens, allocated once here; the step itself allocates nothing. */
+typedef struct lfm25_decode_executor lfm25_decode_executor;
+int32_t lfm25_decode_executor_create(lfm25_blaslt* blaslt, size_t maximum_tokens, lfm25_decode_executor** out);
+void lfm25_decode_executor_destroy(lfm25_decode_executor* executor);
+/* DecodeExecutor::forward_prepared (:183-443) preceded by the device-side metadata step: enqueues one decode step
+ * on the BlasLt handle's stream; sampled ids land in the executor's `sampled` buffer. */
+int32_t lfm25_decode_executor_forward(lfm25_decode_executor* executor, const lfm25_model* model,
+                                      const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance);
+/* Advance-and-step replayed from a CUDA graph captured per (batch size, model, batch buffers): the first call of a
+ * bucket runs eagerly, the second captures, later ones only launch the graph.  No counterpart in the reference,
+ * which launches ~170 kernels and synchronises the host every step (src/engine/serving/radix_owner.rs:230-259). */
+int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* executor, const lfm25_model* model,
+                                         const lfm25_decode_batch* batch, uint32_t use_fp8);
+/* Opt-in region timing of eager steps (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): while
+ * enabled, every op of lfm25_decode_executor_forward is bracketed by CUDA events.  A call with region_ms != NULL
+ * synchronises, returns the milliseconds and op counts accumulated per region since the last collection, and then
+ * applies `enable`.  Graph-replayed steps are never instrumented. */
+#define LFM25_REGION_ATTENTION 0   /* ragged paged attention (+ merge) */
+#define LFM25_REGION_APPEND 1      /* QK-norm + RoPE + paged KV append */
+#define LFM25_REGION_FP8_LINEAR 2  /* quantise / SiLU->E4M3 + E4M3 GEMM */
+#define LFM25_REGION_BF16_LINEAR 3 /* cuBLASLt BF16 GEMM (+ SiLU for BF16 Down) */
+#define LFM25_REGION_OTHER 4       /* metadata, embedding, norms, short conv, argmax */
+#define LFM25_REGION_COUNT 5
+int32_t lfm25_decode_executor_profile(lfm25_decode_executor* executor, uint32_t enable,
+                                      float region_ms[LFM25_REGION_COUNT],
+                                      uint32_t region_launches[LFM25_REGION_COUNT]);
+/* Enqueues device-to-host copies of the last step's sampled ids (u32 [count]) or logits (bf16 [rows, 65536]) on
+ * the executor's stream; the caller synchronises (the reference's pinned-ring download,
+ * src/engine/serving/radix_owner.rs:441-462). */
+int32_t lfm25_decode_executor_download_sampled(lfm25_decode_executor* executor, uint32_t* host, size_t count);
+int32_t lfm25_decode_executor_download_logits(lfm25_decode_executor* executor, void* host, size_t rows);
+const uint32_t* lfm25_decode_executor_sampled(const lfm25_decode_executor* executor); /* u32 [maximum_tokens] */
+const void* lfm25_decode_executor_logits(const lfm25_decode_executor* executor);      /* bf16 [maximum_tokens, 65536] */
 
 #ifdef __cplusplus
 }

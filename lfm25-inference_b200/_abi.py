@@ -73,6 +73,37 @@ class Fp8LinearConfig(ctypes.Structure):
                 ("scale_mode", ctypes.c_uint32), ("output_scale", ctypes.c_float)]
 
 
+class DecodeBatch(ctypes.Structure):
+    _fields_ = [("token_ids", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("request_slots", ctypes.c_void_p),
+                ("physical_slots", ctypes.c_void_p), ("block_tables", ctypes.c_void_p),
+                ("block_table_stride", ctypes.c_size_t), ("block_table_rows", ctypes.c_size_t),
+                ("num_tokens", ctypes.c_size_t), ("max_context_tokens", ctypes.c_size_t)]
+
+
+class Fp8Site(ctypes.Structure):
+    _fields_ = [("data", ctypes.c_void_p), ("activation_quantize", ctypes.c_float),
+                ("activation_dequantize", ctypes.c_float), ("weight_dequantize", ctypes.c_float)]
+
+
+class LinearWeights(ctypes.Structure):
+    _fields_ = [("bf16", ctypes.c_void_p), ("fp8", Fp8Site), ("n", ctypes.c_size_t), ("k", ctypes.c_size_t)]
+
+
+class Layer(ctypes.Structure):
+    _fields_ = [("is_attention", ctypes.c_uint32), ("operator_norm", ctypes.c_void_p), ("ffn_norm", ctypes.c_void_p),
+                ("conv_input", LinearWeights), ("conv_kernel", ctypes.c_void_p), ("conv_output", LinearWeights),
+                ("conv_state", ctypes.c_void_p), ("query", LinearWeights), ("key", LinearWeights),
+                ("value", LinearWeights), ("output", LinearWeights), ("query_norm", ctypes.c_void_p),
+                ("key_norm", ctypes.c_void_p), ("key_cache", ctypes.c_void_p), ("value_cache", ctypes.c_void_p),
+                ("gate_up", LinearWeights), ("down", LinearWeights)]
+
+
+class Model(ctypes.Structure):
+    _fields_ = [("num_layers", ctypes.c_uint32), ("layers", _P(Layer)), ("embedding", ctypes.c_void_p),
+                ("lm_head_fp8", Fp8Site), ("final_norm", ctypes.c_void_p), ("inv_freq", ctypes.c_void_p),
+                ("norm_eps", ctypes.c_float), ("num_pages", ctypes.c_size_t), ("num_request_slots", ctypes.c_size_t)]
+
+
 FP8_SCALE_TENSORWIDE = 0
 FP8_SCALE_BLOCK32 = 1
 
@@ -94,6 +125,30 @@ PROTOTYPES = {
     "lfm25_silu_mul_packed_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
     "lfm25_silu_mul_packed_bf16_to_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size, ctypes.c_float]),
     "lfm25_linear_fp8_scaled": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _P(Fp8LinearConfig)]),
+    "lfm25_blaslt_create": (ctypes.c_int32, [_stream, _P(ctypes.c_void_p)]),
+    "lfm25_blaslt_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_blaslt_set_stream": (ctypes.c_int32, [ctypes.c_void_p, _stream]),
+    "lfm25_blaslt_workspace_size": (_size, [ctypes.c_void_p]),
+    "lfm25_blaslt_linear_fp8_scaled": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _P(Fp8LinearConfig)]),
+    "lfm25_blaslt_linear_bf16": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _size, _size, _size]),
+    "lfm25_embedding_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, _size]),
+    "lfm25_rms_norm_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, ctypes.c_float]),
+    "lfm25_residual_rms_norm_bf16": (
+        ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, _size, _size, ctypes.c_float]),
+    "lfm25_short_conv_decode_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, _size, _size, _size]),
+    "lfm25_argmax_rows_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
+    "lfm25_decode_step_metadata": (ctypes.c_int32, [_stream, _P(DecodeBatch), Slice, _size, ctypes.c_uint32]),
+    "lfm25_decode_executor_create": (ctypes.c_int32, [ctypes.c_void_p, _size, _P(ctypes.c_void_p)]),
+    "lfm25_decode_executor_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_decode_executor_forward": (
+        ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
+    "lfm25_decode_executor_step_graph": (ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32]),
+    "lfm25_decode_executor_profile": (
+        ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint32, _P(ctypes.c_float), _P(ctypes.c_uint32)]),
+    "lfm25_decode_executor_download_sampled": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p, _size]),
+    "lfm25_decode_executor_download_logits": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p, _size]),
+    "lfm25_decode_executor_sampled": (ctypes.c_void_p, [ctypes.c_void_p]),
+    "lfm25_decode_executor_logits": (ctypes.c_void_p, [ctypes.c_void_p]),
 }
 
 _library = None

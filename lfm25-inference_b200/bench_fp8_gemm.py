@@ -3,6 +3,7 @@ M in {1, 8, 32, 128, 256}; weights ~ N(0, 0.02) and activations ~ N(0, 1) quanti
 
     python lfm25-inference_b200/bench_fp8_gemm.py [--iterations 200] [--ms 1 8 32 128 256] [--no-cublaslt]
 
+Launches are timed on the GPU by replaying a CUDA graph of them.
 For every point one JSON line: microseconds per launch with HBM-cold weights (the launches rotate over a ring
 of distinct weight copies of at least 512 MB, larger than L2) and with L2-warm weights (one copy), the
 algorithmic bytes and flops, the achieved GB/s against the measured HBM copy peak, and -- next to it -- cuBLASLt's
@@ -25,25 +26,39 @@ SHAPES = [("gate_up", 16384, 2048), ("down", 2048, 8192), ("lm_head", 65536, 204
 RING_BYTES = 512 << 20
 
 
-def time_launches(function, count):
+def time_launches(function, count, replays=5):
+    """Microseconds per launch, GPU-side: `count` launches are captured in a CUDA graph and the graph is replayed,
+    so the host's launch cadence (Python + ctypes) does not enter the number."""
+    for index in range(3):
+        function(index)
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        with torch.cuda.graph(graph, stream=stream):
+            for index in range(count):
+                function(index)
+    graph.replay()
+    torch.cuda.synchronize()
     start = torch.cuda.Event(enable_timing=True)
     stop = torch.cuda.Event(enable_timing=True)
-    for index in range(5):
-        function(index)
-    torch.cuda.synchronize()
     start.record()
-    for index in range(count):
-        function(index)
+    for _ in range(replays):
+        graph.replay()
     stop.record()
     torch.cuda.synchronize()
-    return start.elapsed_time(stop) * 1e3 / count
+    return start.elapsed_time(stop) * 1e3 / (count * replays)
 
 
 def main():
     parser = argparse.ArgumentParser()
-    parser.add_argument("--iterations", type=int, default=200)
+    parser.add_argument("--iterations", type=int, default=64)
     parser.add_argument("--ms", type=int, nargs="+", default=[1, 8, 32, 128, 256])
     parser.add_argument("--no-cublaslt", action="store_true")
+    parser.add_argument("--paths", nargs="+", default=["auto"],
+                        help="kernel paths to time: auto, stream, umma (sets LFM25_FP8_GEMM_PATH)")
+    parser.add_argument("--handle", action="store_true", help="call through a BlasLt handle (allows split-K)")
     arguments = parser.parse_args()
     entry.load_package()
     from lfm25_inference_b200 import ops
@@ -52,6 +67,7 @@ def main():
     peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm_peak = json.load(open(peak_path))["hbm_gbs"] if os.path.exists(peak_path) else 6650.0
     generator = torch.Generator(device=device).manual_seed(2)
+    blaslt = ops.BlasLt() if arguments.handle else None
     for name, n, k in SHAPES:
         copies = max(2, (RING_BYTES + n * k - 1) // (n * k))
         weight = torch.randn((n, k), generator=generator, device=device) * 0.02
@@ -68,20 +84,33 @@ def main():
             scale = (x_amax / 448.0) * (w_amax / 448.0)
 
             def ours(index, ring=ring, out=out, x_codes=x_codes):
-                ops.linear_fp8_scaled_into(x_codes, ring[index % len(ring)], out, scale)
+                if blaslt is not None:
+                    blaslt.linear_fp8_scaled(x_codes, ring[index % len(ring)], out, scale)
+                else:
+                    ops.linear_fp8_scaled_into(x_codes, ring[index % len(ring)], out, scale)
 
-            def ours_with_quantise(index, ring=ring, out=out, x_codes=x_codes, x=x):
+            def ours_with_quantise(index, x_codes=x_codes, x=x):
                 ops.quantize_bf16_e4m3_into(x, x_codes, 448.0 / x_amax)
-                ops.linear_fp8_scaled_into(x_codes, ring[index % len(ring)], out, scale)
+                ours(index)
 
-            cold = time_launches(ours, arguments.iterations)
-            warm = time_launches(lambda index: ours(0), arguments.iterations)
-            with_quantise = time_launches(ours_with_quantise, arguments.iterations)
             bytes_moved = n * k + m * k + 2 * m * n
-            line = {"shape": name, "m": m, "n": n, "k": k, "us_cold": cold, "us_l2_warm": warm,
-                    "us_cold_with_quantise": with_quantise, "bytes": bytes_moved, "flops": 2 * m * n * k,
-                    "gbs_cold": bytes_moved / cold / 1e3, "hbm_frac_cold": bytes_moved / cold / 1e3 / hbm_peak,
-                    "tflops_cold": 2 * m * n * k / cold / 1e6, "weight_copies": copies}
+            line = {"shape": name, "m": m, "n": n, "k": k, "bytes": bytes_moved, "flops": 2 * m * n * k,
+                    "weight_copies": copies, "handle": arguments.handle}
+            for path in arguments.paths:
+                if path == "auto":
+                    os.environ.pop("LFM25_FP8_GEMM_PATH", None)
+                else:
+                    os.environ["LFM25_FP8_GEMM_PATH"] = path
+                if path == "stream" and m > 64:
+                    continue
+                cold = time_launches(ours, arguments.iterations)
+                line[f"{path}_us_cold"] = cold
+                line[f"{path}_us_l2_warm"] = time_launches(lambda index: ours(0), arguments.iterations)
+                line[f"{path}_us_cold_with_quantise"] = time_launches(ours_with_quantise, arguments.iterations)
+                line[f"{path}_gbs_cold"] = bytes_moved / cold / 1e3
+                line[f"{path}_hbm_frac_cold"] = bytes_moved / cold / 1e3 / hbm_peak
+                line[f"{path}_tflops_cold"] = 2 * m * n * k / cold / 1e6
+            os.environ.pop("LFM25_FP8_GEMM_PATH", None)
             if not arguments.no_cublaslt:
                 try:
                     one = torch.ones((), device=device)
@@ -94,7 +123,9 @@ def main():
 
                     line["cublaslt_us_cold"] = time_launches(cublaslt, arguments.iterations)
                     line["cublaslt_us_l2_warm"] = time_launches(lambda index: cublaslt(0), arguments.iterations)
-                    line["speedup_vs_cublaslt_cold"] = line["cublaslt_us_cold"] / cold
+                    first = arguments.paths[0]
+                    if f"{first}_us_cold" in line:
+                        line["speedup_vs_cublaslt_cold"] = line["cublaslt_us_cold"] / line[f"{first}_us_cold"]
                 except Exception as error:  # shape rules of torch._scaled_mm differ between releases
                     line["cublaslt_error"] = str(error)[:120]
             print(json.dumps(line), flush=True)

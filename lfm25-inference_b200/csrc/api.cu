@@ -3,10 +3,15 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <stdlib.h>
+#include <string.h>
+
 #include <cmath>
 #include <limits>
+#include <new>
 
 #include "../../include/lfm25_b200.h"
+#include "blaslt_handle.h"
 #include "common.cuh"
 #include "kernels.h"
 
@@ -114,6 +119,74 @@ int32_t validate_ragged_common(size_t page_size, const lfm25_slice& query, const
                      (reinterpret_cast<uintptr_t>(value_cache.ptr) & 15) == 0,
                  LFM25_ERR_INVALID_ARGUMENT, "KV cache must be 16-byte aligned");
     return LFM25_OK;
+}
+
+// Validation of Fp8MatmulKey::new + BlasLt::linear_fp8_scaled (src/cuda/blaslt/fp8.rs:23-40,
+// src/cuda/blaslt/mod.rs:222-262), then the choice of kernel:
+//   M <= 8            weight-streaming mma.sync kernel
+//   9 <= M <= 256     tcgen05 / TMEM kernel (K split over a thread-block cluster when there are few tiles)
+//   anything else     generic kernel
+// LFM25_FP8_GEMM_PATH = stream | umma | generic overrides the choice where the shape allows (for measurements).
+int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
+                            const lfm25_fp8_linear_config* config) {
+    LFM25_ENSURE(config != nullptr, LFM25_ERR_NULL_POINTER, "FP8 linear config is null");
+    const size_t m = config->m;
+    const size_t n = config->n;
+    const size_t k = config->k;
+    LFM25_ENSURE(m > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul M must be > 0");
+    LFM25_ENSURE(n > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul N must be > 0");
+    LFM25_ENSURE(k > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul K must be > 0");
+    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE || config->scale_mode == LFM25_FP8_SCALE_BLOCK32,
+                 LFM25_ERR_INVALID_ARGUMENT, "unknown FP8 scale mode %u", config->scale_mode);
+    LFM25_ENSURE(config->scale_mode != LFM25_FP8_SCALE_BLOCK32 || k % 32 == 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "MXFP8 matmul K must be divisible by 32, got %zu", k);
+    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE, LFM25_ERR_UNSUPPORTED,
+                 "Block32 (MXFP8) scaling is not built; use the tensor-wide mode");
+    LFM25_ENSURE(std::isfinite(config->output_scale) && config->output_scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                 "FP8 output scale must be finite and positive");
+    size_t x_required = 0;
+    size_t weight_required = 0;
+    size_t out_required = 0;
+    LFM25_ENSURE(checked_mul(m, k, &x_required), LFM25_ERR_OVERFLOW, "FP8 linear input size overflow");
+    LFM25_ENSURE(checked_mul(n, k, &weight_required), LFM25_ERR_OVERFLOW, "FP8 linear weight size overflow");
+    LFM25_ENSURE(checked_mul(m, n, &out_required), LFM25_ERR_OVERFLOW, "FP8 linear output size overflow");
+    LFM25_ENSURE(x.len >= x_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "FP8 linear input storage too small: required=%zu, actual=%zu", x_required, x.len);
+    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "FP8 linear weight storage too small: required=%zu, actual=%zu", weight_required, weight.len);
+    LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "FP8 linear output storage too small: required=%zu, actual=%zu", out_required, out.len);
+    LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER,
+                 "FP8 linear received a null device pointer");
+    LFM25_ENSURE(m <= 0x7fffffffu && n <= 0x7fffffffu && k <= 0x7fffffffu, LFM25_ERR_INVALID_ARGUMENT,
+                 "FP8 linear dimension exceeds i32");
+    const bool aligned =
+        ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr)) & 15) == 0;
+    const bool stream_ok = aligned && lfm25::fp8_gemm_stream_supports(m, n, k);
+    const bool umma_ok = aligned && lfm25::fp8_gemm_umma_supports(m, n, k);
+    enum { kStream, kUmma, kGeneric } path = kGeneric;
+    if (stream_ok && (m <= 8 || !umma_ok)) {
+        path = kStream;
+    } else if (umma_ok) {
+        path = kUmma;
+    }
+    if (const char* forced = getenv("LFM25_FP8_GEMM_PATH")) {
+        if (strcmp(forced, "stream") == 0 && stream_ok) path = kStream;
+        if (strcmp(forced, "umma") == 0 && umma_ok) path = kUmma;
+        if (strcmp(forced, "generic") == 0) path = kGeneric;
+    }
+    cudaError_t status;
+    if (path == kStream) {
+        status = lfm25::launch_fp8_gemm_stream(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale);
+    } else if (path == kUmma) {
+        unsigned int* status_words = device_status_pointer();
+        LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+        status = lfm25::launch_fp8_gemm_umma(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale,
+                                             status_words);
+    } else {
+        status = lfm25::launch_fp8_gemm_generic(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale);
+    }
+    return cuda_result(status, "FP8 linear launch failed");
 }
 
 }  // namespace
@@ -401,50 +474,193 @@ int32_t lfm25_silu_mul_packed_bf16_to_e4m3(void* stream, lfm25_slice packed, lfm
                        "packed silu_mul FP8 fusion launch failed");
 }
 
+int32_t lfm25_embedding_bf16(void* stream, lfm25_slice token_ids, lfm25_slice weight, lfm25_slice out,
+                             size_t num_tokens, size_t vocab_size, size_t hidden_size) {
+    LFM25_ENSURE(num_tokens > 0 && vocab_size > 0 && hidden_size > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "embedding requires non-empty dimensions");
+    size_t out_required = 0;
+    size_t weight_required = 0;
+    LFM25_ENSURE(checked_mul(num_tokens, hidden_size, &out_required) &&
+                     checked_mul(vocab_size, hidden_size, &weight_required),
+                 LFM25_ERR_OVERFLOW, "embedding size overflow");
+    LFM25_ENSURE(token_ids.len >= num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "embedding token ids too small");
+    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL, "embedding weight storage too small");
+    LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "embedding output storage too small");
+    LFM25_ENSURE(token_ids.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER,
+                 "embedding received a null device pointer");
+    return cuda_result(lfm25::launch_embedding_bf16(static_cast<cudaStream_t>(stream),
+                                                    static_cast<const uint32_t*>(token_ids.ptr), weight.ptr, out.ptr,
+                                                    num_tokens, vocab_size, hidden_size),
+                       "embedding launch failed");
+}
+
+int32_t lfm25_rms_norm_bf16(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out, size_t rows,
+                            size_t hidden_size, float eps) {
+    LFM25_ENSURE(rows > 0 && hidden_size > 0, LFM25_ERR_INVALID_ARGUMENT, "rms_norm requires non-empty dimensions");
+    LFM25_ENSURE(hidden_size % 2 == 0, LFM25_ERR_UNSUPPORTED, "rms_norm requires an even hidden size");
+    size_t required = 0;
+    LFM25_ENSURE(checked_mul(rows, hidden_size, &required), LFM25_ERR_OVERFLOW, "rms_norm size overflow");
+    LFM25_ENSURE(x.len >= required, LFM25_ERR_BUFFER_TOO_SMALL, "rms_norm input storage too small");
+    LFM25_ENSURE(out.len >= required, LFM25_ERR_BUFFER_TOO_SMALL, "rms_norm output storage too small");
+    LFM25_ENSURE(weight.len >= hidden_size, LFM25_ERR_BUFFER_TOO_SMALL, "rms_norm weight storage too small");
+    LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "rms_norm received a null device pointer");
+    return cuda_result(lfm25::launch_rms_norm_bf16(static_cast<cudaStream_t>(stream), x.ptr, weight.ptr, out.ptr, rows,
+                                                   hidden_size, eps),
+                       "rms_norm launch failed");
+}
+
+int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
+                                     lfm25_slice residual_out, lfm25_slice normalized_out, size_t rows,
+                                     size_t hidden_size, float eps) {
+    LFM25_ENSURE(rows > 0 && hidden_size > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "residual rms_norm requires non-empty dimensions");
+    LFM25_ENSURE(hidden_size % 2 == 0, LFM25_ERR_UNSUPPORTED, "residual rms_norm requires an even hidden size");
+    size_t required = 0;
+    LFM25_ENSURE(checked_mul(rows, hidden_size, &required), LFM25_ERR_OVERFLOW, "residual rms_norm size overflow");
+    LFM25_ENSURE(residual.len >= required && update.len >= required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "residual rms_norm input storage too small");
+    LFM25_ENSURE(residual_out.len >= required && normalized_out.len >= required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "residual rms_norm output storage too small");
+    LFM25_ENSURE(weight.len >= hidden_size, LFM25_ERR_BUFFER_TOO_SMALL, "residual rms_norm weight storage too small");
+    LFM25_ENSURE(residual.ptr && update.ptr && weight.ptr && residual_out.ptr && normalized_out.ptr,
+                 LFM25_ERR_NULL_POINTER, "residual rms_norm received a null device pointer");
+    return cuda_result(
+        lfm25::launch_residual_rms_norm_bf16(static_cast<cudaStream_t>(stream), residual.ptr, update.ptr, weight.ptr,
+                                             residual_out.ptr, normalized_out.ptr, rows, hidden_size, eps),
+        "residual rms_norm launch failed");
+}
+
+int32_t lfm25_short_conv_decode_bf16(void* stream, lfm25_slice projected, lfm25_slice weight, lfm25_slice states,
+                                     lfm25_slice request_slots, lfm25_slice output, size_t num_tokens,
+                                     size_t hidden_size, size_t num_request_slots) {
+    LFM25_ENSURE(num_tokens > 0 && hidden_size > 0 && num_request_slots > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "short conv requires non-empty dimensions");
+    size_t out_required = 0;
+    size_t state_required = 0;
+    LFM25_ENSURE(checked_mul(num_tokens, hidden_size, &out_required) &&
+                     checked_mul(num_request_slots, hidden_size * 2, &state_required),
+                 LFM25_ERR_OVERFLOW, "short conv size overflow");
+    LFM25_ENSURE(projected.len >= out_required * 3, LFM25_ERR_BUFFER_TOO_SMALL, "short conv input storage too small");
+    LFM25_ENSURE(weight.len >= hidden_size * 3, LFM25_ERR_BUFFER_TOO_SMALL, "short conv weight storage too small");
+    LFM25_ENSURE(states.len >= state_required, LFM25_ERR_BUFFER_TOO_SMALL, "short conv state storage too small");
+    LFM25_ENSURE(request_slots.len >= num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "short conv slot storage too small");
+    LFM25_ENSURE(output.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "short conv output storage too small");
+    LFM25_ENSURE(projected.ptr && weight.ptr && states.ptr && request_slots.ptr && output.ptr, LFM25_ERR_NULL_POINTER,
+                 "short conv received a null device pointer");
+    return cuda_result(lfm25::launch_short_conv_decode(static_cast<cudaStream_t>(stream), projected.ptr, weight.ptr,
+                                                       states.ptr, static_cast<const uint32_t*>(request_slots.ptr),
+                                                       output.ptr, num_tokens, hidden_size, num_request_slots),
+                       "short conv launch failed");
+}
+
+int32_t lfm25_argmax_rows_bf16(void* stream, lfm25_slice logits, lfm25_slice sampled, size_t rows,
+                               size_t vocab_size) {
+    LFM25_ENSURE(rows > 0 && vocab_size > 0, LFM25_ERR_INVALID_ARGUMENT, "argmax requires non-empty dimensions");
+    LFM25_ENSURE(vocab_size <= 65536, LFM25_ERR_UNSUPPORTED, "argmax supports a vocabulary of at most 65536");
+    size_t required = 0;
+    LFM25_ENSURE(checked_mul(rows, vocab_size, &required), LFM25_ERR_OVERFLOW, "argmax size overflow");
+    LFM25_ENSURE(logits.len >= required, LFM25_ERR_BUFFER_TOO_SMALL, "argmax logits storage too small");
+    LFM25_ENSURE(sampled.len >= rows, LFM25_ERR_BUFFER_TOO_SMALL, "argmax output storage too small");
+    LFM25_ENSURE(logits.ptr && sampled.ptr, LFM25_ERR_NULL_POINTER, "argmax received a null device pointer");
+    return cuda_result(lfm25::launch_argmax_rows_bf16(static_cast<cudaStream_t>(stream), logits.ptr,
+                                                      static_cast<uint32_t*>(sampled.ptr), rows, vocab_size),
+                       "argmax launch failed");
+}
+
+int32_t lfm25_decode_step_metadata(void* stream, const lfm25_decode_batch* batch, lfm25_slice sampled,
+                                   size_t num_pages, uint32_t advance) {
+    LFM25_ENSURE(batch != nullptr, LFM25_ERR_NULL_POINTER, "decode batch is null");
+    LFM25_ENSURE(batch->num_tokens > 0, LFM25_ERR_INVALID_ARGUMENT, "GPU batch needs tokens");
+    LFM25_ENSURE(batch->block_table_stride > 0 && batch->block_table_rows > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "GPU batch needs block tables");
+    LFM25_ENSURE(batch->token_ids && batch->positions && batch->request_slots && batch->physical_slots &&
+                     batch->block_tables,
+                 LFM25_ERR_NULL_POINTER, "decode batch metadata is incomplete");
+    LFM25_ENSURE(!advance || (sampled.ptr != nullptr && sampled.len >= batch->num_tokens), LFM25_ERR_BUFFER_TOO_SMALL,
+                 "sampled ids are needed to advance the batch");
+    return cuda_result(
+        lfm25::launch_decode_metadata(static_cast<cudaStream_t>(stream), batch->token_ids, batch->positions,
+                                      batch->request_slots, batch->block_tables,
+                                      static_cast<const uint32_t*>(sampled.ptr), batch->physical_slots,
+                                      batch->num_tokens, batch->block_table_stride, batch->block_table_rows, num_pages,
+                                      advance != 0),
+        "step metadata launch failed");
+}
+
 int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                 const lfm25_fp8_linear_config* config) {
-    LFM25_ENSURE(config != nullptr, LFM25_ERR_NULL_POINTER, "FP8 linear config is null");
-    const size_t m = config->m;
-    const size_t n = config->n;
-    const size_t k = config->k;
-    LFM25_ENSURE(m > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul M must be > 0");
-    LFM25_ENSURE(n > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul N must be > 0");
-    LFM25_ENSURE(k > 0, LFM25_ERR_INVALID_ARGUMENT, "FP8 matmul K must be > 0");
-    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE || config->scale_mode == LFM25_FP8_SCALE_BLOCK32,
-                 LFM25_ERR_INVALID_ARGUMENT, "unknown FP8 scale mode %u", config->scale_mode);
-    LFM25_ENSURE(config->scale_mode != LFM25_FP8_SCALE_BLOCK32 || k % 32 == 0, LFM25_ERR_INVALID_ARGUMENT,
-                 "MXFP8 matmul K must be divisible by 32, got %zu", k);
-    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE, LFM25_ERR_UNSUPPORTED,
-                 "Block32 (MXFP8) scaling is not built; use the tensor-wide mode");
-    LFM25_ENSURE(std::isfinite(config->output_scale) && config->output_scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
-                 "FP8 output scale must be finite and positive");
+    return linear_fp8_dispatch(static_cast<cudaStream_t>(stream), x, weight, out, config);
+}
+
+int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out) {
+    LFM25_ENSURE(out != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt output handle is null");
+    lfm25_blaslt* handle = new (std::nothrow) lfm25_blaslt();
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_CUDA, "failed to allocate the BlasLt handle");
+    handle->stream = static_cast<cudaStream_t>(stream);
+    handle->library_workspace_bytes = 32u * 1024u * 1024u;   // src/cuda/blaslt/mod.rs:53-57
+    const size_t total = handle->library_workspace_bytes;
+    cudaError_t status = cudaMalloc(&handle->allocation, total);
+    if (status == cudaSuccess) {
+        status = cudaMemsetAsync(handle->allocation, 0, total, handle->stream);
+    }
+    if (status != cudaSuccess) {
+        if (handle->allocation != nullptr) {
+            cudaFree(handle->allocation);
+        }
+        delete handle;
+        return cuda_result(status, "failed to allocate the GEMM workspace");
+    }
+    handle->library_workspace = handle->allocation;
+    handle->cublaslt = nullptr;
+    *out = handle;
+    return LFM25_OK;
+}
+
+void lfm25_blaslt_destroy(lfm25_blaslt* handle) {
+    if (handle != nullptr) {
+        lfm25::cublaslt_bf16_destroy(handle->cublaslt);
+        cudaFree(handle->allocation);
+        delete handle;
+    }
+}
+
+int32_t lfm25_blaslt_set_stream(lfm25_blaslt* handle, void* stream) {
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
+    handle->stream = static_cast<cudaStream_t>(stream);
+    return LFM25_OK;
+}
+
+size_t lfm25_blaslt_workspace_size(const lfm25_blaslt* handle) {
+    return handle != nullptr ? handle->library_workspace_bytes : 0;
+}
+
+int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out, size_t m,
+                                 size_t n, size_t k) {
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
+    LFM25_ENSURE(m > 0 && n > 0 && k > 0, LFM25_ERR_INVALID_ARGUMENT, "linear does not support empty tensors");
     size_t x_required = 0;
     size_t weight_required = 0;
     size_t out_required = 0;
-    LFM25_ENSURE(checked_mul(m, k, &x_required), LFM25_ERR_OVERFLOW, "FP8 linear input size overflow");
-    LFM25_ENSURE(checked_mul(n, k, &weight_required), LFM25_ERR_OVERFLOW, "FP8 linear weight size overflow");
-    LFM25_ENSURE(checked_mul(m, n, &out_required), LFM25_ERR_OVERFLOW, "FP8 linear output size overflow");
-    LFM25_ENSURE(x.len >= x_required, LFM25_ERR_BUFFER_TOO_SMALL,
-                 "FP8 linear input storage too small: required=%zu, actual=%zu", x_required, x.len);
-    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL,
-                 "FP8 linear weight storage too small: required=%zu, actual=%zu", weight_required, weight.len);
-    LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL,
-                 "FP8 linear output storage too small: required=%zu, actual=%zu", out_required, out.len);
-    LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER,
-                 "FP8 linear received a null device pointer");
-    LFM25_ENSURE(m <= 0x7fffffffu && n <= 0x7fffffffu && k <= 0x7fffffffu, LFM25_ERR_INVALID_ARGUMENT,
-                 "FP8 linear dimension exceeds i32");
-    cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
-    const bool aligned =
-        ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr)) & 15) == 0;
-    if (aligned && lfm25::fp8_gemm_stream_supports(m, n, k)) {
-        return cuda_result(
-            lfm25::launch_fp8_gemm_stream(cuda_stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale),
-            "FP8 linear launch failed");
+    LFM25_ENSURE(checked_mul(m, k, &x_required) && checked_mul(n, k, &weight_required) &&
+                     checked_mul(m, n, &out_required),
+                 LFM25_ERR_OVERFLOW, "linear size overflow");
+    LFM25_ENSURE(x.len >= x_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear input storage too small");
+    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear weight storage too small");
+    LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear output storage too small");
+    LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "linear received a null device pointer");
+    if (handle->cublaslt == nullptr) {
+        handle->cublaslt = lfm25::cublaslt_bf16_create(handle->library_workspace, handle->library_workspace_bytes);
+        LFM25_ENSURE(handle->cublaslt != nullptr, LFM25_ERR_CUDA, "cuBLASLt could not be opened");
     }
     return cuda_result(
-        lfm25::launch_fp8_gemm_generic(cuda_stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale),
-        "FP8 linear launch failed");
+        lfm25::cublaslt_bf16_linear(handle->cublaslt, handle->stream, x.ptr, weight.ptr, out.ptr, m, n, k),
+        "cuBLASLt BF16 matmul failed");
+}
+
+int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
+                                       const lfm25_fp8_linear_config* config) {
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
+    return linear_fp8_dispatch(handle->stream, x, weight, out, config);
 }
 
 }  // extern "C"

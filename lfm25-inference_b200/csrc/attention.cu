@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "tensor_map.h"
 
 namespace lfm25 {
 
@@ -377,37 +378,11 @@ merge_splitk_kernel(const float* __restrict__ partials, __nv_bfloat16* __restric
     out_row[lane + 32] = __float2bfloat16_rn(out1 / denominator);
 }
 
-// ---- tensor maps over the arena: rows = pages * 8 heads * 16 tokens, 64 bf16 per row ----
-
-using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled_entry() {
-    static EncodeTiledFn entry = [] {
-        void* pointer = nullptr;
-        cudaDriverEntryPointQueryResult query = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &pointer, cudaEnableDefault, &query) != cudaSuccess ||
-            query != cudaDriverEntryPointSuccess) {
-            pointer = nullptr;
-        }
-        return reinterpret_cast<EncodeTiledFn>(pointer);
-    }();
-    return entry;
-}
-
+// Tensor map over an arena: rows = pages * 8 heads * 16 tokens, 64 bf16 (128 bytes) per row,
+// one box = one (page, KV head) tile.
 bool make_page_map(CUtensorMap* map, const void* cache, uint64_t num_pages) {
-    EncodeTiledFn encode = encode_tiled_entry();
-    if (encode == nullptr) {
-        return false;
-    }
-    const cuuint64_t dims[2] = {kHeadDim, num_pages * kKvHeads * kPageSize};
-    const cuuint64_t strides[1] = {kHeadDim * 2};
-    const cuuint32_t box[2] = {kHeadDim, kPageSize};
-    const cuuint32_t element_strides[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box,
-                  element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    return make_swizzled_2d_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, cache, num_pages * kKvHeads * kPageSize,
+                                kHeadDim * 2, kPageSize);
 }
 
 }  // namespace

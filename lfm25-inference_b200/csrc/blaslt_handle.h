@@ -1,0 +1,22 @@
+// Layout of the opaque lfm25_blaslt handle (internal): the stream it is bound to, the one device allocation it
+// owns (the cuBLASLt workspace) and the lazily opened cuBLASLt state.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace lfm25 {
+struct CublasLtBf16;
+CublasLtBf16* cublaslt_bf16_create(void* workspace, size_t workspace_bytes);
+void cublaslt_bf16_destroy(CublasLtBf16* self);
+cudaError_t cublaslt_bf16_linear(CublasLtBf16* self, cudaStream_t stream, const void* x, const void* weight,
+                                 void* out, size_t m, size_t n, size_t k);
+}  // namespace lfm25
+
+struct lfm25_blaslt {
+    cudaStream_t stream;
+    void* allocation;
+    void* library_workspace;        // handed to cuBLASLt (32 MiB, the size the reference uses)
+    size_t library_workspace_bytes;
+    lfm25::CublasLtBf16* cublaslt;  // null until the first BF16 linear
+};

@@ -1,0 +1,500 @@
+// Decode executor: one continuous-batching decode step of the LFM2.5-1.2B architecture on fixed-address
+// scratch, with the step metadata advanced on the device and the whole step replayed from a CUDA graph.
+//
+// Replaces the reference's DecodeExecutor (src/model/decode_executor.rs:127-155 scratch, :183-443 step) and
+// the host work around it (BatchModelCache::prepare_tokens, src/model/lfm2_base.rs:322-388; GpuBatch::update_*,
+// src/scheduler/batch.rs:142-260).  The op sequence is the reference's; what changes is who runs it:
+//   * positions, token ids and physical slots live on the device and are advanced by a kernel at the head of
+//     the step (the sampled ids of the previous step feed the next one), so a step needs no H2D copy and no
+//     host synchronisation;
+//   * every kernel argument is a fixed device pointer, so one captured graph per batch size replays unchanged.
+#include <stdio.h>
+
+#include <new>
+#include <utility>
+#include <vector>
+
+#include "../../include/lfm25_b200.h"
+#include "blaslt_handle.h"
+#include "kernels.h"
+
+namespace {
+
+constexpr size_t kHidden = 2048;
+constexpr size_t kQueryWidth = 2048;
+constexpr size_t kKvWidth = 512;
+constexpr size_t kFfn = 8192;
+constexpr size_t kVocab = 65536;
+
+}  // namespace
+
+struct lfm25_decode_executor {
+    lfm25_blaslt* blaslt;
+    size_t maximum_tokens;
+    void* allocation;
+    // scratch, fixed addresses (src/model/decode_executor.rs:6-22)
+    void* hidden;
+    void* normalized;
+    void* post_operator;
+    void* operator_output;
+    void* query;
+    void* key;
+    void* value;
+    void* wide;
+    void* activated;
+    void* logits;
+    void* fp8_input;
+    float* partials;
+    uint32_t* sampled;
+    // opt-in region timing (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): CUDA-event pairs
+    // around every op of an eager step, summed per region
+    bool profiling = false;
+    std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> marks;
+    // captured step, one per batch size
+    struct Captured {
+        size_t num_tokens = 0;
+        uint32_t use_fp8 = 0;
+        const void* model_layers = nullptr;
+        const void* token_ids = nullptr;
+        bool warmed = false;
+        cudaGraphExec_t exec = nullptr;
+    } captured[8];
+};
+
+namespace {
+
+// Times one op of an eager step when profiling is on; a no-op otherwise (and always during graph capture).
+struct RegionTimer {
+    lfm25_decode_executor* self;
+    cudaEvent_t start = nullptr;
+    cudaEvent_t stop = nullptr;
+    int region;
+    RegionTimer(lfm25_decode_executor* executor, int which) : self(executor), region(which) {
+        if (self->profiling && cudaEventCreate(&start) == cudaSuccess && cudaEventCreate(&stop) == cudaSuccess) {
+            cudaEventRecord(start, self->blaslt->stream);
+        }
+    }
+    ~RegionTimer() {
+        if (self->profiling && start != nullptr && stop != nullptr) {
+            cudaEventRecord(stop, self->blaslt->stream);
+            self->marks.push_back({region, {start, stop}});
+        }
+    }
+};
+
+int32_t cuda_failure(cudaError_t status, const char* what) {
+    char message[200];
+    snprintf(message, sizeof message, "%s: %s", what, cudaGetErrorString(status));
+    return lfm25::report_error(LFM25_ERR_CUDA, message);
+}
+
+#define LFM25_TRY(expression)          \
+    do {                               \
+        const int32_t rc = (expression); \
+        if (rc != LFM25_OK) {          \
+            return rc;                 \
+        }                              \
+    } while (0)
+
+lfm25_slice slice_of(const void* pointer, size_t elements) {
+    lfm25_slice slice;
+    slice.ptr = const_cast<void*>(pointer);
+    slice.len = elements;
+    return slice;
+}
+
+// linear_decode_into (src/model/decode_executor.rs:78-124): FP8 when the site is promoted and FP8 is on
+// (quantise the activation with the site's static scale, then the E4M3 GEMM with alpha = d_x * d_w), else BF16.
+int32_t linear_decode(lfm25_decode_executor* self, const lfm25_linear_weights& weights, const void* input,
+                      void* output, size_t rows, bool use_fp8) {
+    if (use_fp8 && weights.fp8.data != nullptr) {
+        RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
+        LFM25_TRY(lfm25_quantize_bf16_e4m3(self->blaslt->stream, slice_of(input, rows * weights.k),
+                                           slice_of(self->fp8_input, self->maximum_tokens * kFfn), rows * weights.k,
+                                           weights.fp8.activation_quantize));
+        lfm25_fp8_linear_config config;
+        config.m = rows;
+        config.n = weights.n;
+        config.k = weights.k;
+        config.scale_mode = LFM25_FP8_SCALE_TENSORWIDE;
+        config.output_scale = weights.fp8.activation_dequantize * weights.fp8.weight_dequantize;
+        return lfm25_blaslt_linear_fp8_scaled(self->blaslt, slice_of(self->fp8_input, rows * weights.k),
+                                              slice_of(weights.fp8.data, weights.n * weights.k),
+                                              slice_of(output, rows * weights.n), &config);
+    }
+    if (weights.bf16 == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "linear site has neither BF16 nor FP8 weights resident");
+    }
+    RegionTimer timer(self, LFM25_REGION_BF16_LINEAR);
+    return lfm25_blaslt_linear_bf16(self->blaslt, slice_of(input, rows * weights.k),
+                                    slice_of(weights.bf16, weights.n * weights.k), slice_of(output, rows * weights.n),
+                                    rows, weights.n, weights.k);
+}
+
+int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm25_decode_batch* batch, bool use_fp8,
+                bool advance) {
+    cudaStream_t stream = self->blaslt->stream;
+    const size_t tokens = batch->num_tokens;
+    cudaError_t status = cudaSuccess;
+    {
+    RegionTimer timer(self, LFM25_REGION_OTHER);
+    status = lfm25::launch_decode_metadata(
+        stream, batch->token_ids, batch->positions, batch->request_slots, batch->block_tables, self->sampled,
+        batch->physical_slots, tokens, batch->block_table_stride, batch->block_table_rows, model->num_pages, advance);
+    if (status != cudaSuccess) return cuda_failure(status, "step metadata launch failed");
+    status = lfm25::launch_embedding_bf16(stream, batch->token_ids, model->embedding, self->hidden, tokens, kVocab,
+                                          kHidden);
+    if (status != cudaSuccess) return cuda_failure(status, "embedding launch failed");
+    status = lfm25::launch_rms_norm_bf16(stream, self->hidden, model->layers[0].operator_norm, self->normalized,
+                                         tokens, kHidden, model->norm_eps);
+    if (status != cudaSuccess) return cuda_failure(status, "rms_norm launch failed");
+    }
+
+    for (uint32_t index = 0; index < model->num_layers; ++index) {
+        const lfm25_layer& layer = model->layers[index];
+        if (!layer.is_attention) {
+            LFM25_TRY(linear_decode(self, layer.conv_input, self->normalized, self->wide, tokens, use_fp8));
+            RegionTimer timer(self, LFM25_REGION_OTHER);
+            status = lfm25::launch_short_conv_decode(stream, self->wide, layer.conv_kernel, layer.conv_state,
+                                                     batch->request_slots, self->post_operator, tokens, kHidden,
+                                                     model->num_request_slots);
+            if (status != cudaSuccess) return cuda_failure(status, "short_conv launch failed");
+            LFM25_TRY(linear_decode(self, layer.conv_output, self->post_operator, self->operator_output, tokens,
+                                    use_fp8));
+        } else {
+            LFM25_TRY(linear_decode(self, layer.query, self->normalized, self->query, tokens, use_fp8));
+            LFM25_TRY(linear_decode(self, layer.key, self->normalized, self->key, tokens, use_fp8));
+            LFM25_TRY(linear_decode(self, layer.value, self->normalized, self->value, tokens, use_fp8));
+            const size_t cache_elements = model->num_pages * 8 * 16 * 64;
+            lfm25_qk_postprocess_launch post;
+            post.page_size = 16;
+            post.query = slice_of(self->query, tokens * kQueryWidth);
+            post.key = slice_of(self->key, tokens * kKvWidth);
+            post.value = slice_of(self->value, tokens * kKvWidth);
+            post.query_norm = slice_of(layer.query_norm, 64);
+            post.key_norm = slice_of(layer.key_norm, 64);
+            post.inv_freq = slice_of(model->inv_freq, 32);
+            post.position_ids = slice_of(batch->positions, tokens);
+            post.slot_mapping = slice_of(batch->physical_slots, tokens);
+            post.key_cache = slice_of(layer.key_cache, cache_elements);
+            post.value_cache = slice_of(layer.value_cache, cache_elements);
+            post.num_tokens = tokens;
+            post.num_pages = model->num_pages;
+            post.eps = model->norm_eps;
+            {
+                RegionTimer timer(self, LFM25_REGION_APPEND);
+                LFM25_TRY(lfm25_qk_norm_rope_kv_write_decode(stream, &post));
+            }
+            {
+            RegionTimer attention_timer(self, LFM25_REGION_ATTENTION);
+
+            const size_t splits = lfm25_splitk_decode_splits(tokens, batch->max_context_tokens, 16);
+            lfm25_splitk_ragged_attention_launch attention;
+            attention.page_size = 16;
+            attention.query = post.query;
+            attention.key_cache = post.key_cache;
+            attention.value_cache = post.value_cache;
+            attention.block_tables = slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
+            attention.request_slots = slice_of(batch->request_slots, tokens);
+            attention.position_ids = post.position_ids;
+            attention.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_tokens));
+            attention.output = slice_of(self->post_operator, tokens * kHidden);
+            attention.num_tokens = tokens;
+            attention.num_pages = model->num_pages;
+            attention.block_table_stride = batch->block_table_stride;
+            attention.num_splits = splits;
+            if (splits > 1) {
+                LFM25_TRY(lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &attention));
+            } else {
+                lfm25_fast_ragged_attention_launch unsplit;
+                unsplit.page_size = 16;
+                unsplit.query = attention.query;
+                unsplit.key_cache = attention.key_cache;
+                unsplit.value_cache = attention.value_cache;
+                unsplit.block_tables = attention.block_tables;
+                unsplit.request_slots = attention.request_slots;
+                unsplit.position_ids = attention.position_ids;
+                unsplit.output = attention.output;
+                unsplit.num_tokens = tokens;
+                unsplit.num_pages = model->num_pages;
+                unsplit.block_table_stride = batch->block_table_stride;
+                LFM25_TRY(lfm25_paged_ragged_attention_fast_lfm2_bf16(stream, &unsplit));
+            }
+            }
+            LFM25_TRY(linear_decode(self, layer.output, self->post_operator, self->operator_output, tokens, use_fp8));
+        }
+
+        {
+            RegionTimer timer(self, LFM25_REGION_OTHER);
+            status = lfm25::launch_residual_rms_norm_bf16(stream, self->hidden, self->operator_output, layer.ffn_norm,
+                                                          self->post_operator, self->normalized, tokens, kHidden,
+                                                          model->norm_eps);
+        }
+        if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
+
+        LFM25_TRY(linear_decode(self, layer.gate_up, self->normalized, self->wide, tokens, use_fp8));
+        if (use_fp8 && layer.down.fp8.data != nullptr) {
+            RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
+            LFM25_TRY(lfm25_silu_mul_packed_bf16_to_e4m3(stream, slice_of(self->wide, tokens * 2 * kFfn),
+                                                         slice_of(self->fp8_input, self->maximum_tokens * kFfn),
+                                                         tokens, kFfn, layer.down.fp8.activation_quantize));
+            lfm25_fp8_linear_config config;
+            config.m = tokens;
+            config.n = kHidden;
+            config.k = kFfn;
+            config.scale_mode = LFM25_FP8_SCALE_TENSORWIDE;
+            config.output_scale = layer.down.fp8.activation_dequantize * layer.down.fp8.weight_dequantize;
+            LFM25_TRY(lfm25_blaslt_linear_fp8_scaled(self->blaslt, slice_of(self->fp8_input, tokens * kFfn),
+                                                     slice_of(layer.down.fp8.data, kHidden * kFfn),
+                                                     slice_of(self->operator_output, tokens * kHidden), &config));
+        } else {
+            RegionTimer timer(self, LFM25_REGION_BF16_LINEAR);
+            LFM25_TRY(lfm25_silu_mul_packed_bf16(stream, slice_of(self->wide, tokens * 2 * kFfn),
+                                                 slice_of(self->activated, tokens * kFfn), tokens, kFfn));
+            if (layer.down.bf16 == nullptr) {
+                return lfm25::report_error(LFM25_ERR_NULL_POINTER, "Down site has no BF16 weights resident");
+            }
+            LFM25_TRY(lfm25_blaslt_linear_bf16(self->blaslt, slice_of(self->activated, tokens * kFfn),
+                                               slice_of(layer.down.bf16, kHidden * kFfn),
+                                               slice_of(self->operator_output, tokens * kHidden), tokens, kHidden,
+                                               kFfn));
+        }
+
+        const void* next_norm =
+            index + 1 < model->num_layers ? model->layers[index + 1].operator_norm : model->final_norm;
+        {
+            RegionTimer timer(self, LFM25_REGION_OTHER);
+            status = lfm25::launch_residual_rms_norm_bf16(stream, self->post_operator, self->operator_output,
+                                                          next_norm, self->hidden, self->normalized, tokens, kHidden,
+                                                          model->norm_eps);
+        }
+        if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
+    }
+
+    // tied LM head: the embedding matrix, FP8 when promoted
+    lfm25_linear_weights head;
+    head.bf16 = model->embedding;
+    head.fp8 = model->lm_head_fp8;
+    head.n = kVocab;
+    head.k = kHidden;
+    LFM25_TRY(linear_decode(self, head, self->normalized, self->logits, tokens, use_fp8));
+    {
+        RegionTimer timer(self, LFM25_REGION_OTHER);
+        status = lfm25::launch_argmax_rows_bf16(stream, self->logits, self->sampled, tokens, kVocab);
+    }
+    if (status != cudaSuccess) return cuda_failure(status, "argmax launch failed");
+    return LFM25_OK;
+}
+
+int32_t validate(const lfm25_decode_executor* self, const lfm25_model* model, const lfm25_decode_batch* batch) {
+    if (self == nullptr || model == nullptr || batch == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor received a null argument");
+    }
+    if (batch->num_tokens == 0 || batch->num_tokens > self->maximum_tokens) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "decode executor token count exceeds workspace");
+    }
+    if (model->num_layers == 0 || model->layers == nullptr || model->embedding == nullptr ||
+        model->final_norm == nullptr || model->inv_freq == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor model is incomplete");
+    }
+    if (!batch->token_ids || !batch->positions || !batch->request_slots || !batch->physical_slots ||
+        !batch->block_tables || batch->block_table_stride == 0 || batch->block_table_rows == 0) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode batch metadata is incomplete");
+    }
+    return LFM25_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t lfm25_decode_executor_create(lfm25_blaslt* blaslt, size_t maximum_tokens, lfm25_decode_executor** out) {
+    if (blaslt == nullptr || out == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor needs a BlasLt handle and an output");
+    }
+    if (maximum_tokens == 0 || maximum_tokens > 256) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "decode executor supports 1..=256 tokens per step");
+    }
+    lfm25_decode_executor* self = new (std::nothrow) lfm25_decode_executor();
+    if (self == nullptr) {
+        return lfm25::report_error(LFM25_ERR_CUDA, "failed to allocate the decode executor");
+    }
+    self->blaslt = blaslt;
+    self->maximum_tokens = maximum_tokens;
+    const size_t b = maximum_tokens;
+    const size_t sizes[13] = {
+        b * kHidden * 2, b * kHidden * 2, b * kHidden * 2, b * kHidden * 2,         // hidden .. operator_output
+        b * kQueryWidth * 2, b * kKvWidth * 2, b * kKvWidth * 2,                    // query, key, value
+        b * 2 * kFfn * 2, b * kFfn * 2, b * kVocab * 2,                             // wide, activated, logits
+        b * kFfn,                                                                   // fp8_input
+        lfm25_splitk_workspace_elements(b) * sizeof(float), b * sizeof(uint32_t)};  // partials, sampled
+    size_t total = 0;
+    size_t offsets[13];
+    for (int index = 0; index < 13; ++index) {
+        offsets[index] = total;
+        total += (sizes[index] + 255) & ~static_cast<size_t>(255);
+    }
+    cudaError_t status = cudaMalloc(&self->allocation, total);
+    if (status == cudaSuccess) {
+        status = cudaMemsetAsync(self->allocation, 0, total, blaslt->stream);
+    }
+    if (status != cudaSuccess) {
+        delete self;
+        return cuda_failure(status, "failed to allocate decode scratch");
+    }
+    unsigned char* base = static_cast<unsigned char*>(self->allocation);
+    void** fields[13] = {&self->hidden, &self->normalized, &self->post_operator, &self->operator_output, &self->query,
+                         &self->key, &self->value, &self->wide, &self->activated, &self->logits, &self->fp8_input,
+                         reinterpret_cast<void**>(&self->partials), reinterpret_cast<void**>(&self->sampled)};
+    for (int index = 0; index < 13; ++index) {
+        *fields[index] = base + offsets[index];
+    }
+    *out = self;
+    return LFM25_OK;
+}
+
+void lfm25_decode_executor_destroy(lfm25_decode_executor* self) {
+    if (self == nullptr) {
+        return;
+    }
+    for (auto& entry : self->captured) {
+        if (entry.exec != nullptr) {
+            cudaGraphExecDestroy(entry.exec);
+        }
+    }
+    cudaFree(self->allocation);
+    delete self;
+}
+
+int32_t lfm25_decode_executor_download_sampled(lfm25_decode_executor* self, uint32_t* host, size_t count) {
+    if (self == nullptr || host == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "sampled download received a null argument");
+    }
+    if (count > self->maximum_tokens) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "sampled download exceeds the executor's capacity");
+    }
+    const cudaError_t status = cudaMemcpyAsync(host, self->sampled, count * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                                               self->blaslt->stream);
+    return status == cudaSuccess ? LFM25_OK : cuda_failure(status, "sampled download failed");
+}
+
+int32_t lfm25_decode_executor_download_logits(lfm25_decode_executor* self, void* host, size_t rows) {
+    if (self == nullptr || host == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "logits download received a null argument");
+    }
+    if (rows > self->maximum_tokens) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "logits download exceeds the executor's capacity");
+    }
+    const cudaError_t status = cudaMemcpyAsync(host, self->logits, rows * kVocab * 2, cudaMemcpyDeviceToHost,
+                                               self->blaslt->stream);
+    return status == cudaSuccess ? LFM25_OK : cuda_failure(status, "logits download failed");
+}
+
+const uint32_t* lfm25_decode_executor_sampled(const lfm25_decode_executor* self) {
+    return self != nullptr ? self->sampled : nullptr;
+}
+
+const void* lfm25_decode_executor_logits(const lfm25_decode_executor* self) {
+    return self != nullptr ? self->logits : nullptr;
+}
+
+int32_t lfm25_decode_executor_profile(lfm25_decode_executor* self, uint32_t enable, float region_ms[LFM25_REGION_COUNT],
+                                      uint32_t region_launches[LFM25_REGION_COUNT]) {
+    if (self == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor is null");
+    }
+    if (region_ms != nullptr) {
+        // collect what has been recorded so far (synchronises the stream)
+        const cudaError_t status = cudaStreamSynchronize(self->blaslt->stream);
+        if (status != cudaSuccess) return cuda_failure(status, "profile synchronisation failed");
+        for (int region = 0; region < LFM25_REGION_COUNT; ++region) {
+            region_ms[region] = 0.0f;
+            if (region_launches != nullptr) region_launches[region] = 0;
+        }
+        for (auto& mark : self->marks) {
+            float elapsed = 0.0f;
+            if (cudaEventElapsedTime(&elapsed, mark.second.first, mark.second.second) == cudaSuccess) {
+                region_ms[mark.first] += elapsed;
+                if (region_launches != nullptr) region_launches[mark.first] += 1;
+            }
+            cudaEventDestroy(mark.second.first);
+            cudaEventDestroy(mark.second.second);
+        }
+        self->marks.clear();
+    }
+    self->profiling = enable != 0;
+    return LFM25_OK;
+}
+
+int32_t lfm25_decode_executor_forward(lfm25_decode_executor* self, const lfm25_model* model,
+                                      const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance) {
+    LFM25_TRY(validate(self, model, batch));
+    return forward(self, model, batch, use_fp8 != 0, advance != 0);
+}
+
+int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm25_model* model,
+                                         const lfm25_decode_batch* batch, uint32_t use_fp8) {
+    LFM25_TRY(validate(self, model, batch));
+    lfm25_decode_executor::Captured* entry = nullptr;
+    for (auto& candidate : self->captured) {
+        if (candidate.num_tokens == batch->num_tokens && candidate.use_fp8 == use_fp8 &&
+            candidate.model_layers == model->layers && candidate.token_ids == batch->token_ids) {
+            entry = &candidate;
+            break;
+        }
+    }
+    if (entry == nullptr) {
+        // take a free entry, or recycle the first one
+        for (auto& candidate : self->captured) {
+            if (candidate.num_tokens == 0) {
+                entry = &candidate;
+                break;
+            }
+        }
+        if (entry == nullptr) {
+            entry = &self->captured[0];
+            if (entry->exec != nullptr) {
+                cudaGraphExecDestroy(entry->exec);
+            }
+        }
+        *entry = lfm25_decode_executor::Captured();
+        entry->num_tokens = batch->num_tokens;
+        entry->use_fp8 = use_fp8;
+        entry->model_layers = model->layers;
+        entry->token_ids = batch->token_ids;
+    }
+    cudaStream_t stream = self->blaslt->stream;
+    if (stream == nullptr || stream == cudaStreamLegacy) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT,
+                                   "graph replay needs the BlasLt handle bound to a non-default stream");
+    }
+    if (!entry->warmed) {
+        // The first step of a bucket runs eagerly: cuBLASLt plans, function attributes and symbol lookups happen
+        // here, outside any capture.
+        entry->warmed = true;
+        return forward(self, model, batch, use_fp8 != 0, true);
+    }
+    if (entry->exec == nullptr) {
+        cudaError_t status = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
+        if (status != cudaSuccess) return cuda_failure(status, "stream capture could not begin");
+        const bool was_profiling = self->profiling;
+        self->profiling = false;
+        const int32_t rc = forward(self, model, batch, use_fp8 != 0, true);
+        self->profiling = was_profiling;
+        cudaGraph_t graph = nullptr;
+        status = cudaStreamEndCapture(stream, &graph);
+        if (rc != LFM25_OK) {
+            if (graph != nullptr) cudaGraphDestroy(graph);
+            return rc;
+        }
+        if (status != cudaSuccess) return cuda_failure(status, "stream capture failed");
+        status = cudaGraphInstantiate(&entry->exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (status != cudaSuccess) return cuda_failure(status, "graph instantiation failed");
+    }
+    const cudaError_t status = cudaGraphLaunch(entry->exec, stream);
+    if (status != cudaSuccess) return cuda_failure(status, "graph launch failed");
+    return LFM25_OK;
+}
+
+}  // extern "C"

@@ -61,6 +61,27 @@ cudaError_t launch_fp8_gemm_stream(cudaStream_t stream, const void* x, const voi
 cudaError_t launch_fp8_gemm_generic(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
                                     size_t n, size_t k, float alpha);
 
+bool fp8_gemm_umma_supports(size_t m, size_t n, size_t k);
+cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                 size_t n, size_t k, float alpha, unsigned int* status);
+
+cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids, const void* table, void* out,
+                                  size_t num_tokens, size_t vocab_size, size_t hidden);
+cudaError_t launch_rms_norm_bf16(cudaStream_t stream, const void* x, const void* weight, void* out, size_t rows,
+                                 size_t hidden, float eps);
+cudaError_t launch_residual_rms_norm_bf16(cudaStream_t stream, const void* residual, const void* update,
+                                          const void* weight, void* residual_out, void* normalized_out, size_t rows,
+                                          size_t hidden, float eps);
+cudaError_t launch_short_conv_decode(cudaStream_t stream, const void* projected, const void* weight, void* states,
+                                     const uint32_t* request_slots, void* output, size_t num_tokens, size_t hidden,
+                                     size_t num_request_slots);
+cudaError_t launch_argmax_rows_bf16(cudaStream_t stream, const void* logits, uint32_t* sampled, size_t rows,
+                                    size_t vocab);
+cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uint32_t* positions,
+                                   const uint32_t* request_slots, const uint32_t* block_tables, const uint32_t* sampled,
+                                   int64_t* physical_slots, size_t num_tokens, size_t block_table_stride,
+                                   size_t block_table_rows, size_t num_pages, bool advance);
+
 // Stores `message` as the calling thread's last error (what lfm25_last_error() returns) and returns `code`.
 int32_t report_error(int32_t code, const char* message);
 

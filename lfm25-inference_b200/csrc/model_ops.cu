@@ -1,0 +1,294 @@
+// The remaining small ops of a decode step (everything between the GEMMs and the attention):
+// embedding rows, RMSNorm, residual add + RMSNorm, gated short convolution, greedy argmax, and the
+// device-side step metadata that replaces the reference's per-step host loop and H2D slab.
+//
+// They replace, in the reference: kernels/embedding.cu:65, kernels/rms_norm.cu:342 and :364,
+// kernels/short_conv.cu:100 (one token per segment, the decode case), kernels/sampling.cu:53-217
+// (tie order of the legacy argmax), kernels/metadata.cu:12-69 + src/model/lfm2_base.rs:338-380.
+// All are a few hundred KiB of traffic per launch at decode batch sizes: they are written to be
+// cheap to launch (one CTA per row, 16-byte accesses), not tuned against a roofline.
+#include <float.h>
+
+#include "common.cuh"
+#include "kernels.h"
+
+namespace lfm25 {
+
+namespace {
+
+constexpr uint32_t kRowThreads = 256;
+
+__device__ __forceinline__ float block_sum_256(float value, float* scratch) {
+#pragma unroll
+    for (uint32_t delta = 16; delta > 0; delta >>= 1) {
+        value += __shfl_xor_sync(0xffffffffu, value, delta);
+    }
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t lane = threadIdx.x & 31;
+    if (lane == 0) {
+        scratch[warp] = value;
+    }
+    __syncthreads();
+    float total = lane < (blockDim.x >> 5) ? scratch[lane] : 0.0f;
+#pragma unroll
+    for (uint32_t delta = 4; delta > 0; delta >>= 1) {
+        total += __shfl_xor_sync(0xffffffffu, total, delta);
+    }
+    return __shfl_sync(0xffffffffu, total, 0);
+}
+
+// out[t, :] = table[token_ids[t], :]; an id beyond the vocabulary leaves the row untouched.
+__global__ void __launch_bounds__(kRowThreads)
+embedding_kernel(const uint32_t* __restrict__ token_ids, const __nv_bfloat16* __restrict__ table,
+                 __nv_bfloat16* __restrict__ out, size_t num_tokens, size_t vocab_size, size_t hidden) {
+    const size_t token = blockIdx.x;
+    if (token >= num_tokens) {
+        return;
+    }
+    const uint32_t id = token_ids[token];
+    if (id >= vocab_size) {
+        return;
+    }
+    const __nv_bfloat16* source = table + static_cast<size_t>(id) * hidden;
+    __nv_bfloat16* destination = out + token * hidden;
+    if (hidden % 8 == 0) {
+        for (size_t vector = threadIdx.x; vector < hidden / 8; vector += blockDim.x) {
+            reinterpret_cast<uint4*>(destination)[vector] = __ldg(reinterpret_cast<const uint4*>(source) + vector);
+        }
+    } else {
+        for (size_t index = threadIdx.x; index < hidden; index += blockDim.x) {
+            destination[index] = source[index];
+        }
+    }
+}
+
+// RESIDUAL == false: out = bf16(bf16(x * inv_rms) * weight)                    (kernels/rms_norm.cu:268-278)
+// RESIDUAL == true : r = bf16(residual + update) stored to residual_out; the variance uses the unrounded fp32
+//                    sums; out = bf16(float(r) * inv_rms * float(weight))       (kernels/rms_norm.cu:394-453)
+template <bool RESIDUAL>
+__global__ void __launch_bounds__(kRowThreads)
+rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ update,
+                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ residual_out,
+                __nv_bfloat16* __restrict__ out, size_t rows, size_t hidden, float eps) {
+    __shared__ float scratch[8];
+    const size_t row = blockIdx.x;
+    if (row >= rows) {
+        return;
+    }
+    const __nv_bfloat16* x_row = x + row * hidden;
+    float local = 0.0f;
+    for (size_t index = threadIdx.x * 2; index < hidden; index += blockDim.x * 2) {
+        // hidden is even for every model shape; odd sizes are rejected by the caller
+        float2 value = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(x_row + index));
+        if (RESIDUAL) {
+            const float2 add = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(update + row * hidden + index));
+            value.x += add.x;
+            value.y += add.y;
+            *reinterpret_cast<__nv_bfloat162*>(residual_out + row * hidden + index) =
+                __floats2bfloat162_rn(value.x, value.y);
+        }
+        local = fmaf(value.x, value.x, local);
+        local = fmaf(value.y, value.y, local);
+    }
+    const float total = block_sum_256(local, scratch);
+    const float inv_rms = __frsqrt_rn(total / static_cast<float>(hidden) + eps);
+    const __nv_bfloat16* normal_source = RESIDUAL ? residual_out + row * hidden : x_row;
+    for (size_t index = threadIdx.x * 2; index < hidden; index += blockDim.x * 2) {
+        const __nv_bfloat162 raw = *reinterpret_cast<const __nv_bfloat162*>(normal_source + index);
+        const __nv_bfloat162 scale = *reinterpret_cast<const __nv_bfloat162*>(weight + index);
+        const float2 value = __bfloat1622float2(raw);
+        __nv_bfloat162 result;
+        if (RESIDUAL) {
+            const float2 w = __bfloat1622float2(scale);
+            result = __floats2bfloat162_rn(value.x * inv_rms * w.x, value.y * inv_rms * w.y);
+        } else {
+            result = __hmul2(__floats2bfloat162_rn(value.x * inv_rms, value.y * inv_rms), scale);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(out + row * hidden + index) = result;
+    }
+}
+
+// Decode step of the gated depthwise convolution (width 3): one new token per sequence.
+//   projected[t] = [b | c | x] (3 * hidden);  gated = b * x;
+//   y = c * (w0 * s0 + w1 * s1 + w2 * gated);  state <- (s1, gated), all per channel, fp32 math on bf16 storage.
+__global__ void __launch_bounds__(kRowThreads)
+short_conv_decode_kernel(const __nv_bfloat16* __restrict__ projected, const __nv_bfloat16* __restrict__ weight,
+                         __nv_bfloat16* __restrict__ states, const uint32_t* __restrict__ request_slots,
+                         __nv_bfloat16* __restrict__ output, size_t num_tokens, size_t hidden,
+                         size_t num_request_slots) {
+    const size_t work = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (work >= num_tokens * hidden) {
+        return;
+    }
+    const size_t token = work / hidden;
+    const size_t channel = work % hidden;
+    const size_t slot = request_slots[token];
+    if (slot >= num_request_slots) {
+        return;
+    }
+    __nv_bfloat162* state = reinterpret_cast<__nv_bfloat162*>(states) + slot * hidden + channel;
+    const float2 previous = __bfloat1622float2(*state);
+    const float w0 = __bfloat162float(weight[channel * 3]);
+    const float w1 = __bfloat162float(weight[channel * 3 + 1]);
+    const float w2 = __bfloat162float(weight[channel * 3 + 2]);
+    const size_t base = token * hidden * 3;
+    const float b = __bfloat162float(projected[base + channel]);
+    const float c = __bfloat162float(projected[base + hidden + channel]);
+    const float x = __bfloat162float(projected[base + hidden * 2 + channel]);
+    const float gated = b * x;
+    const float convolved = w0 * previous.x + w1 * previous.y + w2 * gated;
+    output[token * hidden + channel] = __float2bfloat16_rn(c * convolved);
+    *state = __floats2bfloat162_rn(previous.y, gated);
+}
+
+// Sortable key of one logit: larger key wins.  Ties resolve to the smaller (column % 256), then the smaller
+// (column / 256); NaN and -inf map to 0 and never win; +0 and -0 are equal (kernels/sampling.cu:101-134).
+__device__ __forceinline__ uint32_t argmax_key(uint16_t bits, uint32_t column) {
+    const uint16_t magnitude = bits & 0x7fffu;
+    if (magnitude > 0x7f80u || bits == 0xff80u) {
+        return 0u;
+    }
+    if (magnitude == 0u) {
+        bits = 0u;
+    }
+    const uint16_t ordered = (bits & 0x8000u) ? static_cast<uint16_t>(~bits) : static_cast<uint16_t>(bits ^ 0x8000u);
+    return (static_cast<uint32_t>(ordered) << 16) | ((0xffu - (column & 0xffu)) << 8) | (0xffu - (column >> 8));
+}
+
+constexpr uint32_t kArgmaxThreads = 1024;
+__global__ void __launch_bounds__(kArgmaxThreads)
+argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, uint32_t* __restrict__ sampled, size_t rows,
+                   size_t vocab) {
+    __shared__ uint32_t warp_best[32];
+    const size_t row = blockIdx.x;
+    if (row >= rows) {
+        return;
+    }
+    const uint16_t* row_bits = reinterpret_cast<const uint16_t*>(logits) + row * vocab;
+    uint32_t best = 0;
+    if (vocab % 8 == 0) {
+        for (size_t vector = threadIdx.x; vector < vocab / 8; vector += blockDim.x) {
+            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row_bits) + vector);
+            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (uint32_t pair = 0; pair < 4; ++pair) {
+                const uint32_t column = static_cast<uint32_t>(vector) * 8 + pair * 2;
+                best = max(best, argmax_key(static_cast<uint16_t>(words[pair] & 0xffffu), column));
+                best = max(best, argmax_key(static_cast<uint16_t>(words[pair] >> 16), column + 1));
+            }
+        }
+    } else {
+        for (size_t column = threadIdx.x; column < vocab; column += blockDim.x) {
+            best = max(best, argmax_key(row_bits[column], static_cast<uint32_t>(column)));
+        }
+    }
+#pragma unroll
+    for (uint32_t delta = 16; delta > 0; delta >>= 1) {
+        best = max(best, __shfl_xor_sync(0xffffffffu, best, delta));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        warp_best[threadIdx.x >> 5] = best;
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = threadIdx.x < (blockDim.x >> 5) ? warp_best[threadIdx.x] : 0u;
+#pragma unroll
+        for (uint32_t delta = 16; delta > 0; delta >>= 1) {
+            best = max(best, __shfl_xor_sync(0xffffffffu, best, delta));
+        }
+        if (threadIdx.x == 0) {
+            // key 0: every logit was NaN or -inf; the legacy kernel then answers column 0
+            sampled[row] = best == 0u ? 0u : (((0xffu - (best & 0xffu)) << 8) | (0xffu - ((best >> 8) & 0xffu)));
+        }
+    }
+}
+
+// Step metadata on the device.  For token t of the batch: physical_slot = table[slot][pos / 16] * 16 + pos % 16
+// (src/model/lfm2_base.rs:371-378), or -1 when the request slot, the position or the table entry is not valid
+// (the append kernels skip negative slots).  With `advance` the kernel first moves every sequence on by one
+// token: token id <- the id sampled by the previous step, position <- position + 1.  No host round trip.
+__global__ void __launch_bounds__(kRowThreads)
+decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ positions,
+                       const uint32_t* __restrict__ request_slots, const uint32_t* __restrict__ block_tables,
+                       const uint32_t* __restrict__ sampled, int64_t* __restrict__ physical_slots, size_t num_tokens,
+                       size_t block_table_stride, size_t block_table_rows, size_t num_pages, uint32_t advance) {
+    const size_t token = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (token >= num_tokens) {
+        return;
+    }
+    uint32_t position = positions[token];
+    if (advance) {
+        position += 1;
+        positions[token] = position;
+        token_ids[token] = sampled[token];
+    }
+    const size_t row = request_slots[token];
+    int64_t slot = -1;
+    const size_t page_index = position / kPageSize;
+    if (row < block_table_rows && page_index < block_table_stride) {
+        const uint32_t page = block_tables[row * block_table_stride + page_index];
+        if (page < num_pages) {
+            slot = static_cast<int64_t>(page) * kPageSize + position % kPageSize;
+        }
+    }
+    physical_slots[token] = slot;
+}
+
+}  // namespace
+
+cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids, const void* table, void* out,
+                                  size_t num_tokens, size_t vocab_size, size_t hidden) {
+    embedding_kernel<<<static_cast<unsigned int>(num_tokens), kRowThreads, 0, stream>>>(
+        token_ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), num_tokens, vocab_size,
+        hidden);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_rms_norm_bf16(cudaStream_t stream, const void* x, const void* weight, void* out, size_t rows,
+                                 size_t hidden, float eps) {
+    rms_norm_kernel<false><<<static_cast<unsigned int>(rows), kRowThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(weight), nullptr,
+        static_cast<__nv_bfloat16*>(out), rows, hidden, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_residual_rms_norm_bf16(cudaStream_t stream, const void* residual, const void* update,
+                                          const void* weight, void* residual_out, void* normalized_out, size_t rows,
+                                          size_t hidden, float eps) {
+    rms_norm_kernel<true><<<static_cast<unsigned int>(rows), kRowThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(update),
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(residual_out),
+        static_cast<__nv_bfloat16*>(normalized_out), rows, hidden, eps);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_short_conv_decode(cudaStream_t stream, const void* projected, const void* weight, void* states,
+                                     const uint32_t* request_slots, void* output, size_t num_tokens, size_t hidden,
+                                     size_t num_request_slots) {
+    const size_t work = num_tokens * hidden;
+    short_conv_decode_kernel<<<static_cast<unsigned int>((work + kRowThreads - 1) / kRowThreads), kRowThreads, 0,
+                               stream>>>(static_cast<const __nv_bfloat16*>(projected),
+                                         static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(states),
+                                         request_slots, static_cast<__nv_bfloat16*>(output), num_tokens, hidden,
+                                         num_request_slots);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_argmax_rows_bf16(cudaStream_t stream, const void* logits, uint32_t* sampled, size_t rows,
+                                    size_t vocab) {
+    argmax_rows_kernel<<<static_cast<unsigned int>(rows), kArgmaxThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(logits), sampled, rows, vocab);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uint32_t* positions,
+                                   const uint32_t* request_slots, const uint32_t* block_tables, const uint32_t* sampled,
+                                   int64_t* physical_slots, size_t num_tokens, size_t block_table_stride,
+                                   size_t block_table_rows, size_t num_pages, bool advance) {
+    decode_metadata_kernel<<<static_cast<unsigned int>((num_tokens + kRowThreads - 1) / kRowThreads), kRowThreads, 0,
+                             stream>>>(token_ids, positions, request_slots, block_tables, sampled, physical_slots,
+                                       num_tokens, block_table_stride, block_table_rows, num_pages, advance ? 1u : 0u);
+    return cudaGetLastError();
+}
+
+}  // namespace lfm25

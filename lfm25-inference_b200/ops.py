@@ -212,6 +212,56 @@ def linear_fp8_scaled_into(x_codes: torch.Tensor, weight_codes: torch.Tensor, ou
     check(library().lfm25_linear_fp8_scaled(_stream(), _slice(x_codes), _slice(weight_codes), _slice(output), config))
 
 
+class BlasLt:
+    """Mirror of the reference's `BlasLt` (src/cuda/blaslt/mod.rs:30-70): bound to the stream that is current at
+    construction, owns the 32 MiB workspace.  Its FP8 linear may split K across CTAs (Down-shaped problems)."""
+
+    def __init__(self):
+        import ctypes
+        self._handle = ctypes.c_void_p()
+        self._bound_stream = _stream()
+        check(library().lfm25_blaslt_create(self._bound_stream, ctypes.byref(self._handle)))
+        torch.cuda.current_stream().synchronize()   # the workspace is zeroed before any other stream may use it
+
+    def workspace_size(self) -> int:
+        return int(library().lfm25_blaslt_workspace_size(self._handle))
+
+    def linear_fp8_scaled(self, x_codes, weight_codes, output, output_scale: float,
+                          scale_mode: int = _abi.FP8_SCALE_TENSORWIDE) -> None:
+        m, k = x_codes.shape
+        config = _abi.Fp8LinearConfig(m, weight_codes.shape[0], k, scale_mode, output_scale)
+        self.bind_current_stream()
+        check(library().lfm25_blaslt_linear_fp8_scaled(self._handle, _slice(x_codes), _slice(weight_codes),
+                                                       _slice(output), config))
+
+    def bind_current_stream(self) -> None:
+        stream = _stream()
+        if stream != self._bound_stream:
+            check(library().lfm25_blaslt_set_stream(self._handle, stream))
+            self._bound_stream = stream
+
+    def linear_bf16(self, x: torch.Tensor, weight: torch.Tensor, output: torch.Tensor) -> None:
+        """out[M,N] = x[M,K] @ weight[N,K]^T through cuBLASLt (reference: src/ops/linear.rs linear_bf16_into)."""
+        _ensure(weight.dim() == 2, f"linear weight must have rank 2, got {tuple(weight.shape)}")
+        k = x.shape[-1]
+        _ensure(weight.shape[1] == k, "linear K mismatch")
+        rows = x.numel() // k
+        self.bind_current_stream()
+        check(library().lfm25_blaslt_linear_bf16(self._handle, _slice(x), _slice(weight), _slice(output), rows,
+                                                 weight.shape[0], k))
+
+    def close(self) -> None:
+        if self._handle:
+            library().lfm25_blaslt_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def linear_fp8_e4m3(x: torch.Tensor, weight_codes: torch.Tensor, activation_scale, weight_scale) -> torch.Tensor:
     """Quantise a bf16 activation with its static scale, then the FP8 linear
     (reference: src/ops/linear.rs:29-77).  Scales are (quantize_multiplier, dequantize_multiplier) pairs."""
@@ -226,6 +276,36 @@ def linear_fp8_e4m3(x: torch.Tensor, weight_codes: torch.Tensor, activation_scal
     output = torch.empty((*x.shape[:-1], weight_codes.shape[0]), dtype=torch.bfloat16, device=x.device)
     linear_fp8_scaled_into(codes, weight_codes, output.view(rows, -1), activation_scale[1] * weight_scale[1])
     return output
+
+
+def embedding_bf16_into(token_ids: torch.Tensor, weight: torch.Tensor, output: torch.Tensor) -> None:
+    check(library().lfm25_embedding_bf16(_stream(), _slice(token_ids), _slice(weight), _slice(output),
+                                         token_ids.numel(), weight.shape[0], weight.shape[1]))
+
+
+def rms_norm_bf16_into(x: torch.Tensor, weight: torch.Tensor, eps: float, output: torch.Tensor) -> None:
+    hidden = x.shape[-1]
+    check(library().lfm25_rms_norm_bf16(_stream(), _slice(x), _slice(weight), _slice(output), x.numel() // hidden,
+                                        hidden, eps))
+
+
+def residual_rms_norm_bf16_into(residual, update, weight, eps: float, residual_out, normalized_out) -> None:
+    hidden = residual.shape[-1]
+    check(library().lfm25_residual_rms_norm_bf16(_stream(), _slice(residual), _slice(update), _slice(weight),
+                                                 _slice(residual_out), _slice(normalized_out),
+                                                 residual.numel() // hidden, hidden, eps))
+
+
+def short_conv_decode_bf16_into(projected, weight, states, request_slots, output) -> None:
+    hidden = weight.shape[0]
+    check(library().lfm25_short_conv_decode_bf16(_stream(), _slice(projected), _slice(weight), _slice(states),
+                                                 _slice(request_slots), _slice(output), request_slots.numel(), hidden,
+                                                 states.shape[0]))
+
+
+def argmax_rows_bf16_into(logits: torch.Tensor, sampled: torch.Tensor) -> None:
+    check(library().lfm25_argmax_rows_bf16(_stream(), _slice(logits), _slice(sampled), logits.shape[0],
+                                           logits.shape[1]))
 
 
 def device_status() -> tuple[int, int, int, int]:

@@ -565,6 +565,144 @@ void oracle_physical_slots(const uint32_t* block_tables, const uint32_t* request
     }
 }
 
+/* ------------------------------------------------------- other step ops --- */
+
+/*
+ * RMSNorm of rows.  Follows kernels/rms_norm.cu:268-278: inv = rsqrt_rn(mean(x^2) + eps) with the sum in fp32
+ * (here in double, which bounds every fp32 order), n = bf16(x * inv), out = n *bf16 weight.
+ */
+void oracle_rms_norm_bf16(const uint16_t* x, const uint16_t* weight, uint16_t* out, size_t rows, size_t hidden,
+                          float eps) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row) {
+        double sum = 0.0;
+        for (size_t index = 0; index < hidden; ++index) {
+            const double value = (double)bf16_to_f32(x[row * hidden + index]);
+            sum += value * value;
+        }
+        const float inv_rms = (float)(1.0 / sqrt((double)((float)(sum / (double)hidden) + eps)));
+        for (size_t index = 0; index < hidden; ++index) {
+            const float value = bf16_to_f32(x[row * hidden + index]);
+            out[row * hidden + index] = bf16_mul(f32_to_bf16(value * inv_rms), weight[index]);
+        }
+    }
+}
+
+/*
+ * Residual add + RMSNorm.  Follows kernels/rms_norm.cu:394-453: r = bf16(residual + update) is stored; the
+ * variance uses the unrounded fp32 sums; out = bf16(float(r) * inv * float(weight)).
+ */
+void oracle_residual_rms_norm_bf16(const uint16_t* residual, const uint16_t* update, const uint16_t* weight,
+                                   uint16_t* residual_out, uint16_t* normalized_out, size_t rows, size_t hidden,
+                                   float eps) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row) {
+        double sum = 0.0;
+        for (size_t index = 0; index < hidden; ++index) {
+            const size_t offset = row * hidden + index;
+            const float added = bf16_to_f32(residual[offset]) + bf16_to_f32(update[offset]);
+            residual_out[offset] = f32_to_bf16(added);
+            sum += (double)added * (double)added;
+        }
+        const float inv_rms = (float)(1.0 / sqrt((double)((float)(sum / (double)hidden) + eps)));
+        for (size_t index = 0; index < hidden; ++index) {
+            const size_t offset = row * hidden + index;
+            const float value = bf16_to_f32(residual_out[offset]);
+            normalized_out[offset] = f32_to_bf16(value * inv_rms * bf16_to_f32(weight[index]));
+        }
+    }
+}
+
+/*
+ * Gated short convolution, decode step (one token per sequence).  Follows kernels/short_conv.cu:100-143:
+ * projected[t] = (b | c | x); gated = b*x; y = c*(w0*s0 + w1*s1 + w2*gated) in fp32; state <- (s1, gated) as bf16.
+ * A request slot beyond the state table skips the token.
+ */
+void oracle_short_conv_decode_bf16(const uint16_t* projected, const uint16_t* weight, uint16_t* states,
+                                   const uint32_t* request_slots, uint16_t* output, size_t num_tokens, size_t hidden,
+                                   size_t num_request_slots) {
+    for (size_t token = 0; token < num_tokens; ++token) {
+        const size_t slot = request_slots[token];
+        if (slot >= num_request_slots) {
+            continue;
+        }
+        for (size_t channel = 0; channel < hidden; ++channel) {
+            uint16_t* state = states + (slot * hidden + channel) * 2;
+            const float state0 = bf16_to_f32(state[0]);
+            const float state1 = bf16_to_f32(state[1]);
+            const float w0 = bf16_to_f32(weight[channel * 3]);
+            const float w1 = bf16_to_f32(weight[channel * 3 + 1]);
+            const float w2 = bf16_to_f32(weight[channel * 3 + 2]);
+            const size_t base = token * hidden * 3;
+            const float b = bf16_to_f32(projected[base + channel]);
+            const float c = bf16_to_f32(projected[base + hidden + channel]);
+            const float x = bf16_to_f32(projected[base + hidden * 2 + channel]);
+            const float gated = b * x;
+            const float convolved = w0 * state0 + w1 * state1 + w2 * gated;
+            output[token * hidden + channel] = f32_to_bf16(c * convolved);
+            state[0] = f32_to_bf16(state1);
+            state[1] = f32_to_bf16(gated);
+        }
+    }
+}
+
+/*
+ * Greedy argmax per row with the legacy tie order.  Follows kernels/sampling.cu:53-134: the winner is the largest
+ * value; among equal values the smaller (column % 256) wins, then the smaller (column / 256); NaN and -inf never
+ * win (a row of only those answers 0); +0 and -0 are equal.
+ */
+void oracle_argmax_rows_bf16(const uint16_t* logits, uint32_t* sampled, size_t rows, size_t vocab) {
+#pragma omp parallel for schedule(static)
+    for (size_t row = 0; row < rows; ++row) {
+        int found = 0;
+        float best = 0.0f;
+        uint32_t best_column = 0;
+        for (size_t column = 0; column < vocab; ++column) {
+            const uint16_t bits = logits[row * vocab + column];
+            const float value = bf16_to_f32(bits);
+            if (isnan(value) || (isinf(value) && value < 0.0f)) {
+                continue;
+            }
+            int better = !found || value > best;
+            if (found && value == best) {
+                const uint32_t lane = (uint32_t)column & 0xffu, offset = (uint32_t)column >> 8;
+                const uint32_t best_lane = best_column & 0xffu, best_offset = best_column >> 8;
+                better = lane < best_lane || (lane == best_lane && offset < best_offset);
+            }
+            if (better) {
+                found = 1;
+                best = value;
+                best_column = (uint32_t)column;
+            }
+        }
+        sampled[row] = found ? best_column : 0u;
+    }
+}
+
+/*
+ * BF16 linear: Y[M,N] = bf16( sum_k X[m,k] * W[n,k] ).  Follows src/cuda/blaslt/mod.rs:113-186 (cuBLASLt, fp32
+ * compute, order unspecified); products of two bf16 values are exact in fp32, the sum is taken in double.
+ */
+void oracle_linear_bf16(const uint16_t* x, const uint16_t* weight, uint16_t* out, size_t m, size_t n, size_t k) {
+    float* x_f32 = (float*)malloc(m * k * sizeof(float));
+    for (size_t index = 0; index < m * k; ++index) {
+        x_f32[index] = bf16_to_f32(x[index]);
+    }
+#pragma omp parallel for schedule(static)
+    for (size_t column = 0; column < n; ++column) {
+        const uint16_t* w_row = weight + column * k;
+        for (size_t row = 0; row < m; ++row) {
+            const float* x_row = x_f32 + row * k;
+            double sum = 0.0;
+            for (size_t inner = 0; inner < k; ++inner) {
+                sum += (double)(x_row[inner] * bf16_to_f32(w_row[inner]));
+            }
+            out[row * n + column] = f32_to_bf16((float)sum);
+        }
+    }
+    free(x_f32);
+}
+
 int oracle_num_threads(void) {
     int count = 1;
 #ifdef _OPENMP

@@ -68,6 +68,11 @@ def lib() -> ctypes.CDLL:
         ctypes.c_uint32]
     handle.oracle_merge_splitk.argtypes = [_f32p, _u16p, _size, ctypes.c_uint32]
     handle.oracle_physical_slots.argtypes = [_u32p, _u32p, _u32p, _i64p, _size, _size, _size, _size]
+    handle.oracle_rms_norm_bf16.argtypes = [_u16p, _u16p, _u16p, _size, _size, ctypes.c_float]
+    handle.oracle_residual_rms_norm_bf16.argtypes = [_u16p, _u16p, _u16p, _u16p, _u16p, _size, _size, ctypes.c_float]
+    handle.oracle_short_conv_decode_bf16.argtypes = [_u16p, _u16p, _u16p, _u32p, _u16p, _size, _size, _size]
+    handle.oracle_argmax_rows_bf16.argtypes = [_u16p, _u32p, _size, _size]
+    handle.oracle_linear_bf16.argtypes = [_u16p, _u16p, _u16p, _size, _size, _size]
     handle.oracle_num_threads.restype = ctypes.c_int
     _lib = handle
     return handle
@@ -236,6 +241,59 @@ def physical_slots(block_tables, request_slots, position_ids, page_size: int = 1
     lib().oracle_physical_slots(block_tables, request_slots,
                                 np.ascontiguousarray(position_ids, dtype=np.uint32), out,
                                 request_slots.size, stride, rows, page_size)
+    return out
+
+
+# ----------------------------------------------------------------------------- other step ops
+
+
+def rms_norm_bf16(x, weight, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    rows, hidden = x.shape
+    out = np.empty_like(x)
+    lib().oracle_rms_norm_bf16(x, np.ascontiguousarray(weight, dtype=np.uint16), out, rows, hidden, ctypes.c_float(eps))
+    return out
+
+
+def residual_rms_norm_bf16(residual, update, weight, eps: float) -> tuple[np.ndarray, np.ndarray]:
+    """Returns (residual_out, normalized_out)."""
+    residual = np.ascontiguousarray(residual, dtype=np.uint16)
+    rows, hidden = residual.shape
+    residual_out = np.empty_like(residual)
+    normalized = np.empty_like(residual)
+    lib().oracle_residual_rms_norm_bf16(residual, np.ascontiguousarray(update, dtype=np.uint16),
+                                        np.ascontiguousarray(weight, dtype=np.uint16), residual_out, normalized, rows,
+                                        hidden, ctypes.c_float(eps))
+    return residual_out, normalized
+
+
+def short_conv_decode_bf16(projected, weight, states, request_slots) -> np.ndarray:
+    """projected [T, 3H], weight [H, 3], states [slots, H, 2] (updated in place); returns output [T, H]."""
+    projected = np.ascontiguousarray(projected, dtype=np.uint16)
+    tokens = projected.shape[0]
+    hidden = projected.shape[1] // 3
+    output = np.zeros((tokens, hidden), dtype=np.uint16)
+    lib().oracle_short_conv_decode_bf16(projected, np.ascontiguousarray(weight, dtype=np.uint16), states,
+                                        np.ascontiguousarray(request_slots, dtype=np.uint32), output, tokens, hidden,
+                                        states.shape[0])
+    return output
+
+
+def argmax_rows_bf16(logits) -> np.ndarray:
+    logits = np.ascontiguousarray(logits, dtype=np.uint16)
+    rows, vocab = logits.shape
+    sampled = np.empty(rows, dtype=np.uint32)
+    lib().oracle_argmax_rows_bf16(logits, sampled, rows, vocab)
+    return sampled
+
+
+def linear_bf16(x, weight) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    weight = np.ascontiguousarray(weight, dtype=np.uint16)
+    m, k = x.shape
+    n = weight.shape[0]
+    out = np.empty((m, n), dtype=np.uint16)
+    lib().oracle_linear_bf16(x, weight, out, m, n, k)
     return out
 
 
