@@ -1,22 +1,26 @@
-"""Benchmark of the decode hot path: ragged paged GQA decode attention + paged KV append.
+"""Benchmark of the decode hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--splits S]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload step|attention]
 
-Workload (one "step" = one decode step of the batch): 64 sequences with contexts seeded-uniform in
-[16, 8192], page size 16, block tables drawn from a seeded shuffle of a 2^16-page bf16 K/V pool, 32 query /
-8 KV heads of dim 64.  Each step appends one token per sequence (fused QK-norm + RoPE + paged append) and
-then runs ragged paged attention over every sequence's whole context.  Steps run in episodes of 16: step s
-uses positions context + (s mod 16), so the work per episode is fixed for any K.
+Default workload `step` (one "step" = one decode step of the whole model): the LFM2.5-1.2B architecture with
+random-init weights under continuous batching -- 16 layers (6 GQA attention, 10 gated short-conv), hidden 2048,
+vocabulary 65536, SwiGLU 8192, the 16 promoted FP8 sites -- on a batch of 128 sequences with contexts
+seeded-uniform in [128, 4096], page size 16, greedy sampling.  The step is the C++ decode executor replayed from a
+CUDA graph; token ids and positions advance on the device, so the timed region has no host work besides the graph
+launches.  `value` is tokens/s (inputs resident in HBM), `tpot_p50_ms` the median step time, `roofline` the
+attention kernel (the dominant kernel: KV bytes per launch over its CUDA-event duration in an instrumented eager
+pass, against the measured HBM copy bandwidth).  `e2e` drives the same graph the way a serving loop does: every
+step the host uploads the step metadata from pinned memory, launches, downloads the sampled ids and synchronises.
 
-One JSON line is printed by rank 0.  `value` is tokens/s with inputs resident in HBM; `e2e` is the same
-metric through the C ABI with host buffers (pinned H2D of the step's Q/K/V and metadata, D2H of the output,
-inside the timed region); `roofline` is the attention kernel's algorithmic KV bytes per launch over its
-CUDA-event duration against the measured HBM copy bandwidth; `cpu_baseline` is the CPU oracle on a bounded
-sample of the same step.  With --impl reference the CPU implementation itself is timed (the reference
-project has no CPU path of its own, so that arm is the multithreaded oracle port).
+Workload `attention` (one "step" = append + attention of one layer) is the ragged paged attention configuration:
+64 sequences, contexts seeded-uniform in [16, 8192], a 2^16-page pool, fused QK-norm + RoPE + paged append followed
+by ragged paged attention, in episodes of 16 positions.  Its KV GB/s is also reported inside the default line.
 
-Multi-GPU: the path does not shard (a sequence's KV lives on one GPU), so N ranks are N independent engine
-replicas with different seeds; there is no collective on the data path, only the timing barrier.
+`cpu_baseline` / `--impl reference`: the reference project is GPU-only, so the CPU arm is the multithreaded C
+restatement of its kernels (oracle/), timed on a bounded sample of the same step on the host's cores.
+
+Multi-GPU: the path does not shard (the model and every sequence's KV fit one GPU), so N ranks are N independent
+engine replicas with different seeds; there is no collective on the data path, only the timing barrier.
 """
 from __future__ import annotations
 
@@ -41,13 +45,20 @@ NUM_PAGES = 1 << 16
 EPISODE = 16
 METRIC = "decode tok/s (ragged paged GQA decode attention + KV append, 64 sequences, contexts U[16,8192])"
 WORKLOAD = "config1-ragged-paged-decode-attention+kv-append"
+STEP_METRIC = "decode tok/s (full LFM2.5-1.2B-architecture decode step, continuous batching, 128 sequences)"
+STEP_WORKLOAD = "config3-full-decode-step-b128-ctx128-4096-fp8-policy"
+STEP_SEQUENCES = 128
+STEP_CONTEXT = (128, 4096)
+STEP_POOL_PAGES = 32768
 
 
 def parse_arguments():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=1024)
-    parser.add_argument("--warmup", type=int, default=32)
+    parser.add_argument("--workload", default="step", choices=["step", "attention"])
+    parser.add_argument("--steps", type=int, default=0, help="timed steps (default 256 for step, 1024 for attention)")
+    parser.add_argument("--warmup", type=int, default=0, help="warm-up steps (default 8 / 32)")
+    parser.add_argument("--no-fp8", action="store_true", help="step workload: run every site in BF16")
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--splits", type=int, default=0, help="KV-axis splits (0 = library policy)")
     parser.add_argument("--cpu-sequences", type=int, default=0, help="sequences in the CPU sample (0 = auto)")
@@ -56,6 +67,10 @@ def parse_arguments():
     parser.add_argument("--pool-pages", type=int, default=NUM_PAGES, help="pages in the K/V pool (same remark)")
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     arguments = parser.parse_args()
+    if arguments.steps <= 0:
+        arguments.steps = 256 if arguments.workload == "step" else 1024
+    if arguments.warmup <= 0:
+        arguments.warmup = 8 if arguments.workload == "step" else 32
     globals().update(SEQUENCES=arguments.sequences, NUM_PAGES=arguments.pool_pages)
     return arguments
 
@@ -353,6 +368,220 @@ def run_gpu_arm(arguments, rank, world):
         dist.destroy_process_group()
 
 
+# ------------------------------------------------------------------------------------ full decode step
+
+
+def step_cpu_sample(model, batch, token_ids, use_fp8, sequences, repeats):
+    """CPU oracle on `sequences` of the batch's sequences for one full decode step.  Returns (tok/s, s, text, threads)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import step_oracle
+    from oracle import oracle
+    host = step_oracle.HostModel(model)
+    chosen = np.argsort(batch.contexts)[np.linspace(0, batch.num_sequences - 1, sequences).astype(int)]
+    positions = batch.positions(0)[chosen]
+    tables = batch.block_tables[chosen]
+    slots = np.arange(sequences, dtype=np.uint32)
+    for layer in host.layers:                      # conv states of the chosen sequences only
+        if "conv_state" in layer:
+            layer["conv_state"] = np.ascontiguousarray(layer["conv_state"][chosen])
+    times = []
+    for _ in range(repeats):
+        start = time.perf_counter()
+        step_oracle.decode_step(host, token_ids[chosen], positions, slots, tables, use_fp8)
+        times.append(time.perf_counter() - start)
+    best = min(times)
+    keys = int((positions.astype(np.int64) + 1).sum())
+    text = (f"one full decode step (16 layers, LM head, argmax) on {sequences} of the {batch.num_sequences} "
+            f"sequences (evenly spaced by context length, {keys} keys per attention layer), best of {repeats}")
+    return sequences / best, best, text, oracle.num_threads()
+
+
+def build_step_state(arguments, seed, device, capacity_steps):
+    import torch
+    from lfm25_inference_b200 import model as lfm_model
+    from lfm25_inference_b200 import workloads
+    batch = workloads.ragged_decode_batch(seed, STEP_SEQUENCES, STEP_CONTEXT[0], STEP_CONTEXT[1], STEP_POOL_PAGES,
+                                          capacity_steps)
+    model = lfm_model.RandomModel(seed, device, STEP_POOL_PAGES, STEP_SEQUENCES)
+    model.fill_caches(seed + 1)
+    token_ids = np.random.default_rng(seed).integers(0, lfm_model.VOCAB, size=STEP_SEQUENCES).astype(np.uint32)
+    return batch, model, token_ids
+
+
+def run_step_reference_arm(arguments, rank):
+    if rank != 0:
+        return
+    import torch
+    entry.load_package()
+    device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    batch, model, token_ids = build_step_state(arguments, 3, device, 8)
+    sequences = arguments.cpu_sequences or 4
+    steps = max(1, min(arguments.steps, 3))
+    tokens_per_s, seconds, description, threads = step_cpu_sample(model, batch, token_ids, not arguments.no_fp8,
+                                                                  sequences, steps)
+    line = {
+        "impl": "reference", "metric": STEP_METRIC, "value": tokens_per_s, "unit": "tok/s", "n_gpus": arguments.gpus,
+        "steps": steps, "warmup": 0, "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": STEP_WORKLOAD, "sequences": STEP_SEQUENCES, "page_size": 16, "sample": description},
+        "cpu_baseline": {"value": tokens_per_s, "unit": "tok/s", "cores": threads, "kind": "port",
+                         "sample": description},
+        "e2e": {"value": tokens_per_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference project is GPU-only; this arm times the multithreaded C restatement of its kernels",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_step_arm(arguments, rank, world):
+    import torch
+    import torch.distributed as dist
+
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    entry.load_package()
+    from lfm25_inference_b200 import model as lfm_model
+    from lfm25_inference_b200 import ops
+
+    use_fp8 = not arguments.no_fp8
+    steps, warmup = arguments.steps, arguments.warmup
+    e2e_steps = min(steps, 128)
+    profile_steps = 8
+    spin_steps = 320                                # extra steps that keep the GPU busy while clocks are sampled
+    capacity = warmup + steps + e2e_steps + profile_steps + spin_steps + 16
+    seed = 3 + rank
+    batch, model, token_ids = build_step_state(arguments, seed, device, capacity)
+
+    stream = torch.cuda.Stream(device=device)      # graph capture needs a non-default stream
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        blaslt = ops.BlasLt()
+        executor = lfm_model.DecodeExecutor(blaslt, STEP_SEQUENCES)
+        device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0),
+                                             token_ids, STEP_CONTEXT[1] + capacity)
+        executor.forward(model, device_batch, use_fp8=use_fp8, advance=False)
+        for _ in range(max(warmup, 3)):
+            executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=True)
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+
+        # ---- timed region: K graph-replayed steps, ids and positions advance on the device ----
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        with ClockSampler(local_rank) as sampler:
+            stream.synchronize()
+            marks[0].record()
+            for step in range(steps):
+                executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=True)
+                marks[step + 1].record()
+            stream.synchronize()
+            total_ms = marks[0].elapsed_time(marks[steps])
+            if total_ms < 500.0:                   # keep the clocks under observation a little longer
+                until = time.perf_counter() + 0.5
+                for _ in range(spin_steps):
+                    if time.perf_counter() >= until:
+                        break
+                    executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=True)
+                    stream.synchronize()
+        clocks = sampler.summary()
+        step_ms = np.array([marks[i].elapsed_time(marks[i + 1]) for i in range(steps)])
+        positions_now = device_batch.positions.cpu().numpy().view(np.uint32).astype(np.int64)
+
+        # ---- instrumented eager pass: CUDA events around every op, for the per-kernel roofline ----
+        executor.profile(True)
+        for _ in range(profile_steps):
+            executor.forward(model, device_batch, use_fp8=use_fp8, advance=True)
+        regions = executor.profile(False, collect=True)
+        contexts_profiled = positions_now + 1 + (profile_steps + 1) / 2.0      # mean context during the pass
+        attention_ms, attention_ops = regions["attention"]
+        attention_seconds = attention_ms / max(attention_ops, 1) * 1e-3
+        kv_bytes = float((contexts_profiled * 2048).sum())
+        other_bytes = STEP_SEQUENCES * 8192 + 4 * float(np.ceil(contexts_profiled / 16).sum())
+        achieved = (kv_bytes + other_bytes) / attention_seconds / 1e9
+
+        # ---- end to end: host metadata in, sampled ids out, every step ----
+        host_meta = {name: getattr(device_batch, name).cpu().pin_memory()
+                     for name in ("token_ids", "positions", "request_slots")}
+        host_sampled = torch.empty(STEP_SEQUENCES, dtype=torch.int32).pin_memory()
+        h2d_bytes = sum(t.numel() * t.element_size() for t in host_meta.values())
+        d2h_bytes = host_sampled.numel() * host_sampled.element_size()
+
+        def served_step():
+            for name, tensor in host_meta.items():
+                getattr(device_batch, name).copy_(tensor, non_blocking=True)
+            executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=False)
+            executor.download_sampled(host_sampled)
+            stream.synchronize()                   # the serving loop needs the ids (EOS, streaming) before it goes on
+            host_meta["token_ids"].copy_(host_sampled)
+            host_meta["positions"] += 1
+
+        for _ in range(3):
+            served_step()
+        if world > 1:
+            dist.barrier()
+        e2e_start = time.perf_counter()
+        for _ in range(e2e_steps):
+            served_step()
+        e2e_seconds = time.perf_counter() - e2e_start
+        if ops.device_status()[0] != 0:
+            raise RuntimeError("a bounded wait ran out inside the benchmark")
+
+    elapsed = torch.tensor([total_ms, e2e_seconds * 1e3], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = (float(value) for value in elapsed.cpu())
+
+    if rank == 0:
+        hbm_peak, peak_kind = peaks()
+        weight_bytes = model.weight_bytes(use_fp8)
+        mean_context = float(np.mean(batch.contexts)) + warmup + steps / 2.0
+        step_bytes = weight_bytes + 6 * STEP_SEQUENCES * mean_context * 2048
+        if arguments.skip_cpu:
+            cpu_tokens, cpu_description, threads = None, "skipped", 0
+        else:
+            cpu_tokens, _, cpu_description, threads = step_cpu_sample(model, batch, token_ids, use_fp8,
+                                                                      arguments.cpu_sequences or 4, 2)
+        per_step = {name: ops_count // profile_steps for name, (_, ops_count) in regions.items()}
+        bf16_down = sum(1 for layer in model.layers if not (use_fp8 and layer.linears["down"].codes is not None))
+        # kernels of this library per step: attention (+ merge), append, quantise/SiLU + FP8 GEMM, SiLU of the
+        # BF16 Down sites, and the small ops; the BF16 GEMMs themselves are cuBLASLt launches
+        launches = (per_step["attention"] * 2 + per_step["append"] + per_step["fp8_linear"] * 2 + bf16_down +
+                    per_step["other"])
+        library_launches = per_step["bf16_linear"]
+        line = {
+            "metric": STEP_METRIC, "value": STEP_SEQUENCES * steps * world / (total_ms * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": total_ms / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16+e4m3" if use_fp8 else "bf16",
+            "data": "synthetic",
+            "config": {"workload": STEP_WORKLOAD, "sequences": STEP_SEQUENCES, "contexts": list(STEP_CONTEXT),
+                       "page_size": 16, "pool_pages_per_layer": STEP_POOL_PAGES, "fp8_sites": 16 if use_fp8 else 0,
+                       "sampling": "greedy", "replicas": world, "step": "CUDA graph replay, metadata advanced on device",
+                       "l2": "inputs exceed L2 (about 5 GB of weights and KV read per step)"},
+            "tpot_p50_ms": float(np.median(step_ms)), "tpot_p95_ms": float(np.percentile(step_ms, 95)),
+            "step_hbm_frac": step_bytes / (total_ms / steps * 1e-3) / 1e9 / hbm_peak,
+            "step_algorithmic_bytes": step_bytes,
+            "kv_gbs": kv_bytes / attention_seconds / 1e9,
+            "regions_eager_ms_per_step": {name: ms / profile_steps for name, (ms, _) in regions.items()},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                         "kernel": "ragged_decode_attention_kernel + merge_splitk_kernel (one attention layer)",
+                         "algorithmic_bytes_per_launch": kv_bytes + other_bytes},
+            "cpu_baseline": {"value": cpu_tokens, "unit": "tok/s", "cores": threads, "kind": "port",
+                             "sample": cpu_description},
+            "e2e": {"value": STEP_SEQUENCES * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tok/s",
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
+            "gpu_launches": launches * steps, "cublaslt_launches": library_launches * steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    executor.close()
+    blaslt.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def _inv_freq():
     index = np.arange(32, dtype=np.float32)
     return np.power(np.float32(1.0e6), -(np.float32(2.0) * index) / np.float32(64.0)).astype(np.float32)
@@ -362,6 +591,12 @@ def main():
     arguments = parse_arguments()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
+    if arguments.workload == "step":
+        if arguments.impl == "reference":
+            run_step_reference_arm(arguments, rank)
+        else:
+            run_step_arm(arguments, rank, world)
+        return
     if arguments.impl == "reference":
         run_reference_arm(arguments, rank)
         return

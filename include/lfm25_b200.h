@@ -348,11 +348,13 @@ void lfm25_decode_executor_destroy(lfm25_decode_executor* executor);
  * on the BlasLt handle's stream; sampled ids land in the executor's `sampled` buffer. */
 int32_t lfm25_decode_executor_forward(lfm25_decode_executor* executor, const lfm25_model* model,
                                       const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance);
-/* Advance-and-step replayed from a CUDA graph captured per (batch size, model, batch buffers): the first call of a
- * bucket runs eagerly, the second captures, later ones only launch the graph.  No counterpart in the reference,
- * which launches ~170 kernels and synchronises the host every step (src/engine/serving/radix_owner.rs:230-259). */
+/* The same step replayed from a CUDA graph captured per (batch size, model, batch buffers, flags): the first call
+ * of a bucket runs eagerly, the second captures, later ones only launch the graph.  With advance != 0 the step
+ * feeds itself (ids and positions move on the device); with advance == 0 the caller refreshes the metadata
+ * buffers between steps.  The handle must be bound to a non-default stream.  No counterpart in the reference, which
+ * launches ~170 kernels and synchronises the host every step (src/engine/serving/radix_owner.rs:230-259). */
 int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* executor, const lfm25_model* model,
-                                         const lfm25_decode_batch* batch, uint32_t use_fp8);
+                                         const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance);
 /* Opt-in region timing of eager steps (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): while
  * enabled, every op of lfm25_decode_executor_forward is bracketed by CUDA events.  A call with region_ms != NULL
  * synchronises, returns the milliseconds and op counts accumulated per region since the last collection, and then

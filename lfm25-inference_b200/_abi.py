@@ -142,7 +142,8 @@ PROTOTYPES = {
     "lfm25_decode_executor_destroy": (None, [ctypes.c_void_p]),
     "lfm25_decode_executor_forward": (
         ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
-    "lfm25_decode_executor_step_graph": (ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32]),
+    "lfm25_decode_executor_step_graph": (
+        ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
     "lfm25_decode_executor_profile": (
         ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint32, _P(ctypes.c_float), _P(ctypes.c_uint32)]),
     "lfm25_decode_executor_download_sampled": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p, _size]),

@@ -54,6 +54,7 @@ struct lfm25_decode_executor {
     struct Captured {
         size_t num_tokens = 0;
         uint32_t use_fp8 = 0;
+        uint32_t advance = 0;
         const void* model_layers = nullptr;
         const void* token_ids = nullptr;
         bool warmed = false;
@@ -433,12 +434,12 @@ int32_t lfm25_decode_executor_forward(lfm25_decode_executor* self, const lfm25_m
 }
 
 int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm25_model* model,
-                                         const lfm25_decode_batch* batch, uint32_t use_fp8) {
+                                         const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance) {
     LFM25_TRY(validate(self, model, batch));
     lfm25_decode_executor::Captured* entry = nullptr;
     for (auto& candidate : self->captured) {
         if (candidate.num_tokens == batch->num_tokens && candidate.use_fp8 == use_fp8 &&
-            candidate.model_layers == model->layers && candidate.token_ids == batch->token_ids) {
+            candidate.advance == advance && candidate.model_layers == model->layers && candidate.token_ids == batch->token_ids) {
             entry = &candidate;
             break;
         }
@@ -460,6 +461,7 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
         *entry = lfm25_decode_executor::Captured();
         entry->num_tokens = batch->num_tokens;
         entry->use_fp8 = use_fp8;
+        entry->advance = advance;
         entry->model_layers = model->layers;
         entry->token_ids = batch->token_ids;
     }
@@ -472,14 +474,14 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
         // The first step of a bucket runs eagerly: cuBLASLt plans, function attributes and symbol lookups happen
         // here, outside any capture.
         entry->warmed = true;
-        return forward(self, model, batch, use_fp8 != 0, true);
+        return forward(self, model, batch, use_fp8 != 0, advance != 0);
     }
     if (entry->exec == nullptr) {
         cudaError_t status = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal);
         if (status != cudaSuccess) return cuda_failure(status, "stream capture could not begin");
         const bool was_profiling = self->profiling;
         self->profiling = false;
-        const int32_t rc = forward(self, model, batch, use_fp8 != 0, true);
+        const int32_t rc = forward(self, model, batch, use_fp8 != 0, advance != 0);
         self->profiling = was_profiling;
         cudaGraph_t graph = nullptr;
         status = cudaStreamEndCapture(stream, &graph);

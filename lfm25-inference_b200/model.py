@@ -203,9 +203,10 @@ class DecodeExecutor:
         check(library().lfm25_decode_executor_forward(self._handle, model.struct, batch.struct, int(use_fp8),
                                                       int(advance)))
 
-    def step_graph(self, model: RandomModel, batch: DecodeBatch, use_fp8: bool = True) -> None:
+    def step_graph(self, model: RandomModel, batch: DecodeBatch, use_fp8: bool = True, advance: bool = True) -> None:
         self.blaslt.bind_current_stream()
-        check(library().lfm25_decode_executor_step_graph(self._handle, model.struct, batch.struct, int(use_fp8)))
+        check(library().lfm25_decode_executor_step_graph(self._handle, model.struct, batch.struct, int(use_fp8),
+                                                         int(advance)))
 
     REGIONS = ("attention", "append", "fp8_linear", "bf16_linear", "other")
 
