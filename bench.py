@@ -324,6 +324,38 @@ def run_gpu_arm(arguments, rank, world):
         torch.cuda.synchronize()          # the caller consumes the step's result before the next step
     e2e_seconds = time.perf_counter() - e2e_start
 
+    # ---- the reference project's own kernels (rebuilt for sm_100a) on the same buffers, for comparison ----
+    reference_kernels = None
+    if rank == 0:
+        try:
+            from oracle import refkernels
+            if refkernels.available():
+                inputs = episode[0]
+                query = inputs["query"].clone()
+                timings = {}
+                for name, call in (
+                    ("append_us", lambda: refkernels.qk_norm_rope_kv_write_decode(
+                        query, inputs["key"], inputs["value"], ones, ones, inv_freq, inputs["positions"],
+                        inputs["slots"], arena.key, arena.value, 1e-5)),
+                    ("attention_unsplit_us", lambda: refkernels.paged_ragged_attention_fast(
+                        query, arena.key, arena.value, block_tables, request_slots, inputs["positions"], output)),
+                    ("attention_splitk8_us", lambda: refkernels.paged_ragged_attention_splitk(
+                        query, arena.key, arena.value, block_tables, request_slots, inputs["positions"],
+                        partials, output, 8)),
+                ):
+                    call()
+                    torch.cuda.synchronize()
+                    begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    begin.record()
+                    for _ in range(5):
+                        call()
+                    finish.record()
+                    torch.cuda.synchronize()
+                    timings[name] = begin.elapsed_time(finish) / 5 * 1e3
+                reference_kernels = timings
+        except Exception as error:           # the comparison is optional; the metric does not depend on it
+            reference_kernels = {"error": str(error)[:120]}
+
     elapsed = torch.tensor([total_ms, e2e_seconds * 1e3], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
@@ -361,6 +393,7 @@ def run_gpu_arm(arguments, rank, world):
             "e2e": {"value": SEQUENCES * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tok/s",
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": launches_per_step * steps,
+            "reference_kernels_same_gpu": reference_kernels,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -501,6 +534,30 @@ def run_step_arm(arguments, rank, world):
         other_bytes = STEP_SEQUENCES * 8192 + 4 * float(np.ceil(contexts_profiled / 16).sum())
         achieved = (kv_bytes + other_bytes) / attention_seconds / 1e9
 
+        # ---- the reference project's own attention kernels (rebuilt for sm_100a) on the same cache and metadata ----
+        reference_kernels = None
+        if rank == 0:
+            try:
+                from oracle import refkernels
+                if refkernels.available():
+                    layer = next(layer for layer in model.layers if layer.is_attention)
+                    query = torch.randn((STEP_SEQUENCES, 32, 64), device=device, dtype=torch.bfloat16)
+                    output = torch.empty_like(query)
+                    arguments_ = (query, layer.tensors["key_cache"], layer.tensors["value_cache"],
+                                  device_batch.block_tables, device_batch.request_slots, device_batch.positions, output)
+                    refkernels.paged_ragged_attention_fast(*arguments_)
+                    stream.synchronize()
+                    begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    begin.record()
+                    for _ in range(3):
+                        refkernels.paged_ragged_attention_fast(*arguments_)
+                    finish.record()
+                    stream.synchronize()
+                    reference_kernels = {"attention_unsplit_us_per_layer": begin.elapsed_time(finish) / 3 * 1e3,
+                                         "ours_us_per_layer": attention_seconds * 1e6}
+            except Exception as error:       # optional comparison; the metric does not depend on it
+                reference_kernels = {"error": str(error)[:120]}
+
         # ---- end to end: host metadata in, sampled ids out, every step ----
         host_meta = {name: getattr(device_batch, name).cpu().pin_memory()
                      for name in ("token_ids", "positions", "request_slots")}
@@ -573,6 +630,7 @@ def run_step_arm(arguments, rank, world):
             "e2e": {"value": STEP_SEQUENCES * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tok/s",
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": launches * steps, "cublaslt_launches": library_launches * steps,
+            "reference_kernels_same_gpu": reference_kernels,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)

@@ -21,6 +21,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 #include "tensor_map.h"
 
 namespace lfm25 {
@@ -56,6 +57,8 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
                                const __grid_constant__ CUtensorMap value_map, const AttentionParams p) {
     const uint32_t warp = threadIdx.x >> 5;
     const uint32_t lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    pdl_wait();   // positions, block tables, the query and the newest K/V row all come from earlier kernels
 
     // ---- which (token, KV head, split) this CTA owns; every early exit is CTA-uniform ----
     const uint32_t splits = p.num_splits;
@@ -349,6 +352,8 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
 __global__ void __launch_bounds__(kThreads)
 merge_splitk_kernel(const float* __restrict__ partials, __nv_bfloat16* __restrict__ output, uint32_t num_tokens,
                     uint32_t num_splits) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t token = blockIdx.x / kKvHeads;
     const uint32_t kv_head = blockIdx.x % kKvHeads;
     if (token >= num_tokens) {
@@ -414,16 +419,15 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.num_pages = static_cast<uint32_t>(launch.num_pages);
     params.num_splits = launch.num_splits;
     const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
-    ragged_decode_attention_kernel<<<static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream>>>(
-        key_map, value_map, params);
-    cudaError_t status = cudaGetLastError();
+    cudaError_t status = launch_kernel(ragged_decode_attention_kernel, static_cast<unsigned int>(blocks), kThreads,
+                                       kSmemAlloc, stream, 1, key_map, value_map, params);
     if (status != cudaSuccess || launch.num_splits == 1) {
         return status;
     }
-    merge_splitk_kernel<<<static_cast<unsigned int>(launch.num_tokens * kKvHeads), kThreads, 0, stream>>>(
-        launch.partials, static_cast<__nv_bfloat16*>(launch.output), static_cast<uint32_t>(launch.num_tokens),
-        launch.num_splits);
-    return cudaGetLastError();
+    return launch_kernel(merge_splitk_kernel, static_cast<unsigned int>(launch.num_tokens * kKvHeads), kThreads, 0,
+                         stream, 1, static_cast<const float*>(launch.partials),
+                         static_cast<__nv_bfloat16*>(launch.output), static_cast<uint32_t>(launch.num_tokens),
+                         launch.num_splits);
 }
 
 }  // namespace lfm25

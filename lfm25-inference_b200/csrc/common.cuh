@@ -34,6 +34,19 @@ __device__ __forceinline__ void record_wait_timeout(unsigned int* status, uint32
     status[2] = detail;
 }
 
+// ------------------------------------------------------------------ programmatic dependent launch
+// Every kernel of the step is launched so that it may start while its predecessor in the stream is still
+// draining.  A kernel announces early that its successor may be scheduled, and must not touch anything another
+// kernel of the step writes (activations, caches, metadata) before pdl_wait(), which returns once every
+// predecessor grid has finished and its writes are visible.  Only constants (weights) may be read before it.
+// Both are no-ops in a launch without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ------------------------------------------------------------------ shared memory / barriers
 
 __device__ __forceinline__ uint32_t smem_u32(const void* pointer) {

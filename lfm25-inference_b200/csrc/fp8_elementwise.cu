@@ -12,6 +12,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 
 namespace lfm25 {
 
@@ -50,6 +51,8 @@ __device__ __forceinline__ uint2 quantize8(const uint4 raw, float scale) {
 __global__ void __launch_bounds__(kThreads)
 quantize_bf16_e4m3_kernel(const __nv_bfloat16* __restrict__ input, uint8_t* __restrict__ output, size_t numel,
                           float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t thread = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const bool aligned = ((reinterpret_cast<uintptr_t>(input) & 15) == 0) && ((reinterpret_cast<uintptr_t>(output) & 7) == 0);
@@ -68,6 +71,8 @@ template <bool FUSED>
 __global__ void __launch_bounds__(kThreads)
 silu_mul_packed_kernel(const __nv_bfloat16* __restrict__ packed, void* __restrict__ out, size_t rows,
                        size_t intermediate, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t thread = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x;
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
     const bool vector_ok = (intermediate % 8 == 0) && ((reinterpret_cast<uintptr_t>(packed) & 15) == 0) &&
@@ -124,23 +129,20 @@ unsigned int streaming_grid(size_t work_items) {
 
 cudaError_t launch_quantize_bf16_e4m3(cudaStream_t stream, const void* input, void* output, size_t numel,
                                       float scale) {
-    quantize_bf16_e4m3_kernel<<<streaming_grid((numel + 7) / 8), kThreads, 0, stream>>>(
+    return launch_kernel(quantize_bf16_e4m3_kernel, streaming_grid((numel + 7) / 8), kThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(input), static_cast<uint8_t*>(output), numel, scale);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_silu_mul_packed_bf16(cudaStream_t stream, const void* packed, void* out, size_t rows,
                                         size_t intermediate) {
-    silu_mul_packed_kernel<false><<<streaming_grid((rows * intermediate + 7) / 8), kThreads, 0, stream>>>(
+    return launch_kernel(silu_mul_packed_kernel<false>, streaming_grid((rows * intermediate + 7) / 8), kThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(packed), out, rows, intermediate, 1.0f);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_silu_mul_packed_bf16_to_e4m3(cudaStream_t stream, const void* packed, void* out, size_t rows,
                                                 size_t intermediate, float scale) {
-    silu_mul_packed_kernel<true><<<streaming_grid((rows * intermediate + 7) / 8), kThreads, 0, stream>>>(
+    return launch_kernel(silu_mul_packed_kernel<true>, streaming_grid((rows * intermediate + 7) / 8), kThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(packed), out, rows, intermediate, scale);
-    return cudaGetLastError();
 }
 
 }  // namespace lfm25

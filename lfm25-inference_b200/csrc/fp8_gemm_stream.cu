@@ -21,6 +21,7 @@
 // one-warp-per-output-row kernel.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 
 namespace lfm25 {
 
@@ -55,6 +56,7 @@ struct WeightChunk {
 __global__ void __launch_bounds__(kThreads, 1)
 fp8_gemm_stream_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ weight,
                        __nv_bfloat16* __restrict__ out, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+    pdl_launch_dependents();
     __shared__ float tile_sums[kMaxTilesPerCta][16][8];
     // a warp's first and last tile may be shared with its neighbours: those partial tiles are parked here and
     // added in warp order afterwards, so the result does not depend on the order in which warps finish
@@ -136,6 +138,9 @@ fp8_gemm_stream_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
             fetch(ring[stage], unit_begin + stage);
         }
     }
+    // Everything above touched only the weights, which no kernel writes; the activations come from the
+    // predecessor in the stream, so they are read after the dependency wait.
+    pdl_wait();
     {
         const uint32_t vectors_per_row = k / 16;
         for (uint32_t index = threadIdx.x; index < 8 * vectors_per_row; index += kThreads) {
@@ -190,6 +195,8 @@ fp8_gemm_stream_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict_
 __global__ void __launch_bounds__(256)
 fp8_gemm_generic_kernel(const uint8_t* __restrict__ x, const uint8_t* __restrict__ weight,
                         __nv_bfloat16* __restrict__ out, uint32_t m, uint32_t n, uint32_t k, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float table[256];
     {
         const uint32_t code = threadIdx.x;
@@ -245,19 +252,17 @@ cudaError_t launch_fp8_gemm_stream(cudaStream_t stream, const void* x, const voi
     if (attribute_status != cudaSuccess) {
         return attribute_status;
     }
-    fp8_gemm_stream_kernel<<<blocks, kThreads, x_bytes, stream>>>(
+    return launch_kernel(fp8_gemm_stream_kernel, blocks, kThreads, x_bytes, stream, 1, 
         static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(weight), static_cast<__nv_bfloat16*>(out),
         static_cast<uint32_t>(m), static_cast<uint32_t>(n), static_cast<uint32_t>(k), alpha);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_fp8_gemm_generic(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
                                     size_t n, size_t k, float alpha) {
     const unsigned int blocks = static_cast<unsigned int>((n + 7) / 8);
-    fp8_gemm_generic_kernel<<<blocks, 256, 0, stream>>>(
+    return launch_kernel(fp8_gemm_generic_kernel, blocks, 256, 0, stream, 1, 
         static_cast<const uint8_t*>(x), static_cast<const uint8_t*>(weight), static_cast<__nv_bfloat16*>(out),
         static_cast<uint32_t>(m), static_cast<uint32_t>(n), static_cast<uint32_t>(k), alpha);
-    return cudaGetLastError();
 }
 
 }  // namespace lfm25

@@ -26,6 +26,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 #include "tensor_map.h"
 
 namespace lfm25 {
@@ -37,7 +38,8 @@ constexpr uint32_t kBlockK = 128;   // bytes of K per stage = one swizzle row
 constexpr uint32_t kUmmaK = 32;     // K of one tcgen05.mma with 8-bit operands
 constexpr uint32_t kThreads = 192;
 constexpr uint32_t kMaxStages = 8;
-constexpr uint32_t kSmemBudget = 200 * 1024;
+constexpr uint32_t kSmemBudget = 200 * 1024;   // one CTA per SM
+constexpr uint32_t kSmemBudgetShared = 98 * 1024;  // two CTAs per SM: one drains its tile while the other streams
 constexpr uint32_t kWeightTileBytes = kTileN * kBlockK;
 
 struct UmmaParams {
@@ -115,7 +117,7 @@ __device__ __forceinline__ void tmem_load16(uint32_t address, uint32_t (&r)[16])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, 2)
 fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap x_map,
                      const UmmaParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -133,6 +135,7 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(control + 16 * kMaxStages + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&weight_map);
         tma_prefetch_descriptor(&x_map);
@@ -161,20 +164,34 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
 
     if (warp == 0) {
         if (lane == 0) {
-            for (uint32_t block = 0; block < p.k_blocks; ++block) {
+            // The weight tiles are constants: the first ring of them is requested before the dependency wait, so
+            // the stream is already flowing while the predecessor kernel drains.  The activation tiles, which the
+            // predecessor writes, follow after the wait and complete the same barriers.
+            const uint32_t ahead = p.k_blocks < p.stages ? p.k_blocks : p.stages;
+            const int32_t tile_row = static_cast<int32_t>(tile * kTileN);
+            for (uint32_t block = 0; block < ahead; ++block) {
+                const uint32_t bar = bar_full + 8 * block;
+                mbar_arrive_expect_tx(bar, stage_bytes);
+                tma_load_2d(smem_base + block * stage_bytes, &weight_map, bar,
+                            static_cast<int32_t>((k_block0 + block) * kBlockK), tile_row);
+            }
+            pdl_wait();
+            for (uint32_t block = 0; block < ahead; ++block) {
+                tma_load_2d(smem_base + block * stage_bytes + kWeightTileBytes, &x_map, bar_full + 8 * block,
+                            static_cast<int32_t>((k_block0 + block) * kBlockK), 0);
+            }
+            for (uint32_t block = ahead; block < p.k_blocks; ++block) {
                 const uint32_t stage = block % p.stages;
-                if (block >= p.stages) {
-                    if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1)) {
-                        *abort_flag = 1;
-                        record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 1);
-                        break;
-                    }
+                if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1)) {
+                    *abort_flag = 1;
+                    record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 1);
+                    break;
                 }
                 const uint32_t bar = bar_full + 8 * stage;
                 const uint32_t dst = smem_base + stage * stage_bytes;
                 const int32_t k_offset = static_cast<int32_t>((k_block0 + block) * kBlockK);
                 mbar_arrive_expect_tx(bar, stage_bytes);
-                tma_load_2d(dst, &weight_map, bar, k_offset, static_cast<int32_t>(tile * kTileN));
+                tma_load_2d(dst, &weight_map, bar, k_offset, tile_row);
                 tma_load_2d(dst + kWeightTileBytes, &x_map, bar, k_offset, 0);
             }
         }
@@ -210,6 +227,7 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
         // ---- epilogue: 4 warps, each owns the 32 TMEM lanes of its quadrant (warp id modulo 4) ----
         const uint32_t quadrant = warp & 3;
         const uint32_t row = tile * kTileN + quadrant * 32 + lane;   // weight row = output column
+        pdl_wait();   // the output buffer may still be read by an earlier kernel until the dependency resolves
         const bool ready = !*abort_flag && mbar_wait_bounded(bar_accumulator, 0);
         if (!ready) {
             if (lane == 0) {
@@ -300,7 +318,10 @@ cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void*
         splits *= 2;
     }
     const uint32_t stage_bytes = kWeightTileBytes + m_pad * kBlockK;
-    uint32_t stages = kSmemBudget / stage_bytes;
+    // With more CTAs than SMs (LM head: 512 tiles) two CTAs share an SM, so that the epilogue of one tile
+    // overlaps the weight stream of the next; otherwise one CTA takes the whole shared memory for depth.
+    const bool share_sm = tiles * splits > 148 && kSmemBudgetShared / stage_bytes >= 3;
+    uint32_t stages = (share_sm ? kSmemBudgetShared : kSmemBudget) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     const uint32_t k_blocks = k_blocks_total / splits;
     if (stages > k_blocks) stages = k_blocks;
@@ -328,19 +349,8 @@ cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void*
     if (attribute_status != cudaSuccess) {
         return attribute_status;
     }
-    cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(tiles * splits, 1, 1);
-    config.blockDim = dim3(kThreads, 1, 1);
-    config.dynamicSmemBytes = smem_bytes;
-    config.stream = stream;
-    cudaLaunchAttribute attribute;
-    attribute.id = cudaLaunchAttributeClusterDimension;
-    attribute.val.clusterDim.x = splits;
-    attribute.val.clusterDim.y = 1;
-    attribute.val.clusterDim.z = 1;
-    config.attrs = &attribute;
-    config.numAttrs = 1;
-    return cudaLaunchKernelEx(&config, fp8_gemm_umma_kernel, weight_map, x_map, params);
+    return launch_kernel(fp8_gemm_umma_kernel, tiles * splits, kThreads, smem_bytes, stream, splits, weight_map, x_map,
+                         params);
 }
 
 }  // namespace lfm25

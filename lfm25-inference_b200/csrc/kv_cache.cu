@@ -8,6 +8,7 @@
 // Both are latency-bound (a few KiB per token); they exist to be bit-exact and cheap to launch.
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 
 namespace lfm25 {
 
@@ -19,6 +20,8 @@ __global__ void __launch_bounds__(128)
 kv_cache_write_kernel(const uint4* __restrict__ key, const uint4* __restrict__ value, uint4* __restrict__ key_cache,
                       uint4* __restrict__ value_cache, const int64_t* __restrict__ slot_mapping, size_t num_tokens,
                       size_t num_pages) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t token = blockIdx.x;
     if (token >= num_tokens) {
         return;
@@ -82,6 +85,8 @@ qk_norm_rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ query, const __n
                                     const int64_t* __restrict__ slot_mapping, __nv_bfloat16* __restrict__ key_cache,
                                     __nv_bfloat16* __restrict__ value_cache, size_t num_tokens, size_t num_pages,
                                     float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t token = blockIdx.x;
     if (token >= num_tokens) {
         return;
@@ -138,20 +143,18 @@ qk_norm_rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ query, const __n
 cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const void* value, void* key_cache,
                                   void* value_cache, const int64_t* slot_mapping, size_t num_tokens,
                                   size_t num_pages) {
-    kv_cache_write_kernel<<<static_cast<unsigned int>(num_tokens), 128, 0, stream>>>(
+    return launch_kernel(kv_cache_write_kernel, static_cast<unsigned int>(num_tokens), 128, 0, stream, 1, 
         static_cast<const uint4*>(key), static_cast<const uint4*>(value), static_cast<uint4*>(key_cache),
         static_cast<uint4*>(value_cache), slot_mapping, num_tokens, num_pages);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_qk_norm_rope_kv_write_decode(cudaStream_t stream, const QkPostprocessArgs& args) {
-    qk_norm_rope_kv_write_decode_kernel<<<static_cast<unsigned int>(args.num_tokens), kPostWarps * 32, 0, stream>>>(
+    return launch_kernel(qk_norm_rope_kv_write_decode_kernel, static_cast<unsigned int>(args.num_tokens), kPostWarps * 32, 0, stream, 1, 
         static_cast<__nv_bfloat16*>(args.query), static_cast<const __nv_bfloat16*>(args.key),
         static_cast<const __nv_bfloat16*>(args.value), static_cast<const __nv_bfloat16*>(args.query_norm),
         static_cast<const __nv_bfloat16*>(args.key_norm), args.inv_freq, args.position_ids, args.slot_mapping,
         static_cast<__nv_bfloat16*>(args.key_cache), static_cast<__nv_bfloat16*>(args.value_cache), args.num_tokens,
         args.num_pages, args.eps);
-    return cudaGetLastError();
 }
 
 }  // namespace lfm25

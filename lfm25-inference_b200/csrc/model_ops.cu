@@ -11,6 +11,7 @@
 
 #include "common.cuh"
 #include "kernels.h"
+#include "launch.h"
 
 namespace lfm25 {
 
@@ -41,6 +42,8 @@ __device__ __forceinline__ float block_sum_256(float value, float* scratch) {
 __global__ void __launch_bounds__(kRowThreads)
 embedding_kernel(const uint32_t* __restrict__ token_ids, const __nv_bfloat16* __restrict__ table,
                  __nv_bfloat16* __restrict__ out, size_t num_tokens, size_t vocab_size, size_t hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t token = blockIdx.x;
     if (token >= num_tokens) {
         return;
@@ -70,6 +73,8 @@ __global__ void __launch_bounds__(kRowThreads)
 rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ update,
                 const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ residual_out,
                 __nv_bfloat16* __restrict__ out, size_t rows, size_t hidden, float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[8];
     const size_t row = blockIdx.x;
     if (row >= rows) {
@@ -116,6 +121,8 @@ short_conv_decode_kernel(const __nv_bfloat16* __restrict__ projected, const __nv
                          __nv_bfloat16* __restrict__ states, const uint32_t* __restrict__ request_slots,
                          __nv_bfloat16* __restrict__ output, size_t num_tokens, size_t hidden,
                          size_t num_request_slots) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t work = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (work >= num_tokens * hidden) {
         return;
@@ -159,6 +166,8 @@ constexpr uint32_t kArgmaxThreads = 1024;
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, uint32_t* __restrict__ sampled, size_t rows,
                    size_t vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ uint32_t warp_best[32];
     const size_t row = blockIdx.x;
     if (row >= rows) {
@@ -212,6 +221,8 @@ decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ 
                        const uint32_t* __restrict__ request_slots, const uint32_t* __restrict__ block_tables,
                        const uint32_t* __restrict__ sampled, int64_t* __restrict__ physical_slots, size_t num_tokens,
                        size_t block_table_stride, size_t block_table_rows, size_t num_pages, uint32_t advance) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t token = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (token >= num_tokens) {
         return;
@@ -238,57 +249,49 @@ decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ 
 
 cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids, const void* table, void* out,
                                   size_t num_tokens, size_t vocab_size, size_t hidden) {
-    embedding_kernel<<<static_cast<unsigned int>(num_tokens), kRowThreads, 0, stream>>>(
-        token_ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), num_tokens, vocab_size,
-        hidden);
-    return cudaGetLastError();
+    return launch_kernel(embedding_kernel, static_cast<unsigned int>(num_tokens), kRowThreads, 0, stream, 1, token_ids,
+                         static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), num_tokens,
+                         vocab_size, hidden);
 }
 
 cudaError_t launch_rms_norm_bf16(cudaStream_t stream, const void* x, const void* weight, void* out, size_t rows,
                                  size_t hidden, float eps) {
-    rms_norm_kernel<false><<<static_cast<unsigned int>(rows), kRowThreads, 0, stream>>>(
+    return launch_kernel(rms_norm_kernel<false>, static_cast<unsigned int>(rows), kRowThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(weight), nullptr,
         static_cast<__nv_bfloat16*>(out), rows, hidden, eps);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_residual_rms_norm_bf16(cudaStream_t stream, const void* residual, const void* update,
                                           const void* weight, void* residual_out, void* normalized_out, size_t rows,
                                           size_t hidden, float eps) {
-    rms_norm_kernel<true><<<static_cast<unsigned int>(rows), kRowThreads, 0, stream>>>(
+    return launch_kernel(rms_norm_kernel<true>, static_cast<unsigned int>(rows), kRowThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(update),
         static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(residual_out),
         static_cast<__nv_bfloat16*>(normalized_out), rows, hidden, eps);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_short_conv_decode(cudaStream_t stream, const void* projected, const void* weight, void* states,
                                      const uint32_t* request_slots, void* output, size_t num_tokens, size_t hidden,
                                      size_t num_request_slots) {
     const size_t work = num_tokens * hidden;
-    short_conv_decode_kernel<<<static_cast<unsigned int>((work + kRowThreads - 1) / kRowThreads), kRowThreads, 0,
-                               stream>>>(static_cast<const __nv_bfloat16*>(projected),
+    return launch_kernel(short_conv_decode_kernel, static_cast<unsigned int>((work + kRowThreads - 1) / kRowThreads), kRowThreads, 0, stream, 1, static_cast<const __nv_bfloat16*>(projected),
                                          static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(states),
                                          request_slots, static_cast<__nv_bfloat16*>(output), num_tokens, hidden,
                                          num_request_slots);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_argmax_rows_bf16(cudaStream_t stream, const void* logits, uint32_t* sampled, size_t rows,
                                     size_t vocab) {
-    argmax_rows_kernel<<<static_cast<unsigned int>(rows), kArgmaxThreads, 0, stream>>>(
+    return launch_kernel(argmax_rows_kernel, static_cast<unsigned int>(rows), kArgmaxThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(logits), sampled, rows, vocab);
-    return cudaGetLastError();
 }
 
 cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uint32_t* positions,
                                    const uint32_t* request_slots, const uint32_t* block_tables, const uint32_t* sampled,
                                    int64_t* physical_slots, size_t num_tokens, size_t block_table_stride,
                                    size_t block_table_rows, size_t num_pages, bool advance) {
-    decode_metadata_kernel<<<static_cast<unsigned int>((num_tokens + kRowThreads - 1) / kRowThreads), kRowThreads, 0,
-                             stream>>>(token_ids, positions, request_slots, block_tables, sampled, physical_slots,
+    return launch_kernel(decode_metadata_kernel, static_cast<unsigned int>((num_tokens + kRowThreads - 1) / kRowThreads), kRowThreads, 0, stream, 1, token_ids, positions, request_slots, block_tables, sampled, physical_slots,
                                        num_tokens, block_table_stride, block_table_rows, num_pages, advance ? 1u : 0u);
-    return cudaGetLastError();
 }
 
 }  // namespace lfm25
