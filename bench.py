@@ -83,6 +83,21 @@ def peaks():
     return 6650.0, "fallback"
 
 
+def max_over_ranks(values, device, world):
+    """Element-wise maximum of per-rank timings (replicas are independent, so the slowest one defines the job)."""
+    import torch
+    import torch.distributed as dist
+    tensor = torch.tensor(list(values), dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+    return [float(value) for value in tensor.cpu()]
+
+
+def aggregate_throughput(units_per_rank, world, elapsed_ms):
+    """Whole-job throughput of `world` replicas that each processed `units_per_rank` units in `elapsed_ms`."""
+    return units_per_rank * world / (elapsed_ms * 1e-3)
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons while the timed region runs."""
 
@@ -356,10 +371,7 @@ def run_gpu_arm(arguments, rank, world):
         except Exception as error:           # the comparison is optional; the metric does not depend on it
             reference_kernels = {"error": str(error)[:120]}
 
-    elapsed = torch.tensor([total_ms, e2e_seconds * 1e3], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = (float(value) for value in elapsed.cpu())
+    total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
 
     if rank == 0:
         hbm_peak, peak_kind = peaks()
@@ -585,10 +597,7 @@ def run_step_arm(arguments, rank, world):
         if ops.device_status()[0] != 0:
             raise RuntimeError("a bounded wait ran out inside the benchmark")
 
-    elapsed = torch.tensor([total_ms, e2e_seconds * 1e3], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = (float(value) for value in elapsed.cpu())
+    total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
 
     if rank == 0:
         hbm_peak, peak_kind = peaks()

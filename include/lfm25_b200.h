@@ -376,6 +376,72 @@ int32_t lfm25_decode_executor_download_logits(lfm25_decode_executor* executor, v
 const uint32_t* lfm25_decode_executor_sampled(const lfm25_decode_executor* executor); /* u32 [maximum_tokens] */
 const void* lfm25_decode_executor_logits(const lfm25_decode_executor* executor);      /* bf16 [maximum_tokens, 65536] */
 
+/* ------------------------------------------------------------------------------------------
+ * Host-side state: page allocator, block tables, decode scheduling, replica dispatch (no device work)
+ * ------------------------------------------------------------------------------------------ */
+
+/* KvAllocationError (src/cache/allocator.rs:7-24) as negative return values. */
+#define LFM25_KV_PHYSICAL_PAGES_EXHAUSTED (-11)
+#define LFM25_KV_LOGICAL_RESERVATION_EXHAUSTED (-12)
+#define LFM25_KV_SEQUENCE_CAPACITY_EXCEEDED (-13)
+
+/* KvPoolSnapshot (src/cache/allocator.rs:28-35). */
+typedef struct lfm25_kv_pool_snapshot {
+    size_t total_pages;
+    size_t free_pages;
+    size_t allocated_pages;
+    size_t reserved_pages;
+    size_t cached_pages;
+    size_t peak_allocated_pages;
+} lfm25_kv_pool_snapshot;
+
+/* Replaces KvPageAllocator (src/cache/allocator.rs:40-229): LIFO free list (a fresh pool hands out 0, 1, 2, ...),
+ * per-page reference counts, reservation accounting, cache pins.  Single owner thread, as in the reference.
+ * Functions returning int64_t give the count on success or a negative LFM25_KV_* code. */
+typedef struct lfm25_kv_allocator lfm25_kv_allocator;
+int32_t lfm25_kv_allocator_create(size_t total_pages, size_t page_size, lfm25_kv_allocator** out);
+void lfm25_kv_allocator_destroy(lfm25_kv_allocator* allocator);
+int64_t lfm25_kv_allocator_try_reserve_tokens(lfm25_kv_allocator* allocator, size_t maximum_tokens);
+int64_t lfm25_kv_allocator_try_reserve_pages(lfm25_kv_allocator* allocator, size_t pages);
+void lfm25_kv_allocator_release_reservation(lfm25_kv_allocator* allocator, size_t pages);
+int32_t lfm25_kv_allocator_pin_cached_pages(lfm25_kv_allocator* allocator, const uint32_t* pages, size_t count);
+int32_t lfm25_kv_allocator_retain_pages(lfm25_kv_allocator* allocator, const uint32_t* pages, size_t count);
+int64_t lfm25_kv_allocator_grow_sequence(lfm25_kv_allocator* allocator, size_t current_tokens, size_t target_tokens,
+                                         uint32_t* block_table, size_t block_table_len);
+void lfm25_kv_allocator_release_sequence(lfm25_kv_allocator* allocator, size_t tokens, uint32_t* block_table,
+                                         size_t block_table_len);
+void lfm25_kv_allocator_snapshot(const lfm25_kv_allocator* allocator, lfm25_kv_pool_snapshot* out);
+
+/* Replaces FixedBlockTables (src/cache/block_table.rs:3-31): u32 [slots, pages_per_slot], 0xffffffff = unassigned. */
+typedef struct lfm25_block_tables lfm25_block_tables;
+int32_t lfm25_block_tables_create(size_t slots, size_t pages_per_slot, lfm25_block_tables** out);
+void lfm25_block_tables_destroy(lfm25_block_tables* tables);
+uint32_t* lfm25_block_tables_slot(lfm25_block_tables* tables, size_t slot); /* NULL when out of range */
+const uint32_t* lfm25_block_tables_data(const lfm25_block_tables* tables);
+
+/* Replaces the decode half of Scheduler::schedule (src/scheduler/planner.rs:80-113): every slot whose phase is
+ * LFM25_PHASE_DECODING decodes this step, ordered by time to its next-token deadline; also returns the longest
+ * context (used to choose the KV splits).  Returns the number of decode slots written to decode_slots. */
+#define LFM25_PHASE_FREE 0
+#define LFM25_PHASE_QUEUED_PREFILL 1
+#define LFM25_PHASE_DECODING 2
+size_t lfm25_schedule_decode(const uint32_t* phases, const uint64_t* next_token_deadline_us,
+                             const uint32_t* context_tokens, size_t num_slots, uint64_t now_us, uint32_t* decode_slots,
+                             size_t* maximum_context_tokens);
+
+/* Request dispatcher over engine replicas (one replica per GPU; the model and every sequence's KV fit one GPU, so
+ * nothing is sharded and no collective runs on the step path).  A request goes to the live replica with the least
+ * outstanding tokens, except that requests sharing a prompt prefix go to the replica that prefix hashes to, so
+ * that its prefix cache is hit.  No counterpart in the reference, which drives a single GPU. */
+typedef struct lfm25_dispatcher lfm25_dispatcher;
+int32_t lfm25_dispatcher_create(size_t replicas, lfm25_dispatcher** out);
+void lfm25_dispatcher_destroy(lfm25_dispatcher* dispatcher);
+int32_t lfm25_dispatcher_assign(lfm25_dispatcher* dispatcher, uint64_t prefix_hash, uint32_t has_prefix,
+                                uint64_t estimated_tokens); /* replica index, or a negative error */
+void lfm25_dispatcher_complete(lfm25_dispatcher* dispatcher, size_t replica, uint64_t tokens);
+void lfm25_dispatcher_mark_failed(lfm25_dispatcher* dispatcher, size_t replica);
+uint64_t lfm25_dispatcher_load(const lfm25_dispatcher* dispatcher, size_t replica);
+
 #ifdef __cplusplus
 }
 #endif

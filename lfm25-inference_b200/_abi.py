@@ -104,6 +104,15 @@ class Model(ctypes.Structure):
                 ("norm_eps", ctypes.c_float), ("num_pages", ctypes.c_size_t), ("num_request_slots", ctypes.c_size_t)]
 
 
+class KvPoolSnapshot(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_size_t) for name in ("total_pages", "free_pages", "allocated_pages",
+                                                     "reserved_pages", "cached_pages", "peak_allocated_pages")]
+
+
+KV_PHYSICAL_PAGES_EXHAUSTED = -11
+KV_LOGICAL_RESERVATION_EXHAUSTED = -12
+KV_SEQUENCE_CAPACITY_EXCEEDED = -13
+PHASE_FREE, PHASE_QUEUED_PREFILL, PHASE_DECODING = 0, 1, 2
 FP8_SCALE_TENSORWIDE = 0
 FP8_SCALE_BLOCK32 = 1
 
@@ -150,6 +159,28 @@ PROTOTYPES = {
     "lfm25_decode_executor_download_logits": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p, _size]),
     "lfm25_decode_executor_sampled": (ctypes.c_void_p, [ctypes.c_void_p]),
     "lfm25_decode_executor_logits": (ctypes.c_void_p, [ctypes.c_void_p]),
+    "lfm25_kv_allocator_create": (ctypes.c_int32, [_size, _size, _P(ctypes.c_void_p)]),
+    "lfm25_kv_allocator_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_kv_allocator_try_reserve_tokens": (ctypes.c_int64, [ctypes.c_void_p, _size]),
+    "lfm25_kv_allocator_try_reserve_pages": (ctypes.c_int64, [ctypes.c_void_p, _size]),
+    "lfm25_kv_allocator_release_reservation": (None, [ctypes.c_void_p, _size]),
+    "lfm25_kv_allocator_pin_cached_pages": (ctypes.c_int32, [ctypes.c_void_p, _P(ctypes.c_uint32), _size]),
+    "lfm25_kv_allocator_retain_pages": (ctypes.c_int32, [ctypes.c_void_p, _P(ctypes.c_uint32), _size]),
+    "lfm25_kv_allocator_grow_sequence": (ctypes.c_int64, [ctypes.c_void_p, _size, _size, _P(ctypes.c_uint32), _size]),
+    "lfm25_kv_allocator_release_sequence": (None, [ctypes.c_void_p, _size, _P(ctypes.c_uint32), _size]),
+    "lfm25_kv_allocator_snapshot": (None, [ctypes.c_void_p, _P(KvPoolSnapshot)]),
+    "lfm25_block_tables_create": (ctypes.c_int32, [_size, _size, _P(ctypes.c_void_p)]),
+    "lfm25_block_tables_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_block_tables_slot": (_P(ctypes.c_uint32), [ctypes.c_void_p, _size]),
+    "lfm25_block_tables_data": (_P(ctypes.c_uint32), [ctypes.c_void_p]),
+    "lfm25_schedule_decode": (_size, [_P(ctypes.c_uint32), _P(ctypes.c_uint64), _P(ctypes.c_uint32), _size,
+                                      ctypes.c_uint64, _P(ctypes.c_uint32), _P(_size)]),
+    "lfm25_dispatcher_create": (ctypes.c_int32, [_size, _P(ctypes.c_void_p)]),
+    "lfm25_dispatcher_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_dispatcher_assign": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint64]),
+    "lfm25_dispatcher_complete": (None, [ctypes.c_void_p, _size, ctypes.c_uint64]),
+    "lfm25_dispatcher_mark_failed": (None, [ctypes.c_void_p, _size]),
+    "lfm25_dispatcher_load": (ctypes.c_uint64, [ctypes.c_void_p, _size]),
 }
 
 _library = None
