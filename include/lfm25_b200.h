@@ -171,6 +171,39 @@ int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(void* stream,
                                                              const lfm25_fast_ragged_attention_launch* launch,
                                                              size_t num_splits);
 
+/* Replaces FusedAttentionCommon + FusedRaggedDecodeLaunch + FusedAttentionKernels::launch_ragged_decode
+ * (src/cuda/kernels/attention_fused.rs:13-41, :226-323; kernel kernels/attention_fused.cu:89-348): the one-kernel
+ * decode.  Raw Q/K/V projections in; Q RMSNorm + RoPE in registers (query_raw is not modified), K RMSNorm + RoPE and V
+ * written into the paged cache at slot_mapping[t], attention over the updated context, output written.  A token whose
+ * slot is negative or disagrees with block_tables[row][position / 16] and position % 16 is a silent no-op.
+ * Beyond the reference: with num_splits in 2..=8 and a partials workspace the same fused kernel runs split over the
+ * KV axis (num_splits == 1 or 0: one kernel, partials unused).  Results are bit-identical to
+ * lfm25_qk_norm_rope_kv_write_decode followed by the unfused attention entry points. */
+typedef struct lfm25_fused_ragged_decode_launch {
+    size_t page_size;
+    lfm25_slice query_raw;     /* bf16 [num_tokens, 32, 64] */
+    lfm25_slice key_raw;       /* bf16 [num_tokens, 8, 64] */
+    lfm25_slice value_raw;     /* bf16 [num_tokens, 8, 64] */
+    lfm25_slice query_norm;    /* bf16 [64] */
+    lfm25_slice key_norm;      /* bf16 [64] */
+    lfm25_slice inv_freq;      /* f32 [32] */
+    lfm25_slice key_cache;     /* written */
+    lfm25_slice value_cache;   /* written */
+    lfm25_slice position_ids;  /* u32 [num_tokens] */
+    lfm25_slice slot_mapping;  /* i64 [num_tokens] */
+    lfm25_slice output;        /* bf16 [num_tokens, 32, 64], written */
+    size_t num_tokens;
+    size_t num_pages;
+    float eps;
+    lfm25_slice block_tables;  /* u32 [rows, block_table_stride] */
+    lfm25_slice request_slots; /* u32 [num_tokens] */
+    size_t block_table_stride;
+    lfm25_slice partials;      /* f32 [num_tokens, 32, num_splits, 66] when num_splits > 1 */
+    size_t num_splits;
+} lfm25_fused_ragged_decode_launch;
+int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
+                                                            const lfm25_fused_ragged_decode_launch* launch);
+
 /* Replaces splitk_workspace_elements (src/ops/attention_async_fast.rs:24-30):
  * maximum_tokens * 32 * 8 * 66 f32 elements; 0 on overflow. */
 size_t lfm25_splitk_workspace_elements(size_t maximum_tokens);

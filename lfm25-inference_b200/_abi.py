@@ -116,6 +116,11 @@ PHASE_FREE, PHASE_QUEUED_PREFILL, PHASE_DECODING = 0, 1, 2
 FP8_SCALE_TENSORWIDE = 0
 FP8_SCALE_BLOCK32 = 1
 
+FusedRaggedDecodeLaunch = _launch_struct("FusedRaggedDecodeLaunch", [
+    "#page_size", "query_raw", "key_raw", "value_raw", "query_norm", "key_norm", "inv_freq", "key_cache",
+    "value_cache", "position_ids", "slot_mapping", "output", "#num_tokens", "#num_pages", ("eps", ctypes.c_float),
+    "block_tables", "request_slots", "#block_table_stride", "partials", "#num_splits"])
+
 # name -> (restype, argtypes); every symbol that include/lfm25_b200.h declares
 PROTOTYPES = {
     "lfm25_last_error": (ctypes.c_char_p, []),
@@ -128,6 +133,7 @@ PROTOTYPES = {
     "lfm25_paged_ragged_attention_splitk_lfm2_bf16": (ctypes.c_int32, [_stream, _P(SplitKRaggedAttentionLaunch)]),
     "lfm25_paged_ragged_attention_splitk_static_lfm2_bf16": (
         ctypes.c_int32, [_stream, _P(FastRaggedAttentionLaunch), _size]),
+    "lfm25_fused_ragged_paged_attention_decode_lfm2_bf16": (ctypes.c_int32, [_stream, _P(FusedRaggedDecodeLaunch)]),
     "lfm25_splitk_workspace_elements": (_size, [_size]),
     "lfm25_splitk_decode_splits": (_size, [_size, _size, _size]),
     "lfm25_quantize_bf16_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, ctypes.c_float]),

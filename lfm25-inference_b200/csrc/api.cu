@@ -397,6 +397,65 @@ int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream,
                        "split-K ragged attention launch failed");
 }
 
+int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
+                                                            const lfm25_fused_ragged_decode_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "fused ragged decode launch is null");
+    const lfm25_fused_ragged_decode_launch& l = *launch;
+    const int32_t status =
+        validate_ragged_common(l.page_size, l.query_raw, l.key_cache, l.value_cache, l.block_tables, &l.request_slots,
+                               l.position_ids, l.output, l.num_tokens, l.num_pages, l.block_table_stride);
+    if (status != LFM25_OK) {
+        return status;
+    }
+    size_t kv_required = 0;
+    LFM25_ENSURE(checked_mul(l.num_tokens, 8 * 64, &kv_required), LFM25_ERR_OVERFLOW, "fused KV storage overflow");
+    LFM25_ENSURE(l.key_raw.len >= kv_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused K storage too small");
+    LFM25_ENSURE(l.value_raw.len >= kv_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused V storage too small");
+    LFM25_ENSURE(l.query_norm.len >= 64, LFM25_ERR_BUFFER_TOO_SMALL, "query norm weight too small");
+    LFM25_ENSURE(l.key_norm.len >= 64, LFM25_ERR_BUFFER_TOO_SMALL, "key norm weight too small");
+    LFM25_ENSURE(l.inv_freq.len >= 32, LFM25_ERR_BUFFER_TOO_SMALL, "RoPE frequency storage too small");
+    LFM25_ENSURE(l.slot_mapping.len >= l.num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "slot mapping storage too small");
+    LFM25_ENSURE(l.key_raw.ptr && l.value_raw.ptr && l.query_norm.ptr && l.key_norm.ptr && l.inv_freq.ptr &&
+                     l.slot_mapping.ptr,
+                 LFM25_ERR_NULL_POINTER, "fused ragged decode received a null device pointer");
+    const size_t splits = l.num_splits == 0 ? 1 : l.num_splits;
+    LFM25_ENSURE(splits <= 8, LFM25_ERR_INVALID_ARGUMENT, "split-K ragged attention requires 2..=8 splits");
+    if (splits > 1) {
+        size_t partial_required = 0;
+        LFM25_ENSURE(checked_mul(l.num_tokens, 32, &partial_required) &&
+                         checked_mul(partial_required, splits, &partial_required) &&
+                         checked_mul(partial_required, 66, &partial_required),
+                     LFM25_ERR_OVERFLOW, "split-K partial workspace size overflow");
+        LFM25_ENSURE(l.partials.ptr != nullptr && l.partials.len >= partial_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                     "split-K partial workspace too small: need %zu, have %zu", partial_required, l.partials.len);
+    }
+    lfm25::AttentionLaunch args = {};
+    args.query = l.query_raw.ptr;
+    args.key_cache = l.key_cache.ptr;
+    args.value_cache = l.value_cache.ptr;
+    args.block_tables = static_cast<const uint32_t*>(l.block_tables.ptr);
+    args.request_slots = static_cast<const uint32_t*>(l.request_slots.ptr);
+    args.position_ids = static_cast<const uint32_t*>(l.position_ids.ptr);
+    args.output = l.output.ptr;
+    args.partials = static_cast<float*>(l.partials.ptr);
+    args.status = device_status_pointer();
+    args.num_tokens = l.num_tokens;
+    args.num_pages = l.num_pages;
+    args.block_table_stride = l.block_table_stride;
+    args.block_table_rows = l.block_tables.len / l.block_table_stride;
+    args.num_splits = static_cast<uint32_t>(splits);
+    args.key_raw = l.key_raw.ptr;
+    args.value_raw = l.value_raw.ptr;
+    args.query_norm = l.query_norm.ptr;
+    args.key_norm = l.key_norm.ptr;
+    args.inv_freq = static_cast<const float*>(l.inv_freq.ptr);
+    args.slot_mapping = static_cast<const int64_t*>(l.slot_mapping.ptr);
+    args.eps = l.eps;
+    LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
+                       "fused ragged decode launch failed");
+}
+
 size_t lfm25_splitk_workspace_elements(size_t maximum_tokens) {
     size_t value = 0;
     if (!checked_mul(maximum_tokens, 32, &value) || !checked_mul(value, 8, &value) ||

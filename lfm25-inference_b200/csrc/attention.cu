@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.h"
+#include "qk_norm_rope.cuh"
 #include "tensor_map.h"
 
 namespace lfm25 {
@@ -50,8 +51,25 @@ struct AttentionParams {
     uint32_t num_tokens;
     uint32_t num_pages;
     uint32_t num_splits;  // 1: write normalised output; >1: write split records
+    // fused mode only: the raw projections of the step and what is needed to turn them into the new cache row
+    const __nv_bfloat16* key_raw;     // [T, 8, 64]
+    const __nv_bfloat16* value_raw;   // [T, 8, 64]
+    const __nv_bfloat16* query_norm;  // [64]
+    const __nv_bfloat16* key_norm;    // [64]
+    const float* inv_freq;            // [32]
+    const int64_t* slot_mapping;      // [T]
+    __nv_bfloat16* key_cache;
+    __nv_bfloat16* value_cache;
+    float eps;
 };
 
+// FUSED == false: the query is already normalised and rotated and the newest K/V row is already in the cache.
+// FUSED == true : the kernel takes the raw Q/K/V projections of the step (the reference's one-kernel decode,
+//   kernels/attention_fused.cu:89-348): every CTA normalises and rotates its four query heads in registers, and
+//   the warp that owns the sequence's last page also normalises and rotates the new key, writes it and the new
+//   value into the paged cache, and patches them into its staged copy of that page before using it.  The
+//   arithmetic is the stand-alone append kernel's, operation for operation, so both routes give the same bits.
+template <bool FUSED>
 __global__ void __launch_bounds__(kThreads, 3)
 ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
                                const __grid_constant__ CUtensorMap value_map, const AttentionParams p) {
@@ -87,6 +105,21 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     if (splits > 1) {
         first_page = static_cast<uint32_t>(static_cast<uint64_t>(total_pages) * split / splits);
         end_page = static_cast<uint32_t>(static_cast<uint64_t>(total_pages) * (split + 1) / splits);
+    }
+    uint32_t new_row_offset = 0;
+    if (FUSED) {
+        // the slot given for the new token must be the one the block table implies, else the whole token is a
+        // silent no-op (kernels/attention_fused.cu:131-147)
+        const uint32_t current_page = table[total_pages - 1];
+        const int64_t slot_value = p.slot_mapping[token];
+        if (current_page >= p.num_pages || slot_value < 0) {
+            return;
+        }
+        new_row_offset = position % kPageSize;
+        if (static_cast<uint64_t>(slot_value) / kPageSize != current_page ||
+            static_cast<uint64_t>(slot_value) % kPageSize != new_row_offset) {
+            return;
+        }
     }
     const uint32_t range_pages = end_page - first_page;
     // warp w owns pages first_page + w + 4*i
@@ -168,6 +201,81 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
             qa[ks][1] = *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + 8 + quad * 2);
         }
     }
+    if (FUSED) {
+        // This lane holds dims d = 16*ks + 8*h + 2*quad + e of head `group`; d and d + 32 (ks and ks + 2) are
+        // both here, so RMSNorm + RoPE stay inside the quad.  The sum of squares follows the butterfly of
+        // warp_tree_sum level by level (16 and 8 are local, 4 and 2 cross the quad, 1 is local again).
+        float raw[4][4];
+#pragma unroll
+        for (uint32_t ks = 0; ks < 4; ++ks) {
+            const float2 low = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[ks][0]));
+            const float2 high = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[ks][1]));
+            raw[ks][0] = low.x;
+            raw[ks][1] = low.y;
+            raw[ks][2] = high.x;
+            raw[ks][3] = high.y;
+        }
+        float level[2];
+#pragma unroll
+        for (uint32_t e = 0; e < 2; ++e) {
+            // t[l] = fma(x[l], x[l], x[l+32]^2) for l = 2*quad + e + 8*h + 16*b  (b = ks & 1 with ks < 2)
+            float t[2][2];
+#pragma unroll
+            for (uint32_t b = 0; b < 2; ++b) {
+#pragma unroll
+                for (uint32_t h = 0; h < 2; ++h) {
+                    t[b][h] = fmaf(raw[b][2 * h + e], raw[b][2 * h + e], raw[b + 2][2 * h + e] * raw[b + 2][2 * h + e]);
+                }
+            }
+            const float pair0 = t[0][0] + t[1][0];   // level 16: l and l ^ 16
+            const float pair1 = t[0][1] + t[1][1];
+            level[e] = pair0 + pair1;                // level 8: l and l ^ 8
+            level[e] += __shfl_xor_sync(0xffffffffu, level[e], 2);   // level 4: quad ^ 2
+            level[e] += __shfl_xor_sync(0xffffffffu, level[e], 1);   // level 2: quad ^ 1
+        }
+        const float inv_rms = __frsqrt_rn((level[0] + level[1]) * (1.0f / 64.0f) + p.eps);   // level 1
+        if (group < kQPerKv) {
+            const float position_f = static_cast<float>(position);
+#pragma unroll
+            for (uint32_t b = 0; b < 2; ++b) {
+#pragma unroll
+                for (uint32_t h = 0; h < 2; ++h) {
+                    __nv_bfloat16 rotated[2][2];   // [e][first / second half]
+#pragma unroll
+                    for (uint32_t e = 0; e < 2; ++e) {
+                        const uint32_t dim = 16 * b + 8 * h + 2 * quad + e;   // < 32
+                        float sin_value, cos_value;
+                        sincosf(position_f * p.inv_freq[dim], &sin_value, &cos_value);
+                        rotate_pair(raw[b][2 * h + e], raw[b + 2][2 * h + e], inv_rms, p.query_norm[dim],
+                                    p.query_norm[dim + kHalfDim], sin_value, cos_value, rotated[e][0], rotated[e][1]);
+                    }
+                    const __nv_bfloat162 first = __halves2bfloat162(rotated[0][0], rotated[1][0]);
+                    const __nv_bfloat162 second = __halves2bfloat162(rotated[0][1], rotated[1][1]);
+                    qa[b][h] = *reinterpret_cast<const uint32_t*>(&first);
+                    qa[b + 2][h] = *reinterpret_cast<const uint32_t*>(&second);
+                }
+            }
+        }
+    }
+
+    // fused mode: the warp that owns the last page of the sequence produces the new K/V row
+    const bool owns_new_row = FUSED && end_page == total_pages && my_pages > 0 &&
+                              (first_page + warp + (my_pages - 1) * kWarps == total_pages - 1);
+    __nv_bfloat16 new_key0, new_key1;
+    uint32_t new_value = 0;
+    if (owns_new_row) {
+        const size_t source = (static_cast<size_t>(token) * kKvHeads + kv_head) * kHeadDim;
+        float sin_value, cos_value;
+        sincosf(static_cast<float>(position) * p.inv_freq[lane], &sin_value, &cos_value);
+        norm_rope(__bfloat162float(p.key_raw[source + lane]), __bfloat162float(p.key_raw[source + lane + kHalfDim]),
+                  p.key_norm[lane], p.key_norm[lane + kHalfDim], sin_value, cos_value, p.eps, new_key0, new_key1);
+        new_value = reinterpret_cast<const uint32_t*>(p.value_raw + source)[lane];
+        const size_t destination =
+            ((static_cast<size_t>(table[total_pages - 1]) * kKvHeads + kv_head) * kPageSize + new_row_offset) * kHeadDim;
+        p.key_cache[destination + lane] = new_key0;
+        p.key_cache[destination + lane + kHalfDim] = new_key1;
+        reinterpret_cast<uint32_t*>(p.value_cache + destination)[lane] = new_value;
+    }
 
     constexpr float kScaleLog2 = kAttnScale * kLog2e;
     float running_max = -INFINITY;  // in units of the raw dot product
@@ -202,6 +310,22 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         const uint32_t v_base = k_base + kPageTileBytes;
         const uint32_t page = first_page + warp + iteration * kWarps;
         const uint32_t valid = (page + 1 == total_pages) ? (position - page * kPageSize + 1) : kPageSize;
+
+        if (owns_new_row && iteration + 1 == my_pages) {
+            // the staged copy of the last page predates (or races with) the cache write above: put the new row in
+            const uint32_t row_base = new_row_offset * 128;
+            const uint32_t swizzle = new_row_offset & 7;
+            const uint32_t byte0 = lane * 2;             // dim lane
+            const uint32_t byte1 = (lane + kHalfDim) * 2;
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(k_base + row_base + (((byte0 >> 4) ^ swizzle) << 4) + (byte0 & 15)),
+                         "h"(__bfloat16_as_ushort(new_key0)) : "memory");
+            asm volatile("st.shared.u16 [%0], %1;" ::"r"(k_base + row_base + (((byte1 >> 4) ^ swizzle) << 4) + (byte1 & 15)),
+                         "h"(__bfloat16_as_ushort(new_key1)) : "memory");
+            const uint32_t value_byte = lane * 4;
+            asm volatile("st.shared.u32 [%0], %1;" ::"r"(v_base + row_base + (((value_byte >> 4) ^ swizzle) << 4) + (value_byte & 15)),
+                         "r"(new_value) : "memory");
+            __syncwarp();
+        }
 
         // S[head, token] = Q K^T over this page: 2 token tiles x 4 dim steps
         float s[2][4];
@@ -399,9 +523,11 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
         !make_page_map(&value_map, launch.value_cache, launch.num_pages)) {
         return cudaErrorInvalidValue;
     }
+    const bool fused = launch.key_raw != nullptr;
+    auto kernel = fused ? ragged_decode_attention_kernel<true> : ragged_decode_attention_kernel<false>;
     // per launch: the attribute belongs to the current device's copy of the kernel
-    const cudaError_t attribute_status = cudaFuncSetAttribute(
-        ragged_decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemAlloc));
+    const cudaError_t attribute_status =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemAlloc));
     if (attribute_status != cudaSuccess) {
         return attribute_status;
     }
@@ -418,9 +544,18 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.num_tokens = static_cast<uint32_t>(launch.num_tokens);
     params.num_pages = static_cast<uint32_t>(launch.num_pages);
     params.num_splits = launch.num_splits;
+    params.key_raw = static_cast<const __nv_bfloat16*>(launch.key_raw);
+    params.value_raw = static_cast<const __nv_bfloat16*>(launch.value_raw);
+    params.query_norm = static_cast<const __nv_bfloat16*>(launch.query_norm);
+    params.key_norm = static_cast<const __nv_bfloat16*>(launch.key_norm);
+    params.inv_freq = launch.inv_freq;
+    params.slot_mapping = launch.slot_mapping;
+    params.key_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(launch.key_cache));
+    params.value_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(launch.value_cache));
+    params.eps = launch.eps;
     const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
-    cudaError_t status = launch_kernel(ragged_decode_attention_kernel, static_cast<unsigned int>(blocks), kThreads,
-                                       kSmemAlloc, stream, 1, key_map, value_map, params);
+    cudaError_t status = launch_kernel(kernel, static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream, 1,
+                                       key_map, value_map, params);
     if (status != cudaSuccess || launch.num_splits == 1) {
         return status;
     }

@@ -9,6 +9,8 @@
 //     host synchronisation;
 //   * every kernel argument is a fixed device pointer, so one captured graph per batch size replays unchanged.
 #include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include <new>
 #include <utility>
@@ -182,14 +184,40 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             post.num_tokens = tokens;
             post.num_pages = model->num_pages;
             post.eps = model->norm_eps;
+            const size_t splits = lfm25_splitk_decode_splits(tokens, batch->max_context_tokens, 16);
+            const char* fused_switch = getenv("LFM25_FUSED_APPEND");
+            if (fused_switch == nullptr || strcmp(fused_switch, "0") != 0) {
+                // one launch: QK-norm + RoPE + paged append + attention (+ merge when split)
+                RegionTimer timer(self, LFM25_REGION_ATTENTION);
+                lfm25_fused_ragged_decode_launch fused;
+                fused.page_size = 16;
+                fused.query_raw = post.query;
+                fused.key_raw = post.key;
+                fused.value_raw = post.value;
+                fused.query_norm = post.query_norm;
+                fused.key_norm = post.key_norm;
+                fused.inv_freq = post.inv_freq;
+                fused.key_cache = post.key_cache;
+                fused.value_cache = post.value_cache;
+                fused.position_ids = post.position_ids;
+                fused.slot_mapping = post.slot_mapping;
+                fused.output = slice_of(self->post_operator, tokens * kHidden);
+                fused.num_tokens = tokens;
+                fused.num_pages = model->num_pages;
+                fused.eps = model->norm_eps;
+                fused.block_tables = slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
+                fused.request_slots = slice_of(batch->request_slots, tokens);
+                fused.block_table_stride = batch->block_table_stride;
+                fused.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_tokens));
+                fused.num_splits = splits;
+                LFM25_TRY(lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(stream, &fused));
+            } else {
             {
                 RegionTimer timer(self, LFM25_REGION_APPEND);
                 LFM25_TRY(lfm25_qk_norm_rope_kv_write_decode(stream, &post));
             }
             {
             RegionTimer attention_timer(self, LFM25_REGION_ATTENTION);
-
-            const size_t splits = lfm25_splitk_decode_splits(tokens, batch->max_context_tokens, 16);
             lfm25_splitk_ragged_attention_launch attention;
             attention.page_size = 16;
             attention.query = post.query;
@@ -220,6 +248,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 unsplit.num_pages = model->num_pages;
                 unsplit.block_table_stride = batch->block_table_stride;
                 LFM25_TRY(lfm25_paged_ragged_attention_fast_lfm2_bf16(stream, &unsplit));
+            }
             }
             }
             LFM25_TRY(linear_decode(self, layer.output, self->post_operator, self->operator_output, tokens, use_fp8));

@@ -271,15 +271,33 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
             const uint32_t row_in_tile = quadrant * 32 + lane;
             const uint32_t columns = p.m_pad / p.splits;
             const uint32_t parked_base = smem_base;
-            for (uint32_t index = 0; index < columns; ++index) {
+            // columns is even (m_pad is a multiple of 16, splits at most 8).  All remote loads of a column pair
+            // are issued before the first add, so their latencies overlap instead of adding up.
+            for (uint32_t index = 0; index < columns; index += 2) {
                 const uint32_t batch = split * columns + index;
-                float sum = 0.0f;
-                for (uint32_t peer = 0; peer < p.splits; ++peer) {
-                    sum += load_peer_smem(parked_base + (batch * kTileN + row_in_tile) * 4, peer);
+                float part[2][8];
+#pragma unroll
+                for (uint32_t column = 0; column < 2; ++column) {
+#pragma unroll
+                    for (uint32_t peer = 0; peer < 8; ++peer) {
+                        part[column][peer] = 0.0f;
+                        if (peer < p.splits) {
+                            part[column][peer] =
+                                load_peer_smem(parked_base + ((batch + column) * kTileN + row_in_tile) * 4, peer);
+                        }
+                    }
                 }
-                if (batch < p.m) {
-                    p.out[static_cast<size_t>(batch) * p.n + tile * kTileN + row_in_tile] =
-                        __float2bfloat16_rn(sum * p.alpha);
+#pragma unroll
+                for (uint32_t column = 0; column < 2; ++column) {
+                    float sum = 0.0f;
+#pragma unroll
+                    for (uint32_t peer = 0; peer < 8; ++peer) {
+                        sum += part[column][peer];   // rank order; absent ranks contribute exact zeros
+                    }
+                    if (batch + column < p.m) {
+                        p.out[static_cast<size_t>(batch + column) * p.n + tile * kTileN + row_in_tile] =
+                            __float2bfloat16_rn(sum * p.alpha);
+                    }
                 }
             }
         }

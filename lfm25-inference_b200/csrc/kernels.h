@@ -23,6 +23,14 @@ struct AttentionLaunch {
     size_t block_table_stride;
     size_t block_table_rows;
     uint32_t num_splits;          // 1 = unsplit
+    // fused mode (key_raw != nullptr): raw projections in, new cache row produced inside the kernel
+    const void* key_raw = nullptr;      // bf16 [T,8,64]
+    const void* value_raw = nullptr;    // bf16 [T,8,64]
+    const void* query_norm = nullptr;   // bf16 [64]
+    const void* key_norm = nullptr;     // bf16 [64]
+    const float* inv_freq = nullptr;    // f32 [32]
+    const int64_t* slot_mapping = nullptr;
+    float eps = 0.0f;
 };
 cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionLaunch& launch);
 

@@ -7,6 +7,7 @@
 //
 // Both are latency-bound (a few KiB per token); they exist to be bit-exact and cheap to launch.
 #include "common.cuh"
+#include "qk_norm_rope.cuh"
 #include "kernels.h"
 #include "launch.h"
 
@@ -45,31 +46,6 @@ kv_cache_write_kernel(const uint4* __restrict__ key, const uint4* __restrict__ v
     } else {
         value_cache[destination] = value[source];
     }
-}
-
-// Sum over the 32 lanes in the association order of a shuffle-down tree read at lane 0
-// (16, 8, 4, 2, 1).  The xor butterfly adds the same pairs at every level, and addition is
-// commutative, so every lane ends with exactly the bits lane 0 of the tree would hold.
-__device__ __forceinline__ float warp_tree_sum(float value) {
-#pragma unroll
-    for (uint32_t delta = 16; delta > 0; delta >>= 1) {
-        value += __shfl_xor_sync(0xffffffffu, value, delta);
-    }
-    return value;
-}
-
-// RMSNorm + RoPE of one 64-wide head held as (dim lane, dim lane+32) per lane.  The rounding
-// points are the reference's (kernels/qk_postprocess.cu:21-30,104-112): normalise -> bf16 ->
-// bf16 multiply by the weight -> fp32 rotation with fmaf -> bf16.
-__device__ __forceinline__ void norm_rope(float raw0, float raw1, __nv_bfloat16 weight0, __nv_bfloat16 weight1,
-                                          float sin_value, float cos_value, float eps, __nv_bfloat16& out0,
-                                          __nv_bfloat16& out1) {
-    const float sum = warp_tree_sum(fmaf(raw0, raw0, raw1 * raw1));
-    const float inv_rms = __frsqrt_rn(sum * (1.0f / 64.0f) + eps);
-    const float x0 = __bfloat162float(__hmul(__float2bfloat16_rn(raw0 * inv_rms), weight0));
-    const float x1 = __bfloat162float(__hmul(__float2bfloat16_rn(raw1 * inv_rms), weight1));
-    out0 = __float2bfloat16_rn(fmaf(-x1, sin_value, x0 * cos_value));
-    out1 = __float2bfloat16_rn(fmaf(x0, sin_value, x1 * cos_value));
 }
 
 // One CTA per token, 10 warps: warps 0..7 each take 4 query heads, warps 8..9 each take 4 KV

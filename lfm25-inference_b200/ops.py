@@ -160,6 +160,27 @@ def paged_ragged_attention_splitk_lfm2_bf16_into(inputs: FastRaggedAttentionInpu
     check(library().lfm25_paged_ragged_attention_splitk_lfm2_bf16(_stream(), launch))
 
 
+def fused_ragged_paged_attention_decode_lfm2_bf16_into(query_raw, key_raw, value_raw, query_norm, key_norm, inv_freq,
+                                                       position_ids, slot_mapping, arena: PagedKvArena, block_tables,
+                                                       block_table_stride: int, request_slots, eps: float, output,
+                                                       partials=None, num_splits: int = 1) -> None:
+    """One-kernel decode: QK-norm + RoPE + paged KV append + attention
+    (reference: src/ops/attention_fused.rs:95-153); optionally split over the KV axis."""
+    _ensure(query_raw.dim() == 3 and tuple(query_raw.shape[1:]) == (32, 64), "fused query must have shape [N,32,64]")
+    num_tokens = query_raw.shape[0]
+    _ensure(tuple(key_raw.shape) == (num_tokens, 8, 64), "fused key must have shape [N,8,64]")
+    _ensure(tuple(value_raw.shape) == (num_tokens, 8, 64), "fused value must have shape [N,8,64]")
+    _ensure(block_tables.dim() == 2 and block_tables.shape[1] == block_table_stride,
+            "fused block table stride/shape mismatch")
+    empty = Slice(None, 0)
+    launch = _abi.FusedRaggedDecodeLaunch(
+        arena.page_size, _slice(query_raw), _slice(key_raw), _slice(value_raw), _slice(query_norm), _slice(key_norm),
+        _slice(inv_freq), _slice(arena.key), _slice(arena.value), _slice(position_ids), _slice(slot_mapping),
+        _slice(output), num_tokens, arena.num_pages, eps, _slice(block_tables), _slice(request_slots),
+        block_table_stride, _slice(partials) if partials is not None else empty, num_splits)
+    check(library().lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(_stream(), launch))
+
+
 def paged_ragged_attention_splitk_static_lfm2_bf16_into(inputs: FastRaggedAttentionInput, num_splits: int,
                                                         output: torch.Tensor) -> None:
     """Split-K attention without a caller workspace, for hosts that may not allocate device memory while
