@@ -64,6 +64,8 @@ def parse_arguments():
     parser.add_argument("--cpu-sequences", type=int, default=0, help="sequences in the CPU sample (0 = auto)")
     parser.add_argument("--sequences", type=int, default=SEQUENCES,
                         help="batch size; values other than 64 are for profiling a smaller case, not the metric")
+    parser.add_argument("--step-sequences", type=int, default=STEP_SEQUENCES,
+                        help="step workload: sequences in the batch (the headline number needs the default)")
     parser.add_argument("--pool-pages", type=int, default=NUM_PAGES, help="pages in the K/V pool (same remark)")
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     arguments = parser.parse_args()
@@ -71,7 +73,8 @@ def parse_arguments():
         arguments.steps = 256 if arguments.workload == "step" else 1024
     if arguments.warmup <= 0:
         arguments.warmup = 8 if arguments.workload == "step" else 32
-    globals().update(SEQUENCES=arguments.sequences, NUM_PAGES=arguments.pool_pages)
+    globals().update(SEQUENCES=arguments.sequences, NUM_PAGES=arguments.pool_pages,
+                     STEP_SEQUENCES=arguments.step_sequences)
     return arguments
 
 

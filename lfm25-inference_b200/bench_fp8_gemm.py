@@ -23,6 +23,10 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
 SHAPES = [("gate_up", 16384, 2048), ("down", 2048, 8192), ("lm_head", 65536, 2048)]
+# BF16 sites of the decode step (reference src/model/lfm2.rs: conv in/out projections, q/k/v/o, the FFN of the
+# layers outside the FP8 policy)
+BF16_SHAPES = [("conv_in", 6144, 2048), ("proj_2048", 2048, 2048), ("kv_proj", 512, 2048),
+               ("ffn_w1", 8192, 2048), ("ffn_w2", 2048, 8192)]
 RING_BYTES = 512 << 20
 
 
@@ -51,14 +55,49 @@ def time_launches(function, count, replays=5):
     return start.elapsed_time(stop) * 1e3 / (count * replays)
 
 
+def sweep_bf16(arguments, ops, device, hbm_peak):
+    """BF16 sites: this library's tcgen05 kernel (LFM25_BF16_GEMM=umma) beside cuBLASLt through the same handle."""
+    generator = torch.Generator(device=device).manual_seed(3)
+    blaslt = ops.BlasLt()
+    for name, n, k in BF16_SHAPES:
+        if arguments.shapes and name not in arguments.shapes:
+            continue
+        copies = max(2, (RING_BYTES + 2 * n * k - 1) // (2 * n * k))
+        ring = [(torch.randn((n, k), generator=generator, device=device) * 0.02).to(torch.bfloat16)
+                for _ in range(copies)]
+        for m in arguments.ms:
+            x = torch.randn((m, k), generator=generator, device=device, dtype=torch.bfloat16)
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+
+            def linear(index, ring=ring, out=out, x=x):
+                blaslt.bind_current_stream()
+                blaslt.linear_bf16(x, ring[index % len(ring)], out)
+
+            bytes_moved = 2 * (n * k + m * k + m * n)
+            line = {"shape": name, "dtype": "bf16", "m": m, "n": n, "k": k, "bytes": bytes_moved,
+                    "weight_copies": copies}
+            for path in ("umma", "cublaslt"):
+                os.environ["LFM25_BF16_GEMM"] = path
+                cold = time_launches(linear, arguments.iterations)
+                line[f"{path}_us_cold"] = cold
+                line[f"{path}_us_l2_warm"] = time_launches(lambda index: linear(0), arguments.iterations)
+                line[f"{path}_hbm_frac_cold"] = bytes_moved / cold / 1e3 / hbm_peak
+            os.environ.pop("LFM25_BF16_GEMM", None)
+            print(json.dumps(line), flush=True)
+        del ring
+    blaslt.close()
+
+
 def main():
     parser = argparse.ArgumentParser()
+    parser.add_argument("--dtype", choices=["e4m3", "bf16"], default="e4m3")
     parser.add_argument("--iterations", type=int, default=64)
     parser.add_argument("--ms", type=int, nargs="+", default=[1, 8, 32, 128, 256])
     parser.add_argument("--no-cublaslt", action="store_true")
     parser.add_argument("--paths", nargs="+", default=["auto"],
                         help="kernel paths to time: auto, stream, umma (sets LFM25_FP8_GEMM_PATH)")
     parser.add_argument("--handle", action="store_true", help="call through a BlasLt handle (allows split-K)")
+    parser.add_argument("--shapes", nargs="+", default=None, help="only these sites (gate_up, down, lm_head, ...)")
     arguments = parser.parse_args()
     entry.load_package()
     from lfm25_inference_b200 import ops
@@ -66,9 +105,14 @@ def main():
     device = torch.device("cuda:0")
     peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm_peak = json.load(open(peak_path))["hbm_gbs"] if os.path.exists(peak_path) else 6650.0
+    if arguments.dtype == "bf16":
+        sweep_bf16(arguments, ops, device, hbm_peak)
+        return
     generator = torch.Generator(device=device).manual_seed(2)
     blaslt = ops.BlasLt() if arguments.handle else None
     for name, n, k in SHAPES:
+        if arguments.shapes and name not in arguments.shapes:
+            continue
         copies = max(2, (RING_BYTES + n * k - 1) // (n * k))
         weight = torch.randn((n, k), generator=generator, device=device) * 0.02
         w_amax = float(weight.abs().max())

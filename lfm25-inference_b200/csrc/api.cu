@@ -127,8 +127,9 @@ int32_t validate_ragged_common(size_t page_size, const lfm25_slice& query, const
 //   9 <= M <= 256     tcgen05 / TMEM kernel (K split over a thread-block cluster when there are few tiles)
 //   anything else     generic kernel
 // LFM25_FP8_GEMM_PATH = stream | umma | generic overrides the choice where the shape allows (for measurements).
+// `exchange` is the split-K scratch of a BlasLt handle; the handle-free entry point passes null and never splits K.
 int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
-                            const lfm25_fp8_linear_config* config) {
+                            const lfm25_fp8_linear_config* config, void* exchange, size_t exchange_bytes) {
     LFM25_ENSURE(config != nullptr, LFM25_ERR_NULL_POINTER, "FP8 linear config is null");
     const size_t m = config->m;
     const size_t n = config->n;
@@ -160,8 +161,9 @@ int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weig
                  "FP8 linear received a null device pointer");
     LFM25_ENSURE(m <= 0x7fffffffu && n <= 0x7fffffffu && k <= 0x7fffffffu, LFM25_ERR_INVALID_ARGUMENT,
                  "FP8 linear dimension exceeds i32");
-    const bool aligned =
-        ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr)) & 15) == 0;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
+                           reinterpret_cast<uintptr_t>(out.ptr)) &
+                          15) == 0;
     const bool stream_ok = aligned && lfm25::fp8_gemm_stream_supports(m, n, k);
     const bool umma_ok = aligned && lfm25::fp8_gemm_umma_supports(m, n, k);
     enum { kStream, kUmma, kGeneric } path = kGeneric;
@@ -182,7 +184,7 @@ int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weig
         unsigned int* status_words = device_status_pointer();
         LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
         status = lfm25::launch_fp8_gemm_umma(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale,
-                                             status_words);
+                                             exchange, exchange_bytes, status_words);
     } else {
         status = lfm25::launch_fp8_gemm_generic(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale);
     }
@@ -648,7 +650,7 @@ int32_t lfm25_decode_step_metadata(void* stream, const lfm25_decode_batch* batch
 
 int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                 const lfm25_fp8_linear_config* config) {
-    return linear_fp8_dispatch(static_cast<cudaStream_t>(stream), x, weight, out, config);
+    return linear_fp8_dispatch(static_cast<cudaStream_t>(stream), x, weight, out, config, nullptr, 0);
 }
 
 int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out) {
@@ -657,7 +659,8 @@ int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out) {
     LFM25_ENSURE(handle != nullptr, LFM25_ERR_CUDA, "failed to allocate the BlasLt handle");
     handle->stream = static_cast<cudaStream_t>(stream);
     handle->library_workspace_bytes = 32u * 1024u * 1024u;   // src/cuda/blaslt/mod.rs:53-57
-    const size_t total = handle->library_workspace_bytes;
+    handle->exchange_bytes = lfm25::kUmmaExchangeBytes;
+    const size_t total = handle->library_workspace_bytes + handle->exchange_bytes;
     cudaError_t status = cudaMalloc(&handle->allocation, total);
     if (status == cudaSuccess) {
         status = cudaMemsetAsync(handle->allocation, 0, total, handle->stream);
@@ -670,6 +673,7 @@ int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out) {
         return cuda_result(status, "failed to allocate the GEMM workspace");
     }
     handle->library_workspace = handle->allocation;
+    handle->exchange = static_cast<char*>(handle->allocation) + handle->library_workspace_bytes;
     handle->cublaslt = nullptr;
     *out = handle;
     return LFM25_OK;
@@ -707,6 +711,25 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
     LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear weight storage too small");
     LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear output storage too small");
     LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "linear received a null device pointer");
+    // Batches of up to 16 rows go to this library's tcgen05 kernel where it supports the shape (N % 128 == 0,
+    // K % 64 == 0): with programmatic dependent launch and the weight prefetch it is ahead of cuBLASLt there
+    // (measured on the whole step: 12 % at 1 row, 8 % at 8 rows), and behind it from 32 rows on.
+    // LFM25_BF16_GEMM = umma | cublaslt forces one of the two (for measurements).
+    const char* bf16_path = getenv("LFM25_BF16_GEMM");
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
+                           reinterpret_cast<uintptr_t>(out.ptr)) &
+                          15) == 0;
+    bool own_kernel = m <= 16;
+    if (bf16_path != nullptr && strcmp(bf16_path, "umma") == 0) own_kernel = true;
+    if (bf16_path != nullptr && strcmp(bf16_path, "cublaslt") == 0) own_kernel = false;
+    if (own_kernel && aligned && lfm25::bf16_gemm_umma_supports(m, n, k)) {
+        unsigned int* status_words = device_status_pointer();
+        LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+        return cuda_result(
+            lfm25::launch_bf16_gemm_umma(handle->stream, x.ptr, weight.ptr, out.ptr, m, n, k, handle->exchange,
+                                         handle->exchange_bytes, status_words),
+            "BF16 linear launch failed");
+    }
     if (handle->cublaslt == nullptr) {
         handle->cublaslt = lfm25::cublaslt_bf16_create(handle->library_workspace, handle->library_workspace_bytes);
         LFM25_ENSURE(handle->cublaslt != nullptr, LFM25_ERR_CUDA, "cuBLASLt could not be opened");
@@ -719,7 +742,7 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
 int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                        const lfm25_fp8_linear_config* config) {
     LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
-    return linear_fp8_dispatch(handle->stream, x, weight, out, config);
+    return linear_fp8_dispatch(handle->stream, x, weight, out, config, handle->exchange, handle->exchange_bytes);
 }
 
 }  // extern "C"

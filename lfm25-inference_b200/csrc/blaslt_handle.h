@@ -1,5 +1,6 @@
 // Layout of the opaque lfm25_blaslt handle (internal): the stream it is bound to, the one device allocation it
-// owns (the cuBLASLt workspace) and the lazily opened cuBLASLt state.
+// owns (the cuBLASLt workspace followed by the split-K exchange buffer of this library's tcgen05 GEMM) and the
+// lazily opened cuBLASLt state.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -18,5 +19,7 @@ struct lfm25_blaslt {
     void* allocation;
     void* library_workspace;        // handed to cuBLASLt (32 MiB, the size the reference uses)
     size_t library_workspace_bytes;
+    void* exchange;                 // split-K partial tiles of the tcgen05 GEMM; one stream at a time
+    size_t exchange_bytes;
     lfm25::CublasLtBf16* cublaslt;  // null until the first BF16 linear
 };

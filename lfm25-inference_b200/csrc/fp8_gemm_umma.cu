@@ -11,14 +11,19 @@
 //   warp 1   allocates TMEM; one thread issues 4 tcgen05.mma per stage (K = 32 each) into a
 //            128-lane x M_pad-column fp32 accumulator and releases the stage with tcgen05.commit
 //   warps 2-5  epilogue: tcgen05.ld the accumulator (thread = weight row, registers = batch columns),
-//            scale, round to bf16, store; a warp's store covers 32 consecutive outputs of one batch row
+//            scale, round to bf16, transpose through shared memory and store 16 bytes per lane
 //
 // The op is bound by the weight stream (N*K bytes) for every batch size here, so what matters is the number
 // of bytes in flight: stages are as deep as shared memory allows (up to 8 x 16 KiB of weights per SM).
 // When N/128 tiles cannot occupy the machine (Down: 16 tiles), K is split over the CTAs of a thread-block
-// cluster (up to 8 per tile).  Each parks its fp32 partial tile in its own shared memory; after a cluster
-// barrier every CTA finishes one slice of the batch columns, reading the partners' tiles through distributed
-// shared memory and adding them in rank order (reproducible, no atomics, no workspace, no second launch).
+// cluster (up to 8 per tile).  The partial tiles are reduce-scattered through distributed shared memory:
+// after a cluster barrier each CTA pushes the slice of batch columns that partner q owns straight from its
+// TMEM registers into q's shared memory (st.shared::cluster, fire-and-forget), and after a second barrier
+// every CTA adds the slices it received in rank order (reproducible, no atomics, no workspace, no second
+// launch) and stores its share of the output.
+//
+// The same kernel serves the BF16 sites (template parameter): a 128-byte swizzle row then holds 64 bf16 values,
+// one tcgen05.mma (kind::f16) covers K = 16 of them, i.e. the same 32 bytes, and everything else is unchanged.
 //
 // Every mbarrier wait is bounded; a wait that runs out sets an abort flag, is recorded in the device
 // status words, and the CTA still frees its TMEM and exits.
@@ -44,13 +49,14 @@ constexpr uint32_t kWeightTileBytes = kTileN * kBlockK;
 
 struct UmmaParams {
     __nv_bfloat16* out;
+    float* exchange;         // split-K partial tiles [tile][split][batch column][128 rows] fp32 (L2-resident)
     unsigned int* status;
     uint32_t m;
     uint32_t n;
     uint32_t m_pad;          // batch rounded up to 16 = UMMA N
     uint32_t stages;
     uint32_t data_bytes;     // shared memory in front of the control block: the stages, or the parked tile
-    uint32_t k_blocks;       // 128-byte K blocks per split
+    uint32_t k_blocks;       // 128-byte K blocks in total; split s takes the s-th of `splits` near-equal ranges
     uint32_t splits;         // CTAs of a cluster that share one weight tile, each with its own K range
     uint32_t tmem_columns;   // power of two >= max(32, m_pad)
     float alpha;
@@ -66,16 +72,28 @@ __device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
     return descriptor;
 }
 
-__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                        uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
+template <bool BF16>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                     uint32_t accumulate) {
+    if (BF16) {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n"
+            ".reg .pred p;\n"
+            "setp.ne.b32 p, %4, 0;\n"
+            "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+            "}\n" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -99,14 +117,6 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     return rank;
 }
-__device__ __forceinline__ float load_peer_smem(uint32_t local_address, uint32_t peer) {
-    uint32_t remote;
-    float value;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(peer));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
-    return value;
-}
-
 __device__ __forceinline__ void tmem_load16(uint32_t address, uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
@@ -117,8 +127,9 @@ __device__ __forceinline__ void tmem_load16(uint32_t address, uint32_t (&r)[16])
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 2)
-fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap x_map,
+gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap x_map,
                      const UmmaParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -160,14 +171,18 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    const uint32_t k_block0 = split * p.k_blocks;
+    // K range of this split: the first (k_blocks % splits) splits take one block more
+    const uint32_t k_share = p.k_blocks / p.splits;
+    const uint32_t k_extra = p.k_blocks % p.splits;
+    const uint32_t k_count = k_share + (split < k_extra ? 1u : 0u);
+    const uint32_t k_block0 = split * k_share + (split < k_extra ? split : k_extra);
 
     if (warp == 0) {
         if (lane == 0) {
             // The weight tiles are constants: the first ring of them is requested before the dependency wait, so
             // the stream is already flowing while the predecessor kernel drains.  The activation tiles, which the
             // predecessor writes, follow after the wait and complete the same barriers.
-            const uint32_t ahead = p.k_blocks < p.stages ? p.k_blocks : p.stages;
+            const uint32_t ahead = k_count < p.stages ? k_count : p.stages;
             const int32_t tile_row = static_cast<int32_t>(tile * kTileN);
             for (uint32_t block = 0; block < ahead; ++block) {
                 const uint32_t bar = bar_full + 8 * block;
@@ -180,7 +195,7 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
                 tma_load_2d(smem_base + block * stage_bytes + kWeightTileBytes, &x_map, bar_full + 8 * block,
                             static_cast<int32_t>((k_block0 + block) * kBlockK), 0);
             }
-            for (uint32_t block = ahead; block < p.k_blocks; ++block) {
+            for (uint32_t block = ahead; block < k_count; ++block) {
                 const uint32_t stage = block % p.stages;
                 if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1)) {
                     *abort_flag = 1;
@@ -197,10 +212,12 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // instruction descriptor: D = f32, A = B = E4M3, both K-major, N = m_pad, M = 128
-            const uint32_t idesc = (1u << 4) | ((p.m_pad >> 3) << 17) | ((kTileN >> 4) << 24);
+            // instruction descriptor: D = f32, A = B = E4M3 (format 0) or BF16 (format 1), both K-major,
+            // N = m_pad, M = 128
+            const uint32_t formats = BF16 ? ((1u << 7) | (1u << 10)) : 0u;
+            const uint32_t idesc = (1u << 4) | formats | ((p.m_pad >> 3) << 17) | ((kTileN >> 4) << 24);
             bool ok = true;
-            for (uint32_t block = 0; block < p.k_blocks && ok; ++block) {
+            for (uint32_t block = 0; block < k_count && ok; ++block) {
                 const uint32_t stage = block % p.stages;
                 if (*abort_flag || !mbar_wait_bounded(bar_full + 8 * stage, (block / p.stages) & 1)) {
                     *abort_flag = 1;
@@ -215,7 +232,7 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
 #pragma unroll
                 for (uint32_t step = 0; step < kBlockK / kUmmaK; ++step) {
                     // advancing 32 bytes inside the swizzle row = +2 in the (address >> 4) field
-                    umma_f8(tmem_base, a_desc + step * 2, b_desc + step * 2, idesc, (block | step) != 0 ? 1u : 0u);
+                    umma<BF16>(tmem_base, a_desc + step * 2, b_desc + step * 2, idesc, (block | step) != 0 ? 1u : 0u);
                 }
                 umma_commit(bar_empty + 8 * stage);
             }
@@ -226,82 +243,99 @@ fp8_gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gri
     } else {
         // ---- epilogue: 4 warps, each owns the 32 TMEM lanes of its quadrant (warp id modulo 4) ----
         const uint32_t quadrant = warp & 3;
-        const uint32_t row = tile * kTileN + quadrant * 32 + lane;   // weight row = output column
         pdl_wait();   // the output buffer may still be read by an earlier kernel until the dependency resolves
-        const bool ready = !*abort_flag && mbar_wait_bounded(bar_accumulator, 0);
-        if (!ready) {
-            if (lane == 0) {
-                *abort_flag = 1;
-                record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 3);
+        const bool ready = __all_sync(0xffffffffu, !*abort_flag && mbar_wait_bounded(bar_accumulator, 0));
+        if (!ready && lane == 0) {
+            *abort_flag = 1;
+            record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 3);
+        }
+        tcgen05_fence_after();
+        const uint32_t lane_address = tmem_base + ((quadrant * 32) << 16);
+        if (p.splits == 1) {
+            if (ready) {
+                // Transpose through this warp's slice of the (now idle) pipeline memory so that the global stores
+                // are 16 bytes wide: staged[column][32 rows] as bf16, then lane -> (column l/4, 8 rows l%4).
+                uint8_t* staged = smem + quadrant * (p.m_pad * 64);
+                for (uint32_t column0 = 0; column0 < p.m_pad; column0 += 16) {
+                    uint32_t raw[16];
+                    tmem_load16(lane_address + column0, raw);
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j) {
+                        reinterpret_cast<__nv_bfloat16*>(staged + (column0 + j) * 64)[lane] =
+                            __float2bfloat16_rn(__uint_as_float(raw[j]) * p.alpha);
+                    }
+                }
+                __syncwarp();
+                __nv_bfloat16* out_rows = p.out + tile * kTileN + quadrant * 32 + (lane & 3) * 8;
+                for (uint32_t column0 = 0; column0 < p.m; column0 += 8) {
+                    const uint32_t batch = column0 + (lane >> 2);
+                    if (batch < p.m) {
+                        const uint4 value = *reinterpret_cast<const uint4*>(staged + batch * 64 + (lane & 3) * 16);
+                        *reinterpret_cast<uint4*>(out_rows + static_cast<size_t>(batch) * p.n) = value;
+                    }
+                }
             }
         } else {
-            tcgen05_fence_after();
-            const uint32_t lane_address = tmem_base + ((quadrant * 32) << 16);
-            for (uint32_t column0 = 0; column0 < p.m_pad; column0 += 16) {
-                uint32_t raw[16];
-                tmem_load16(lane_address + column0, raw);
-                if (p.splits == 1) {
+            // Split K, step 1 of 2: the fp32 partial tile goes to the exchange buffer, one coalesced 128-byte
+            // store per warp and batch column.  The buffer is written and read back within microseconds, so it
+            // lives in L2.  (Distributed shared memory was measured for this exchange, pushed and pulled: at a
+            // cluster of 8 it moved a few GB/s per CTA.)
+            if (ready) {
+                float* mine = p.exchange + static_cast<size_t>(tile * p.splits + split) * p.m_pad * kTileN +
+                              quadrant * 32 + lane;
+                for (uint32_t column0 = 0; column0 < p.m; column0 += 16) {
+                    uint32_t raw[16];
+                    tmem_load16(lane_address + column0, raw);
 #pragma unroll
                     for (uint32_t j = 0; j < 16; ++j) {
-                        const uint32_t batch = column0 + j;
-                        if (batch < p.m) {
-                            p.out[static_cast<size_t>(batch) * p.n + row] =
-                                __float2bfloat16_rn(__uint_as_float(raw[j]) * p.alpha);
+                        if (column0 + j < p.m) {
+                            __stcg(mine + (column0 + j) * kTileN, __uint_as_float(raw[j]));
                         }
-                    }
-                } else {
-                    // park the partial tile in this CTA's (now idle) pipeline memory as fp32 [column][128 rows]
-                    float* parked = reinterpret_cast<float*>(smem);
-#pragma unroll
-                    for (uint32_t j = 0; j < 16; ++j) {
-                        parked[(column0 + j) * kTileN + quadrant * 32 + lane] = __uint_as_float(raw[j]);
                     }
                 }
             }
         }
     }
-
     if (p.splits > 1) {
-        // Reduce-scatter across the cluster: rank q finishes the batch columns [q, q+1) * m_pad / splits of the
-        // tile, adding the partners' parked tiles in rank order (so the sum is reproducible).
+        // Split K, step 2 of 2: after the cluster barrier (release / acquire at cluster scope, and the partners are
+        // the only readers) CTA q of the cluster finishes batch columns [q, q+1) * ceil(m / splits): it adds the
+        // partials in rank order (reproducible, no atomics) and stores bf16.  A warp covers the 128 rows of one
+        // column with 16-byte loads; the loads of all ranks are in flight together.
+        __syncwarp();
         tcgen05_fence_before();
         cluster_sync_all();
         if (warp >= 2 && !*abort_flag) {
-            const uint32_t quadrant = warp & 3;
-            const uint32_t row_in_tile = quadrant * 32 + lane;
-            const uint32_t columns = p.m_pad / p.splits;
-            const uint32_t parked_base = smem_base;
-            // columns is even (m_pad is a multiple of 16, splits at most 8).  All remote loads of a column pair
-            // are issued before the first add, so their latencies overlap instead of adding up.
-            for (uint32_t index = 0; index < columns; index += 2) {
-                const uint32_t batch = split * columns + index;
-                float part[2][8];
+            const uint32_t columns = (p.m + p.splits - 1) / p.splits;
+            const uint32_t row4 = lane * 4;
+            const float* partials = p.exchange + static_cast<size_t>(tile) * p.splits * p.m_pad * kTileN + row4;
+            for (uint32_t column = warp - 2; column < columns; column += 4) {
+                const uint32_t batch = split * columns + column;
+                if (batch >= p.m) break;
+                float4 part[8];
 #pragma unroll
-                for (uint32_t column = 0; column < 2; ++column) {
-#pragma unroll
-                    for (uint32_t peer = 0; peer < 8; ++peer) {
-                        part[column][peer] = 0.0f;
-                        if (peer < p.splits) {
-                            part[column][peer] =
-                                load_peer_smem(parked_base + ((batch + column) * kTileN + row_in_tile) * 4, peer);
-                        }
+                for (uint32_t rank = 0; rank < 8; ++rank) {
+                    part[rank] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (rank < p.splits) {
+                        part[rank] = __ldcg(reinterpret_cast<const float4*>(
+                            partials + (static_cast<size_t>(rank) * p.m_pad + batch) * kTileN));
                     }
                 }
+                float4 sum = part[0];
 #pragma unroll
-                for (uint32_t column = 0; column < 2; ++column) {
-                    float sum = 0.0f;
-#pragma unroll
-                    for (uint32_t peer = 0; peer < 8; ++peer) {
-                        sum += part[column][peer];   // rank order; absent ranks contribute exact zeros
-                    }
-                    if (batch + column < p.m) {
-                        p.out[static_cast<size_t>(batch + column) * p.n + tile * kTileN + row_in_tile] =
-                            __float2bfloat16_rn(sum * p.alpha);
-                    }
+                for (uint32_t rank = 1; rank < 8; ++rank) {   // absent ranks add exact zeros
+                    sum.x += part[rank].x;
+                    sum.y += part[rank].y;
+                    sum.z += part[rank].z;
+                    sum.w += part[rank].w;
                 }
+                const __nv_bfloat162 low = __floats2bfloat162_rn(sum.x * p.alpha, sum.y * p.alpha);
+                const __nv_bfloat162 high = __floats2bfloat162_rn(sum.z * p.alpha, sum.w * p.alpha);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&low);
+                packed.y = *reinterpret_cast<const uint32_t*>(&high);
+                *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(batch) * p.n + tile * kTileN + row4) = packed;
             }
         }
-        cluster_sync_all();   // nobody leaves while a partner may still read its shared memory
     }
 
     tcgen05_fence_before();
@@ -318,57 +352,122 @@ bool fp8_gemm_umma_supports(size_t m, size_t n, size_t k) {
     return m >= 1 && m <= 256 && n % kTileN == 0 && k % kBlockK == 0 && n <= 0x7fffffffu && k <= 0x7fffffffu;
 }
 
-cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
-                                 size_t n, size_t k, float alpha, unsigned int* status) {
+bool bf16_gemm_umma_supports(size_t m, size_t n, size_t k) { return fp8_gemm_umma_supports(m, n, k * 2); }
+
+namespace {
+
+constexpr uint32_t kControlBytes = 16 * kMaxStages + 64 + 1024;   // barriers, TMEM slot, alignment slack
+
+// How many clusters of `size` CTAs, one CTA per SM with the whole shared-memory budget, the device keeps resident
+// at once; asked once per size and kept.  0 when the runtime cannot tell.
+template <bool BF16>
+uint32_t resident_clusters(uint32_t size) {
+    static int known[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+    if (size < 2 || size > 8) return 0;
+    if (known[size] < 0) {
+        const uint32_t smem_bytes = kSmemBudget + kControlBytes;
+        int clusters = 0;
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(size, 1, 1);
+        config.blockDim = dim3(kThreads, 1, 1);
+        config.dynamicSmemBytes = smem_bytes;
+        cudaLaunchAttribute attribute;
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = size;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        if (cudaFuncSetAttribute(gemm_umma_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem_bytes)) != cudaSuccess ||
+            cudaOccupancyMaxActiveClusters(&clusters, gemm_umma_kernel<BF16>, &config) != cudaSuccess) {
+            (void)cudaGetLastError();
+            clusters = 0;
+        }
+        known[size] = clusters;
+    }
+    return static_cast<uint32_t>(known[size]);
+}
+
+// `k_bytes` is the length of a weight / activation row in bytes (K for E4M3, 2 K for BF16).
+template <bool BF16>
+cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m, size_t n,
+                        size_t k_bytes, float alpha, void* exchange, size_t exchange_bytes, unsigned int* status) {
     const uint32_t m_pad = static_cast<uint32_t>((m + 15) / 16 * 16);
     CUtensorMap weight_map;
     CUtensorMap x_map;
-    if (!make_swizzled_2d_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, weight, n, k, kTileN) ||
-        !make_swizzled_2d_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, m, k, m_pad)) {
+    if (!make_swizzled_2d_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, weight, n, k_bytes, kTileN) ||
+        !make_swizzled_2d_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, m, k_bytes, m_pad)) {
         return cudaErrorInvalidValue;
     }
     const uint32_t tiles = static_cast<uint32_t>(n / kTileN);
-    const uint32_t k_blocks_total = static_cast<uint32_t>(k / kBlockK);
-    // Split K (cluster of up to 8 CTAs per tile) only while the tiles alone leave most SMs idle.
-    uint32_t splits = 1;
-    while (splits < 8 && tiles * splits * 2 <= 148 && k_blocks_total % (splits * 2) == 0 &&
-           k_blocks_total / (splits * 2) >= 4) {
-        splits *= 2;
-    }
+    const uint32_t k_blocks_total = static_cast<uint32_t>(k_bytes / kBlockK);
     const uint32_t stage_bytes = kWeightTileBytes + m_pad * kBlockK;
-    // With more CTAs than SMs (LM head: 512 tiles) two CTAs share an SM, so that the epilogue of one tile
-    // overlaps the weight stream of the next; otherwise one CTA takes the whole shared memory for depth.
-    const bool share_sm = tiles * splits > 148 && kSmemBudgetShared / stage_bytes >= 3;
+    // Two CTAs share an SM whenever three stages still fit in half the shared memory: with more CTAs than SMs
+    // (LM head: 512 tiles) the epilogue of one tile then overlaps the weight stream of the next.
+    const bool can_share = kSmemBudgetShared / stage_bytes >= 3;
+    // Split K over a cluster of up to 8 CTAs per tile when the tiles alone would leave a third of the SMs idle.
+    // Measured on the decode shapes (4, 16, 48 and 64 tiles), the best split count is the largest one that keeps
+    // the grid within 256 CTAs at two CTAs per SM (16 tiles: 8, 48: 5, 64: 4).  Where the stages are too large to
+    // share an SM (batches over 128) the grid must fit one wave of one CTA per SM, and since a cluster needs its
+    // SMs inside one GPC the runtime is asked how many clusters of that size are resident (15 of size 8).  Each
+    // CTA keeps at least 2 K blocks.  Needs the exchange buffer.
+    uint32_t splits = 1;
+    if (exchange != nullptr && tiles < 100) {
+        for (uint32_t candidate = 2; candidate <= 8; ++candidate) {
+            const bool fits = static_cast<size_t>(tiles) * candidate * m_pad * kTileN * 4 <= exchange_bytes;
+            const bool resident = can_share ? tiles * candidate <= 256
+                                            : tiles * candidate <= 148 &&
+                                                  tiles <= resident_clusters<BF16>(candidate);
+            if (fits && resident && k_blocks_total / candidate >= 2) {
+                splits = candidate;
+            }
+        }
+    }
+    const bool share_sm = can_share && (splits > 1 || tiles > 148);
     uint32_t stages = (share_sm ? kSmemBudgetShared : kSmemBudget) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
-    const uint32_t k_blocks = k_blocks_total / splits;
-    if (stages > k_blocks) stages = k_blocks;
+    const uint32_t k_blocks_least = k_blocks_total / splits;
+    if (stages > k_blocks_least) stages = k_blocks_least;
     uint32_t data_bytes = stages * stage_bytes;
-    const uint32_t parked_bytes = splits > 1 ? m_pad * kTileN * 4 : 0;
-    if (data_bytes < parked_bytes) data_bytes = parked_bytes;
-    const uint32_t smem_bytes = data_bytes + 16 * kMaxStages + 64 + 1024;
+    if (data_bytes < m_pad * 256) data_bytes = m_pad * 256;   // bf16 staging of the epilogue: 4 warps x m_pad x 64 B
+    const uint32_t smem_bytes = data_bytes + kControlBytes;
 
     UmmaParams params;
     params.out = static_cast<__nv_bfloat16*>(out);
+    params.exchange = static_cast<float*>(exchange);
     params.status = status;
     params.m = static_cast<uint32_t>(m);
     params.n = static_cast<uint32_t>(n);
     params.m_pad = m_pad;
     params.stages = stages;
     params.data_bytes = data_bytes;
-    params.k_blocks = k_blocks;
+    params.k_blocks = k_blocks_total;
     params.splits = splits;
     params.tmem_columns = 32;
     while (params.tmem_columns < m_pad) params.tmem_columns *= 2;
     params.alpha = alpha;
 
     const cudaError_t attribute_status = cudaFuncSetAttribute(
-        fp8_gemm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
+        gemm_umma_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
     if (attribute_status != cudaSuccess) {
         return attribute_status;
     }
-    return launch_kernel(fp8_gemm_umma_kernel, tiles * splits, kThreads, smem_bytes, stream, splits, weight_map, x_map,
-                         params);
+    return launch_kernel(gemm_umma_kernel<BF16>, tiles * splits, kThreads, smem_bytes, stream, splits, weight_map,
+                         x_map, params);
+}
+
+}  // namespace
+
+cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                 size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,
+                                 unsigned int* status) {
+    return launch_umma<false>(stream, x, weight, out, m, n, k, alpha, exchange, exchange_bytes, status);
+}
+
+cudaError_t launch_bf16_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                  size_t n, size_t k, void* exchange, size_t exchange_bytes, unsigned int* status) {
+    return launch_umma<true>(stream, x, weight, out, m, n, k * 2, 1.0f, exchange, exchange_bytes, status);
 }
 
 }  // namespace lfm25

@@ -70,8 +70,12 @@ cudaError_t launch_fp8_gemm_generic(cudaStream_t stream, const void* x, const vo
                                     size_t n, size_t k, float alpha);
 
 bool fp8_gemm_umma_supports(size_t m, size_t n, size_t k);
+// `exchange` (may be null: K is then not split) is scratch for split-K partial tiles, owned by the caller and
+// used by one stream at a time; kUmmaExchangeBytes covers every supported shape.
+constexpr size_t kUmmaExchangeBytes = 148u * 256u * 128u * 4u;
 cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
-                                 size_t n, size_t k, float alpha, unsigned int* status);
+                                 size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,
+                                 unsigned int* status);
 
 cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids, const void* table, void* out,
                                   size_t num_tokens, size_t vocab_size, size_t hidden);
@@ -89,6 +93,10 @@ cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uin
                                    const uint32_t* request_slots, const uint32_t* block_tables, const uint32_t* sampled,
                                    int64_t* physical_slots, size_t num_tokens, size_t block_table_stride,
                                    size_t block_table_rows, size_t num_pages, bool advance);
+
+bool bf16_gemm_umma_supports(size_t m, size_t n, size_t k);
+cudaError_t launch_bf16_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                  size_t n, size_t k, void* exchange, size_t exchange_bytes, unsigned int* status);
 
 // Stores `message` as the calling thread's last error (what lfm25_last_error() returns) and returns `code`.
 int32_t report_error(int32_t code, const char* message);

@@ -89,11 +89,11 @@ def test_paths_agree_bit_for_bit_on_exact_sums(device, monkeypatch):
     assert np.array_equal(results[0], oracle.linear_fp8(x, w, 0.25))
 
 
-@pytest.mark.parametrize("m", [16, 128, 256])
-@pytest.mark.parametrize("n,k", [(2048, 8192), (256, 4096), (16384, 2048)])
+@pytest.mark.parametrize("m", [16, 100, 128, 256])
+@pytest.mark.parametrize("n,k", [(2048, 8192), (256, 4096), (16384, 2048), (6144, 2048)])
 def test_blaslt_handle_split_k(device, m, n, k):
-    """The handle's workspace lets Down-shaped problems split K across CTAs; the workspace must come back zeroed,
-    so calling twice (and then a different problem) has to keep giving the right answer."""
+    """The handle's exchange buffer lets problems with few weight tiles split K over a cluster of CTAs; calling
+    repeatedly (and then the handle-free entry point, which never splits) has to keep giving the right answer."""
     blaslt = ops.BlasLt()
     assert blaslt.workspace_size() == 32 * 1024 * 1024
     _, x_codes, w_codes, (_, xd), (_, wd) = quantised_problem(m + n + k, m, n, k)

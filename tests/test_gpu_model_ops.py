@@ -129,7 +129,8 @@ def test_step_metadata_on_device(device):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (128, 512, 2048), (7, 6144, 2048), (128, 2048, 8192)])
-def test_bf16_linear_through_cublaslt(device, m, n, k):
+def test_bf16_linear_through_cublaslt(device, monkeypatch, m, n, k):
+    monkeypatch.setenv("LFM25_BF16_GEMM", "cublaslt")
     rng = np.random.default_rng(m + n)
     x = workloads.bf16_normal(rng, (m, k))
     weight = workloads.bf16_normal(rng, (n, k), std=0.02)
@@ -137,4 +138,21 @@ def test_bf16_linear_through_cublaslt(device, m, n, k):
     out = torch.zeros((m, n), dtype=torch.bfloat16, device=device)
     blaslt.linear_bf16(to_bf16(x, device), to_bf16(weight, device), out)
     assert_close_bf16(bits_of(out), oracle.linear_bf16(x, weight), 2e-3, 2 ** -7)
+    blaslt.close()
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (128, 512, 2048), (7, 6144, 2048), (128, 2048, 8192),
+                                   (33, 16384, 2048), (256, 2048, 2048), (128, 65536, 2048)])
+def test_bf16_linear_through_tcgen05(device, monkeypatch, m, n, k):
+    """The BF16 sites of the step through this library's tcgen05 kernel (fp32 accumulation, one rounding)."""
+    monkeypatch.setenv("LFM25_BF16_GEMM", "umma")
+    rng = np.random.default_rng(m + n + 1)
+    x = workloads.bf16_normal(rng, (m, k))
+    weight = workloads.bf16_normal(rng, (n, k), std=0.02)
+    blaslt = ops.BlasLt()
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device=device)
+    blaslt.linear_bf16(to_bf16(x, device), to_bf16(weight, device), out)
+    torch.cuda.synchronize()
+    assert_close_bf16(bits_of(out), oracle.linear_bf16(x, weight), 2e-3, 2 ** -7)
+    assert not ops.device_status()[0]
     blaslt.close()
