@@ -613,12 +613,13 @@ def run_step_arm(arguments, rank, world):
             cpu_tokens, _, cpu_description, threads = step_cpu_sample(model, batch, token_ids, use_fp8,
                                                                       arguments.cpu_sequences or 4, 2)
         per_step = {name: ops_count // profile_steps for name, (_, ops_count) in regions.items()}
-        bf16_down = sum(1 for layer in model.layers if not (use_fp8 and layer.linears["down"].codes is not None))
-        # kernels of this library per step: attention (+ merge), append, quantise/SiLU + FP8 GEMM, SiLU of the
-        # BF16 Down sites, and the small ops; the BF16 GEMMs themselves are cuBLASLt launches
-        launches = (per_step["attention"] * 2 + per_step["append"] + per_step["fp8_linear"] * 2 + bf16_down +
-                    per_step["other"])
-        library_launches = per_step["bf16_linear"]
+        # GPU kernels per step, counted from the captured graph; the BF16 GEMMs of batches above 32 rows are
+        # cuBLASLt's kernels (one per call), everything else is this library's
+        graph_kernels = executor.graph_kernels()
+        forced = os.environ.get("LFM25_BF16_GEMM")
+        through_library = forced == "cublaslt" or (forced != "umma" and STEP_SEQUENCES > 32)
+        library_launches = per_step["bf16_linear"] if through_library else 0
+        launches = graph_kernels - library_launches
         line = {
             "metric": STEP_METRIC, "value": STEP_SEQUENCES * steps * world / (total_ms * 1e-3), "unit": "tok/s",
             "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": total_ms / steps,

@@ -200,6 +200,11 @@ typedef struct lfm25_fused_ragged_decode_launch {
     size_t block_table_stride;
     lfm25_slice partials;      /* f32 [num_tokens, 32, num_splits, 66] when num_splits > 1 */
     size_t num_splits;
+    /* Extension (no counterpart in the reference's launch struct): elements between consecutive tokens of
+     * query_raw and of key_raw / value_raw, for projections that one packed GEMM wrote side by side
+     * ([num_tokens, 3072] = q | k | v).  0 = dense (2048 and 512). */
+    size_t query_token_stride;
+    size_t kv_token_stride;
 } lfm25_fused_ragged_decode_launch;
 int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
                                                             const lfm25_fused_ragged_decode_launch* launch);
@@ -289,6 +294,12 @@ int32_t lfm25_rms_norm_bf16(void* stream, lfm25_slice x, lfm25_slice weight, lfm
 int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
                                      lfm25_slice residual_out, lfm25_slice normalized_out, size_t rows,
                                      size_t hidden_size, float eps);
+/* residual_rms_norm_bf16 (kernels/rms_norm.cu:364-463) and quantize_bf16_e4m3 (kernels/fp8_quantize.cu:9-45) of
+ * its normalised output in one launch, for a norm whose consumer is an FP8 linear: codes_out (u8 [rows, hidden]) =
+ * cvt.rn.satfinite.e4m3(float(normalized_out) * scale), bit-identical to the two launches. */
+int32_t lfm25_residual_rms_norm_bf16_e4m3(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
+                                          lfm25_slice residual_out, lfm25_slice normalized_out, lfm25_slice codes_out,
+                                          size_t rows, size_t hidden_size, float eps, float scale);
 /* Replaces short_conv_segmented_lfm2_bf16 (kernels/short_conv.cu:100-143) for decode (one token per segment):
  * projected [T, 3*hidden] = (b | c | x), weight [hidden, 3], states [request_slots, hidden, 2] updated in place. */
 int32_t lfm25_short_conv_decode_bf16(void* stream, lfm25_slice projected, lfm25_slice weight, lfm25_slice states,
@@ -348,6 +359,8 @@ typedef struct lfm25_layer {
     const void* conv_kernel;          /* bf16 [2048, 3] */
     lfm25_linear_weights conv_output; /* [2048, 2048] */
     void* conv_state;                 /* bf16 [request_slots, 2048, 2] */
+    /* When the BF16 query, key and value matrices are adjacent in memory in this order (one [3072, 2048]
+     * allocation) the executor computes the three projections with one GEMM. */
     lfm25_linear_weights query;       /* [2048, 2048] */
     lfm25_linear_weights key;         /* [512, 2048] */
     lfm25_linear_weights value;       /* [512, 2048] */
@@ -388,6 +401,9 @@ int32_t lfm25_decode_executor_forward(lfm25_decode_executor* executor, const lfm
  * launches ~170 kernels and synchronises the host every step (src/engine/serving/radix_owner.rs:230-259). */
 int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* executor, const lfm25_model* model,
                                          const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance);
+/* Kernel nodes of the CUDA graph that the last lfm25_decode_executor_step_graph call replayed (0 before the first
+ * replay): the number of GPU kernels one step launches, this library's and cuBLASLt's together. */
+size_t lfm25_decode_executor_graph_kernels(const lfm25_decode_executor* executor);
 /* Opt-in region timing of eager steps (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): while
  * enabled, every op of lfm25_decode_executor_forward is bracketed by CUDA events.  A call with region_ms != NULL
  * synchronises, returns the milliseconds and op counts accumulated per region since the last collection, and then

@@ -119,7 +119,8 @@ FP8_SCALE_BLOCK32 = 1
 FusedRaggedDecodeLaunch = _launch_struct("FusedRaggedDecodeLaunch", [
     "#page_size", "query_raw", "key_raw", "value_raw", "query_norm", "key_norm", "inv_freq", "key_cache",
     "value_cache", "position_ids", "slot_mapping", "output", "#num_tokens", "#num_pages", ("eps", ctypes.c_float),
-    "block_tables", "request_slots", "#block_table_stride", "partials", "#num_splits"])
+    "block_tables", "request_slots", "#block_table_stride", "partials", "#num_splits", "#query_token_stride",
+    "#kv_token_stride"])
 
 # name -> (restype, argtypes); every symbol that include/lfm25_b200.h declares
 PROTOTYPES = {
@@ -150,11 +151,15 @@ PROTOTYPES = {
     "lfm25_rms_norm_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, ctypes.c_float]),
     "lfm25_residual_rms_norm_bf16": (
         ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, _size, _size, ctypes.c_float]),
+    "lfm25_residual_rms_norm_bf16_e4m3": (
+        ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, Slice, _size, _size, ctypes.c_float,
+                         ctypes.c_float]),
     "lfm25_short_conv_decode_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_argmax_rows_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
     "lfm25_decode_step_metadata": (ctypes.c_int32, [_stream, _P(DecodeBatch), Slice, _size, ctypes.c_uint32]),
     "lfm25_decode_executor_create": (ctypes.c_int32, [ctypes.c_void_p, _size, _P(ctypes.c_void_p)]),
     "lfm25_decode_executor_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_decode_executor_graph_kernels": (ctypes.c_size_t, [ctypes.c_void_p]),
     "lfm25_decode_executor_forward": (
         ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
     "lfm25_decode_executor_step_graph": (

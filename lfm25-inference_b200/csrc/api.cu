@@ -411,6 +411,19 @@ int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
     }
     size_t kv_required = 0;
     LFM25_ENSURE(checked_mul(l.num_tokens, 8 * 64, &kv_required), LFM25_ERR_OVERFLOW, "fused KV storage overflow");
+    const size_t query_stride = l.query_token_stride == 0 ? 32 * 64 : l.query_token_stride;
+    const size_t kv_stride = l.kv_token_stride == 0 ? 8 * 64 : l.kv_token_stride;
+    LFM25_ENSURE(query_stride >= 32 * 64 && kv_stride >= 8 * 64 && query_stride % 2 == 0 && kv_stride % 2 == 0,
+                 LFM25_ERR_INVALID_ARGUMENT, "fused token strides must be even and at least 2048 / 512 elements");
+    if (l.num_tokens > 0) {
+        size_t query_required = 0;
+        LFM25_ENSURE(checked_mul(l.num_tokens - 1, query_stride, &query_required) &&
+                         checked_mul(l.num_tokens - 1, kv_stride, &kv_required),
+                     LFM25_ERR_OVERFLOW, "fused strided storage overflow");
+        query_required += 32 * 64;
+        kv_required += 8 * 64;
+        LFM25_ENSURE(l.query_raw.len >= query_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused Q storage too small");
+    }
     LFM25_ENSURE(l.key_raw.len >= kv_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused K storage too small");
     LFM25_ENSURE(l.value_raw.len >= kv_required, LFM25_ERR_BUFFER_TOO_SMALL, "fused V storage too small");
     LFM25_ENSURE(l.query_norm.len >= 64, LFM25_ERR_BUFFER_TOO_SMALL, "query norm weight too small");
@@ -453,6 +466,8 @@ int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
     args.inv_freq = static_cast<const float*>(l.inv_freq.ptr);
     args.slot_mapping = static_cast<const int64_t*>(l.slot_mapping.ptr);
     args.eps = l.eps;
+    args.query_token_stride = query_stride;
+    args.kv_token_stride = kv_stride;
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
     return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
                        "fused ragged decode launch failed");
@@ -570,9 +585,11 @@ int32_t lfm25_rms_norm_bf16(void* stream, lfm25_slice x, lfm25_slice weight, lfm
                        "rms_norm launch failed");
 }
 
-int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
-                                     lfm25_slice residual_out, lfm25_slice normalized_out, size_t rows,
-                                     size_t hidden_size, float eps) {
+namespace {
+
+int32_t residual_rms_norm(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
+                          lfm25_slice residual_out, lfm25_slice normalized_out, const lfm25_slice* codes_out,
+                          size_t rows, size_t hidden_size, float eps, float scale) {
     LFM25_ENSURE(rows > 0 && hidden_size > 0, LFM25_ERR_INVALID_ARGUMENT,
                  "residual rms_norm requires non-empty dimensions");
     LFM25_ENSURE(hidden_size % 2 == 0, LFM25_ERR_UNSUPPORTED, "residual rms_norm requires an even hidden size");
@@ -585,10 +602,34 @@ int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_s
     LFM25_ENSURE(weight.len >= hidden_size, LFM25_ERR_BUFFER_TOO_SMALL, "residual rms_norm weight storage too small");
     LFM25_ENSURE(residual.ptr && update.ptr && weight.ptr && residual_out.ptr && normalized_out.ptr,
                  LFM25_ERR_NULL_POINTER, "residual rms_norm received a null device pointer");
+    if (codes_out != nullptr) {
+        LFM25_ENSURE(codes_out->ptr != nullptr, LFM25_ERR_NULL_POINTER, "residual rms_norm codes output is null");
+        LFM25_ENSURE(codes_out->len >= required, LFM25_ERR_BUFFER_TOO_SMALL,
+                     "residual rms_norm codes storage too small");
+        LFM25_ENSURE(std::isfinite(scale) && scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                     "FP8 quantize scale must be finite and positive");
+    }
     return cuda_result(
         lfm25::launch_residual_rms_norm_bf16(static_cast<cudaStream_t>(stream), residual.ptr, update.ptr, weight.ptr,
-                                             residual_out.ptr, normalized_out.ptr, rows, hidden_size, eps),
+                                             residual_out.ptr, normalized_out.ptr, rows, hidden_size, eps,
+                                             codes_out != nullptr ? codes_out->ptr : nullptr, scale),
         "residual rms_norm launch failed");
+}
+
+}  // namespace
+
+int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
+                                     lfm25_slice residual_out, lfm25_slice normalized_out, size_t rows,
+                                     size_t hidden_size, float eps) {
+    return residual_rms_norm(stream, residual, update, weight, residual_out, normalized_out, nullptr, rows,
+                             hidden_size, eps, 1.0f);
+}
+
+int32_t lfm25_residual_rms_norm_bf16_e4m3(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
+                                          lfm25_slice residual_out, lfm25_slice normalized_out, lfm25_slice codes_out,
+                                          size_t rows, size_t hidden_size, float eps, float scale) {
+    return residual_rms_norm(stream, residual, update, weight, residual_out, normalized_out, &codes_out, rows,
+                             hidden_size, eps, scale);
 }
 
 int32_t lfm25_short_conv_decode_bf16(void* stream, lfm25_slice projected, lfm25_slice weight, lfm25_slice states,
@@ -711,15 +752,15 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
     LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear weight storage too small");
     LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear output storage too small");
     LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "linear received a null device pointer");
-    // Batches of up to 16 rows go to this library's tcgen05 kernel where it supports the shape (N % 128 == 0,
+    // Batches of up to 32 rows go to this library's tcgen05 kernel where it supports the shape (N % 128 == 0,
     // K % 64 == 0): with programmatic dependent launch and the weight prefetch it is ahead of cuBLASLt there
-    // (measured on the whole step: 12 % at 1 row, 8 % at 8 rows), and behind it from 32 rows on.
+    // (measured on the whole step: 12 % at 1 row, 8 % at 8 rows, 2 % at 32 rows), and behind it at 128 rows.
     // LFM25_BF16_GEMM = umma | cublaslt forces one of the two (for measurements).
     const char* bf16_path = getenv("LFM25_BF16_GEMM");
     const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
                            reinterpret_cast<uintptr_t>(out.ptr)) &
                           15) == 0;
-    bool own_kernel = m <= 16;
+    bool own_kernel = m <= 32;
     if (bf16_path != nullptr && strcmp(bf16_path, "umma") == 0) own_kernel = true;
     if (bf16_path != nullptr && strcmp(bf16_path, "cublaslt") == 0) own_kernel = false;
     if (own_kernel && aligned && lfm25::bf16_gemm_umma_supports(m, n, k)) {

@@ -51,6 +51,8 @@ struct AttentionParams {
     uint32_t num_tokens;
     uint32_t num_pages;
     uint32_t num_splits;  // 1: write normalised output; >1: write split records
+    uint32_t query_token_stride;  // elements between tokens of `query` (2048 when dense)
+    uint32_t kv_token_stride;     // elements between tokens of key_raw / value_raw (512 when dense)
     // fused mode only: the raw projections of the step and what is needed to turn them into the new cache row
     const __nv_bfloat16* key_raw;     // [T, 8, 64]
     const __nv_bfloat16* value_raw;   // [T, 8, 64]
@@ -194,7 +196,8 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         qa[ks][1] = 0;
     }
     if (group < kQPerKv) {
-        const __nv_bfloat16* q_row = p.query + (static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + group) * kHeadDim;
+        const __nv_bfloat16* q_row =
+            p.query + static_cast<size_t>(token) * p.query_token_stride + (kv_head * kQPerKv + group) * kHeadDim;
 #pragma unroll
         for (uint32_t ks = 0; ks < 4; ++ks) {
             qa[ks][0] = *reinterpret_cast<const uint32_t*>(q_row + ks * 16 + quad * 2);
@@ -264,7 +267,7 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     __nv_bfloat16 new_key0, new_key1;
     uint32_t new_value = 0;
     if (owns_new_row) {
-        const size_t source = (static_cast<size_t>(token) * kKvHeads + kv_head) * kHeadDim;
+        const size_t source = static_cast<size_t>(token) * p.kv_token_stride + kv_head * kHeadDim;
         float sin_value, cos_value;
         sincosf(static_cast<float>(position) * p.inv_freq[lane], &sin_value, &cos_value);
         norm_rope(__bfloat162float(p.key_raw[source + lane]), __bfloat162float(p.key_raw[source + lane + kHalfDim]),
@@ -544,6 +547,8 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.num_tokens = static_cast<uint32_t>(launch.num_tokens);
     params.num_pages = static_cast<uint32_t>(launch.num_pages);
     params.num_splits = launch.num_splits;
+    params.query_token_stride = static_cast<uint32_t>(launch.query_token_stride);
+    params.kv_token_stride = static_cast<uint32_t>(launch.kv_token_stride);
     params.key_raw = static_cast<const __nv_bfloat16*>(launch.key_raw);
     params.value_raw = static_cast<const __nv_bfloat16*>(launch.value_raw);
     params.query_norm = static_cast<const __nv_bfloat16*>(launch.query_norm);

@@ -61,7 +61,9 @@ struct lfm25_decode_executor {
         const void* token_ids = nullptr;
         bool warmed = false;
         cudaGraphExec_t exec = nullptr;
+        size_t kernel_nodes = 0;
     } captured[8];
+    size_t last_graph_kernel_nodes = 0;   // of the graph launched most recently
 };
 
 namespace {
@@ -108,13 +110,16 @@ lfm25_slice slice_of(const void* pointer, size_t elements) {
 
 // linear_decode_into (src/model/decode_executor.rs:78-124): FP8 when the site is promoted and FP8 is on
 // (quantise the activation with the site's static scale, then the E4M3 GEMM with alpha = d_x * d_w), else BF16.
+// `prequantized`: fp8_input already holds the codes of `input` (the producing norm wrote them).
 int32_t linear_decode(lfm25_decode_executor* self, const lfm25_linear_weights& weights, const void* input,
-                      void* output, size_t rows, bool use_fp8) {
+                      void* output, size_t rows, bool use_fp8, bool prequantized = false) {
     if (use_fp8 && weights.fp8.data != nullptr) {
         RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
-        LFM25_TRY(lfm25_quantize_bf16_e4m3(self->blaslt->stream, slice_of(input, rows * weights.k),
-                                           slice_of(self->fp8_input, self->maximum_tokens * kFfn), rows * weights.k,
-                                           weights.fp8.activation_quantize));
+        if (!prequantized) {
+            LFM25_TRY(lfm25_quantize_bf16_e4m3(self->blaslt->stream, slice_of(input, rows * weights.k),
+                                               slice_of(self->fp8_input, self->maximum_tokens * kFfn),
+                                               rows * weights.k, weights.fp8.activation_quantize));
+        }
         lfm25_fp8_linear_config config;
         config.m = rows;
         config.n = weights.n;
@@ -165,9 +170,27 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             LFM25_TRY(linear_decode(self, layer.conv_output, self->post_operator, self->operator_output, tokens,
                                     use_fp8));
         } else {
-            LFM25_TRY(linear_decode(self, layer.query, self->normalized, self->query, tokens, use_fp8));
-            LFM25_TRY(linear_decode(self, layer.key, self->normalized, self->key, tokens, use_fp8));
-            LFM25_TRY(linear_decode(self, layer.value, self->normalized, self->value, tokens, use_fp8));
+            const char* fused_switch = getenv("LFM25_FUSED_APPEND");
+            const bool fused_append = fused_switch == nullptr || strcmp(fused_switch, "0") != 0;
+            // One GEMM for the three projections when their BF16 matrices are adjacent in memory (q | k | v rows of
+            // one [3072, 2048] allocation): the outputs then sit side by side in `wide`, [tokens, 3072], which only
+            // the one-kernel attention reads (it takes token strides).
+            const uint16_t* query_weight = static_cast<const uint16_t*>(layer.query.bf16);
+            const bool packed_qkv = fused_append && query_weight != nullptr &&
+                                    !(use_fp8 && (layer.query.fp8.data || layer.key.fp8.data || layer.value.fp8.data)) &&
+                                    layer.key.bf16 == query_weight + kQueryWidth * kHidden &&
+                                    layer.value.bf16 == query_weight + (kQueryWidth + kKvWidth) * kHidden &&
+                                    layer.query.k == kHidden && layer.key.k == kHidden && layer.value.k == kHidden;
+            constexpr size_t kPackedWidth = kQueryWidth + 2 * kKvWidth;
+            if (packed_qkv) {
+                lfm25_linear_weights packed = layer.query;
+                packed.n = kPackedWidth;
+                LFM25_TRY(linear_decode(self, packed, self->normalized, self->wide, tokens, false));
+            } else {
+                LFM25_TRY(linear_decode(self, layer.query, self->normalized, self->query, tokens, use_fp8));
+                LFM25_TRY(linear_decode(self, layer.key, self->normalized, self->key, tokens, use_fp8));
+                LFM25_TRY(linear_decode(self, layer.value, self->normalized, self->value, tokens, use_fp8));
+            }
             const size_t cache_elements = model->num_pages * 8 * 16 * 64;
             lfm25_qk_postprocess_launch post;
             post.page_size = 16;
@@ -185,8 +208,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             post.num_pages = model->num_pages;
             post.eps = model->norm_eps;
             const size_t splits = lfm25_splitk_decode_splits(tokens, batch->max_context_tokens, 16);
-            const char* fused_switch = getenv("LFM25_FUSED_APPEND");
-            if (fused_switch == nullptr || strcmp(fused_switch, "0") != 0) {
+            if (fused_append) {
                 // one launch: QK-norm + RoPE + paged append + attention (+ merge when split)
                 RegionTimer timer(self, LFM25_REGION_ATTENTION);
                 lfm25_fused_ragged_decode_launch fused;
@@ -210,6 +232,17 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 fused.block_table_stride = batch->block_table_stride;
                 fused.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_tokens));
                 fused.num_splits = splits;
+                fused.query_token_stride = 0;
+                fused.kv_token_stride = 0;
+                if (packed_qkv) {
+                    uint16_t* packed_rows = static_cast<uint16_t*>(self->wide);
+                    const size_t span = (tokens - 1) * kPackedWidth;
+                    fused.query_raw = slice_of(packed_rows, span + kQueryWidth);
+                    fused.key_raw = slice_of(packed_rows + kQueryWidth, span + kKvWidth);
+                    fused.value_raw = slice_of(packed_rows + kQueryWidth + kKvWidth, span + kKvWidth);
+                    fused.query_token_stride = kPackedWidth;
+                    fused.kv_token_stride = kPackedWidth;
+                }
                 LFM25_TRY(lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(stream, &fused));
             } else {
             {
@@ -254,15 +287,18 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             LFM25_TRY(linear_decode(self, layer.output, self->post_operator, self->operator_output, tokens, use_fp8));
         }
 
+        // the norm in front of an FP8 Gate/Up also writes the E4M3 codes the GEMM reads (one launch less)
+        const bool gate_up_fp8 = use_fp8 && layer.gate_up.fp8.data != nullptr && layer.gate_up.k == kHidden;
         {
             RegionTimer timer(self, LFM25_REGION_OTHER);
-            status = lfm25::launch_residual_rms_norm_bf16(stream, self->hidden, self->operator_output, layer.ffn_norm,
-                                                          self->post_operator, self->normalized, tokens, kHidden,
-                                                          model->norm_eps);
+            status = lfm25::launch_residual_rms_norm_bf16(
+                stream, self->hidden, self->operator_output, layer.ffn_norm, self->post_operator, self->normalized,
+                tokens, kHidden, model->norm_eps, gate_up_fp8 ? self->fp8_input : nullptr,
+                gate_up_fp8 ? layer.gate_up.fp8.activation_quantize : 1.0f);
         }
         if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
 
-        LFM25_TRY(linear_decode(self, layer.gate_up, self->normalized, self->wide, tokens, use_fp8));
+        LFM25_TRY(linear_decode(self, layer.gate_up, self->normalized, self->wide, tokens, use_fp8, gate_up_fp8));
         if (use_fp8 && layer.down.fp8.data != nullptr) {
             RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
             LFM25_TRY(lfm25_silu_mul_packed_bf16_to_e4m3(stream, slice_of(self->wide, tokens * 2 * kFfn),
@@ -290,13 +326,15 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                                                kFfn));
         }
 
-        const void* next_norm =
-            index + 1 < model->num_layers ? model->layers[index + 1].operator_norm : model->final_norm;
+        const bool last_layer = index + 1 == model->num_layers;
+        const void* next_norm = last_layer ? model->final_norm : model->layers[index + 1].operator_norm;
+        const bool head_fp8 = last_layer && use_fp8 && model->lm_head_fp8.data != nullptr;
         {
             RegionTimer timer(self, LFM25_REGION_OTHER);
-            status = lfm25::launch_residual_rms_norm_bf16(stream, self->post_operator, self->operator_output,
-                                                          next_norm, self->hidden, self->normalized, tokens, kHidden,
-                                                          model->norm_eps);
+            status = lfm25::launch_residual_rms_norm_bf16(
+                stream, self->post_operator, self->operator_output, next_norm, self->hidden, self->normalized, tokens,
+                kHidden, model->norm_eps, head_fp8 ? self->fp8_input : nullptr,
+                head_fp8 ? model->lm_head_fp8.activation_quantize : 1.0f);
         }
         if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
     }
@@ -307,7 +345,8 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
     head.fp8 = model->lm_head_fp8;
     head.n = kVocab;
     head.k = kHidden;
-    LFM25_TRY(linear_decode(self, head, self->normalized, self->logits, tokens, use_fp8));
+    LFM25_TRY(linear_decode(self, head, self->normalized, self->logits, tokens, use_fp8,
+                            use_fp8 && model->lm_head_fp8.data != nullptr));
     {
         RegionTimer timer(self, LFM25_REGION_OTHER);
         status = lfm25::launch_argmax_rows_bf16(stream, self->logits, self->sampled, tokens, kVocab);
@@ -519,13 +558,30 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
             return rc;
         }
         if (status != cudaSuccess) return cuda_failure(status, "stream capture failed");
+        size_t node_count = 0;
+        if (cudaGraphGetNodes(graph, nullptr, &node_count) == cudaSuccess && node_count > 0) {
+            std::vector<cudaGraphNode_t> nodes(node_count);
+            if (cudaGraphGetNodes(graph, nodes.data(), &node_count) == cudaSuccess) {
+                for (size_t node = 0; node < node_count; ++node) {
+                    cudaGraphNodeType type;
+                    if (cudaGraphNodeGetType(nodes[node], &type) == cudaSuccess && type == cudaGraphNodeTypeKernel) {
+                        ++entry->kernel_nodes;
+                    }
+                }
+            }
+        }
         status = cudaGraphInstantiate(&entry->exec, graph, 0);
         cudaGraphDestroy(graph);
         if (status != cudaSuccess) return cuda_failure(status, "graph instantiation failed");
     }
     const cudaError_t status = cudaGraphLaunch(entry->exec, stream);
     if (status != cudaSuccess) return cuda_failure(status, "graph launch failed");
+    self->last_graph_kernel_nodes = entry->kernel_nodes;
     return LFM25_OK;
+}
+
+size_t lfm25_decode_executor_graph_kernels(const lfm25_decode_executor* self) {
+    return self != nullptr ? self->last_graph_kernel_nodes : 0;
 }
 
 }  // extern "C"

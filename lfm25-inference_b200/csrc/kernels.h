@@ -31,6 +31,8 @@ struct AttentionLaunch {
     const float* inv_freq = nullptr;    // f32 [32]
     const int64_t* slot_mapping = nullptr;
     float eps = 0.0f;
+    size_t query_token_stride = 32 * 64;   // elements between tokens of `query`
+    size_t kv_token_stride = 8 * 64;       // elements between tokens of key_raw / value_raw
 };
 cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionLaunch& launch);
 
@@ -81,9 +83,11 @@ cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids
                                   size_t num_tokens, size_t vocab_size, size_t hidden);
 cudaError_t launch_rms_norm_bf16(cudaStream_t stream, const void* x, const void* weight, void* out, size_t rows,
                                  size_t hidden, float eps);
+// `codes` (optional): the normalised rows also as E4M3 with multiplier `code_scale`, bit-identical to quantising
+// `normalized_out` afterwards.
 cudaError_t launch_residual_rms_norm_bf16(cudaStream_t stream, const void* residual, const void* update,
                                           const void* weight, void* residual_out, void* normalized_out, size_t rows,
-                                          size_t hidden, float eps);
+                                          size_t hidden, float eps, void* codes = nullptr, float code_scale = 1.0f);
 cudaError_t launch_short_conv_decode(cudaStream_t stream, const void* projected, const void* weight, void* states,
                                      const uint32_t* request_slots, void* output, size_t num_tokens, size_t hidden,
                                      size_t num_request_slots);

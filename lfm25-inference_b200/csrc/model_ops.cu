@@ -68,11 +68,14 @@ embedding_kernel(const uint32_t* __restrict__ token_ids, const __nv_bfloat16* __
 // RESIDUAL == false: out = bf16(bf16(x * inv_rms) * weight)                    (kernels/rms_norm.cu:268-278)
 // RESIDUAL == true : r = bf16(residual + update) stored to residual_out; the variance uses the unrounded fp32
 //                    sums; out = bf16(float(r) * inv_rms * float(weight))       (kernels/rms_norm.cu:394-453)
+// `codes` (may be null): the normalised row again as E4M3, code = cvt.rn.satfinite(float(out) * code_scale) -- what
+// quantize_bf16_e4m3 would produce from `out` -- for a consumer that is an FP8 linear.
 template <bool RESIDUAL>
 __global__ void __launch_bounds__(kRowThreads)
 rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ update,
                 const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ residual_out,
-                __nv_bfloat16* __restrict__ out, size_t rows, size_t hidden, float eps) {
+                __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ codes, float code_scale, size_t rows,
+                size_t hidden, float eps) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[8];
@@ -110,6 +113,14 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
             result = __hmul2(__floats2bfloat162_rn(value.x * inv_rms, value.y * inv_rms), scale);
         }
         *reinterpret_cast<__nv_bfloat162*>(out + row * hidden + index) = result;
+        if (codes != nullptr) {
+            const float2 rounded = __bfloat1622float2(result);
+            uint16_t pair;
+            asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;"
+                : "=h"(pair)
+                : "f"(rounded.x * code_scale), "f"(rounded.y * code_scale));
+            *reinterpret_cast<uint16_t*>(codes + row * hidden + index) = pair;
+        }
     }
 }
 
@@ -258,16 +269,16 @@ cudaError_t launch_rms_norm_bf16(cudaStream_t stream, const void* x, const void*
                                  size_t hidden, float eps) {
     return launch_kernel(rms_norm_kernel<false>, static_cast<unsigned int>(rows), kRowThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(weight), nullptr,
-        static_cast<__nv_bfloat16*>(out), rows, hidden, eps);
+        static_cast<__nv_bfloat16*>(out), static_cast<uint8_t*>(nullptr), 1.0f, rows, hidden, eps);
 }
 
 cudaError_t launch_residual_rms_norm_bf16(cudaStream_t stream, const void* residual, const void* update,
                                           const void* weight, void* residual_out, void* normalized_out, size_t rows,
-                                          size_t hidden, float eps) {
+                                          size_t hidden, float eps, void* codes, float code_scale) {
     return launch_kernel(rms_norm_kernel<true>, static_cast<unsigned int>(rows), kRowThreads, 0, stream, 1, 
         static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(update),
         static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(residual_out),
-        static_cast<__nv_bfloat16*>(normalized_out), rows, hidden, eps);
+        static_cast<__nv_bfloat16*>(normalized_out), static_cast<uint8_t*>(codes), code_scale, rows, hidden, eps);
 }
 
 cudaError_t launch_short_conv_decode(cudaStream_t stream, const void* projected, const void* weight, void* states,

@@ -78,7 +78,11 @@ class LayerState:
 class RandomModel:
     """Random-init weights of the architecture plus per-layer caches, resident on `device`."""
 
-    def __init__(self, seed: int, device, num_pages: int, num_request_slots: int, fp8_policy: bool = True):
+    def __init__(self, seed: int, device, num_pages: int, num_request_slots: int, fp8_policy: bool = True,
+                 pack_qkv: bool = True):
+        """`pack_qkv`: the query, key and value matrices of a layer share one [3072, 2048] allocation (as a loader
+        that concatenates them would leave them), which lets the executor run the three projections as one GEMM;
+        False keeps three separate allocations (three GEMMs, the reference's layout)."""
         self.device = device
         self.num_pages = num_pages
         self.num_request_slots = num_request_slots
@@ -99,9 +103,15 @@ class RandomModel:
             layer.tensors["operator_norm"] = ones(HIDDEN)
             layer.tensors["ffn_norm"] = ones(HIDDEN)
             if layer.is_attention:
-                layer.linears["query"] = Linear(normal(HIDDEN, HIDDEN))
-                layer.linears["key"] = Linear(normal(KV_WIDTH, HIDDEN))
-                layer.linears["value"] = Linear(normal(KV_WIDTH, HIDDEN))
+                query, key, value = normal(HIDDEN, HIDDEN), normal(KV_WIDTH, HIDDEN), normal(KV_WIDTH, HIDDEN)
+                if pack_qkv:
+                    packed = torch.cat([query, key, value], dim=0).contiguous()
+                    query, key, value = (packed[:HIDDEN], packed[HIDDEN:HIDDEN + KV_WIDTH],
+                                         packed[HIDDEN + KV_WIDTH:])
+                    layer.tensors["qkv_packed"] = packed
+                layer.linears["query"] = Linear(query)
+                layer.linears["key"] = Linear(key)
+                layer.linears["value"] = Linear(value)
                 layer.linears["output"] = Linear(normal(HIDDEN, HIDDEN))
                 layer.tensors["query_norm"] = ones(64)
                 layer.tensors["key_norm"] = ones(64)
@@ -207,6 +217,10 @@ class DecodeExecutor:
         self.blaslt.bind_current_stream()
         check(library().lfm25_decode_executor_step_graph(self._handle, model.struct, batch.struct, int(use_fp8),
                                                          int(advance)))
+
+    def graph_kernels(self) -> int:
+        """GPU kernels per step in the graph that the last step_graph call replayed (0 before the first replay)."""
+        return int(library().lfm25_decode_executor_graph_kernels(self._handle))
 
     REGIONS = ("attention", "append", "fp8_linear", "bf16_linear", "other")
 

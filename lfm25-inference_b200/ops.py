@@ -26,6 +26,16 @@ def _slice(tensor: torch.Tensor) -> Slice:
     return Slice(tensor.data_ptr(), tensor.numel())
 
 
+def _row_strided_slice(tensor: torch.Tensor) -> Slice:
+    """A tensor whose rows (dimension 0) may be spaced apart but are dense inside: the span it covers."""
+    if not tensor.is_cuda:
+        raise Lfm25Error(_abi.ERR_INVALID_ARGUMENT, "tensor is not on a CUDA device")
+    if tensor.shape[0] == 0:
+        return Slice(tensor.data_ptr(), 0)
+    row = tensor[0].numel()
+    return Slice(tensor.data_ptr(), (tensor.shape[0] - 1) * tensor.stride(0) + row)
+
+
 def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
@@ -165,19 +175,25 @@ def fused_ragged_paged_attention_decode_lfm2_bf16_into(query_raw, key_raw, value
                                                        block_table_stride: int, request_slots, eps: float, output,
                                                        partials=None, num_splits: int = 1) -> None:
     """One-kernel decode: QK-norm + RoPE + paged KV append + attention
-    (reference: src/ops/attention_fused.rs:95-153); optionally split over the KV axis."""
+    (reference: src/ops/attention_fused.rs:95-153); optionally split over the KV axis.  The three projections may
+    be row-strided views (columns of one packed [N, 3072] GEMM output); the last two dimensions must be dense."""
     _ensure(query_raw.dim() == 3 and tuple(query_raw.shape[1:]) == (32, 64), "fused query must have shape [N,32,64]")
     num_tokens = query_raw.shape[0]
     _ensure(tuple(key_raw.shape) == (num_tokens, 8, 64), "fused key must have shape [N,8,64]")
     _ensure(tuple(value_raw.shape) == (num_tokens, 8, 64), "fused value must have shape [N,8,64]")
+    for name, tensor in (("query", query_raw), ("key", key_raw), ("value", value_raw)):
+        _ensure(tuple(tensor.stride()[1:]) == (64, 1), f"fused {name} heads must be dense")
+    _ensure(key_raw.stride(0) == value_raw.stride(0), "fused key and value must share their token stride")
     _ensure(block_tables.dim() == 2 and block_tables.shape[1] == block_table_stride,
             "fused block table stride/shape mismatch")
     empty = Slice(None, 0)
     launch = _abi.FusedRaggedDecodeLaunch(
-        arena.page_size, _slice(query_raw), _slice(key_raw), _slice(value_raw), _slice(query_norm), _slice(key_norm),
+        arena.page_size, _row_strided_slice(query_raw), _row_strided_slice(key_raw), _row_strided_slice(value_raw),
+        _slice(query_norm), _slice(key_norm),
         _slice(inv_freq), _slice(arena.key), _slice(arena.value), _slice(position_ids), _slice(slot_mapping),
         _slice(output), num_tokens, arena.num_pages, eps, _slice(block_tables), _slice(request_slots),
-        block_table_stride, _slice(partials) if partials is not None else empty, num_splits)
+        block_table_stride, _slice(partials) if partials is not None else empty, num_splits,
+        query_raw.stride(0) if num_tokens > 1 else 0, key_raw.stride(0) if num_tokens > 1 else 0)
     check(library().lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(_stream(), launch))
 
 
@@ -315,6 +331,15 @@ def residual_rms_norm_bf16_into(residual, update, weight, eps: float, residual_o
     check(library().lfm25_residual_rms_norm_bf16(_stream(), _slice(residual), _slice(update), _slice(weight),
                                                  _slice(residual_out), _slice(normalized_out),
                                                  residual.numel() // hidden, hidden, eps))
+
+
+def residual_rms_norm_bf16_e4m3_into(residual, update, weight, eps: float, residual_out, normalized_out, codes_out,
+                                     scale: float) -> None:
+    """residual_rms_norm_bf16_into plus the E4M3 codes of the normalised rows (multiplier `scale`) in one launch."""
+    hidden = residual.shape[-1]
+    check(library().lfm25_residual_rms_norm_bf16_e4m3(_stream(), _slice(residual), _slice(update), _slice(weight),
+                                                      _slice(residual_out), _slice(normalized_out), _slice(codes_out),
+                                                      residual.numel() // hidden, hidden, eps, scale))
 
 
 def short_conv_decode_bf16_into(projected, weight, states, request_slots, output) -> None:

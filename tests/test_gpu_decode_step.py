@@ -20,10 +20,11 @@ def small_batch(device, seed, tokens, pages, steps):
     return batch, token_ids
 
 
+@pytest.mark.parametrize("pack_qkv", [True, False])
 @pytest.mark.parametrize("use_fp8", [False, True])
-def test_one_step_against_the_oracle(device, use_fp8):
+def test_one_step_against_the_oracle(device, use_fp8, pack_qkv):
     tokens, pages = 3, 32
-    model = lfm_model.RandomModel(3, device, pages, 4)
+    model = lfm_model.RandomModel(3, device, pages, 4, pack_qkv=pack_qkv)
     model.fill_caches(4)
     batch, token_ids = small_batch(device, 3, tokens, pages, 2)
     host = step_oracle.HostModel(model)

@@ -45,21 +45,29 @@ def run_two_kernels(case, device, splits):
     return bits_of(output), bits_of(arena.key), bits_of(arena.value), bits_of(query)
 
 
-def run_fused(case, device, splits, slots=None, sentinel=None):
+def run_fused(case, device, splits, slots=None, sentinel=None, packed=False):
     arena = ops.PagedKvArena(to_bf16(case["key_cache"], device), to_bf16(case["value_cache"], device))
     query = to_bf16(case["query"], device)
+    key, value = to_bf16(case["key"], device), to_bf16(case["value"], device)
+    if packed:
+        # the three projections as columns of one [N, 3072] buffer (what a packed q|k|v GEMM writes)
+        tokens = query.shape[0]
+        rows = torch.cat([query.reshape(tokens, -1), key.reshape(tokens, -1), value.reshape(tokens, -1)], dim=1)
+        query = rows[:, :2048].unflatten(1, (32, 64))
+        key = rows[:, 2048:2560].unflatten(1, (8, 64))
+        value = rows[:, 2560:].unflatten(1, (8, 64))
     batch = case["batch"]
     output = torch.zeros_like(query)
     if sentinel is not None:
         output = torch.zeros(query.shape, dtype=torch.int16, device=device).fill_(sentinel).view(torch.bfloat16)
     partials = torch.empty(ops.splitk_workspace_elements(query.shape[0]), dtype=torch.float32, device=device)
     ops.fused_ragged_paged_attention_decode_lfm2_bf16_into(
-        query, to_bf16(case["key"], device), to_bf16(case["value"], device), to_bf16(case["query_norm"], device),
+        query, key, value, to_bf16(case["query_norm"], device),
         to_bf16(case["key_norm"], device), torch.from_numpy(case["inv_freq"]).to(device),
         to_u32(case["positions"], device), to_i64(case["slots"] if slots is None else slots, device), arena,
         to_u32(batch.block_tables, device), batch.stride, to_u32(batch.request_slots, device), 1e-5, output,
         partials=partials, num_splits=splits)
-    assert np.array_equal(bits_of(query), case["query"])          # the raw query is not modified
+    assert np.array_equal(bits_of(query.contiguous()), case["query"])          # the raw query is not modified
     return bits_of(output), bits_of(arena.key), bits_of(arena.value)
 
 
@@ -78,6 +86,17 @@ def test_fused_equals_two_kernel_route(device, seed, sequences, low, high, pages
         _, exact = oracle.paged_ragged_attention(rotated_query, want_key, want_value, case["batch"].block_tables,
                                                  case["batch"].request_slots, case["positions"], want_exact=True)
         assert_within_oracle(got_output, exact)
+
+
+@pytest.mark.parametrize("splits", [1, 4])
+def test_token_strided_projections(device, splits):
+    """q | k | v side by side in one [N, 3072] buffer give the bits of the dense call."""
+    case = build_case(24, 19, 5, 700, 1024)
+    dense = run_fused(case, device, splits)
+    packed = run_fused(case, device, splits, packed=True)
+    for a, b in zip(packed, dense):
+        assert np.array_equal(a, b)
+    assert ops.device_status()[0] == 0
 
 
 def test_context_of_one_token(device):

@@ -46,6 +46,15 @@ def test_rms_norms(device, rows, hidden):
     assert np.array_equal(bits_of(residual_out), want_residual)
     assert_close_bf16(bits_of(normalized), want_normalized, 1e-6, 2 ** -7)
     assert (bits_of(normalized) != want_normalized).mean() < 0.01
+    # the variant that also emits E4M3 codes: same bf16 outputs, and the codes of quantising them afterwards
+    scale = 448.0 / 6.0
+    residual_fused, normalized_fused = torch.zeros_like(out), torch.zeros_like(out)
+    codes = torch.zeros((rows, hidden), dtype=torch.uint8, device=device)
+    ops.residual_rms_norm_bf16_e4m3_into(to_bf16(x, device), to_bf16(update, device), to_bf16(weight, device), 1e-5,
+                                         residual_fused, normalized_fused, codes, scale)
+    assert np.array_equal(bits_of(residual_fused), bits_of(residual_out))
+    assert np.array_equal(bits_of(normalized_fused), bits_of(normalized))
+    assert np.array_equal(codes.cpu().numpy(), oracle.quantize_bf16_e4m3(bits_of(normalized), scale))
 
 
 def test_short_conv_decode(device):
