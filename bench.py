@@ -157,6 +157,7 @@ def cpu_sample(batch, seed, sequences, repeats):
     Returns (tokens per second, seconds per pass, description)."""
     from lfm25_inference_b200 import workloads
     from oracle import oracle
+    oracle.use_all_cores()
     rng = np.random.default_rng(seed)
     chosen = np.argsort(batch.contexts)[np.linspace(0, batch.num_sequences - 1, sequences).astype(int)]
     tables, positions, pages_total = [], [], 0
@@ -424,6 +425,7 @@ def step_cpu_sample(model, batch, token_ids, use_fp8, sequences, repeats):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import step_oracle
     from oracle import oracle
+    oracle.use_all_cores()
     host = step_oracle.HostModel(model)
     chosen = np.argsort(batch.contexts)[np.linspace(0, batch.num_sequences - 1, sequences).astype(int)]
     positions = batch.positions(0)[chosen]

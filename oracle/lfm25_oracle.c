@@ -703,6 +703,17 @@ void oracle_linear_bf16(const uint16_t* x, const uint16_t* weight, uint16_t* out
     free(x_f32);
 }
 
+/* Sets the OpenMP team size of the following calls (a launcher may have exported OMP_NUM_THREADS=1). */
+void oracle_set_num_threads(int count) {
+#ifdef _OPENMP
+    if (count > 0) {
+        omp_set_num_threads(count);
+    }
+#else
+    (void)count;
+#endif
+}
+
 int oracle_num_threads(void) {
     int count = 1;
 #ifdef _OPENMP

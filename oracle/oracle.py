@@ -74,6 +74,8 @@ def lib() -> ctypes.CDLL:
     handle.oracle_argmax_rows_bf16.argtypes = [_u16p, _u32p, _size, _size]
     handle.oracle_linear_bf16.argtypes = [_u16p, _u16p, _u16p, _size, _size, _size]
     handle.oracle_num_threads.restype = ctypes.c_int
+    handle.oracle_set_num_threads.argtypes = [ctypes.c_int]
+    handle.oracle_set_num_threads.restype = None
     _lib = handle
     return handle
 
@@ -299,3 +301,12 @@ def linear_bf16(x, weight) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores() -> int:
+    """Sizes the OpenMP team to the cores this process may run on (torchrun exports OMP_NUM_THREADS=1 to its
+    ranks); returns the team size."""
+    import os
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(cores)
+    return num_threads()
