@@ -123,9 +123,10 @@ int32_t validate_ragged_common(size_t page_size, const lfm25_slice& query, const
 
 // Validation of Fp8MatmulKey::new + BlasLt::linear_fp8_scaled (src/cuda/blaslt/fp8.rs:23-40,
 // src/cuda/blaslt/mod.rs:222-262), then the choice of kernel:
-//   M <= 8            weight-streaming mma.sync kernel
-//   9 <= M <= 256     tcgen05 / TMEM kernel (K split over a thread-block cluster when there are few tiles)
-//   anything else     generic kernel
+//   M <= 256, N % 128 == 0, K % 128 == 0   tcgen05 / TMEM kernel (K split over a thread-block cluster when there
+//                                          are few tiles and the caller is a handle with an exchange buffer)
+//   M <= 8 otherwise, or few tiles without a handle   weight-streaming mma.sync kernel
+//   anything else                          generic kernel
 // LFM25_FP8_GEMM_PATH = stream | umma | generic overrides the choice where the shape allows (for measurements).
 // `exchange` is the split-K scratch of a BlasLt handle; the handle-free entry point passes null and never splits K.
 int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
@@ -166,11 +167,15 @@ int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weig
                           15) == 0;
     const bool stream_ok = aligned && lfm25::fp8_gemm_stream_supports(m, n, k);
     const bool umma_ok = aligned && lfm25::fp8_gemm_umma_supports(m, n, k);
+    // The tcgen05 kernel is at least as fast as the streaming kernel from M = 1 on once it can occupy the machine
+    // (LM head at M = 1: 24.1 against 29.2 us), i.e. with at least 100 weight tiles or with an exchange buffer to
+    // split K through; without either (few tiles, handle-free call) small batches stay on the streaming kernel.
+    const bool umma_occupies = umma_ok && (n / 128 >= 100 || exchange != nullptr);
     enum { kStream, kUmma, kGeneric } path = kGeneric;
-    if (stream_ok && (m <= 8 || !umma_ok)) {
-        path = kStream;
-    } else if (umma_ok) {
+    if (umma_occupies || (umma_ok && !(stream_ok && m <= 8))) {
         path = kUmma;
+    } else if (stream_ok) {
+        path = kStream;
     }
     if (const char* forced = getenv("LFM25_FP8_GEMM_PATH")) {
         if (strcmp(forced, "stream") == 0 && stream_ok) path = kStream;

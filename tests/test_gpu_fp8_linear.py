@@ -89,7 +89,7 @@ def test_paths_agree_bit_for_bit_on_exact_sums(device, monkeypatch):
     assert np.array_equal(results[0], oracle.linear_fp8(x, w, 0.25))
 
 
-@pytest.mark.parametrize("m", [16, 100, 128, 256])
+@pytest.mark.parametrize("m", [1, 8, 16, 100, 128, 256])
 @pytest.mark.parametrize("n,k", [(2048, 8192), (256, 4096), (16384, 2048), (6144, 2048)])
 def test_blaslt_handle_split_k(device, m, n, k):
     """The handle's exchange buffer lets problems with few weight tiles split K over a cluster of CTAs; calling
