@@ -209,6 +209,38 @@ typedef struct lfm25_fused_ragged_decode_launch {
 int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
                                                             const lfm25_fused_ragged_decode_launch* launch);
 
+/* Replaces AttentionKernels::launch_hybrid_ragged_lfm2_bf16 with HybridAttentionLaunch
+ * (src/cuda/kernels/attention.rs:41-57,131-226; kernel kernels/attention.cu:389-585): attention of a step that
+ * mixes prefill chunks and decode tokens.  Token t of the segment [segment_offsets[s], segment_offsets[s+1]) that
+ * contains it, at offset o and position p, attends to the p - o tokens of its sequence already in the paged cache
+ * (through block_tables[request_slots[t]]) and to the step's own tokens segment_begin..t in current_key /
+ * current_value.  A token with p < o, or whose key range meets a block-table entry >= num_pages, is left untouched;
+ * the tokens of a segment must sit at consecutive positions of one request slot (GpuBatch::update_segments,
+ * src/scheduler/batch.rs:142-215): a token that does not continue its 16-token tile is left untouched as well.
+ * Extensions: current_key.ptr == NULL reads every key up to each token's position from the cache (the step's K/V
+ * were appended first); query_token_stride / kv_token_stride (elements, 0 = dense 2048 / 512) accept projections
+ * that one packed GEMM wrote side by side. */
+typedef struct lfm25_hybrid_attention_launch {
+    size_t page_size;
+    lfm25_slice query;            /* bf16 [num_tokens, 32, 64] */
+    lfm25_slice current_key;      /* bf16 [num_tokens, 8, 64] (16-byte aligned) or ptr NULL */
+    lfm25_slice current_value;
+    lfm25_slice key_cache;        /* bf16 [num_pages, 8, 16, 64] */
+    lfm25_slice value_cache;
+    lfm25_slice block_tables;     /* u32 [rows, block_table_stride] */
+    lfm25_slice request_slots;    /* u32 [num_tokens] */
+    lfm25_slice position_ids;     /* u32 [num_tokens] */
+    lfm25_slice segment_offsets;  /* u32 [num_segments + 1] */
+    lfm25_slice output;           /* bf16 [num_tokens, 32, 64], written */
+    size_t num_tokens;
+    size_t num_pages;
+    size_t block_table_stride;
+    size_t num_segments;
+    size_t query_token_stride;
+    size_t kv_token_stride;
+} lfm25_hybrid_attention_launch;
+int32_t lfm25_hybrid_ragged_attention_lfm2_bf16(void* stream, const lfm25_hybrid_attention_launch* launch);
+
 /* Replaces splitk_workspace_elements (src/ops/attention_async_fast.rs:24-30):
  * maximum_tokens * 32 * 8 * 66 f32 elements; 0 on overflow. */
 size_t lfm25_splitk_workspace_elements(size_t maximum_tokens);
@@ -300,6 +332,19 @@ int32_t lfm25_residual_rms_norm_bf16(void* stream, lfm25_slice residual, lfm25_s
 int32_t lfm25_residual_rms_norm_bf16_e4m3(void* stream, lfm25_slice residual, lfm25_slice update, lfm25_slice weight,
                                           lfm25_slice residual_out, lfm25_slice normalized_out, lfm25_slice codes_out,
                                           size_t rows, size_t hidden_size, float eps, float scale);
+/* Replaces short_conv_segmented_lfm2_bf16 (kernels/short_conv.cu:100-143, src/cuda/kernels/short_conv.rs) for
+ * segments of any length: projected [num_tokens, 3*hidden] = (b | c | x), weight [hidden, 3], states
+ * [num_request_slots, hidden, 2] updated in place, segment_offsets u32 [num_segments + 1], segment_slots u32
+ * [num_segments]; inside a segment the carried values stay unrounded fp32, the stored state is bf16.  A segment
+ * whose slot is beyond the state table is skipped. */
+int32_t lfm25_short_conv_segmented_lfm2_bf16(void* stream, lfm25_slice projected, lfm25_slice weight,
+                                             lfm25_slice states, lfm25_slice segment_offsets,
+                                             lfm25_slice segment_slots, lfm25_slice output, size_t num_tokens,
+                                             size_t num_segments, size_t hidden_size, size_t num_request_slots);
+/* Replaces gather_rows_bf16 (kernels/gather.cu): output[r] = input[row_indices[r]] for r < output_rows; an index
+ * >= input_rows leaves the output row untouched.  columns must be even. */
+int32_t lfm25_gather_rows_bf16(void* stream, lfm25_slice input, lfm25_slice row_indices, lfm25_slice output,
+                               size_t output_rows, size_t input_rows, size_t columns);
 /* Replaces short_conv_segmented_lfm2_bf16 (kernels/short_conv.cu:100-143) for decode (one token per segment):
  * projected [T, 3*hidden] = (b | c | x), weight [hidden, 3], states [request_slots, hidden, 2] updated in place. */
 int32_t lfm25_short_conv_decode_bf16(void* stream, lfm25_slice projected, lfm25_slice weight, lfm25_slice states,

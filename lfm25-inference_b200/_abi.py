@@ -122,6 +122,11 @@ FusedRaggedDecodeLaunch = _launch_struct("FusedRaggedDecodeLaunch", [
     "block_tables", "request_slots", "#block_table_stride", "partials", "#num_splits", "#query_token_stride",
     "#kv_token_stride"])
 
+HybridAttentionLaunch = _launch_struct("HybridAttentionLaunch", [
+    "#page_size", "query", "current_key", "current_value", "key_cache", "value_cache", "block_tables", "request_slots",
+    "position_ids", "segment_offsets", "output", "#num_tokens", "#num_pages", "#block_table_stride", "#num_segments",
+    "#query_token_stride", "#kv_token_stride"])
+
 # name -> (restype, argtypes); every symbol that include/lfm25_b200.h declares
 PROTOTYPES = {
     "lfm25_last_error": (ctypes.c_char_p, []),
@@ -154,6 +159,10 @@ PROTOTYPES = {
     "lfm25_residual_rms_norm_bf16_e4m3": (
         ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, Slice, _size, _size, ctypes.c_float,
                          ctypes.c_float]),
+    "lfm25_hybrid_ragged_attention_lfm2_bf16": (ctypes.c_int32, [_stream, _P(HybridAttentionLaunch)]),
+    "lfm25_short_conv_segmented_lfm2_bf16": (
+        ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, Slice, _size, _size, _size, _size]),
+    "lfm25_gather_rows_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_short_conv_decode_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_argmax_rows_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
     "lfm25_decode_step_metadata": (ctypes.c_int32, [_stream, _P(DecodeBatch), Slice, _size, ctypes.c_uint32]),

@@ -478,6 +478,84 @@ int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
                        "fused ragged decode launch failed");
 }
 
+int32_t lfm25_hybrid_ragged_attention_lfm2_bf16(void* stream, const lfm25_hybrid_attention_launch* launch) {
+    LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "hybrid attention launch is null");
+    const lfm25_hybrid_attention_launch& l = *launch;
+    // src/cuda/kernels/attention.rs:153-196
+    LFM25_ENSURE(l.page_size == 16 || l.page_size == 32, LFM25_ERR_INVALID_ARGUMENT,
+                 "unsupported hybrid attention page size %zu", l.page_size);
+    LFM25_ENSURE(l.page_size == 16, LFM25_ERR_UNSUPPORTED, "page size 32 is not built; use 16");
+    LFM25_ENSURE(l.num_tokens > 0, LFM25_ERR_INVALID_ARGUMENT, "hybrid ragged attention requires tokens");
+    LFM25_ENSURE(l.num_segments > 0, LFM25_ERR_INVALID_ARGUMENT, "hybrid ragged attention requires segments");
+    LFM25_ENSURE(l.num_pages > 0, LFM25_ERR_INVALID_ARGUMENT, "hybrid ragged attention requires cache pages");
+    LFM25_ENSURE(l.block_table_stride > 0, LFM25_ERR_INVALID_ARGUMENT, "hybrid block table is empty");
+    LFM25_ENSURE(l.request_slots.len >= l.num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "request slots too small");
+    LFM25_ENSURE(l.position_ids.len >= l.num_tokens, LFM25_ERR_BUFFER_TOO_SMALL, "positions too small");
+    LFM25_ENSURE(l.segment_offsets.len > l.num_segments, LFM25_ERR_BUFFER_TOO_SMALL, "segment offsets too small");
+    LFM25_ENSURE(l.num_tokens <= 0x7fffffffu && l.num_pages <= 0x00ffffffu && l.num_segments <= 0x7fffffffu,
+                 LFM25_ERR_INVALID_ARGUMENT, "hybrid attention sizes exceed the kernel's index range");
+    const size_t query_stride = l.query_token_stride == 0 ? 32 * 64 : l.query_token_stride;
+    const size_t kv_stride = l.kv_token_stride == 0 ? 8 * 64 : l.kv_token_stride;
+    LFM25_ENSURE(query_stride >= 32 * 64 && query_stride % 2 == 0 && kv_stride >= 8 * 64 && kv_stride % 8 == 0,
+                 LFM25_ERR_INVALID_ARGUMENT,
+                 "hybrid token strides: query even and >= 2048, K/V a multiple of 8 and >= 512 elements");
+    size_t q_dense = 0;
+    size_t q_required = 0;
+    size_t kv_required = 0;
+    size_t cache_required = 0;
+    LFM25_ENSURE(checked_mul(l.num_tokens, 32 * 64, &q_dense) &&
+                     checked_mul(l.num_tokens - 1, query_stride, &q_required) &&
+                     checked_mul(l.num_tokens - 1, kv_stride, &kv_required),
+                 LFM25_ERR_OVERFLOW, "hybrid query size overflow");
+    q_required += 32 * 64;
+    kv_required += 8 * 64;
+    LFM25_ENSURE(checked_mul(l.num_pages, 8 * 16 * 64, &cache_required), LFM25_ERR_OVERFLOW,
+                 "hybrid cache size overflow");
+    LFM25_ENSURE(l.query.len >= q_required && l.output.len >= q_dense, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "hybrid Q/O storage too small");
+    const bool contiguous = l.current_key.ptr != nullptr;
+    if (contiguous) {
+        LFM25_ENSURE(l.current_value.ptr != nullptr, LFM25_ERR_NULL_POINTER, "hybrid current V is null");
+        LFM25_ENSURE(l.current_key.len >= kv_required && l.current_value.len >= kv_required,
+                     LFM25_ERR_BUFFER_TOO_SMALL, "hybrid contiguous KV storage too small");
+        LFM25_ENSURE(((reinterpret_cast<uintptr_t>(l.current_key.ptr) |
+                       reinterpret_cast<uintptr_t>(l.current_value.ptr)) & 15) == 0,
+                     LFM25_ERR_INVALID_ARGUMENT, "hybrid contiguous K/V must be 16-byte aligned");
+    }
+    LFM25_ENSURE(l.key_cache.len >= cache_required && l.value_cache.len >= cache_required,
+                 LFM25_ERR_BUFFER_TOO_SMALL, "hybrid paged KV storage too small");
+    LFM25_ENSURE(l.block_tables.len >= l.block_table_stride, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "hybrid block table storage too small");
+    LFM25_ENSURE(l.query.ptr && l.output.ptr && l.key_cache.ptr && l.value_cache.ptr && l.block_tables.ptr &&
+                     l.request_slots.ptr && l.position_ids.ptr && l.segment_offsets.ptr,
+                 LFM25_ERR_NULL_POINTER, "hybrid attention received a null device pointer");
+    LFM25_ENSURE(((reinterpret_cast<uintptr_t>(l.key_cache.ptr) | reinterpret_cast<uintptr_t>(l.value_cache.ptr)) &
+                  127) == 0,
+                 LFM25_ERR_INVALID_ARGUMENT, "hybrid paged K/V must be 128-byte aligned");
+    lfm25::HybridAttentionLaunch args = {};
+    args.query = l.query.ptr;
+    args.current_key = contiguous ? l.current_key.ptr : nullptr;
+    args.current_value = contiguous ? l.current_value.ptr : nullptr;
+    args.key_cache = l.key_cache.ptr;
+    args.value_cache = l.value_cache.ptr;
+    args.block_tables = static_cast<const uint32_t*>(l.block_tables.ptr);
+    args.request_slots = static_cast<const uint32_t*>(l.request_slots.ptr);
+    args.position_ids = static_cast<const uint32_t*>(l.position_ids.ptr);
+    args.segment_offsets = static_cast<const uint32_t*>(l.segment_offsets.ptr);
+    args.output = l.output.ptr;
+    args.status = device_status_pointer();
+    args.num_tokens = l.num_tokens;
+    args.num_pages = l.num_pages;
+    args.block_table_stride = l.block_table_stride;
+    args.block_table_rows = l.block_tables.len / l.block_table_stride;
+    args.num_segments = l.num_segments;
+    args.query_token_stride = query_stride;
+    args.kv_token_stride = kv_stride;
+    LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(lfm25::launch_hybrid_ragged_attention(static_cast<cudaStream_t>(stream), args),
+                       "hybrid ragged attention launch failed");
+}
+
 size_t lfm25_splitk_workspace_elements(size_t maximum_tokens) {
     size_t value = 0;
     if (!checked_mul(maximum_tokens, 32, &value) || !checked_mul(value, 8, &value) ||
@@ -635,6 +713,60 @@ int32_t lfm25_residual_rms_norm_bf16_e4m3(void* stream, lfm25_slice residual, lf
                                           size_t rows, size_t hidden_size, float eps, float scale) {
     return residual_rms_norm(stream, residual, update, weight, residual_out, normalized_out, &codes_out, rows,
                              hidden_size, eps, scale);
+}
+
+int32_t lfm25_short_conv_segmented_lfm2_bf16(void* stream, lfm25_slice projected, lfm25_slice weight,
+                                             lfm25_slice states, lfm25_slice segment_offsets,
+                                             lfm25_slice segment_slots, lfm25_slice output, size_t num_tokens,
+                                             size_t num_segments, size_t hidden_size, size_t num_request_slots) {
+    LFM25_ENSURE(num_tokens > 0 && num_segments > 0 && hidden_size > 0 && num_request_slots > 0,
+                 LFM25_ERR_INVALID_ARGUMENT, "segmented short conv requires non-empty dimensions");
+    size_t projected_required = 0;
+    size_t output_required = 0;
+    size_t state_required = 0;
+    LFM25_ENSURE(checked_mul(num_tokens, hidden_size, &output_required) &&
+                     checked_mul(output_required, 3, &projected_required) &&
+                     checked_mul(num_request_slots, hidden_size, &state_required) &&
+                     checked_mul(state_required, 2, &state_required),
+                 LFM25_ERR_OVERFLOW, "segmented short conv size overflow");
+    LFM25_ENSURE(projected.len >= projected_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "segmented short conv input storage too small");
+    LFM25_ENSURE(output.len >= output_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "segmented short conv output storage too small");
+    LFM25_ENSURE(states.len >= state_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "segmented short conv state storage too small");
+    LFM25_ENSURE(weight.len >= hidden_size * 3, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "segmented short conv weight storage too small");
+    LFM25_ENSURE(segment_offsets.len > num_segments && segment_slots.len >= num_segments, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "segmented short conv segment metadata too small");
+    LFM25_ENSURE(projected.ptr && weight.ptr && states.ptr && segment_offsets.ptr && segment_slots.ptr && output.ptr,
+                 LFM25_ERR_NULL_POINTER, "segmented short conv received a null device pointer");
+    return cuda_result(
+        lfm25::launch_short_conv_segmented(static_cast<cudaStream_t>(stream), projected.ptr, weight.ptr, states.ptr,
+                                           static_cast<const uint32_t*>(segment_offsets.ptr),
+                                           static_cast<const uint32_t*>(segment_slots.ptr), output.ptr, num_tokens,
+                                           num_segments, hidden_size, num_request_slots),
+        "segmented short conv launch failed");
+}
+
+int32_t lfm25_gather_rows_bf16(void* stream, lfm25_slice input, lfm25_slice row_indices, lfm25_slice output,
+                               size_t output_rows, size_t input_rows, size_t columns) {
+    LFM25_ENSURE(output_rows > 0 && input_rows > 0 && columns > 0, LFM25_ERR_INVALID_ARGUMENT,
+                 "gather requires non-empty dimensions");
+    LFM25_ENSURE(columns % 2 == 0, LFM25_ERR_UNSUPPORTED, "gather requires an even number of columns");
+    size_t input_required = 0;
+    size_t output_required = 0;
+    LFM25_ENSURE(checked_mul(input_rows, columns, &input_required) &&
+                     checked_mul(output_rows, columns, &output_required),
+                 LFM25_ERR_OVERFLOW, "gather size overflow");
+    LFM25_ENSURE(input.len >= input_required && output.len >= output_required && row_indices.len >= output_rows,
+                 LFM25_ERR_BUFFER_TOO_SMALL, "gather storage too small");
+    LFM25_ENSURE(input.ptr && row_indices.ptr && output.ptr, LFM25_ERR_NULL_POINTER,
+                 "gather received a null device pointer");
+    return cuda_result(lfm25::launch_gather_rows_bf16(static_cast<cudaStream_t>(stream), input.ptr,
+                                                      static_cast<const uint32_t*>(row_indices.ptr), output.ptr,
+                                                      output_rows, input_rows, columns),
+                       "gather launch failed");
 }
 
 int32_t lfm25_short_conv_decode_bf16(void* stream, lfm25_slice projected, lfm25_slice weight, lfm25_slice states,

@@ -27,7 +27,7 @@ constexpr uint32_t kPageTileBytes = kPageSize * kHeadDim * 2;  // 2048
 // trapping or spinning for ever; the host reads the words with lfm25_device_status().  The
 // words live in one translation unit (api.cu); kernels receive their device address.
 //   [0] number of waits that ran out   [1] kernel tag of the last one   [2] detail (stage / item)
-enum StatusTag : uint32_t { kTagAttention = 1, kTagGemmStream = 2, kTagGemmUmma = 3, kTagPlanned = 4 };
+enum StatusTag : uint32_t { kTagAttention = 1, kTagGemmStream = 2, kTagGemmUmma = 3, kTagHybridAttention = 4 };
 __device__ __forceinline__ void record_wait_timeout(unsigned int* status, uint32_t tag, uint32_t detail) {
     atomicAdd(&status[0], 1u);
     status[1] = tag;

@@ -36,6 +36,30 @@ struct AttentionLaunch {
 };
 cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionLaunch& launch);
 
+// Attention of a mixed prefill / decode step (hybrid_attention.cu).  `current_key` == nullptr: every key up to a
+// token's position is read from the cache; otherwise the segment's own tokens come from current_key / current_value.
+struct HybridAttentionLaunch {
+    const void* query;             // bf16 [T,32,64], rows query_token_stride apart
+    const void* current_key;       // bf16 [T,8,64], rows kv_token_stride apart, or nullptr
+    const void* current_value;
+    const void* key_cache;         // bf16 [pages,8,16,64]
+    const void* value_cache;
+    const uint32_t* block_tables;  // [rows, stride]
+    const uint32_t* request_slots; // [T]
+    const uint32_t* position_ids;  // [T]
+    const uint32_t* segment_offsets;  // [S + 1]
+    void* output;                  // bf16 [T,32,64], dense
+    unsigned int* status;
+    size_t num_tokens;
+    size_t num_pages;
+    size_t block_table_stride;
+    size_t block_table_rows;
+    size_t num_segments;
+    size_t query_token_stride = 32 * 64;
+    size_t kv_token_stride = 8 * 64;
+};
+cudaError_t launch_hybrid_ragged_attention(cudaStream_t stream, const HybridAttentionLaunch& launch);
+
 cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const void* value, void* key_cache,
                                   void* value_cache, const int64_t* slot_mapping, size_t num_tokens,
                                   size_t num_pages);
@@ -91,6 +115,12 @@ cudaError_t launch_residual_rms_norm_bf16(cudaStream_t stream, const void* resid
 cudaError_t launch_short_conv_decode(cudaStream_t stream, const void* projected, const void* weight, void* states,
                                      const uint32_t* request_slots, void* output, size_t num_tokens, size_t hidden,
                                      size_t num_request_slots);
+cudaError_t launch_short_conv_segmented(cudaStream_t stream, const void* projected, const void* weight, void* states,
+                                        const uint32_t* segment_offsets, const uint32_t* segment_slots, void* output,
+                                        size_t num_tokens, size_t num_segments, size_t hidden,
+                                        size_t num_request_slots);
+cudaError_t launch_gather_rows_bf16(cudaStream_t stream, const void* input, const uint32_t* row_indices, void* output,
+                                    size_t output_rows, size_t input_rows, size_t columns);
 cudaError_t launch_argmax_rows_bf16(cudaStream_t stream, const void* logits, uint32_t* sampled, size_t rows,
                                     size_t vocab);
 cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uint32_t* positions,

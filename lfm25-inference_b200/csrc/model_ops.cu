@@ -258,6 +258,100 @@ decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ 
 
 }  // namespace
 
+// Gated short convolution over token segments (prefill chunks and decode tokens in one batch), the reference's
+// short_conv_segmented_lfm2_bf16 (kernels/short_conv.cu:100-143) without its loop over the tokens of a segment:
+// the "state" it carries is just the gated inputs g = b * x of the two previous tokens, kept unrounded inside a
+// segment, so y[t] = c[t] * (w0 g[t-2] + w1 g[t-1] + w2 g[t]) can be evaluated per token, operation for operation.
+// One CTA per token.  Only a segment's first two tokens need the stored state and only its first token's CTA
+// touches it: that CTA produces y for offsets 0 and 1 and then stores the new state (the gated inputs of the
+// segment's last two tokens, rounded to bf16), so no CTA reads a state another one writes.
+__global__ void __launch_bounds__(kRowThreads)
+short_conv_segmented_kernel(const __nv_bfloat16* __restrict__ projected, const __nv_bfloat16* __restrict__ weight,
+                            __nv_bfloat16* __restrict__ states, const uint32_t* __restrict__ segment_offsets,
+                            const uint32_t* __restrict__ segment_slots, __nv_bfloat16* __restrict__ output,
+                            size_t num_tokens, size_t num_segments, size_t hidden, size_t num_request_slots) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t token = blockIdx.x;
+    if (token >= num_tokens) {
+        return;
+    }
+    size_t begin = 0;
+    size_t end = 0;
+    size_t slot = num_request_slots;
+    for (size_t segment = 0; segment < num_segments; ++segment) {
+        const size_t first = segment_offsets[segment];
+        const size_t last = segment_offsets[segment + 1];
+        if (token >= first && token < last) {
+            begin = first;
+            end = last < num_tokens ? last : num_tokens;
+            slot = segment_slots[segment];
+            break;
+        }
+    }
+    if (slot >= num_request_slots) {
+        return;   // not in any segment, or a slot beyond the state table: the reference skips the segment
+    }
+    const size_t offset = token - begin;
+    if (offset == 1) {
+        return;   // produced by the CTA of the segment's first token
+    }
+    const size_t row = hidden * 3;
+    for (size_t channel = threadIdx.x; channel < hidden; channel += blockDim.x) {
+        const float w0 = __bfloat162float(weight[channel * 3]);
+        const float w1 = __bfloat162float(weight[channel * 3 + 1]);
+        const float w2 = __bfloat162float(weight[channel * 3 + 2]);
+        auto gated_at = [&](size_t at) {
+            return __bfloat162float(projected[at * row + channel]) * __bfloat162float(projected[at * row + 2 * hidden + channel]);
+        };
+        auto gate_at = [&](size_t at) { return __bfloat162float(projected[at * row + hidden + channel]); };
+        if (offset >= 2) {
+            const float convolved = w0 * gated_at(token - 2) + w1 * gated_at(token - 1) + w2 * gated_at(token);
+            output[token * hidden + channel] = __float2bfloat16_rn(gate_at(token) * convolved);
+            continue;
+        }
+        __nv_bfloat162* state = reinterpret_cast<__nv_bfloat162*>(states) + slot * hidden + channel;
+        const float2 previous = __bfloat1622float2(*state);
+        const float g0 = gated_at(token);
+        output[token * hidden + channel] = __float2bfloat16_rn(gate_at(token) * (w0 * previous.x + w1 * previous.y + w2 * g0));
+        float state0 = previous.y;
+        float state1 = g0;
+        if (token + 1 < end) {
+            const float g1 = gated_at(token + 1);
+            output[(token + 1) * hidden + channel] =
+                __float2bfloat16_rn(gate_at(token + 1) * (w0 * previous.y + w1 * g0 + w2 * g1));
+            state0 = g0;
+            state1 = g1;
+            if (token + 2 < end) {
+                state0 = gated_at(end - 2);
+                state1 = gated_at(end - 1);
+            }
+        }
+        *state = __floats2bfloat162_rn(state0, state1);
+    }
+}
+
+// Row gather (kernels/gather.cu): output[r] = input[row_indices[r]]; an index beyond the input leaves the row as is.
+__global__ void __launch_bounds__(kRowThreads)
+gather_rows_kernel(const __nv_bfloat16* __restrict__ input, const uint32_t* __restrict__ row_indices,
+                   __nv_bfloat16* __restrict__ output, size_t output_rows, size_t input_rows, size_t columns) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    if (row >= output_rows) {
+        return;
+    }
+    const size_t source = row_indices[row];
+    if (source >= input_rows) {
+        return;
+    }
+    const uint32_t* from = reinterpret_cast<const uint32_t*>(input + source * columns);
+    uint32_t* to = reinterpret_cast<uint32_t*>(output + row * columns);
+    for (size_t pair = threadIdx.x; pair < columns / 2; pair += blockDim.x) {
+        to[pair] = from[pair];
+    }
+}
+
 cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids, const void* table, void* out,
                                   size_t num_tokens, size_t vocab_size, size_t hidden) {
     return launch_kernel(embedding_kernel, static_cast<unsigned int>(num_tokens), kRowThreads, 0, stream, 1, token_ids,
@@ -303,6 +397,23 @@ cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uin
                                    size_t block_table_rows, size_t num_pages, bool advance) {
     return launch_kernel(decode_metadata_kernel, static_cast<unsigned int>((num_tokens + kRowThreads - 1) / kRowThreads), kRowThreads, 0, stream, 1, token_ids, positions, request_slots, block_tables, sampled, physical_slots,
                                        num_tokens, block_table_stride, block_table_rows, num_pages, advance ? 1u : 0u);
+}
+
+cudaError_t launch_short_conv_segmented(cudaStream_t stream, const void* projected, const void* weight, void* states,
+                                        const uint32_t* segment_offsets, const uint32_t* segment_slots, void* output,
+                                        size_t num_tokens, size_t num_segments, size_t hidden,
+                                        size_t num_request_slots) {
+    return launch_kernel(short_conv_segmented_kernel, static_cast<unsigned int>(num_tokens), kRowThreads, 0, stream, 1,
+                         static_cast<const __nv_bfloat16*>(projected), static_cast<const __nv_bfloat16*>(weight),
+                         static_cast<__nv_bfloat16*>(states), segment_offsets, segment_slots,
+                         static_cast<__nv_bfloat16*>(output), num_tokens, num_segments, hidden, num_request_slots);
+}
+
+cudaError_t launch_gather_rows_bf16(cudaStream_t stream, const void* input, const uint32_t* row_indices, void* output,
+                                    size_t output_rows, size_t input_rows, size_t columns) {
+    return launch_kernel(gather_rows_kernel, static_cast<unsigned int>(output_rows), kRowThreads, 0, stream, 1,
+                         static_cast<const __nv_bfloat16*>(input), row_indices, static_cast<__nv_bfloat16*>(output),
+                         output_rows, input_rows, columns);
 }
 
 }  // namespace lfm25

@@ -42,4 +42,22 @@ inline bool make_swizzled_2d_map(CUtensorMap* map, CUtensorMapDataType type, uin
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same for a tensor whose rows are `width` elements wide but `pitch_bytes` apart (a column block of a wider
+// buffer); `pitch_bytes` must be a multiple of 16 and `base` 16-byte aligned.
+inline bool make_swizzled_2d_map_width(CUtensorMap* map, CUtensorMapDataType type, uint32_t element_size,
+                                       const void* base, uint64_t rows, uint64_t width, uint64_t pitch_bytes,
+                                       uint32_t box_rows) {
+    EncodeTiledFn encode = encode_tiled_entry();
+    if (encode == nullptr) {
+        return false;
+    }
+    const cuuint64_t dims[2] = {width, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {128 / element_size, box_rows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    return encode(map, type, 2, const_cast<void*>(base), dims, strides, box, element_strides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace lfm25

@@ -197,6 +197,38 @@ def fused_ragged_paged_attention_decode_lfm2_bf16_into(query_raw, key_raw, value
     check(library().lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(_stream(), launch))
 
 
+def hybrid_ragged_attention_lfm2_bf16_into(query, current_key, current_value, arena: PagedKvArena, block_tables,
+                                           block_table_stride: int, request_slots, position_ids, segment_offsets,
+                                           output) -> None:
+    """Attention of a step that mixes prefill chunks and decode tokens: paged prefix + the step's own contiguous K/V
+    (reference: src/ops/attention.rs:121-185, HybridRaggedAttentionInput).  `current_key` / `current_value` None:
+    every key up to each token's position is read from the cache (the step's K/V were appended before).  The
+    projections may be row-strided views of one packed buffer."""
+    _ensure(query.dim() == 3 and tuple(query.shape[1:]) == (32, 64), "hybrid LFM2 query must have shape [N,32,64]")
+    num_tokens = query.shape[0]
+    _ensure(tuple(query.stride()[1:]) == (64, 1), "hybrid query heads must be dense")
+    empty = Slice(None, 0)
+    key_slice, value_slice, kv_stride = empty, empty, 0
+    if current_key is not None:
+        _ensure(tuple(current_key.shape) == (num_tokens, 8, 64) and current_value.shape == current_key.shape,
+                "hybrid contiguous K/V shape mismatch")
+        _ensure(tuple(current_key.stride()[1:]) == (64, 1) and current_value.stride() == current_key.stride(),
+                "hybrid contiguous K/V must be dense per token and share their token stride")
+        key_slice, value_slice = _row_strided_slice(current_key), _row_strided_slice(current_value)
+        kv_stride = current_key.stride(0) if num_tokens > 1 else 0
+    _ensure(block_tables.dim() == 2, "block tables must have rank 2")
+    _ensure(block_tables.shape[1] == block_table_stride, "block table stride/shape mismatch")
+    _ensure(request_slots.numel() == num_tokens, "request slot mismatch")
+    _ensure(position_ids.numel() == num_tokens, "position mismatch")
+    _ensure(segment_offsets.numel() >= 2, "hybrid segments are empty")
+    launch = _abi.HybridAttentionLaunch(
+        arena.page_size, _row_strided_slice(query), key_slice, value_slice, _slice(arena.key), _slice(arena.value),
+        _slice(block_tables), _slice(request_slots), _slice(position_ids), _slice(segment_offsets), _slice(output),
+        num_tokens, arena.num_pages, block_table_stride, segment_offsets.numel() - 1,
+        query.stride(0) if num_tokens > 1 else 0, kv_stride)
+    check(library().lfm25_hybrid_ragged_attention_lfm2_bf16(_stream(), launch))
+
+
 def paged_ragged_attention_splitk_static_lfm2_bf16_into(inputs: FastRaggedAttentionInput, num_splits: int,
                                                         output: torch.Tensor) -> None:
     """Split-K attention without a caller workspace, for hosts that may not allocate device memory while
@@ -347,6 +379,23 @@ def short_conv_decode_bf16_into(projected, weight, states, request_slots, output
     check(library().lfm25_short_conv_decode_bf16(_stream(), _slice(projected), _slice(weight), _slice(states),
                                                  _slice(request_slots), _slice(output), request_slots.numel(), hidden,
                                                  states.shape[0]))
+
+
+def short_conv_segmented_lfm2_bf16_into(projected, weight, states, segment_offsets, segment_slots, output) -> None:
+    """Reference: src/ops/short_conv.rs (short_conv_segmented_lfm2_bf16): gated width-3 convolution over token
+    segments, one state row per request slot."""
+    hidden = weight.shape[0]
+    _ensure(projected.dim() == 2 and projected.shape[1] == 3 * hidden, "projected must have shape [N, 3*hidden]")
+    _ensure(segment_offsets.numel() == segment_slots.numel() + 1, "segment offsets / slots mismatch")
+    check(library().lfm25_short_conv_segmented_lfm2_bf16(
+        _stream(), _slice(projected), _slice(weight), _slice(states), _slice(segment_offsets), _slice(segment_slots),
+        _slice(output), projected.shape[0], segment_slots.numel(), hidden, states.shape[0]))
+
+
+def gather_rows_bf16_into(values, row_indices, output) -> None:
+    """Reference: src/ops/gather.rs (gather_rows_bf16)."""
+    check(library().lfm25_gather_rows_bf16(_stream(), _slice(values), _slice(row_indices), _slice(output),
+                                           row_indices.numel(), values.shape[0], values.shape[1]))
 
 
 def argmax_rows_bf16_into(logits: torch.Tensor, sampled: torch.Tensor) -> None:

@@ -123,3 +123,93 @@ def fill_pool_for_batch(rng: np.random.Generator, batch: RaggedDecodeBatch):
     key[owned] = bf16_normal(rng, (owned.size, KV_HEADS, PAGE_SIZE, HEAD_DIM))
     value[owned] = bf16_normal(rng, (owned.size, KV_HEADS, PAGE_SIZE, HEAD_DIM))
     return key, value
+
+
+@dataclass
+class MixedStepBatch:
+    """One step that mixes prefill chunks and decode tokens: segment s holds `chunks[s]` consecutive tokens of the
+    sequence in request slot `segment_slots[s]`, whose first `prefixes[s]` tokens are already in the paged cache
+    (a decode token is a segment of one token)."""
+
+    num_pages: int
+    block_tables: np.ndarray      # uint32 [request slots, stride], 0xffffffff = unassigned
+    prefixes: np.ndarray          # int64 [segments]
+    chunks: np.ndarray            # int64 [segments]
+    segment_slots: np.ndarray     # uint32 [segments]
+
+    @property
+    def num_segments(self) -> int:
+        return int(self.chunks.shape[0])
+
+    @property
+    def num_tokens(self) -> int:
+        return int(self.chunks.sum())
+
+    @property
+    def stride(self) -> int:
+        return int(self.block_tables.shape[1])
+
+    @property
+    def segment_offsets(self) -> np.ndarray:
+        return np.concatenate([[0], np.cumsum(self.chunks)]).astype(np.uint32)
+
+    @property
+    def request_slots(self) -> np.ndarray:
+        return np.repeat(self.segment_slots, self.chunks).astype(np.uint32)
+
+    @property
+    def positions(self) -> np.ndarray:
+        return np.concatenate([prefix + np.arange(chunk) for prefix, chunk in zip(self.prefixes, self.chunks)]).astype(
+            np.uint32)
+
+    @property
+    def physical_slots(self) -> np.ndarray:
+        positions = self.positions.astype(np.int64)
+        pages = self.block_tables[self.request_slots.astype(np.int64), positions // PAGE_SIZE].astype(np.int64)
+        return pages * PAGE_SIZE + positions % PAGE_SIZE
+
+    @property
+    def output_rows(self) -> np.ndarray:
+        """Row of each segment's last token: the rows whose logits a serving step needs."""
+        return (np.cumsum(self.chunks) - 1).astype(np.uint32)
+
+
+def mixed_step_batch(seed: int, prefixes, chunks, num_pages: int, shuffle_slots: bool = True) -> MixedStepBatch:
+    """Block tables are consecutive slices of one seeded shuffle of the pool, sized for prefix + chunk tokens; the
+    request slots are a seeded permutation of 0..segments-1 unless `shuffle_slots` is off."""
+    rng = np.random.default_rng(seed)
+    prefixes = np.asarray(prefixes, dtype=np.int64)
+    chunks = np.asarray(chunks, dtype=np.int64)
+    pages_needed = (prefixes + chunks + PAGE_SIZE - 1) // PAGE_SIZE
+    if int(pages_needed.sum()) > num_pages:
+        raise ValueError("page pool too small for the batch")
+    stride = int(pages_needed.max())
+    shuffle = rng.permutation(num_pages).astype(np.uint32)
+    slots = rng.permutation(len(chunks)).astype(np.uint32) if shuffle_slots else np.arange(len(chunks),
+                                                                                         dtype=np.uint32)
+    tables = np.full((len(chunks), stride), 0xFFFFFFFF, dtype=np.uint32)
+    cursor = 0
+    for segment, slot in enumerate(slots):
+        count = int(pages_needed[segment])
+        tables[slot, :count] = shuffle[cursor:cursor + count]
+        cursor += count
+    return MixedStepBatch(num_pages, tables, prefixes, chunks, slots)
+
+
+def fill_prefixes(rng: np.random.Generator, batch: MixedStepBatch):
+    """K and V pools [pages, 8, 16, 64] (bf16 bits) with N(0,1) in the first `prefix` token rows of every segment's
+    sequence; rows at and beyond the prefix hold a NaN pattern (0x7fc1), so that a kernel that reads a row it
+    must not read shows up in the result."""
+    shape = (batch.num_pages, KV_HEADS, PAGE_SIZE, HEAD_DIM)
+    key = np.full(shape, 0x7FC1, dtype=np.uint16)
+    value = np.full(shape, 0x7FC1, dtype=np.uint16)
+    for segment in range(batch.num_segments):
+        prefix = int(batch.prefixes[segment])
+        if prefix == 0:
+            continue
+        positions = np.arange(prefix)
+        pages = batch.block_tables[int(batch.segment_slots[segment]), positions // PAGE_SIZE].astype(np.int64)
+        offsets = positions % PAGE_SIZE
+        key[pages, :, offsets, :] = bf16_normal(rng, (prefix, KV_HEADS, HEAD_DIM))
+        value[pages, :, offsets, :] = bf16_normal(rng, (prefix, KV_HEADS, HEAD_DIM))
+    return key, value

@@ -647,6 +647,139 @@ void oracle_short_conv_decode_bf16(const uint16_t* projected, const uint16_t* we
 }
 
 /*
+ * Gated short convolution over token segments (prefill chunks and decode tokens in one batch).  Follows
+ * kernels/short_conv.cu:100-143 (short_conv_segmented_lfm2_bf16): per (segment, channel) the two state values are
+ * loaded once, carried in fp32 across the segment's tokens (state1 <- gated is NOT rounded between tokens) and
+ * stored as bf16 at the end; y[token] = bf16(c * (w0*s0 + w1*s1 + w2*gated)).  A segment whose slot is beyond
+ * the state table is skipped.
+ */
+void oracle_short_conv_segmented_bf16(const uint16_t* projected, const uint16_t* weight, uint16_t* states,
+                                      const uint32_t* segment_offsets, const uint32_t* segment_slots,
+                                      uint16_t* output, size_t num_segments, size_t hidden,
+                                      size_t num_request_slots) {
+#pragma omp parallel for schedule(static)
+    for (size_t channel = 0; channel < hidden; ++channel) {
+        for (size_t segment = 0; segment < num_segments; ++segment) {
+            const size_t slot = segment_slots[segment];
+            if (slot >= num_request_slots) {
+                continue;
+            }
+            uint16_t* state = states + (slot * hidden + channel) * 2;
+            float state0 = bf16_to_f32(state[0]);
+            float state1 = bf16_to_f32(state[1]);
+            const float w0 = bf16_to_f32(weight[channel * 3]);
+            const float w1 = bf16_to_f32(weight[channel * 3 + 1]);
+            const float w2 = bf16_to_f32(weight[channel * 3 + 2]);
+            for (size_t token = segment_offsets[segment]; token < segment_offsets[segment + 1]; ++token) {
+                const size_t base = token * hidden * 3;
+                const float b = bf16_to_f32(projected[base + channel]);
+                const float c = bf16_to_f32(projected[base + hidden + channel]);
+                const float x = bf16_to_f32(projected[base + hidden * 2 + channel]);
+                const float gated = b * x;
+                const float convolved = w0 * state0 + w1 * state1 + w2 * gated;
+                output[token * hidden + channel] = f32_to_bf16(c * convolved);
+                state0 = state1;
+                state1 = gated;
+            }
+            state[0] = f32_to_bf16(state0);
+            state[1] = f32_to_bf16(state1);
+        }
+    }
+}
+
+/*
+ * Hybrid ragged attention of a mixed prefill / decode step.  Follows kernels/attention.cu:389-558
+ * (hybrid_ragged_gqa_lfm2_bf16_body) for everything but the order of floating-point operations: token t belongs
+ * to the segment [segment_offsets[s], segment_offsets[s+1]) that contains it (segment 0's start if none does);
+ * with current_offset = t - segment_begin and prefix = position_ids[t] - current_offset it attends to
+ *   keys 0 .. prefix-1            of the paged cache, through block_tables[request_slots[t]], and
+ *   tokens segment_begin .. t     of the contiguous current_key / current_value [T, 8, 64],
+ * scale 0.125, kv head = q head / 4, exact two-pass softmax in double, O = bf16(acc / denominator).
+ * A token whose position is smaller than its offset, or that meets a block-table entry >= num_pages, leaves
+ * its output rows untouched.  `exact_out` (may be NULL) receives the unrounded result.
+ */
+void oracle_hybrid_ragged_attention(const uint16_t* query, const uint16_t* current_key,
+                                    const uint16_t* current_value, const uint16_t* key_cache,
+                                    const uint16_t* value_cache, const uint32_t* block_tables,
+                                    const uint32_t* request_slots, const uint32_t* position_ids,
+                                    const uint32_t* segment_offsets, uint16_t* output, double* exact_out,
+                                    size_t num_tokens, size_t num_pages, size_t block_table_stride,
+                                    size_t num_segments, size_t page_size) {
+#pragma omp parallel for schedule(dynamic, 1) collapse(2)
+    for (size_t token = 0; token < num_tokens; ++token) {
+        for (size_t q_head = 0; q_head < Q_HEADS; ++q_head) {
+            const size_t kv_head = q_head / Q_PER_KV;
+            size_t segment_begin = 0;
+            for (size_t segment = 0; segment < num_segments; ++segment) {
+                if (token >= segment_offsets[segment] && token < segment_offsets[segment + 1]) {
+                    segment_begin = segment_offsets[segment];
+                    break;
+                }
+            }
+            const size_t position = position_ids[token];
+            const size_t current_offset = token - segment_begin;
+            if (position < current_offset) {
+                continue;
+            }
+            const size_t prefix = position - current_offset;
+            const uint32_t* table = block_tables + (size_t)request_slots[token] * block_table_stride;
+            const size_t count = prefix + current_offset + 1;
+            double* scores = (double*)malloc(count * sizeof(double));
+            const uint16_t** value_rows = (const uint16_t**)malloc(count * sizeof(const uint16_t*));
+            const uint16_t* q_row = query + (token * Q_HEADS + q_head) * HEAD_DIM;
+            double maximum = -INFINITY;
+            int valid = 1;
+            for (size_t index = 0; index < count && valid; ++index) {
+                const uint16_t* k_row;
+                if (index < prefix) {
+                    const size_t physical_page = table[index / page_size];
+                    if (physical_page >= num_pages) {
+                        valid = 0;
+                        break;
+                    }
+                    const size_t at = cache_index(physical_page, kv_head, index % page_size, 0, page_size);
+                    k_row = key_cache + at;
+                    value_rows[index] = value_cache + at;
+                } else {
+                    const size_t at = ((segment_begin + (index - prefix)) * KV_HEADS + kv_head) * HEAD_DIM;
+                    k_row = current_key + at;
+                    value_rows[index] = current_value + at;
+                }
+                double dot = 0.0;
+                for (int dim = 0; dim < HEAD_DIM; ++dim) {
+                    dot += (double)bf16_to_f32(q_row[dim]) * (double)bf16_to_f32(k_row[dim]);
+                }
+                scores[index] = dot * ATTN_SCALE;
+                if (scores[index] > maximum) {
+                    maximum = scores[index];
+                }
+            }
+            if (valid) {
+                double accumulator[HEAD_DIM] = {0.0};
+                double denominator = 0.0;
+                for (size_t index = 0; index < count; ++index) {
+                    const double weight = exp(scores[index] - maximum);
+                    denominator += weight;
+                    for (int dim = 0; dim < HEAD_DIM; ++dim) {
+                        accumulator[dim] += weight * (double)bf16_to_f32(value_rows[index][dim]);
+                    }
+                }
+                const size_t base = (token * Q_HEADS + q_head) * HEAD_DIM;
+                for (int dim = 0; dim < HEAD_DIM; ++dim) {
+                    const double value = accumulator[dim] / denominator;
+                    if (exact_out) {
+                        exact_out[base + dim] = value;
+                    }
+                    output[base + dim] = f32_to_bf16((float)value);
+                }
+            }
+            free(scores);
+            free(value_rows);
+        }
+    }
+}
+
+/*
  * Greedy argmax per row with the legacy tie order.  Follows kernels/sampling.cu:53-134: the winner is the largest
  * value; among equal values the smaller (column % 256) wins, then the smaller (column / 256); NaN and -inf never
  * win (a row of only those answers 0); +0 and -0 are equal.

@@ -71,6 +71,10 @@ def lib() -> ctypes.CDLL:
     handle.oracle_rms_norm_bf16.argtypes = [_u16p, _u16p, _u16p, _size, _size, ctypes.c_float]
     handle.oracle_residual_rms_norm_bf16.argtypes = [_u16p, _u16p, _u16p, _u16p, _u16p, _size, _size, ctypes.c_float]
     handle.oracle_short_conv_decode_bf16.argtypes = [_u16p, _u16p, _u16p, _u32p, _u16p, _size, _size, _size]
+    handle.oracle_short_conv_segmented_bf16.argtypes = [_u16p, _u16p, _u16p, _u32p, _u32p, _u16p, _size, _size, _size]
+    handle.oracle_hybrid_ragged_attention.argtypes = [
+        _u16p, _u16p, _u16p, _u16p, _u16p, _u32p, _u32p, _u32p, _u32p, _u16p, ctypes.c_void_p, _size, _size, _size,
+        _size, _size]
     handle.oracle_argmax_rows_bf16.argtypes = [_u16p, _u32p, _size, _size]
     handle.oracle_linear_bf16.argtypes = [_u16p, _u16p, _u16p, _size, _size, _size]
     handle.oracle_num_threads.restype = ctypes.c_int
@@ -279,6 +283,41 @@ def short_conv_decode_bf16(projected, weight, states, request_slots) -> np.ndarr
                                         np.ascontiguousarray(request_slots, dtype=np.uint32), output, tokens, hidden,
                                         states.shape[0])
     return output
+
+
+def short_conv_segmented_bf16(projected, weight, states, segment_offsets, segment_slots) -> np.ndarray:
+    """projected [T, 3H], weight [H, 3], states [slots, H, 2] (updated in place), segment_offsets [S+1],
+    segment_slots [S]; returns output [T, H] (rows of skipped segments stay zero)."""
+    projected = np.ascontiguousarray(projected, dtype=np.uint16)
+    tokens = projected.shape[0]
+    hidden = projected.shape[1] // 3
+    output = np.zeros((tokens, hidden), dtype=np.uint16)
+    segment_slots = np.ascontiguousarray(segment_slots, dtype=np.uint32)
+    lib().oracle_short_conv_segmented_bf16(projected, np.ascontiguousarray(weight, dtype=np.uint16), states,
+                                           np.ascontiguousarray(segment_offsets, dtype=np.uint32), segment_slots,
+                                           output, segment_slots.size, hidden, states.shape[0])
+    return output
+
+
+def hybrid_ragged_attention(query, current_key, current_value, key_cache, value_cache, block_tables, request_slots,
+                            position_ids, segment_offsets, page_size: int = 16, output=None,
+                            want_exact: bool = False):
+    """Mixed prefill / decode attention: paged prefix + the contiguous K/V of the token's own segment.
+    Returns bf16 output [T,32,64] (and the unrounded float64 result when asked); `output` may be passed in to
+    observe which rows skipped tokens leave untouched."""
+    block_tables = np.ascontiguousarray(block_tables, dtype=np.uint32)
+    num_tokens = query.shape[0]
+    if output is None:
+        output = np.zeros((num_tokens, 32, 64), dtype=np.uint16)
+    exact = np.zeros((num_tokens, 32, 64), dtype=np.float64) if want_exact else None
+    segment_offsets = np.ascontiguousarray(segment_offsets, dtype=np.uint32)
+    lib().oracle_hybrid_ragged_attention(
+        np.ascontiguousarray(query, dtype=np.uint16), np.ascontiguousarray(current_key, dtype=np.uint16),
+        np.ascontiguousarray(current_value, dtype=np.uint16), key_cache, value_cache, block_tables,
+        np.ascontiguousarray(request_slots, dtype=np.uint32), np.ascontiguousarray(position_ids, dtype=np.uint32),
+        segment_offsets, output, exact.ctypes.data if want_exact else None, num_tokens, key_cache.shape[0],
+        block_tables.shape[1], segment_offsets.size - 1, page_size)
+    return (output, exact) if want_exact else output
 
 
 def argmax_rows_bf16(logits) -> np.ndarray:

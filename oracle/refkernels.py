@@ -134,3 +134,24 @@ def silu_mul_packed_bf16_to_e4m3(packed, output, scale: float) -> None:
     blocks = max(1, min((rows * width // 4 + _BLOCK - 1) // _BLOCK, 65535))
     _launch("silu_mul", "silu_mul_packed_bf16_to_e4m3", blocks,
             [packed, output, _sz(rows), _sz(width // 2), ctypes.c_float(scale)])
+
+
+def hybrid_ragged_attention(query, current_key, current_value, key_cache, value_cache, block_tables, request_slots,
+                            position_ids, segment_offsets, output) -> None:
+    """kernels/attention.cu `hybrid_ragged_gqa_lfm2_bf16_ps16` (the reference's mixed prefill / decode attention),
+    grid = tokens * 8 as in src/cuda/kernels/attention.rs:211."""
+    tokens = query.shape[0]
+    _launch("attention", "hybrid_ragged_gqa_lfm2_bf16_ps16", tokens * 8,
+            [query, current_key, current_value, key_cache, value_cache, block_tables, request_slots, position_ids,
+             segment_offsets, output, _sz(tokens), _sz(key_cache.shape[0]), _sz(block_tables.shape[1]),
+             _sz(segment_offsets.numel() - 1)])
+
+
+def short_conv_segmented(projected, weight, states, segment_offsets, segment_slots, output) -> None:
+    """kernels/short_conv.cu `short_conv_segmented_lfm2_bf16` (grid-stride over segments * hidden)."""
+    hidden = weight.shape[0]
+    segments = segment_slots.numel()
+    blocks = max(1, min((segments * hidden + _BLOCK - 1) // _BLOCK, 65535))
+    _launch("short_conv", "short_conv_segmented_lfm2_bf16", blocks,
+            [projected, weight, states, segment_offsets, segment_slots, output, _sz(segments), _sz(hidden),
+             _sz(states.shape[0])])

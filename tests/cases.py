@@ -101,3 +101,45 @@ def fp8_inputs(seed=21, rows=5, width=1000):
                                                          dtype=np.float32))
     packed = workloads.bf16_normal(rng, (rows, 2 * width), std=2.0)
     return values, packed
+
+
+def hybrid_known_answer_case():
+    """src/ops/attention_regression_tests.rs:64-111: zero queries and keys, a prefix of two cached tokens with
+    V = 2 and a current chunk of two tokens with V = 6; the outputs are the plain means 10/3 and 4."""
+    prefix_value = oracle.f32_to_bf16(np.full((2, 8, 64), 2.0, dtype=np.float32))
+    key_cache, value_cache = write_cache(np.zeros((2, 8, 64), dtype=np.uint16), prefix_value, [0, 1], 1)
+    return dict(query=np.zeros((2, 32, 64), dtype=np.uint16), current_key=np.zeros((2, 8, 64), dtype=np.uint16),
+                current_value=oracle.f32_to_bf16(np.full((2, 8, 64), 6.0, dtype=np.float32)),
+                key_cache=key_cache, value_cache=value_cache, block_tables=np.zeros((1, 1), dtype=np.uint32),
+                request_slots=np.zeros(2, dtype=np.uint32), position_ids=np.array([2, 3], dtype=np.uint32),
+                segment_offsets=np.array([0, 2], dtype=np.uint32))
+
+
+def mixed_step_case(seed, prefixes, chunks, pages):
+    """Seeded N(0,1) mixed prefill / decode step: prefixes in the paged cache (NaN patterns everywhere else),
+    the step's own K/V contiguous."""
+    rng = np.random.default_rng(seed)
+    batch = workloads.mixed_step_batch(seed, prefixes, chunks, pages)
+    key_cache, value_cache = workloads.fill_prefixes(rng, batch)
+    tokens = batch.num_tokens
+    return dict(batch=batch, query=workloads.bf16_normal(rng, (tokens, 32, 64)),
+                current_key=workloads.bf16_normal(rng, (tokens, 8, 64)),
+                current_value=workloads.bf16_normal(rng, (tokens, 8, 64)), key_cache=key_cache,
+                value_cache=value_cache, block_tables=batch.block_tables, request_slots=batch.request_slots,
+                position_ids=batch.positions, segment_offsets=batch.segment_offsets)
+
+
+# (prefixes, chunks): page-aligned and ragged prefixes, chunks shorter and longer than a page and than a query
+# tile, decode tokens (chunk 1) among prefill chunks, an empty prefix
+MIXED_SMALL = ([0, 16, 5, 40, 33, 7], [1, 16, 37, 1, 3, 70])
+
+
+def short_conv_segmented_case(seed=31, hidden=256):
+    rng = np.random.default_rng(seed)
+    chunks = np.array([1, 5, 1, 12, 2], dtype=np.int64)
+    tokens = int(chunks.sum())
+    return dict(projected=workloads.bf16_normal(rng, (tokens, 3 * hidden)),
+                weight=workloads.bf16_normal(rng, (hidden, 3), std=0.5),
+                states=workloads.bf16_normal(rng, (7, hidden, 2)),
+                segment_offsets=np.concatenate([[0], np.cumsum(chunks)]).astype(np.uint32),
+                segment_slots=np.array([3, 0, 9, 6, 1], dtype=np.uint32))      # slot 9 is beyond the table: skipped

@@ -79,6 +79,28 @@ def main(path):
     refkernels.silu_mul_packed_bf16_to_e4m3(to_bf16(packed, device), fused, 9.75)
     golden["silu_codes"] = fused.cpu().numpy()
 
+    # mixed prefill / decode step: the reference's hybrid attention and segmented short convolution
+    hybrid_cases = {"hybrid_known": cases.hybrid_known_answer_case(),
+                    "hybrid_mixed": cases.mixed_step_case(5, *cases.MIXED_SMALL, 64)}
+    for name, case in hybrid_cases.items():
+        case.pop("batch", None)
+        output = torch.zeros(case["query"].shape, dtype=torch.bfloat16, device=device)
+        refkernels.hybrid_ragged_attention(
+            to_bf16(case["query"], device), to_bf16(case["current_key"], device),
+            to_bf16(case["current_value"], device), to_bf16(case["key_cache"], device),
+            to_bf16(case["value_cache"], device), to_u32(case["block_tables"], device),
+            to_u32(case["request_slots"], device), to_u32(case["position_ids"], device),
+            to_u32(case["segment_offsets"], device), output)
+        golden[name] = bits_of(output)
+    case = cases.short_conv_segmented_case()
+    states = to_bf16(case["states"], device)
+    output = torch.zeros((case["projected"].shape[0], case["weight"].shape[0]), dtype=torch.bfloat16, device=device)
+    refkernels.short_conv_segmented(to_bf16(case["projected"], device), to_bf16(case["weight"], device), states,
+                                    to_u32(case["segment_offsets"], device), to_u32(case["segment_slots"], device),
+                                    output)
+    golden["conv_segmented_output"] = bits_of(output)
+    golden["conv_segmented_states"] = bits_of(states)
+
     torch.cuda.synchronize()
     np.savez_compressed(path, **golden)
     print(f"wrote {len(golden)} arrays to {path}")

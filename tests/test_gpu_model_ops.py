@@ -79,6 +79,37 @@ def test_short_conv_decode(device):
     assert np.array_equal(bits_of(states_device), want_states)       # products of two bf16 values round identically
 
 
+def test_short_conv_segmented(device):
+    """Segments of 1..12 tokens, one slot beyond the state table; bit-exact against the oracle, and a segment of
+    one token equals the decode kernel."""
+    import cases
+    case = cases.short_conv_segmented_case(hidden=2048)
+    want_states = case["states"].copy()
+    want = oracle.short_conv_segmented_bf16(case["projected"], case["weight"], want_states, case["segment_offsets"],
+                                            case["segment_slots"])
+    states = to_bf16(case["states"], device)
+    output = torch.zeros((case["projected"].shape[0], 2048), dtype=torch.bfloat16, device=device)
+    ops.short_conv_segmented_lfm2_bf16_into(to_bf16(case["projected"], device), to_bf16(case["weight"], device),
+                                            states, to_u32(case["segment_offsets"], device),
+                                            to_u32(case["segment_slots"], device), output)
+    assert np.array_equal(bits_of(output), want)
+    assert np.array_equal(bits_of(states), want_states)
+
+
+def test_gather_rows(device):
+    rng = np.random.default_rng(9)
+    values = workloads.bf16_normal(rng, (11, 2048))
+    rows = np.array([10, 0, 3, 99, 3], dtype=np.uint32)              # 99 is beyond the input: row left as is
+    output = torch.full((5, 2048), 7.0, dtype=torch.bfloat16, device=device)
+    ops.gather_rows_bf16_into(to_bf16(values, device), to_u32(rows, device), output)
+    got = bits_of(output)
+    for row, source in enumerate(rows):
+        if source < 11:
+            assert np.array_equal(got[row], values[source])
+        else:
+            assert (got[row] == bits_of(torch.tensor([7.0], dtype=torch.bfloat16))[0]).all()
+
+
 def test_argmax_tie_order(device):
     # src/ops/sampling.rs:105-182: ties, NaN, -inf, +-0, low-cardinality rows over the full vocabulary
     rng = np.random.default_rng(6)

@@ -80,3 +80,25 @@ def test_fp8_producers(golden):
     hidden, codes = oracle.silu_mul_packed(packed, 9.75)
     assert (hidden != golden["silu_hidden"]).mean() <= 1e-3
     assert (codes != golden["silu_codes"]).mean() <= 1e-3
+
+
+def test_hybrid_attention(golden):
+    """kernels/attention.cu hybrid_ragged_gqa_lfm2_bf16_ps16 (expf, sequential online softmax) against the exact
+    oracle: one bf16 step, as for the reference's precise paged kernel."""
+    for name, case in (("hybrid_known", cases.hybrid_known_answer_case()),
+                       ("hybrid_mixed", cases.mixed_step_case(5, *cases.MIXED_SMALL, 64))):
+        if name not in golden:
+            pytest.skip("fixture predates the mixed-step cases")
+        case.pop("batch", None)
+        assert_close_bf16(golden[name], oracle.hybrid_ragged_attention(**case), 1e-6, 2 ** -7)
+
+
+def test_short_conv_segmented(golden):
+    if "conv_segmented_output" not in golden:
+        pytest.skip("fixture predates the mixed-step cases")
+    case = cases.short_conv_segmented_case()
+    states = case["states"].copy()
+    output = oracle.short_conv_segmented_bf16(case["projected"], case["weight"], states, case["segment_offsets"],
+                                              case["segment_slots"])
+    assert np.array_equal(golden["conv_segmented_output"], output)
+    assert np.array_equal(golden["conv_segmented_states"], states)

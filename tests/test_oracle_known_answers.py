@@ -10,6 +10,7 @@ import pytest
 from lfm25_inference_b200 import workloads
 from oracle import oracle
 
+import cases
 from conftest import assert_close_bf16
 
 
@@ -341,3 +342,72 @@ def test_qk_postprocess_against_plain_formulas():
     oracle.qk_norm_rope_kv_write_decode(untouched, key, value, q_norm, k_norm, inv_freq, positions,
                                         np.full(tokens, -1, dtype=np.int64), key_cache.copy(), value_cache.copy(), 1e-5)
     assert np.array_equal(untouched, query)
+
+
+def test_hybrid_attention_uses_paged_prefix_and_contiguous_current_chunk():
+    # src/ops/attention_regression_tests.rs:64-111
+    case = cases.hybrid_known_answer_case()
+    output = oracle.bf16_to_f32(oracle.hybrid_ragged_attention(**case))
+    assert np.abs(output[0] - 10.0 / 3.0).max() < 0.02
+    assert np.abs(output[1] - 4.0).max() < 0.02
+
+
+def test_hybrid_attention_equals_paged_attention_after_the_append():
+    """Appending the step's K/V to the cache and attending through the block tables is the same function."""
+    prefixes, chunks = cases.MIXED_SMALL
+    case = cases.mixed_step_case(5, prefixes, chunks, 64)
+    batch = case.pop("batch")
+    _, hybrid = oracle.hybrid_ragged_attention(**case, want_exact=True)
+    key_cache, value_cache = case["key_cache"].copy(), case["value_cache"].copy()
+    oracle.kv_cache_write(case["current_key"], case["current_value"], key_cache, value_cache, batch.physical_slots)
+    _, paged = oracle.paged_ragged_attention(case["query"], key_cache, value_cache, case["block_tables"],
+                                             case["request_slots"], case["position_ids"], want_exact=True)
+    assert np.isfinite(hybrid).all()          # no NaN-pattern row of the pool was read
+    assert np.abs(hybrid - paged).max() < 1e-12
+
+
+def test_hybrid_attention_skips_inconsistent_tokens():
+    # kernels/attention.cu:419-423 (position < offset) and :465-468 (unassigned page)
+    prefixes, chunks = [20, 3], [4, 2]
+    case = cases.mixed_step_case(6, prefixes, chunks, 16)
+    case.pop("batch")
+    positions = case["position_ids"].copy()
+    positions[2] = 1                          # third token of its segment cannot sit at position 1
+    tables = case["block_tables"].copy()
+    tables[case["request_slots"][4], 0] = 0xFFFFFFFF
+    sentinel = np.full((6, 32, 64), 0x1234, dtype=np.uint16)
+    got = oracle.hybrid_ragged_attention(case["query"], case["current_key"], case["current_value"],
+                                         case["key_cache"], case["value_cache"], tables, case["request_slots"],
+                                         positions, case["segment_offsets"], output=sentinel.copy())
+    untouched = [bool((got[token] == 0x1234).all()) for token in range(6)]
+    assert untouched == [False, False, True, False, True, True]
+
+
+def test_short_conv_segmented_equals_token_steps_with_fp32_carry():
+    """kernels/short_conv.cu:100-143: inside a segment the state is carried unrounded."""
+    case = cases.short_conv_segmented_case()
+    states = case["states"].copy()
+    got = oracle.short_conv_segmented_bf16(case["projected"], case["weight"], states, case["segment_offsets"],
+                                           case["segment_slots"])
+    hidden = case["weight"].shape[0]
+    projected = oracle.bf16_to_f32(case["projected"]).astype(np.float32)
+    weight = oracle.bf16_to_f32(case["weight"]).astype(np.float32)
+    want_states = case["states"].copy()
+    want = np.zeros_like(got)
+    for segment, slot in enumerate(case["segment_slots"]):
+        if slot >= want_states.shape[0]:
+            continue
+        state = oracle.bf16_to_f32(want_states[slot]).astype(np.float32)
+        s0, s1 = state[:, 0].copy(), state[:, 1].copy()
+        for token in range(case["segment_offsets"][segment], case["segment_offsets"][segment + 1]):
+            b, c, x = (projected[token, :hidden], projected[token, hidden:2 * hidden], projected[token, 2 * hidden:])
+            gated = b * x
+            convolved = (weight[:, 0] * s0 + weight[:, 1] * s1) + weight[:, 2] * gated
+            want[token] = oracle.f32_to_bf16(c * convolved)
+            s0, s1 = s1, gated
+        want_states[slot, :, 0] = oracle.f32_to_bf16(s0)
+        want_states[slot, :, 1] = oracle.f32_to_bf16(s1)
+    assert np.array_equal(got, want)
+    assert np.array_equal(states, want_states)
+    skipped = slice(int(case["segment_offsets"][2]), int(case["segment_offsets"][3]))
+    assert not got[skipped].any()
