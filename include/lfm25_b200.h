@@ -439,6 +439,35 @@ void lfm25_decode_executor_destroy(lfm25_decode_executor* executor);
  * on the BlasLt handle's stream; sampled ids land in the executor's `sampled` buffer. */
 int32_t lfm25_decode_executor_forward(lfm25_decode_executor* executor, const lfm25_model* model,
                                       const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance);
+/* Device-resident metadata of a step that mixes prefill chunks and decode tokens (GpuBatch after
+ * update_segments, src/scheduler/batch.rs:126-215): segment s holds tokens [segment_offsets[s],
+ * segment_offsets[s+1]) of the sequence in request slot segment_slots[s], at consecutive positions;
+ * output_rows[s] is the row of its last token.  physical_slots is written by the step. */
+typedef struct lfm25_ragged_batch {
+    const uint32_t* token_ids;       /* u32 [num_tokens] */
+    const uint32_t* positions;       /* u32 [num_tokens] */
+    const uint32_t* request_slots;   /* u32 [num_tokens] */
+    int64_t* physical_slots;         /* i64 [num_tokens], written */
+    const uint32_t* segment_offsets; /* u32 [num_segments + 1] */
+    const uint32_t* segment_slots;   /* u32 [num_segments] */
+    const uint32_t* output_rows;     /* u32 [num_segments] */
+    const uint32_t* block_tables;    /* u32 [block_table_rows, block_table_stride] */
+    size_t block_table_stride;
+    size_t block_table_rows;
+    size_t num_tokens;
+    size_t num_segments;
+} lfm25_ragged_batch;
+/* An executor for steps of up to maximum_tokens tokens (<= 8192) in up to maximum_segments sequences (<= 256):
+ * lfm25_decode_executor_create is the case maximum_tokens == maximum_segments. */
+int32_t lfm25_decode_executor_create_ragged(lfm25_blaslt* blaslt, size_t maximum_tokens, size_t maximum_segments,
+                                            lfm25_decode_executor** out);
+/* Lfm2Model::forward_prepared_batch (src/model/lfm2_base.rs:924-997) for a mixed step: embedding, 16 layers
+ * (segmented short conv; q/k/v, fused QK-norm + RoPE + paged append of every token, hybrid ragged attention over
+ * the cache), logits and greedy ids for each segment's last token: row s of the executor's `logits` / `sampled`
+ * belongs to segment s.  FP8 sites are used for steps of up to 256 tokens; larger steps run in BF16, as the
+ * reference does above its maximum FP8 batch. */
+int32_t lfm25_decode_executor_forward_ragged(lfm25_decode_executor* executor, const lfm25_model* model,
+                                             const lfm25_ragged_batch* batch, uint32_t use_fp8);
 /* The same step replayed from a CUDA graph captured per (batch size, model, batch buffers, flags): the first call
  * of a bucket runs eagerly, the second captures, later ones only launch the graph.  With advance != 0 the step
  * feeds itself (ids and positions move on the device); with advance == 0 the caller refreshes the metadata

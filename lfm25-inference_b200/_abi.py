@@ -80,6 +80,15 @@ class DecodeBatch(ctypes.Structure):
                 ("num_tokens", ctypes.c_size_t), ("max_context_tokens", ctypes.c_size_t)]
 
 
+class RaggedBatch(ctypes.Structure):
+    _fields_ = [("token_ids", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("request_slots", ctypes.c_void_p),
+                ("physical_slots", ctypes.c_void_p), ("segment_offsets", ctypes.c_void_p),
+                ("segment_slots", ctypes.c_void_p), ("output_rows", ctypes.c_void_p),
+                ("block_tables", ctypes.c_void_p), ("block_table_stride", ctypes.c_size_t),
+                ("block_table_rows", ctypes.c_size_t), ("num_tokens", ctypes.c_size_t),
+                ("num_segments", ctypes.c_size_t)]
+
+
 class Fp8Site(ctypes.Structure):
     _fields_ = [("data", ctypes.c_void_p), ("activation_quantize", ctypes.c_float),
                 ("activation_dequantize", ctypes.c_float), ("weight_dequantize", ctypes.c_float)]
@@ -167,6 +176,9 @@ PROTOTYPES = {
     "lfm25_argmax_rows_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),
     "lfm25_decode_step_metadata": (ctypes.c_int32, [_stream, _P(DecodeBatch), Slice, _size, ctypes.c_uint32]),
     "lfm25_decode_executor_create": (ctypes.c_int32, [ctypes.c_void_p, _size, _P(ctypes.c_void_p)]),
+    "lfm25_decode_executor_create_ragged": (ctypes.c_int32, [ctypes.c_void_p, _size, _size, _P(ctypes.c_void_p)]),
+    "lfm25_decode_executor_forward_ragged": (
+        ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(RaggedBatch), ctypes.c_uint32]),
     "lfm25_decode_executor_destroy": (None, [ctypes.c_void_p]),
     "lfm25_decode_executor_graph_kernels": (ctypes.c_size_t, [ctypes.c_void_p]),
     "lfm25_decode_executor_forward": (

@@ -33,6 +33,7 @@ constexpr size_t kVocab = 65536;
 struct lfm25_decode_executor {
     lfm25_blaslt* blaslt;
     size_t maximum_tokens;
+    size_t maximum_rows;   // rows that get logits in one step (= sequences in it): decode tokens / segments
     void* allocation;
     // scratch, fixed addresses (src/model/decode_executor.rs:6-22)
     void* hidden;
@@ -48,6 +49,7 @@ struct lfm25_decode_executor {
     void* fp8_input;
     float* partials;
     uint32_t* sampled;
+    void* head_input;      // [maximum_rows, 2048]: the rows that go to the LM head in a mixed step
     // opt-in region timing (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): CUDA-event pairs
     // around every op of an eager step, summed per region
     bool profiling = false;
@@ -230,7 +232,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 fused.block_tables = slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
                 fused.request_slots = slice_of(batch->request_slots, tokens);
                 fused.block_table_stride = batch->block_table_stride;
-                fused.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_tokens));
+                fused.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
                 fused.num_splits = splits;
                 fused.query_token_stride = 0;
                 fused.kv_token_stride = 0;
@@ -259,7 +261,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             attention.block_tables = slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
             attention.request_slots = slice_of(batch->request_slots, tokens);
             attention.position_ids = post.position_ids;
-            attention.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_tokens));
+            attention.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
             attention.output = slice_of(self->post_operator, tokens * kHidden);
             attention.num_tokens = tokens;
             attention.num_pages = model->num_pages;
@@ -355,11 +357,171 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
     return LFM25_OK;
 }
 
+// The mixed prefill / decode step: Lfm2Model::forward_prepared_batch (src/model/lfm2_base.rs:924-997) with
+// attention_batch's prefill branch (:1794-1829) and short_conv_batch (:1511-1530).  Differences from that op list:
+// QK-norm, RoPE and the paged append are the one fused kernel of the decode route, applied to every token, and the
+// attention kernel then reads all keys through the block tables (the chunk is already in the cache).
+int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, const lfm25_ragged_batch* batch,
+                       bool use_fp8) {
+    cudaStream_t stream = self->blaslt->stream;
+    const size_t tokens = batch->num_tokens;
+    const size_t segments = batch->num_segments;
+    // FP8 sites only up to the batch the FP8 GEMM covers, as the reference does with maximum_fp8_batch
+    // (src/model/lfm2_base.rs:929); larger steps run every site in BF16
+    use_fp8 = use_fp8 && tokens <= 256;
+    cudaError_t status = cudaSuccess;
+    {
+        RegionTimer timer(self, LFM25_REGION_OTHER);
+        status = lfm25::launch_decode_metadata(stream, const_cast<uint32_t*>(batch->token_ids),
+                                               const_cast<uint32_t*>(batch->positions), batch->request_slots,
+                                               batch->block_tables, self->sampled, batch->physical_slots, tokens,
+                                               batch->block_table_stride, batch->block_table_rows, model->num_pages,
+                                               false);
+        if (status != cudaSuccess) return cuda_failure(status, "step metadata launch failed");
+        status = lfm25::launch_embedding_bf16(stream, batch->token_ids, model->embedding, self->hidden, tokens, kVocab,
+                                              kHidden);
+        if (status != cudaSuccess) return cuda_failure(status, "embedding launch failed");
+        status = lfm25::launch_rms_norm_bf16(stream, self->hidden, model->layers[0].operator_norm, self->normalized,
+                                             tokens, kHidden, model->norm_eps);
+        if (status != cudaSuccess) return cuda_failure(status, "rms_norm launch failed");
+    }
+    for (uint32_t index = 0; index < model->num_layers; ++index) {
+        const lfm25_layer& layer = model->layers[index];
+        if (!layer.is_attention) {
+            LFM25_TRY(linear_decode(self, layer.conv_input, self->normalized, self->wide, tokens, use_fp8));
+            {
+                RegionTimer timer(self, LFM25_REGION_OTHER);
+                status = lfm25::launch_short_conv_segmented(stream, self->wide, layer.conv_kernel, layer.conv_state,
+                                                            batch->segment_offsets, batch->segment_slots,
+                                                            self->post_operator, tokens, segments, kHidden,
+                                                            model->num_request_slots);
+            }
+            if (status != cudaSuccess) return cuda_failure(status, "segmented short_conv launch failed");
+            LFM25_TRY(linear_decode(self, layer.conv_output, self->post_operator, self->operator_output, tokens,
+                                    use_fp8));
+        } else {
+            LFM25_TRY(linear_decode(self, layer.query, self->normalized, self->query, tokens, use_fp8));
+            LFM25_TRY(linear_decode(self, layer.key, self->normalized, self->key, tokens, use_fp8));
+            LFM25_TRY(linear_decode(self, layer.value, self->normalized, self->value, tokens, use_fp8));
+            const size_t cache_elements = model->num_pages * 8 * 16 * 64;
+            lfm25_qk_postprocess_launch post;
+            post.page_size = 16;
+            post.query = slice_of(self->query, tokens * kQueryWidth);
+            post.key = slice_of(self->key, tokens * kKvWidth);
+            post.value = slice_of(self->value, tokens * kKvWidth);
+            post.query_norm = slice_of(layer.query_norm, 64);
+            post.key_norm = slice_of(layer.key_norm, 64);
+            post.inv_freq = slice_of(model->inv_freq, 32);
+            post.position_ids = slice_of(batch->positions, tokens);
+            post.slot_mapping = slice_of(batch->physical_slots, tokens);
+            post.key_cache = slice_of(layer.key_cache, cache_elements);
+            post.value_cache = slice_of(layer.value_cache, cache_elements);
+            post.num_tokens = tokens;
+            post.num_pages = model->num_pages;
+            post.eps = model->norm_eps;
+            {
+                RegionTimer timer(self, LFM25_REGION_APPEND);
+                LFM25_TRY(lfm25_qk_norm_rope_kv_write_decode(stream, &post));
+            }
+            {
+                RegionTimer timer(self, LFM25_REGION_ATTENTION);
+                lfm25_hybrid_attention_launch attention;
+                attention.page_size = 16;
+                attention.query = post.query;
+                attention.current_key = slice_of(nullptr, 0);
+                attention.current_value = slice_of(nullptr, 0);
+                attention.key_cache = post.key_cache;
+                attention.value_cache = post.value_cache;
+                attention.block_tables = slice_of(batch->block_tables,
+                                                  batch->block_table_stride * batch->block_table_rows);
+                attention.request_slots = slice_of(batch->request_slots, tokens);
+                attention.position_ids = post.position_ids;
+                attention.segment_offsets = slice_of(batch->segment_offsets, segments + 1);
+                attention.output = slice_of(self->post_operator, tokens * kHidden);
+                attention.num_tokens = tokens;
+                attention.num_pages = model->num_pages;
+                attention.block_table_stride = batch->block_table_stride;
+                attention.num_segments = segments;
+                attention.query_token_stride = 0;
+                attention.kv_token_stride = 0;
+                LFM25_TRY(lfm25_hybrid_ragged_attention_lfm2_bf16(stream, &attention));
+            }
+            LFM25_TRY(linear_decode(self, layer.output, self->post_operator, self->operator_output, tokens, use_fp8));
+        }
+
+        const bool gate_up_fp8 = use_fp8 && layer.gate_up.fp8.data != nullptr && layer.gate_up.k == kHidden;
+        {
+            RegionTimer timer(self, LFM25_REGION_OTHER);
+            status = lfm25::launch_residual_rms_norm_bf16(
+                stream, self->hidden, self->operator_output, layer.ffn_norm, self->post_operator, self->normalized,
+                tokens, kHidden, model->norm_eps, gate_up_fp8 ? self->fp8_input : nullptr,
+                gate_up_fp8 ? layer.gate_up.fp8.activation_quantize : 1.0f);
+        }
+        if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
+        LFM25_TRY(linear_decode(self, layer.gate_up, self->normalized, self->wide, tokens, use_fp8, gate_up_fp8));
+        if (use_fp8 && layer.down.fp8.data != nullptr) {
+            RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
+            LFM25_TRY(lfm25_silu_mul_packed_bf16_to_e4m3(stream, slice_of(self->wide, tokens * 2 * kFfn),
+                                                         slice_of(self->fp8_input, self->maximum_tokens * kFfn),
+                                                         tokens, kFfn, layer.down.fp8.activation_quantize));
+            lfm25_fp8_linear_config config;
+            config.m = tokens;
+            config.n = kHidden;
+            config.k = kFfn;
+            config.scale_mode = LFM25_FP8_SCALE_TENSORWIDE;
+            config.output_scale = layer.down.fp8.activation_dequantize * layer.down.fp8.weight_dequantize;
+            LFM25_TRY(lfm25_blaslt_linear_fp8_scaled(self->blaslt, slice_of(self->fp8_input, tokens * kFfn),
+                                                     slice_of(layer.down.fp8.data, kHidden * kFfn),
+                                                     slice_of(self->operator_output, tokens * kHidden), &config));
+        } else {
+            RegionTimer timer(self, LFM25_REGION_BF16_LINEAR);
+            LFM25_TRY(lfm25_silu_mul_packed_bf16(stream, slice_of(self->wide, tokens * 2 * kFfn),
+                                                 slice_of(self->activated, tokens * kFfn), tokens, kFfn));
+            if (layer.down.bf16 == nullptr) {
+                return lfm25::report_error(LFM25_ERR_NULL_POINTER, "Down site has no BF16 weights resident");
+            }
+            LFM25_TRY(lfm25_blaslt_linear_bf16(self->blaslt, slice_of(self->activated, tokens * kFfn),
+                                               slice_of(layer.down.bf16, kHidden * kFfn),
+                                               slice_of(self->operator_output, tokens * kHidden), tokens, kHidden,
+                                               kFfn));
+        }
+        const bool last_layer = index + 1 == model->num_layers;
+        const void* next_norm = last_layer ? model->final_norm : model->layers[index + 1].operator_norm;
+        {
+            RegionTimer timer(self, LFM25_REGION_OTHER);
+            status = lfm25::launch_residual_rms_norm_bf16(stream, self->post_operator, self->operator_output, next_norm,
+                                                          self->hidden, self->normalized, tokens, kHidden,
+                                                          model->norm_eps);
+        }
+        if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
+    }
+
+    // logits only for each segment's last token (gather_rows_bf16 on output_rows, lfm2_base.rs:984)
+    {
+        RegionTimer timer(self, LFM25_REGION_OTHER);
+        status = lfm25::launch_gather_rows_bf16(stream, self->normalized, batch->output_rows, self->head_input, segments,
+                                                tokens, kHidden);
+    }
+    if (status != cudaSuccess) return cuda_failure(status, "gather launch failed");
+    lfm25_linear_weights head;
+    head.bf16 = model->embedding;
+    head.fp8 = model->lm_head_fp8;
+    head.n = kVocab;
+    head.k = kHidden;
+    LFM25_TRY(linear_decode(self, head, self->head_input, self->logits, segments, use_fp8));
+    {
+        RegionTimer timer(self, LFM25_REGION_OTHER);
+        status = lfm25::launch_argmax_rows_bf16(stream, self->logits, self->sampled, segments, kVocab);
+    }
+    if (status != cudaSuccess) return cuda_failure(status, "argmax launch failed");
+    return LFM25_OK;
+}
+
 int32_t validate(const lfm25_decode_executor* self, const lfm25_model* model, const lfm25_decode_batch* batch) {
     if (self == nullptr || model == nullptr || batch == nullptr) {
         return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor received a null argument");
     }
-    if (batch->num_tokens == 0 || batch->num_tokens > self->maximum_tokens) {
+    if (batch->num_tokens == 0 || batch->num_tokens > self->maximum_tokens || batch->num_tokens > self->maximum_rows) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "decode executor token count exceeds workspace");
     }
     if (model->num_layers == 0 || model->layers == nullptr || model->embedding == nullptr ||
@@ -378,11 +540,21 @@ int32_t validate(const lfm25_decode_executor* self, const lfm25_model* model, co
 extern "C" {
 
 int32_t lfm25_decode_executor_create(lfm25_blaslt* blaslt, size_t maximum_tokens, lfm25_decode_executor** out) {
+    if (maximum_tokens == 0 || maximum_tokens > 256) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "decode executor supports 1..=256 tokens per step");
+    }
+    return lfm25_decode_executor_create_ragged(blaslt, maximum_tokens, maximum_tokens, out);
+}
+
+int32_t lfm25_decode_executor_create_ragged(lfm25_blaslt* blaslt, size_t maximum_tokens, size_t maximum_segments,
+                                            lfm25_decode_executor** out) {
     if (blaslt == nullptr || out == nullptr) {
         return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor needs a BlasLt handle and an output");
     }
-    if (maximum_tokens == 0 || maximum_tokens > 256) {
-        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "decode executor supports 1..=256 tokens per step");
+    if (maximum_segments == 0 || maximum_segments > 256 || maximum_tokens < maximum_segments ||
+        maximum_tokens > 8192) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT,
+                                   "executor supports 1..=256 sequences and up to 8192 tokens per step");
     }
     lfm25_decode_executor* self = new (std::nothrow) lfm25_decode_executor();
     if (self == nullptr) {
@@ -390,16 +562,19 @@ int32_t lfm25_decode_executor_create(lfm25_blaslt* blaslt, size_t maximum_tokens
     }
     self->blaslt = blaslt;
     self->maximum_tokens = maximum_tokens;
+    self->maximum_rows = maximum_segments;
     const size_t b = maximum_tokens;
-    const size_t sizes[13] = {
+    const size_t r = maximum_segments;
+    const size_t sizes[14] = {
         b * kHidden * 2, b * kHidden * 2, b * kHidden * 2, b * kHidden * 2,         // hidden .. operator_output
         b * kQueryWidth * 2, b * kKvWidth * 2, b * kKvWidth * 2,                    // query, key, value
-        b * 2 * kFfn * 2, b * kFfn * 2, b * kVocab * 2,                             // wide, activated, logits
+        b * 2 * kFfn * 2, b * kFfn * 2, r * kVocab * 2,                             // wide, activated, logits
         b * kFfn,                                                                   // fp8_input
-        lfm25_splitk_workspace_elements(b) * sizeof(float), b * sizeof(uint32_t)};  // partials, sampled
+        lfm25_splitk_workspace_elements(r) * sizeof(float), r * sizeof(uint32_t),   // partials, sampled
+        r * kHidden * 2};                                                           // head_input
     size_t total = 0;
-    size_t offsets[13];
-    for (int index = 0; index < 13; ++index) {
+    size_t offsets[14];
+    for (int index = 0; index < 14; ++index) {
         offsets[index] = total;
         total += (sizes[index] + 255) & ~static_cast<size_t>(255);
     }
@@ -412,10 +587,11 @@ int32_t lfm25_decode_executor_create(lfm25_blaslt* blaslt, size_t maximum_tokens
         return cuda_failure(status, "failed to allocate decode scratch");
     }
     unsigned char* base = static_cast<unsigned char*>(self->allocation);
-    void** fields[13] = {&self->hidden, &self->normalized, &self->post_operator, &self->operator_output, &self->query,
+    void** fields[14] = {&self->hidden, &self->normalized, &self->post_operator, &self->operator_output, &self->query,
                          &self->key, &self->value, &self->wide, &self->activated, &self->logits, &self->fp8_input,
-                         reinterpret_cast<void**>(&self->partials), reinterpret_cast<void**>(&self->sampled)};
-    for (int index = 0; index < 13; ++index) {
+                         reinterpret_cast<void**>(&self->partials), reinterpret_cast<void**>(&self->sampled),
+                         &self->head_input};
+    for (int index = 0; index < 14; ++index) {
         *fields[index] = base + offsets[index];
     }
     *out = self;
@@ -439,7 +615,7 @@ int32_t lfm25_decode_executor_download_sampled(lfm25_decode_executor* self, uint
     if (self == nullptr || host == nullptr) {
         return lfm25::report_error(LFM25_ERR_NULL_POINTER, "sampled download received a null argument");
     }
-    if (count > self->maximum_tokens) {
+    if (count > self->maximum_rows) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "sampled download exceeds the executor's capacity");
     }
     const cudaError_t status = cudaMemcpyAsync(host, self->sampled, count * sizeof(uint32_t), cudaMemcpyDeviceToHost,
@@ -451,7 +627,7 @@ int32_t lfm25_decode_executor_download_logits(lfm25_decode_executor* self, void*
     if (self == nullptr || host == nullptr) {
         return lfm25::report_error(LFM25_ERR_NULL_POINTER, "logits download received a null argument");
     }
-    if (rows > self->maximum_tokens) {
+    if (rows > self->maximum_rows) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "logits download exceeds the executor's capacity");
     }
     const cudaError_t status = cudaMemcpyAsync(host, self->logits, rows * kVocab * 2, cudaMemcpyDeviceToHost,
@@ -499,6 +675,30 @@ int32_t lfm25_decode_executor_forward(lfm25_decode_executor* self, const lfm25_m
                                       const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance) {
     LFM25_TRY(validate(self, model, batch));
     return forward(self, model, batch, use_fp8 != 0, advance != 0);
+}
+
+int32_t lfm25_decode_executor_forward_ragged(lfm25_decode_executor* self, const lfm25_model* model,
+                                             const lfm25_ragged_batch* batch, uint32_t use_fp8) {
+    if (self == nullptr || model == nullptr || batch == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor received a null argument");
+    }
+    if (batch->num_tokens == 0 || batch->num_tokens > self->maximum_tokens) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "ragged step token count exceeds workspace");
+    }
+    if (batch->num_segments == 0 || batch->num_segments > self->maximum_rows ||
+        batch->num_segments > batch->num_tokens) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "ragged step segment count exceeds workspace");
+    }
+    if (model->num_layers == 0 || model->layers == nullptr || model->embedding == nullptr ||
+        model->final_norm == nullptr || model->inv_freq == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "decode executor model is incomplete");
+    }
+    if (!batch->token_ids || !batch->positions || !batch->request_slots || !batch->physical_slots ||
+        !batch->segment_offsets || !batch->segment_slots || !batch->output_rows || !batch->block_tables ||
+        batch->block_table_stride == 0 || batch->block_table_rows == 0) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "ragged batch metadata is incomplete");
+    }
+    return forward_ragged(self, model, batch, use_fp8 != 0);
 }
 
 int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm25_model* model,

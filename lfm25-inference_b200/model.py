@@ -199,14 +199,49 @@ class DecodeBatch:
             self.num_tokens, max_context_tokens)
 
 
-class DecodeExecutor:
-    """Mirror of the reference's DecodeExecutor over the C ABI; bound to the BlasLt handle's stream."""
+class RaggedBatch:
+    """Device-resident metadata of a step that mixes prefill chunks and decode tokens
+    (a `workloads.MixedStepBatch` plus the token ids)."""
 
-    def __init__(self, blaslt: BlasLt, maximum_tokens: int):
+    def __init__(self, device, batch, token_ids: np.ndarray):
+        def u32(values):
+            return torch.from_numpy(np.ascontiguousarray(values, dtype=np.uint32).view(np.int32).copy()).to(device)
+
+        self.block_tables = u32(batch.block_tables)
+        self.request_slots = u32(batch.request_slots)
+        self.positions = u32(batch.positions)
+        self.token_ids = u32(token_ids)
+        self.segment_offsets = u32(batch.segment_offsets)
+        self.segment_slots = u32(batch.segment_slots)
+        self.output_rows = u32(batch.output_rows)
+        self.num_tokens = batch.num_tokens
+        self.num_segments = batch.num_segments
+        self.physical_slots = torch.zeros(self.num_tokens, dtype=torch.int64, device=device)
+        self.struct = _abi.RaggedBatch(
+            self.token_ids.data_ptr(), self.positions.data_ptr(), self.request_slots.data_ptr(),
+            self.physical_slots.data_ptr(), self.segment_offsets.data_ptr(), self.segment_slots.data_ptr(),
+            self.output_rows.data_ptr(), self.block_tables.data_ptr(), batch.block_tables.shape[1],
+            batch.block_tables.shape[0], self.num_tokens, self.num_segments)
+
+
+class DecodeExecutor:
+    """Mirror of the reference's DecodeExecutor over the C ABI; bound to the BlasLt handle's stream.
+    `maximum_segments` (sequences per step) below `maximum_tokens` makes room for prefill chunks."""
+
+    def __init__(self, blaslt: BlasLt, maximum_tokens: int, maximum_segments: int | None = None):
         self.blaslt = blaslt
         self.maximum_tokens = maximum_tokens
         self._handle = ctypes.c_void_p()
-        check(library().lfm25_decode_executor_create(blaslt._handle, maximum_tokens, ctypes.byref(self._handle)))
+        if maximum_segments is None:
+            check(library().lfm25_decode_executor_create(blaslt._handle, maximum_tokens, ctypes.byref(self._handle)))
+        else:
+            check(library().lfm25_decode_executor_create_ragged(blaslt._handle, maximum_tokens, maximum_segments,
+                                                                ctypes.byref(self._handle)))
+
+    def forward_ragged(self, model: RandomModel, batch: RaggedBatch, use_fp8: bool = True) -> None:
+        """One mixed prefill / decode step; row s of logits / sampled belongs to segment s."""
+        self.blaslt.bind_current_stream()
+        check(library().lfm25_decode_executor_forward_ragged(self._handle, model.struct, batch.struct, int(use_fp8)))
 
     def forward(self, model: RandomModel, batch: DecodeBatch, use_fp8: bool = True, advance: bool = False) -> None:
         self.blaslt.bind_current_stream()
