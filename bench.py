@@ -55,7 +55,7 @@ STEP_POOL_PAGES = 32768
 def parse_arguments():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--workload", default="step", choices=["step", "attention"])
+    parser.add_argument("--workload", default="step", choices=["step", "attention", "prefill"])
     parser.add_argument("--steps", type=int, default=0, help="timed steps (default 256 for step, 1024 for attention)")
     parser.add_argument("--warmup", type=int, default=0, help="warm-up steps (default 8 / 32)")
     parser.add_argument("--no-fp8", action="store_true", help="step workload: run every site in BF16")
@@ -70,9 +70,9 @@ def parse_arguments():
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     arguments = parser.parse_args()
     if arguments.steps <= 0:
-        arguments.steps = 256 if arguments.workload == "step" else 1024
+        arguments.steps = {"step": 256, "attention": 1024, "prefill": 16}[arguments.workload]
     if arguments.warmup <= 0:
-        arguments.warmup = 8 if arguments.workload == "step" else 32
+        arguments.warmup = {"step": 8, "attention": 32, "prefill": 3}[arguments.workload]
     globals().update(SEQUENCES=arguments.sequences, NUM_PAGES=arguments.pool_pages,
                      STEP_SEQUENCES=arguments.step_sequences)
     return arguments
@@ -660,6 +660,171 @@ def _inv_freq():
     return np.power(np.float32(1.0e6), -(np.float32(2.0) * index) / np.float32(64.0)).astype(np.float32)
 
 
+# ------------------------------------------------------------------------------------ chunked prefill step
+
+PREFILL_METRIC = "prefill tok/s (mixed step: 8 chunks of 512 prompt tokens on prefixes of 0..3584 cached tokens)"
+PREFILL_WORKLOAD = "chunked-prefill-8x512-prefix0-3584-bf16"
+PREFILL_CHUNK = 512
+PREFILL_PREFIXES = [0, 512, 1024, 1536, 2048, 2560, 3072, 3584]
+
+
+def run_prefill_arm(arguments, rank, world):
+    """One step = one mixed step of the executor holding eight 512-token prefill chunks (the chunk size the
+    reference's planner prefers, src/scheduler/planner.rs:201) whose sequences already have 0..3584 tokens in the
+    paged cache: 4096 tokens per step, BF16 at every site (the step is above the FP8 batch limit, as in the
+    reference).  `roofline` is the hybrid attention kernel: tensor-core flops 4 * 2048 * sum(position + 1) per launch
+    over its CUDA-event time in an instrumented pass, against the measured dense BF16 peak."""
+    import torch
+    import torch.distributed as dist
+
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    entry.load_package()
+    from lfm25_inference_b200 import model as lfm_model
+    from lfm25_inference_b200 import ops, workloads
+
+    seed = 5 + rank
+    chunks = [PREFILL_CHUNK] * len(PREFILL_PREFIXES)
+    pages = sum((prefix + PREFILL_CHUNK + 15) // 16 for prefix in PREFILL_PREFIXES)
+    batch = workloads.mixed_step_batch(seed, PREFILL_PREFIXES, chunks, pages)
+    model = lfm_model.RandomModel(seed, device, pages, batch.num_segments)
+    model.fill_caches(seed + 1)
+    token_ids = np.random.default_rng(seed).integers(0, lfm_model.VOCAB, size=batch.num_tokens).astype(np.uint32)
+    steps, warmup = arguments.steps, max(arguments.warmup, 3)
+    stream = torch.cuda.Stream(device=device)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(stream):
+        blaslt = ops.BlasLt()
+        executor = lfm_model.DecodeExecutor(blaslt, batch.num_tokens, maximum_segments=batch.num_segments)
+        device_batch = lfm_model.RaggedBatch(device, batch, token_ids)
+        for _ in range(warmup):
+            executor.forward_ragged(model, device_batch, use_fp8=False)
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as sampler:
+            stream.synchronize()
+            start.record()
+            for _ in range(steps):
+                executor.forward_ragged(model, device_batch, use_fp8=False)
+            stop.record()
+            stream.synchronize()
+            total_ms = start.elapsed_time(stop)
+            until = time.perf_counter() + 0.5
+            while total_ms < 500.0 and time.perf_counter() < until:
+                executor.forward_ragged(model, device_batch, use_fp8=False)
+                stream.synchronize()
+        clocks = sampler.summary()
+
+        # e2e: the serving call -- upload the step's token ids from pinned memory, run, download the sampled ids
+        pinned_ids = torch.from_numpy(token_ids.view(np.int32).copy()).pin_memory()
+        host_sampled = torch.empty(batch.num_segments, dtype=torch.int32).pin_memory()
+        e2e_steps = min(steps, 16)
+        stream.synchronize()
+        begin = time.perf_counter()
+        for _ in range(e2e_steps):
+            device_batch.token_ids.copy_(pinned_ids, non_blocking=True)
+            executor.forward_ragged(model, device_batch, use_fp8=False)
+            executor.download_sampled(host_sampled)
+            stream.synchronize()
+        e2e_ms = (time.perf_counter() - begin) * 1e3
+
+        executor.profile(True)
+        profile_steps = 4
+        for _ in range(profile_steps):
+            executor.forward_ragged(model, device_batch, use_fp8=False)
+        regions = executor.profile(False, collect=True)
+        graph_free_launches = sum(ops_count for _, ops_count in regions.values()) // profile_steps
+
+        attention_ms, attention_ops = regions["attention"]
+        attention_seconds = attention_ms / max(attention_ops, 1) * 1e-3
+        attention_flops = 4.0 * 2048.0 * float((batch.positions.astype(np.float64) + 1.0).sum())
+        # the reference's own hybrid kernel on the same buffers
+        reference_kernels = None
+        if rank == 0:
+            try:
+                from oracle import refkernels
+                if refkernels.available():
+                    layer = next(layer for layer in model.layers if layer.is_attention)
+                    query = torch.randn((batch.num_tokens, 32, 64), device=device, dtype=torch.bfloat16)
+                    key = torch.randn((batch.num_tokens, 8, 64), device=device, dtype=torch.bfloat16)
+                    output = torch.zeros_like(query)
+                    arguments_list = [query, key, key, layer.tensors["key_cache"], layer.tensors["value_cache"],
+                                      device_batch.block_tables, device_batch.request_slots, device_batch.positions,
+                                      device_batch.segment_offsets, output]
+                    refkernels.hybrid_ragged_attention(*arguments_list)
+                    stream.synchronize()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    refkernels.hybrid_ragged_attention(*arguments_list)
+                    b.record()
+                    stream.synchronize()
+                    reference_kernels = {"hybrid_attention_us_per_layer": a.elapsed_time(b) * 1e3,
+                                         "ours_us_per_layer": attention_seconds * 1e6}
+            except Exception as error:   # the reference images are optional
+                reference_kernels = {"unavailable": str(error)[:120]}
+    total_ms, e2e_ms = max_over_ranks([total_ms, e2e_ms], device, world)
+    if rank == 0:
+        peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        tensor_peak, peak_source = 1590.0, "fallback"
+        if os.path.exists(peak_path):
+            with open(peak_path) as handle:
+                tensor_peak, peak_source = float(json.load(handle)["bf16_tflops"]), "measured"
+        achieved = attention_flops / attention_seconds / 1e12
+        cpu = None
+        if not arguments.skip_cpu:
+            cpu = prefill_cpu_sample(model, batch, token_ids)
+        line = {
+            "metric": PREFILL_METRIC, "value": batch.num_tokens * steps * world / (total_ms * 1e-3), "unit": "tok/s",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": total_ms / steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": PREFILL_WORKLOAD, "segments": batch.num_segments, "chunk": PREFILL_CHUNK,
+                       "prefixes": PREFILL_PREFIXES, "tokens_per_step": batch.num_tokens, "page_size": 16,
+                       "replicas": world, "step": "eager launches (no graph)",
+                       "l2": "2.3 GB of BF16 weights streamed per step exceed L2"},
+            "regions_eager_ms_per_step": {name: ms / profile_steps for name, (ms, _) in regions.items()},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+                         "frac": achieved / tensor_peak, "traffic": None, "peak_source": peak_source,
+                         "kernel": "hybrid_ragged_attention_kernel (one attention layer, mma.sync path)",
+                         "algorithmic_flops_per_launch": attention_flops},
+            "cpu_baseline": cpu,
+            "e2e": {"value": batch.num_tokens * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tok/s",
+                    "h2d_bytes_per_step": int(token_ids.nbytes), "d2h_bytes_per_step": 4 * batch.num_segments,
+                    "steps": e2e_steps},
+            "gpu_launches": graph_free_launches * steps,
+            "reference_kernels_same_gpu": reference_kernels, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    executor.close()
+    blaslt.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def prefill_cpu_sample(model, batch, token_ids):
+    """CPU oracle on a small mixed step of the same kind (one 64-token chunk on a 192-token prefix)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import step_oracle
+    from lfm25_inference_b200 import workloads
+    from oracle import oracle
+    oracle.use_all_cores()
+    host = step_oracle.HostModel(model)
+    small = workloads.MixedStepBatch(batch.num_pages, batch.block_tables[:1].copy(), np.array([192]), np.array([64]),
+                                     np.zeros(1, dtype=np.uint32))
+    for layer in host.layers:
+        if "conv_state" in layer:
+            layer["conv_state"] = np.ascontiguousarray(layer["conv_state"][:1])
+    begin = time.perf_counter()
+    step_oracle.ragged_step(host, token_ids[:64], small, False)
+    seconds = time.perf_counter() - begin
+    return {"value": 64 / seconds, "unit": "tok/s", "cores": oracle.num_threads(), "kind": "port",
+            "sample": "one mixed step with one 64-token chunk on a 192-token prefix (16 layers, BF16), once"}
+
+
 def main():
     arguments = parse_arguments()
     rank = int(os.environ.get("RANK", 0))
@@ -669,6 +834,11 @@ def main():
             run_step_reference_arm(arguments, rank)
         else:
             run_step_arm(arguments, rank, world)
+        return
+    if arguments.workload == "prefill":
+        if arguments.impl == "reference":
+            raise SystemExit("--impl reference times the decode workloads; the prefill line carries its own cpu_baseline")
+        run_prefill_arm(arguments, rank, world)
         return
     if arguments.impl == "reference":
         run_reference_arm(arguments, rank)

@@ -9,9 +9,11 @@
 //
 //   warp 4      producer: one thread walks the tile's key range -- pages of the cached prefix, then 16-token slabs
 //               of the step's own K/V -- and issues TMA tile loads (128-byte swizzle, mbarrier complete_tx) into a
-//               ring of 8 stages shared by the CTA; a stage is refilled once the four compute warps have released it
-//   warps 0-3   4 tokens x 4 query heads each = the 16 rows of one mma.sync.m16n8k16 tile: S = Q K^T (8 MMAs),
-//               causal mask per row, online softmax in the exp2 domain with two rows per thread, O += P V (8 MMAs)
+//               ring of 3 stages of 64 keys shared by the CTA; a stage is refilled once the four compute warps have
+//               released it
+//   warps 0-3   4 tokens x 4 query heads each = the 16 rows of one mma.sync.m16n8k16 tile; per stage S = Q K^T
+//               (32 MMAs), causal mask per row, one online-softmax update in the exp2 domain for the 64 keys with
+//               two rows per thread, O += P V (32 MMAs)
 //
 // With current_key == nullptr the kernel reads every key up to each token's position from the cache (the caller
 // appended the step's K/V first, which is what the decode executor's fused append does); with it, the prefix comes
@@ -25,6 +27,8 @@
 // stores nothing.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.h"
@@ -37,9 +41,11 @@ namespace {
 constexpr uint32_t kTileTokens = 16;
 constexpr uint32_t kComputeWarps = 4;
 constexpr uint32_t kHybridThreads = (kComputeWarps + 1) * 32;
-constexpr uint32_t kHybridStages = 8;
+constexpr uint32_t kHybridStages = 3;
+constexpr uint32_t kSubTiles = 4;                            // 16-key tiles per stage: softmax works on 64 keys
 constexpr uint32_t kSlabBytes = kPageSize * kHeadDim * 2;   // one K or V tile: 16 keys x 128 B
-constexpr uint32_t kHybridStageBytes = 2 * kSlabBytes;
+constexpr uint32_t kSubTileBytes = 2 * kSlabBytes;          // K tile then V tile
+constexpr uint32_t kHybridStageBytes = kSubTiles * kSubTileBytes;
 constexpr uint32_t kHybridSmem = kHybridStages * kHybridStageBytes + 2 * kHybridStages * 8 + 16 + 1024;
 
 struct HybridParams {
@@ -59,7 +65,7 @@ struct HybridParams {
     uint32_t contiguous_current;   // 1: the segment's own K/V come from the contiguous buffers
 };
 
-__global__ void __launch_bounds__(kHybridThreads)
+__global__ void __launch_bounds__(kHybridThreads, 3)
 hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, const __grid_constant__ CUtensorMap value_map,
                                const __grid_constant__ CUtensorMap current_key_map,
                                const __grid_constant__ CUtensorMap current_value_map, const HybridParams p) {
@@ -69,8 +75,10 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
     pdl_wait();
 
     // ---- which (segment, 16-token tile, KV head) this CTA owns; every early exit is CTA-uniform ----
+    // Later tiles of a segment (and, in a typical batch, later segments) have longer key ranges: the grid is walked
+    // backwards so that the long CTAs start first and the short ones fill the tail.
     const uint32_t kv_head = blockIdx.x % kKvHeads;
-    uint32_t tile_slot = blockIdx.x / kKvHeads;
+    uint32_t tile_slot = (gridDim.x - 1 - blockIdx.x) / kKvHeads;
     uint32_t segment_begin = 0;
     uint32_t segment_end = 0;
     bool found = false;
@@ -113,6 +121,7 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
     const uint32_t paged_tiles = (paged_keys + kPageSize - 1) / kPageSize;
     const uint32_t current_tiles = p.contiguous_current ? last_offset / kPageSize + 1 : 0;
     const uint32_t total_tiles = paged_tiles + current_tiles;
+    const uint32_t macro_tiles = (total_tiles + kSubTiles - 1) / kSubTiles;   // stages of up to 64 keys
 
     extern __shared__ uint8_t hybrid_smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(hybrid_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -137,10 +146,10 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
         // ---------------------------------------------------------------- producer
         if (lane == 0) {
             const int32_t head_row = static_cast<int32_t>(kv_head * kPageSize);
-            for (uint32_t tile = 0; tile < total_tiles; ++tile) {
-                const uint32_t stage = tile % kHybridStages;
-                if (tile >= kHybridStages) {
-                    if (flags[1] || !mbar_wait_bounded(bar_empty + stage * 8, ((tile / kHybridStages) - 1) & 1)) {
+            for (uint32_t macro = 0; macro < macro_tiles; ++macro) {
+                const uint32_t stage = macro % kHybridStages;
+                if (macro >= kHybridStages) {
+                    if (flags[1] || !mbar_wait_bounded(bar_empty + stage * 8, ((macro / kHybridStages) - 1) & 1)) {
                         if (!flags[1]) {
                             flags[1] = 1;
                             record_wait_timeout(p.status, kTagHybridAttention, (blockIdx.x << 1) | 1);
@@ -150,23 +159,30 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
                     fence_proxy_async_smem();
                 }
                 const uint32_t bar = bar_full + stage * 8;
-                const uint32_t dst = ring + stage * kHybridStageBytes;
-                mbar_arrive_expect_tx(bar, kHybridStageBytes);
-                if (tile < paged_tiles) {
-                    uint32_t entry = __ldg(table + tile);
-                    if (entry >= p.num_pages) {
-                        flags[0] = 1;   // unassigned page: keep the pipeline uniform, discard the result
-                        entry = 0;
+                const uint32_t first_tile = macro * kSubTiles;
+                const uint32_t count = min(kSubTiles, total_tiles - first_tile);
+                mbar_arrive_expect_tx(bar, count * kSubTileBytes);
+                for (uint32_t sub = 0; sub < count; ++sub) {
+                    const uint32_t tile = first_tile + sub;
+                    const uint32_t dst = ring + stage * kHybridStageBytes + sub * kSubTileBytes;
+                    if (tile < paged_tiles) {
+                        uint32_t entry = __ldg(table + tile);
+                        if (entry >= p.num_pages) {
+                            flags[0] = 1;   // unassigned page: keep the pipeline uniform, discard the result
+                            entry = 0;
+                        }
+                        const int32_t row =
+                            static_cast<int32_t>(entry) * static_cast<int32_t>(kKvHeads * kPageSize) + head_row;
+                        tma_load_2d(dst, &key_map, bar, 0, row);
+                        tma_load_2d(dst + kSlabBytes, &value_map, bar, 0, row);
+                    } else {
+                        // rows past the last token of the step are filled with zeros by the copy engine
+                        const int32_t token_row =
+                            static_cast<int32_t>(segment_begin + (tile - paged_tiles) * kPageSize);
+                        const int32_t column = static_cast<int32_t>(kv_head * kHeadDim);
+                        tma_load_2d(dst, &current_key_map, bar, column, token_row);
+                        tma_load_2d(dst + kSlabBytes, &current_value_map, bar, column, token_row);
                     }
-                    const int32_t row = static_cast<int32_t>(entry) * static_cast<int32_t>(kKvHeads * kPageSize) + head_row;
-                    tma_load_2d(dst, &key_map, bar, 0, row);
-                    tma_load_2d(dst + kSlabBytes, &value_map, bar, 0, row);
-                } else {
-                    // rows past the last token of the step are filled with zeros by the copy engine
-                    const int32_t token_row = static_cast<int32_t>(segment_begin + (tile - paged_tiles) * kPageSize);
-                    const int32_t column = static_cast<int32_t>(kv_head * kHeadDim);
-                    tma_load_2d(dst, &current_key_map, bar, column, token_row);
-                    tma_load_2d(dst + kSlabBytes, &current_value_map, bar, column, token_row);
                 }
             }
         }
@@ -237,98 +253,174 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
         const uint32_t v_chunk = ld_matrix >> 1;
 
         bool timed_out = false;
-        uint32_t failed_tile = 0;
-        for (uint32_t tile = 0; tile < total_tiles; ++tile) {
-            const uint32_t stage = tile % kHybridStages;
-            const bool ready = !flags[1] && mbar_wait_bounded(bar_full + stage * 8, (tile / kHybridStages) & 1);
+        uint32_t failed_macro = 0;
+        for (uint32_t macro = 0; macro < macro_tiles; ++macro) {
+            const uint32_t stage = macro % kHybridStages;
+            const bool ready = !flags[1] && mbar_wait_bounded(bar_full + stage * 8, (macro / kHybridStages) & 1);
             if (!__all_sync(0xffffffffu, ready)) {
                 timed_out = true;
-                failed_tile = tile;
+                failed_macro = macro;
                 break;
             }
-            const uint32_t k_base = ring + stage * kHybridStageBytes;
-            const uint32_t v_base = k_base + kSlabBytes;
-            const bool paged = tile < paged_tiles;
-            // index in the sequence of the tile's first key, and the last key of the tile that exists at all
-            const int64_t first_key = paged ? static_cast<int64_t>(tile) * kPageSize
-                                            : static_cast<int64_t>(prefix) + (tile - paged_tiles) * kPageSize;
-            const int64_t tile_limit = paged ? static_cast<int64_t>(paged_keys) - 1 : static_cast<int64_t>(last_position);
-
+            const uint32_t stage_base = ring + stage * kHybridStageBytes;
+            const uint32_t first_tile = macro * kSubTiles;
+            const uint32_t count = min(kSubTiles, total_tiles - first_tile);
             bool wrote_stage = false;
-            if (warp_live && first_key <= static_cast<int64_t>(warp_last_position)) {
-                if (tile_limit < first_key + kPageSize - 1) {
-                    wrote_stage = true;
-                    // Keys past the limit do not exist (or are not this tile's to read): their V rows may hold
-                    // anything, so clear them; every warp does it for itself before its own reads.
-                    for (int64_t row = tile_limit - first_key + 1; row < kPageSize; ++row) {
-                        asm volatile("st.shared.u32 [%0], %1;" ::"r"(v_base + static_cast<uint32_t>(row) * 128 + lane * 4),
-                                     "r"(0u) : "memory");
-                    }
-                    __syncwarp();
-                }
-                float s[2][4];
+
+            // index in the sequence of a tile's first key, and the last key of the tile that exists at all
+            auto tile_first_key = [&](uint32_t tile) -> int64_t {
+                return tile < paged_tiles ? static_cast<int64_t>(tile) * kPageSize
+                                          : static_cast<int64_t>(prefix) + (tile - paged_tiles) * kPageSize;
+            };
+            auto tile_last_key = [&](uint32_t tile) -> int64_t {
+                return tile < paged_tiles ? static_cast<int64_t>(paged_keys) - 1 : static_cast<int64_t>(last_position);
+            };
+            // The common stage -- four tiles, every key of them exists and the warp sees all four -- runs with
+            // compile-time trip counts, so that the MMAs of the four tiles (eight independent accumulator chains)
+            // are interleaved; the edge stages take the same code with per-tile tests.
+            const uint32_t last_tile = first_tile + kSubTiles - 1;
+            const bool fast = count == kSubTiles && warp_live &&
+                              tile_first_key(last_tile) <= static_cast<int64_t>(warp_last_position) &&
+                              tile_last_key(first_tile) >= tile_first_key(first_tile) + kPageSize - 1 &&
+                              tile_last_key(last_tile) >= tile_first_key(last_tile) + kPageSize - 1 &&
+                              (first_tile >= paged_tiles || last_tile < paged_tiles ||
+                               tile_last_key(paged_tiles - 1) >= tile_first_key(paged_tiles - 1) + kPageSize - 1);
+
+            float s[2 * kSubTiles][4];
+            bool used[kSubTiles];
+            auto scores = [&](auto fast_tag) {
+                constexpr bool kFast = decltype(fast_tag)::value;
 #pragma unroll
-                for (uint32_t nt = 0; nt < 2; ++nt) {
-                    s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+                for (uint32_t sub = 0; sub < kSubTiles; ++sub) {
+                    const uint32_t tile = first_tile + sub;
+                    used[sub] = kFast || (sub < count && warp_live &&
+                                          tile_first_key(tile) <= static_cast<int64_t>(warp_last_position));
+#pragma unroll
+                    for (uint32_t nt = 0; nt < 2; ++nt) {
+                        const float fill = used[sub] ? 0.0f : -INFINITY;
+                        s[sub * 2 + nt][0] = s[sub * 2 + nt][1] = s[sub * 2 + nt][2] = s[sub * 2 + nt][3] = fill;
+                    }
+                    if (!kFast && used[sub]) {
+                        const int64_t first_key = tile_first_key(tile);
+                        const int64_t tile_limit = tile_last_key(tile);
+                        if (tile_limit < first_key + kPageSize - 1) {
+                            // Keys past the limit do not exist (or are not this tile's to read): their V rows may
+                            // hold anything, so clear them; every warp does it for itself before its own reads.
+                            wrote_stage = true;
+                            const uint32_t v_base = stage_base + sub * kSubTileBytes + kSlabBytes;
+                            for (int64_t row = tile_limit - first_key + 1; row < kPageSize; ++row) {
+                                asm volatile("st.shared.u32 [%0], %1;" ::"r"(v_base + static_cast<uint32_t>(row) * 128 + lane * 4),
+                                             "r"(0u) : "memory");
+                            }
+                        }
+                    }
                 }
 #pragma unroll
                 for (uint32_t ks = 0; ks < 4; ++ks) {
-                    uint32_t b0, b1, b2, b3;
-                    const uint32_t chunk = ks * 2 + k_chunk;
-                    ldmatrix_x4(k_base + k_token * 128 + ((chunk ^ ld_row) << 4), b0, b1, b2, b3);
-                    mma_bf16_16816(s[0], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
-                    mma_bf16_16816(s[1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
-                }
-                // causal mask: row r sees key k iff k <= min(row position, tile limit)
-                float tile_max[2];
 #pragma unroll
-                for (uint32_t half = 0; half < 2; ++half) {
-                    const int64_t limit = row_position[half] < tile_limit ? row_position[half] : tile_limit;
-#pragma unroll
-                    for (uint32_t nt = 0; nt < 2; ++nt) {
-                        const int64_t key = first_key + nt * 8 + quad * 2;
-                        if (key > limit) s[nt][half * 2] = -INFINITY;
-                        if (key + 1 > limit) s[nt][half * 2 + 1] = -INFINITY;
+                    for (uint32_t sub = 0; sub < kSubTiles; ++sub) {
+                        if (kFast || used[sub]) {
+                            uint32_t b0, b1, b2, b3;
+                            const uint32_t chunk = ks * 2 + k_chunk;
+                            ldmatrix_x4(stage_base + sub * kSubTileBytes + k_token * 128 + ((chunk ^ ld_row) << 4), b0, b1,
+                                        b2, b3);
+                            mma_bf16_16816(s[sub * 2], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b0, b1);
+                            mma_bf16_16816(s[sub * 2 + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b2, b3);
+                        }
                     }
-                    float maximum = fmaxf(fmaxf(s[0][half * 2], s[0][half * 2 + 1]),
-                                          fmaxf(s[1][half * 2], s[1][half * 2 + 1]));
-                    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
-                    maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 2));
-                    tile_max[half] = maximum;
                 }
-                uint32_t pa[4];
-                float rescale[2];
+                // causal mask: row r sees key k iff k <= min(row position, last key of the tile)
 #pragma unroll
-                for (uint32_t half = 0; half < 2; ++half) {
-                    const float new_max = fmaxf(running_max[half], tile_max[half]);
-                    const float base = new_max == -INFINITY ? 0.0f : new_max;   // a row that has seen no key yet
-                    rescale[half] = fast_exp2((running_max[half] - base) * kScaleLog2);
-                    const float offset = -base * kScaleLog2;
-                    pa[half] = pack_bf16x2(fast_exp2(fmaf(s[0][half * 2], kScaleLog2, offset)),
-                                           fast_exp2(fmaf(s[0][half * 2 + 1], kScaleLog2, offset)));
-                    pa[half + 2] = pack_bf16x2(fast_exp2(fmaf(s[1][half * 2], kScaleLog2, offset)),
-                                               fast_exp2(fmaf(s[1][half * 2 + 1], kScaleLog2, offset)));
+                for (uint32_t sub = 0; sub < kSubTiles; ++sub) {
+                    if (kFast || used[sub]) {
+                        const uint32_t tile = first_tile + sub;
+                        const int64_t first_key = tile_first_key(tile);
+                        const int64_t tile_limit = kFast ? first_key + kPageSize - 1 : tile_last_key(tile);
+#pragma unroll
+                        for (uint32_t half = 0; half < 2; ++half) {
+                            const int64_t limit = row_position[half] < tile_limit ? row_position[half] : tile_limit;
+                            if (limit < first_key + kPageSize - 1) {
+#pragma unroll
+                                for (uint32_t nt = 0; nt < 2; ++nt) {
+                                    const int64_t key = first_key + nt * 8 + quad * 2;
+                                    if (key > limit) s[sub * 2 + nt][half * 2] = -INFINITY;
+                                    if (key + 1 > limit) s[sub * 2 + nt][half * 2 + 1] = -INFINITY;
+                                }
+                            }
+                        }
+                    }
+                }
+            };
+            if (fast) {
+                scores(std::true_type{});
+            } else {
+                scores(std::false_type{});
+            }
+            if (wrote_stage) {
+                __syncwarp();
+            }
+
+            // ---- online softmax over the stage's keys, two rows per thread ----
+            uint32_t pa[kSubTiles][4];
+            float rescale[2];
+#pragma unroll
+            for (uint32_t half = 0; half < 2; ++half) {
+                float maximum = -INFINITY;
+#pragma unroll
+                for (uint32_t nt = 0; nt < 2 * kSubTiles; ++nt) {
+                    maximum = fmaxf(maximum, fmaxf(s[nt][half * 2], s[nt][half * 2 + 1]));
+                }
+                maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
+                maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, 2));
+                const float new_max = fmaxf(running_max[half], maximum);
+                const float base = new_max == -INFINITY ? 0.0f : new_max;   // a row that has seen no key yet
+                rescale[half] = fast_exp2((running_max[half] - base) * kScaleLog2);
+                const float offset = -base * kScaleLog2;
+                float tile_sum = 0.0f;
+#pragma unroll
+                for (uint32_t sub = 0; sub < kSubTiles; ++sub) {
+                    pa[sub][half] = pack_bf16x2(fast_exp2(fmaf(s[sub * 2][half * 2], kScaleLog2, offset)),
+                                                fast_exp2(fmaf(s[sub * 2][half * 2 + 1], kScaleLog2, offset)));
+                    pa[sub][half + 2] = pack_bf16x2(fast_exp2(fmaf(s[sub * 2 + 1][half * 2], kScaleLog2, offset)),
+                                                    fast_exp2(fmaf(s[sub * 2 + 1][half * 2 + 1], kScaleLog2, offset)));
                     // the denominator sums the same bf16-rounded weights that multiply V
-                    const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[half]));
-                    const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[half + 2]));
-                    running_sum[half] = fmaf(running_sum[half], rescale[half], (w0.x + w0.y) + (w1.x + w1.y));
-                    running_max[half] = new_max;
+                    const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[sub][half]));
+                    const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pa[sub][half + 2]));
+                    tile_sum += (w0.x + w0.y) + (w1.x + w1.y);
                 }
+                running_sum[half] = fmaf(running_sum[half], rescale[half], tile_sum);
+                running_max[half] = new_max;
+            }
 #pragma unroll
-                for (uint32_t nt = 0; nt < 8; ++nt) {
-                    acc[nt][0] *= rescale[0];
-                    acc[nt][1] *= rescale[0];
-                    acc[nt][2] *= rescale[1];
-                    acc[nt][3] *= rescale[1];
-                }
+            for (uint32_t nt = 0; nt < 8; ++nt) {
+                acc[nt][0] *= rescale[0];
+                acc[nt][1] *= rescale[0];
+                acc[nt][2] *= rescale[1];
+                acc[nt][3] *= rescale[1];
+            }
+
+            // ---- O += P V ----
+            auto weighted_values = [&](auto fast_tag) {
+                constexpr bool kFast = decltype(fast_tag)::value;
 #pragma unroll
-                for (uint32_t pair = 0; pair < 4; ++pair) {
-                    uint32_t b0, b1, b2, b3;
-                    const uint32_t chunk = pair * 2 + v_chunk;
-                    ldmatrix_x4_trans(v_base + v_token * 128 + ((chunk ^ ld_row) << 4), b0, b1, b2, b3);
-                    mma_bf16_16816(acc[pair * 2], pa[0], pa[1], pa[2], pa[3], b0, b1);
-                    mma_bf16_16816(acc[pair * 2 + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
+                for (uint32_t sub = 0; sub < kSubTiles; ++sub) {
+                    if (kFast || used[sub]) {
+                        const uint32_t v_base = stage_base + sub * kSubTileBytes + kSlabBytes;
+#pragma unroll
+                        for (uint32_t pair = 0; pair < 4; ++pair) {
+                            uint32_t b0, b1, b2, b3;
+                            const uint32_t chunk = pair * 2 + v_chunk;
+                            ldmatrix_x4_trans(v_base + v_token * 128 + ((chunk ^ ld_row) << 4), b0, b1, b2, b3);
+                            mma_bf16_16816(acc[pair * 2], pa[sub][0], pa[sub][1], pa[sub][2], pa[sub][3], b0, b1);
+                            mma_bf16_16816(acc[pair * 2 + 1], pa[sub][0], pa[sub][1], pa[sub][2], pa[sub][3], b2, b3);
+                        }
+                    }
                 }
+            };
+            if (fast) {
+                weighted_values(std::true_type{});
+            } else {
+                weighted_values(std::false_type{});
             }
             if (wrote_stage) {
                 fence_proxy_async_smem();   // the stage is refilled by the copy engine after plain stores to it
@@ -340,7 +432,8 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
         }
         if (timed_out) {
             // give the copies still in flight a bounded chance to land before the shared memory is released
-            for (uint32_t pending = failed_tile; pending < total_tiles && pending < failed_tile + kHybridStages; ++pending) {
+            for (uint32_t pending = failed_macro; pending < macro_tiles && pending < failed_macro + kHybridStages;
+                 ++pending) {
                 (void)mbar_wait_bounded(bar_full + (pending % kHybridStages) * 8, (pending / kHybridStages) & 1);
             }
             if (lane == 0 && !flags[1]) {
