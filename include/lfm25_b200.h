@@ -552,6 +552,127 @@ size_t lfm25_schedule_decode(const uint32_t* phases, const uint64_t* next_token_
                              const uint32_t* context_tokens, size_t num_slots, uint64_t now_us, uint32_t* decode_slots,
                              size_t* maximum_context_tokens);
 
+/* Replaces CostCurve / HardwareCostModel (src/scheduler/cost_model.rs:7-231): measured step times as points
+ * (batch, tokens per sequence, context) -> milliseconds, one curve each for BF16 decode, FP8 decode and BF16
+ * prefill.  predict: an exact point, else the nearest point that dominates the query in every dimension, else a
+ * conservative extrapolation; predict_decode_ms: bilinear interpolation inside the measured decode grid
+ * (predict_decode_interpolated); predict_prefill_ms(tokens) = prefill curve at (1, tokens, tokens). */
+typedef struct lfm25_cost_point {
+    size_t batch;
+    size_t tokens;
+    size_t context;
+    double milliseconds;
+} lfm25_cost_point;
+typedef struct lfm25_cost_model lfm25_cost_model;
+#define LFM25_CURVE_DECODE_BF16 0
+#define LFM25_CURVE_DECODE_FP8 1
+#define LFM25_CURVE_PREFILL_BF16 2
+int32_t lfm25_cost_model_create(const lfm25_cost_point* decode_bf16, size_t decode_bf16_points,
+                                const lfm25_cost_point* decode_fp8, size_t decode_fp8_points,
+                                const lfm25_cost_point* prefill_bf16, size_t prefill_bf16_points, size_t page_size,
+                                lfm25_cost_model** out);
+void lfm25_cost_model_destroy(lfm25_cost_model* model);
+double lfm25_cost_model_predict(const lfm25_cost_model* model, uint32_t curve, size_t batch, size_t tokens,
+                                size_t context);
+double lfm25_cost_model_predict_decode_ms(const lfm25_cost_model* model, size_t batch, size_t maximum_context,
+                                          uint32_t fp8);
+double lfm25_cost_model_predict_prefill_ms(const lfm25_cost_model* model, size_t tokens);
+
+/* Replaces Scheduler::schedule (src/scheduler/planner.rs:80-236).  `requests` is the request-slot table as plain
+ * views (the fields of SequenceRequest the planner reads; context_tokens = tokens().len()).  Every decoding slot
+ * decodes, ordered by time to its next-token deadline; the rest of the step budget goes to queued prefills, most
+ * urgent first (time to the first-token deadline, aged by a quarter of the waiting time), in chunks of the largest
+ * power of two <= 512 that the cost model fits into the budget; with >= 24 queued prefills of which one is a short
+ * tail (<= one page left) of a long context (>= 1536 cached) the step stays decode-shaped and takes one token of
+ * every such tail instead.  work needs room for num_requests entries. */
+#define LFM25_WORK_DECODE 0
+#define LFM25_WORK_PREFILL 1
+typedef struct lfm25_scheduler_config {
+    double step_budget_ms;
+    uint64_t ttft_slo_us;
+    uint64_t tpot_slo_us;
+    uint32_t fp8_decode;
+    size_t maximum_prefill_tokens;
+} lfm25_scheduler_config;
+typedef struct lfm25_request_view {
+    uint32_t phase;                   /* LFM25_PHASE_* */
+    size_t prompt_len;
+    size_t prefilled;
+    size_t context_tokens;
+    uint64_t arrival_us;
+    uint64_t first_token_deadline_us;
+    uint64_t next_token_deadline_us;
+} lfm25_request_view;
+typedef struct lfm25_scheduled_work {
+    uint32_t kind;                    /* LFM25_WORK_* */
+    uint32_t slot;
+    size_t tokens;
+} lfm25_scheduled_work;
+typedef struct lfm25_batch_plan {
+    double predicted_ms;
+    size_t decode_count;
+    size_t prefill_tokens;
+    size_t work_count;
+} lfm25_batch_plan;
+int32_t lfm25_schedule(const lfm25_cost_model* cost, const lfm25_scheduler_config* config,
+                       const lfm25_request_view* requests, size_t num_requests, uint64_t now_us,
+                       lfm25_scheduled_work* work, size_t work_capacity, lfm25_batch_plan* plan);
+
+/* Replaces PageRadixCache (src/cache/radix.rs:61-287): host-only radix index over page-sized token blocks.  Every
+ * non-root node stands for one immutable physical KV page (the caller pins newly indexed pages with
+ * lfm25_kv_allocator_pin_cached_pages); a node may carry the slot of a convolution-state checkpoint taken right
+ * after its last token.  One owner thread, like the allocator. */
+typedef struct lfm25_radix_cache lfm25_radix_cache;
+typedef struct lfm25_prefix_cache_snapshot {
+    size_t nodes;
+    size_t cached_pages;
+    size_t checkpoints;
+    uint64_t hits;
+    uint64_t misses;
+    uint64_t matched_tokens;
+} lfm25_prefix_cache_snapshot;
+int32_t lfm25_radix_cache_create(size_t page_size, size_t max_cached_pages, lfm25_radix_cache** out);
+void lfm25_radix_cache_destroy(lfm25_radix_cache* cache);
+/* longest_checkpoint (:100-107): the deepest indexed prefix of tokens[0 .. min(num_tokens, maximum_tokens)) that has
+ * a checkpoint.  Returns its length in tokens (0 = miss) and fills physical_pages[0 .. *num_pages) and
+ * *checkpoint_slot; counts a hit or a miss.  Negative: error (page buffer too small for the hit). */
+int64_t lfm25_radix_cache_longest_checkpoint(lfm25_radix_cache* cache, const uint32_t* tokens, size_t num_tokens,
+                                             size_t maximum_tokens, uint32_t* physical_pages, size_t pages_capacity,
+                                             size_t* num_pages, uint32_t* checkpoint_slot);
+/* probe_checkpoint (:109-114): the same lookup without touching the hit / miss counters. */
+int64_t lfm25_radix_cache_probe_checkpoint(lfm25_radix_cache* cache, const uint32_t* tokens, size_t num_tokens,
+                                           size_t maximum_tokens, uint32_t* physical_pages, size_t pages_capacity,
+                                           size_t* num_pages, uint32_t* checkpoint_slot);
+/* can_publish (:181-206): 1 when the page-aligned prefix is not yet checkpointed and its new pages fit the budget. */
+uint32_t lfm25_radix_cache_can_publish(const lfm25_radix_cache* cache, const uint32_t* tokens, size_t num_tokens,
+                                       size_t prefix_tokens);
+/* insert_checkpoint (:210-271): indexes the prefix; newly_cached_pages (room for prefix_tokens / page_size entries)
+ * receives the physical pages that became owned by new nodes, their count is the return value (negative: error). */
+int64_t lfm25_radix_cache_insert_checkpoint(lfm25_radix_cache* cache, const uint32_t* tokens, size_t num_tokens,
+                                            size_t prefix_tokens, const uint32_t* physical_pages,
+                                            size_t num_physical_pages, uint32_t checkpoint_slot,
+                                            uint32_t* newly_cached_pages);
+void lfm25_radix_cache_snapshot(const lfm25_radix_cache* cache, lfm25_prefix_cache_snapshot* out);
+
+/* Replaces ConvCheckpointPool (src/model/prefix.rs:15-129): `capacity` snapshots of every gated-convolution layer's
+ * recurrent state, [capacity, hidden_size, state_width] bf16 per layer on the device.  acquire: a free slot or -1;
+ * capture / restore: same-stream device-to-device copy between slot `checkpoint_slot` of layer `convolution_index`
+ * and row `request_slot` of that layer's live state tensor [num_request_slots, hidden_size, state_width]. */
+typedef struct lfm25_conv_checkpoints lfm25_conv_checkpoints;
+int32_t lfm25_conv_checkpoints_create(size_t convolution_layers, size_t capacity, size_t hidden_size,
+                                      size_t state_width, lfm25_conv_checkpoints** out);
+void lfm25_conv_checkpoints_destroy(lfm25_conv_checkpoints* pool);
+int64_t lfm25_conv_checkpoints_acquire(lfm25_conv_checkpoints* pool);
+void lfm25_conv_checkpoints_release(lfm25_conv_checkpoints* pool, uint32_t slot);
+size_t lfm25_conv_checkpoints_available(const lfm25_conv_checkpoints* pool);
+size_t lfm25_conv_checkpoints_capacity(const lfm25_conv_checkpoints* pool);
+int32_t lfm25_conv_checkpoints_capture_layer(lfm25_conv_checkpoints* pool, void* stream, uint32_t checkpoint_slot,
+                                             size_t convolution_index, const void* states, size_t request_slot,
+                                             size_t num_request_slots);
+int32_t lfm25_conv_checkpoints_restore_layer(lfm25_conv_checkpoints* pool, void* stream, uint32_t checkpoint_slot,
+                                             size_t convolution_index, void* states, size_t request_slot,
+                                             size_t num_request_slots);
+
 /* Request dispatcher over engine replicas (one replica per GPU; the model and every sequence's KV fit one GPU, so
  * nothing is sharded and no collective runs on the step path).  A request goes to the live replica with the least
  * outstanding tokens, except that requests sharing a prompt prefix go to the replica that prefix hashes to, so

@@ -89,6 +89,37 @@ class RaggedBatch(ctypes.Structure):
                 ("num_segments", ctypes.c_size_t)]
 
 
+class PrefixCacheSnapshot(ctypes.Structure):
+    _fields_ = [("nodes", ctypes.c_size_t), ("cached_pages", ctypes.c_size_t), ("checkpoints", ctypes.c_size_t),
+                ("hits", ctypes.c_uint64), ("misses", ctypes.c_uint64), ("matched_tokens", ctypes.c_uint64)]
+
+
+class CostPoint(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_size_t), ("tokens", ctypes.c_size_t), ("context", ctypes.c_size_t),
+                ("milliseconds", ctypes.c_double)]
+
+
+class SchedulerConfig(ctypes.Structure):
+    _fields_ = [("step_budget_ms", ctypes.c_double), ("ttft_slo_us", ctypes.c_uint64),
+                ("tpot_slo_us", ctypes.c_uint64), ("fp8_decode", ctypes.c_uint32),
+                ("maximum_prefill_tokens", ctypes.c_size_t)]
+
+
+class RequestView(ctypes.Structure):
+    _fields_ = [("phase", ctypes.c_uint32), ("prompt_len", ctypes.c_size_t), ("prefilled", ctypes.c_size_t),
+                ("context_tokens", ctypes.c_size_t), ("arrival_us", ctypes.c_uint64),
+                ("first_token_deadline_us", ctypes.c_uint64), ("next_token_deadline_us", ctypes.c_uint64)]
+
+
+class ScheduledWork(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_uint32), ("slot", ctypes.c_uint32), ("tokens", ctypes.c_size_t)]
+
+
+class BatchPlan(ctypes.Structure):
+    _fields_ = [("predicted_ms", ctypes.c_double), ("decode_count", ctypes.c_size_t),
+                ("prefill_tokens", ctypes.c_size_t), ("work_count", ctypes.c_size_t)]
+
+
 class Fp8Site(ctypes.Structure):
     _fields_ = [("data", ctypes.c_void_p), ("activation_quantize", ctypes.c_float),
                 ("activation_dequantize", ctypes.c_float), ("weight_dequantize", ctypes.c_float)]
@@ -207,6 +238,39 @@ PROTOTYPES = {
     "lfm25_block_tables_data": (_P(ctypes.c_uint32), [ctypes.c_void_p]),
     "lfm25_schedule_decode": (_size, [_P(ctypes.c_uint32), _P(ctypes.c_uint64), _P(ctypes.c_uint32), _size,
                                       ctypes.c_uint64, _P(ctypes.c_uint32), _P(_size)]),
+    "lfm25_cost_model_create": (
+        ctypes.c_int32, [_P(CostPoint), _size, _P(CostPoint), _size, _P(CostPoint), _size, _size,
+                         _P(ctypes.c_void_p)]),
+    "lfm25_cost_model_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_cost_model_predict": (ctypes.c_double, [ctypes.c_void_p, ctypes.c_uint32, _size, _size, _size]),
+    "lfm25_cost_model_predict_decode_ms": (ctypes.c_double, [ctypes.c_void_p, _size, _size, ctypes.c_uint32]),
+    "lfm25_cost_model_predict_prefill_ms": (ctypes.c_double, [ctypes.c_void_p, _size]),
+    "lfm25_schedule": (
+        ctypes.c_int32, [ctypes.c_void_p, _P(SchedulerConfig), _P(RequestView), _size, ctypes.c_uint64,
+                         _P(ScheduledWork), _size, _P(BatchPlan)]),
+    "lfm25_radix_cache_create": (ctypes.c_int32, [_size, _size, _P(ctypes.c_void_p)]),
+    "lfm25_radix_cache_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_radix_cache_longest_checkpoint": (
+        ctypes.c_int64, [ctypes.c_void_p, _P(ctypes.c_uint32), _size, _size, _P(ctypes.c_uint32), _size, _P(_size),
+                         _P(ctypes.c_uint32)]),
+    "lfm25_radix_cache_probe_checkpoint": (
+        ctypes.c_int64, [ctypes.c_void_p, _P(ctypes.c_uint32), _size, _size, _P(ctypes.c_uint32), _size, _P(_size),
+                         _P(ctypes.c_uint32)]),
+    "lfm25_radix_cache_can_publish": (ctypes.c_uint32, [ctypes.c_void_p, _P(ctypes.c_uint32), _size, _size]),
+    "lfm25_radix_cache_insert_checkpoint": (
+        ctypes.c_int64, [ctypes.c_void_p, _P(ctypes.c_uint32), _size, _size, _P(ctypes.c_uint32), _size,
+                         ctypes.c_uint32, _P(ctypes.c_uint32)]),
+    "lfm25_radix_cache_snapshot": (None, [ctypes.c_void_p, _P(PrefixCacheSnapshot)]),
+    "lfm25_conv_checkpoints_create": (ctypes.c_int32, [_size, _size, _size, _size, _P(ctypes.c_void_p)]),
+    "lfm25_conv_checkpoints_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_conv_checkpoints_acquire": (ctypes.c_int64, [ctypes.c_void_p]),
+    "lfm25_conv_checkpoints_release": (None, [ctypes.c_void_p, ctypes.c_uint32]),
+    "lfm25_conv_checkpoints_available": (ctypes.c_size_t, [ctypes.c_void_p]),
+    "lfm25_conv_checkpoints_capacity": (ctypes.c_size_t, [ctypes.c_void_p]),
+    "lfm25_conv_checkpoints_capture_layer": (
+        ctypes.c_int32, [ctypes.c_void_p, _stream, ctypes.c_uint32, _size, ctypes.c_void_p, _size, _size]),
+    "lfm25_conv_checkpoints_restore_layer": (
+        ctypes.c_int32, [ctypes.c_void_p, _stream, ctypes.c_uint32, _size, ctypes.c_void_p, _size, _size]),
     "lfm25_dispatcher_create": (ctypes.c_int32, [_size, _P(ctypes.c_void_p)]),
     "lfm25_dispatcher_destroy": (None, [ctypes.c_void_p]),
     "lfm25_dispatcher_assign": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint64]),

@@ -142,3 +142,152 @@ class Dispatcher:
         if getattr(self, "_handle", None):
             library().lfm25_dispatcher_destroy(self._handle)
             self._handle = None
+
+
+class PageRadixCache:
+    """Reference: src/cache/radix.rs:61-287.  Host-only radix index over page-sized token blocks; a node may carry
+    the slot of a convolution-state checkpoint."""
+
+    def __init__(self, page_size: int, max_cached_pages: int):
+        self._handle = ctypes.c_void_p()
+        self.page_size = page_size
+        check(library().lfm25_radix_cache_create(page_size, max_cached_pages, ctypes.byref(self._handle)))
+
+    def _lookup(self, function, tokens, maximum_tokens: int):
+        array = np.ascontiguousarray(tokens, dtype=np.uint32)
+        capacity = max(1, array.size // self.page_size)
+        pages = np.zeros(capacity, dtype=np.uint32)
+        count = ctypes.c_size_t(0)
+        slot = ctypes.c_uint32(0)
+        matched = function(self._handle, _table_pointer(array), array.size, maximum_tokens, _table_pointer(pages),
+                           capacity, ctypes.byref(count), ctypes.byref(slot))
+        if matched < 0:
+            check(int(matched))
+        if matched == 0:
+            return None
+        return int(matched), int(slot.value), pages[:count.value].copy()
+
+    def longest_checkpoint(self, tokens, maximum_tokens: int):
+        """(matched tokens, checkpoint slot, physical pages) of the deepest checkpointed prefix, or None; counts a
+        hit or a miss."""
+        return self._lookup(library().lfm25_radix_cache_longest_checkpoint, tokens, maximum_tokens)
+
+    def probe_checkpoint(self, tokens, maximum_tokens: int):
+        """The same lookup without touching the admission statistics."""
+        return self._lookup(library().lfm25_radix_cache_probe_checkpoint, tokens, maximum_tokens)
+
+    def can_publish(self, tokens, prefix_tokens: int) -> bool:
+        array = np.ascontiguousarray(tokens, dtype=np.uint32)
+        return bool(library().lfm25_radix_cache_can_publish(self._handle, _table_pointer(array), array.size,
+                                                            prefix_tokens))
+
+    def insert_checkpoint(self, tokens, prefix_tokens: int, physical_pages, checkpoint_slot: int) -> np.ndarray:
+        """Indexes the prefix; returns the physical pages that became owned by new nodes (to be pinned)."""
+        array = np.ascontiguousarray(tokens, dtype=np.uint32)
+        pages = np.ascontiguousarray(physical_pages, dtype=np.uint32)
+        fresh = np.zeros(max(1, pages.size), dtype=np.uint32)
+        created = library().lfm25_radix_cache_insert_checkpoint(
+            self._handle, _table_pointer(array), array.size, prefix_tokens, _table_pointer(pages), pages.size,
+            checkpoint_slot, _table_pointer(fresh))
+        if created < 0:
+            check(int(created))
+        return fresh[:created].copy()
+
+    def snapshot(self) -> dict:
+        out = _abi.PrefixCacheSnapshot()
+        library().lfm25_radix_cache_snapshot(self._handle, ctypes.byref(out))
+        return {name: int(getattr(out, name)) for name, _ in out._fields_}
+
+    def close(self) -> None:
+        if self._handle:
+            library().lfm25_radix_cache_destroy(self._handle)
+            self._handle = None
+
+
+class ConvCheckpointPool:
+    """Reference: src/model/prefix.rs:15-129.  Device-resident snapshots of every convolution layer's state."""
+
+    def __init__(self, convolution_layers: int, capacity: int, hidden_size: int = 2048, state_width: int = 2):
+        self._handle = ctypes.c_void_p()
+        check(library().lfm25_conv_checkpoints_create(convolution_layers, capacity, hidden_size, state_width,
+                                                      ctypes.byref(self._handle)))
+
+    def acquire(self):
+        slot = library().lfm25_conv_checkpoints_acquire(self._handle)
+        return None if slot < 0 else int(slot)
+
+    def release(self, slot: int) -> None:
+        library().lfm25_conv_checkpoints_release(self._handle, slot)
+
+    def available(self) -> int:
+        return int(library().lfm25_conv_checkpoints_available(self._handle))
+
+    def capacity(self) -> int:
+        return int(library().lfm25_conv_checkpoints_capacity(self._handle))
+
+    def capture_layer(self, stream: int, checkpoint_slot: int, convolution_index: int, states, request_slot: int):
+        check(library().lfm25_conv_checkpoints_capture_layer(self._handle, stream, checkpoint_slot,
+                                                             convolution_index, states.data_ptr(), request_slot,
+                                                             states.shape[0]))
+
+    def restore_layer(self, stream: int, checkpoint_slot: int, convolution_index: int, states, request_slot: int):
+        check(library().lfm25_conv_checkpoints_restore_layer(self._handle, stream, checkpoint_slot,
+                                                             convolution_index, states.data_ptr(), request_slot,
+                                                             states.shape[0]))
+
+    def close(self) -> None:
+        if self._handle:
+            library().lfm25_conv_checkpoints_destroy(self._handle)
+            self._handle = None
+
+
+class HardwareCostModel:
+    """Reference: src/scheduler/cost_model.rs:185-231.  Curves are lists of (batch, tokens, context, milliseconds)."""
+
+    CURVES = {"decode_bf16": 0, "decode_fp8": 1, "prefill_bf16": 2}
+
+    def __init__(self, decode_bf16, decode_fp8, prefill_bf16, page_size: int = 16):
+        def points(values):
+            return (_abi.CostPoint * len(values))(*[_abi.CostPoint(*value) for value in values])
+
+        self._handle = ctypes.c_void_p()
+        a, b, c = points(decode_bf16), points(decode_fp8), points(prefill_bf16)
+        check(library().lfm25_cost_model_create(a, len(decode_bf16), b, len(decode_fp8), c, len(prefill_bf16),
+                                                page_size, ctypes.byref(self._handle)))
+
+    def predict(self, curve: str, batch: int, tokens: int, context: int) -> float:
+        return float(library().lfm25_cost_model_predict(self._handle, self.CURVES[curve], batch, tokens, context))
+
+    def predict_decode_ms(self, batch: int, maximum_context: int, fp8: bool) -> float:
+        return float(library().lfm25_cost_model_predict_decode_ms(self._handle, batch, maximum_context, int(fp8)))
+
+    def predict_prefill_ms(self, tokens: int) -> float:
+        return float(library().lfm25_cost_model_predict_prefill_ms(self._handle, tokens))
+
+    def close(self) -> None:
+        if self._handle:
+            library().lfm25_cost_model_destroy(self._handle)
+            self._handle = None
+
+
+def schedule(cost: HardwareCostModel, requests, now_us: int, step_budget_ms: float = 40.0,
+             ttft_slo_us: int = 400_000, tpot_slo_us: int = 50_000, fp8_decode: bool = True,
+             maximum_prefill_tokens: int = 512):
+    """Scheduler::schedule (src/scheduler/planner.rs:80-236) with SchedulerConfig's defaults (:17-27).  `requests`:
+    one dict per request slot with phase, prompt_len, prefilled, context_tokens, arrival_us,
+    first_token_deadline_us, next_token_deadline_us.  Returns (work list of ("decode" | "prefill", slot, tokens),
+    plan dict)."""
+    views = (_abi.RequestView * max(1, len(requests)))()
+    for index, request in enumerate(requests):
+        views[index] = _abi.RequestView(request["phase"], request["prompt_len"], request["prefilled"],
+                                        request["context_tokens"], request["arrival_us"],
+                                        request["first_token_deadline_us"], request["next_token_deadline_us"])
+    config = _abi.SchedulerConfig(step_budget_ms, ttft_slo_us, tpot_slo_us, int(fp8_decode), maximum_prefill_tokens)
+    work = (_abi.ScheduledWork * max(1, len(requests)))()
+    plan = _abi.BatchPlan()
+    check(library().lfm25_schedule(cost._handle, ctypes.byref(config), views, len(requests), now_us, work,
+                                   len(requests), ctypes.byref(plan)))
+    items = [("decode" if work[i].kind == 0 else "prefill", int(work[i].slot), int(work[i].tokens))
+             for i in range(plan.work_count)]
+    return items, {"predicted_ms": float(plan.predicted_ms), "decode_count": int(plan.decode_count),
+                   "prefill_tokens": int(plan.prefill_tokens)}

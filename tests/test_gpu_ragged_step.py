@@ -147,3 +147,62 @@ def test_ragged_step_argument_checks(device):
     with pytest.raises(ops.Lfm25Error, match="up to 8192 tokens"):
         lfm_model.DecodeExecutor(blaslt, 9000, maximum_segments=4)
     blaslt.close()
+
+
+def test_prefix_reuse_through_radix_index_and_conv_checkpoints(device):
+    """The reuse path of the serving loop (src/engine/serving/radix_owner.rs:464-547): request A prefills a prompt
+    in two chunks and publishes the page-aligned first chunk (radix index + convolution checkpoint); request B with
+    the same prompt finds it, shares the KV pages, restores the convolution states and prefills only the rest.
+    Same chunk, same inputs: B's logits must be A's, bit for bit."""
+    from lfm25_inference_b200 import cache
+
+    pages, prompt_length, shared = 16, 45, 32
+    rng = np.random.default_rng(21)
+    prompt = rng.integers(0, lfm_model.VOCAB, size=prompt_length).astype(np.uint32)
+    model = lfm_model.RandomModel(9, device, pages, 2)
+    conv_layers = [layer for layer in model.layers if not layer.is_attention]
+    allocator = cache.KvPageAllocator(pages)
+    tables = cache.FixedBlockTables(2, 4)
+    radix = cache.PageRadixCache(16, 8)
+    checkpoints = cache.ConvCheckpointPool(len(conv_layers), 4)
+    blaslt = ops.BlasLt()
+    executor = lfm_model.DecodeExecutor(blaslt, 64, maximum_segments=2)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def prefill(slot, start, stop):
+        batch = workloads.MixedStepBatch(pages, tables.as_array().copy(), np.array([start]), np.array([stop - start]),
+                                         np.array([slot], dtype=np.uint32))
+        executor.forward_ragged(model, lfm_model.RaggedBatch(device, batch, prompt[start:stop]), use_fp8=False)
+
+    # request A, slot 0
+    allocator.try_reserve_tokens(prompt_length)
+    allocator.grow_sequence(0, prompt_length, tables.slot(0))
+    prefill(0, 0, shared)
+    slot = checkpoints.acquire()
+    for index, layer in enumerate(conv_layers):
+        checkpoints.capture_layer(stream, slot, index, layer.tensors["conv_state"], 0)
+    assert radix.can_publish(prompt, shared)
+    allocator.pin_cached_pages(radix.insert_checkpoint(prompt, shared, tables.slot(0)[:shared // 16], slot))
+    prefill(0, shared, prompt_length)
+    logits_a = executor.logits(1).copy()
+
+    # request B, slot 1: the admission lookup leaves at least one prompt token to compute
+    matched, found_slot, shared_pages = radix.longest_checkpoint(prompt, prompt_length - 1)
+    assert (matched, found_slot) == (shared, slot) and list(shared_pages) == list(tables.slot(0)[:2])
+    allocator.retain_pages(shared_pages)
+    tables.slot(1)[:len(shared_pages)] = shared_pages
+    allocator.try_reserve_tokens(prompt_length - matched)
+    allocator.grow_sequence(matched, prompt_length, tables.slot(1))
+    assert tables.slot(1)[2] != tables.slot(0)[2]                     # the unshared tail has its own page
+    for index, layer in enumerate(conv_layers):
+        checkpoints.restore_layer(stream, found_slot, index, layer.tensors["conv_state"], 1)
+    prefill(1, matched, prompt_length)
+    logits_b = executor.logits(1).copy()
+
+    assert np.array_equal(logits_a, logits_b)
+    assert radix.snapshot()["hits"] == 1 and checkpoints.available() == 3
+    assert ops.device_status()[0] == 0
+    executor.close()
+    blaslt.close()
+    checkpoints.close()
+    radix.close()
