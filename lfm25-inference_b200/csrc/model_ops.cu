@@ -77,9 +77,78 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
                 __nv_bfloat16* __restrict__ out, uint8_t* __restrict__ codes, float code_scale, size_t rows,
                 size_t hidden, float eps) {
     pdl_launch_dependents();
-    pdl_wait();
     __shared__ float scratch[8];
     const size_t row = blockIdx.x;
+    const uintptr_t alignment = reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(update) |
+                                reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(residual_out) |
+                                reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(codes);
+    if (hidden == 8 * kRowThreads && blockDim.x == kRowThreads && (alignment & 15) == 0) {
+        // The model's width (2048): every thread keeps its 8 consecutive elements in registers between the two
+        // passes, all accesses are 16 bytes wide, and the norm weights (constants) are fetched before the
+        // dependency wait.
+        const uint4 weight_raw = *reinterpret_cast<const uint4*>(weight + threadIdx.x * 8);
+        pdl_wait();
+        if (row >= rows) {
+            return;
+        }
+        const size_t base = row * hidden + threadIdx.x * 8;
+        const uint4 x_raw = *reinterpret_cast<const uint4*>(x + base);
+        const __nv_bfloat162* x_pairs = reinterpret_cast<const __nv_bfloat162*>(&x_raw);
+        const __nv_bfloat162* weight_pairs = reinterpret_cast<const __nv_bfloat162*>(&weight_raw);
+        float2 value[4];
+        __nv_bfloat162 source[4];   // what the second pass normalises: x, or the rounded residual
+        float local = 0.0f;
+        if (RESIDUAL) {
+            const uint4 update_raw = *reinterpret_cast<const uint4*>(update + base);
+            const __nv_bfloat162* update_pairs = reinterpret_cast<const __nv_bfloat162*>(&update_raw);
+#pragma unroll
+            for (uint32_t pair = 0; pair < 4; ++pair) {
+                const float2 a = __bfloat1622float2(x_pairs[pair]);
+                const float2 b = __bfloat1622float2(update_pairs[pair]);
+                value[pair] = make_float2(a.x + b.x, a.y + b.y);
+                source[pair] = __floats2bfloat162_rn(value[pair].x, value[pair].y);
+            }
+            *reinterpret_cast<uint4*>(residual_out + base) = *reinterpret_cast<const uint4*>(source);
+        } else {
+#pragma unroll
+            for (uint32_t pair = 0; pair < 4; ++pair) {
+                value[pair] = __bfloat1622float2(x_pairs[pair]);
+                source[pair] = x_pairs[pair];
+            }
+        }
+#pragma unroll
+        for (uint32_t pair = 0; pair < 4; ++pair) {
+            local = fmaf(value[pair].x, value[pair].x, local);
+            local = fmaf(value[pair].y, value[pair].y, local);
+        }
+        const float total = block_sum_256(local, scratch);
+        const float inv_rms = __frsqrt_rn(total / static_cast<float>(hidden) + eps);
+        __nv_bfloat162 result[4];
+#pragma unroll
+        for (uint32_t pair = 0; pair < 4; ++pair) {
+            const float2 r = __bfloat1622float2(source[pair]);
+            if (RESIDUAL) {
+                const float2 w = __bfloat1622float2(weight_pairs[pair]);
+                result[pair] = __floats2bfloat162_rn(r.x * inv_rms * w.x, r.y * inv_rms * w.y);
+            } else {
+                result[pair] = __hmul2(__floats2bfloat162_rn(r.x * inv_rms, r.y * inv_rms), weight_pairs[pair]);
+            }
+        }
+        *reinterpret_cast<uint4*>(out + base) = *reinterpret_cast<const uint4*>(result);
+        if (codes != nullptr) {
+            uint16_t packed[4];
+#pragma unroll
+            for (uint32_t pair = 0; pair < 4; ++pair) {
+                const float2 rounded = __bfloat1622float2(result[pair]);
+                asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;"
+                    : "=h"(packed[pair])
+                    : "f"(rounded.x * code_scale), "f"(rounded.y * code_scale));
+            }
+            *reinterpret_cast<uint2*>(codes + base) = *reinterpret_cast<const uint2*>(packed);
+        }
+        return;
+    }
+    pdl_wait();
     if (row >= rows) {
         return;
     }
