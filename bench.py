@@ -55,7 +55,7 @@ STEP_POOL_PAGES = 32768
 def parse_arguments():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--workload", default="step", choices=["step", "attention", "prefill"])
+    parser.add_argument("--workload", default="step", choices=["step", "attention", "prefill", "serving"])
     parser.add_argument("--steps", type=int, default=0, help="timed steps (default 256 for step, 1024 for attention)")
     parser.add_argument("--warmup", type=int, default=0, help="warm-up steps (default 8 / 32)")
     parser.add_argument("--no-fp8", action="store_true", help="step workload: run every site in BF16")
@@ -68,11 +68,13 @@ def parse_arguments():
                         help="step workload: sequences in the batch (the headline number needs the default)")
     parser.add_argument("--pool-pages", type=int, default=NUM_PAGES, help="pages in the K/V pool (same remark)")
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
+    parser.add_argument("--requests", type=int, default=192, help="serving workload: requests in the trace")
+    parser.add_argument("--rate", type=float, default=32.0, help="serving workload: Poisson arrival rate, requests/s")
     arguments = parser.parse_args()
     if arguments.steps <= 0:
-        arguments.steps = {"step": 256, "attention": 1024, "prefill": 16}[arguments.workload]
+        arguments.steps = {"step": 256, "attention": 1024, "prefill": 16, "serving": 1}[arguments.workload]
     if arguments.warmup <= 0:
-        arguments.warmup = {"step": 8, "attention": 32, "prefill": 3}[arguments.workload]
+        arguments.warmup = {"step": 8, "attention": 32, "prefill": 3, "serving": 3}[arguments.workload]
     globals().update(SEQUENCES=arguments.sequences, NUM_PAGES=arguments.pool_pages,
                      STEP_SEQUENCES=arguments.step_sequences)
     return arguments
@@ -825,6 +827,104 @@ def prefill_cpu_sample(model, batch, token_ids):
             "sample": "one mixed step with one 64-token chunk on a 192-token prefix (16 layers, BF16), once"}
 
 
+# ------------------------------------------------------------------------------------ serving trace (config 4)
+
+SERVING_METRIC = "serving generated tok/s (continuous batching over a Poisson trace, 64 request slots)"
+SERVING_WORKLOAD = "config4-poisson-trace-prompt-lognormal512-output-u64-512-shared-prefix256"
+
+
+def serving_trace(seed, count, rate_per_s):
+    """BASELINE config 4 as seeded synthetic requests: Poisson arrivals (exponential gaps), prompt length
+    round(exp(N(ln 512, 1.0))) clipped to [16, 8192] (the spread 1.0 is an assumption of this build: the source names
+    only the median), uniform token ids, output length U{64..512}, and half of the requests starting with one fixed
+    256-token prefix."""
+    from lfm25_inference_b200 import model as lfm_model
+    from lfm25_inference_b200 import serving
+    rng = np.random.default_rng(seed)
+    shared = rng.integers(0, lfm_model.VOCAB, size=256).astype(np.uint32)
+    arrivals = np.cumsum(rng.exponential(1.0 / rate_per_s, size=count))
+    requests = []
+    for index in range(count):
+        length = int(np.clip(round(float(np.exp(rng.normal(np.log(512.0), 1.0)))), 16, 8192))
+        prompt = rng.integers(0, lfm_model.VOCAB, size=length).astype(np.uint32)
+        if rng.random() < 0.5:
+            prompt = np.concatenate([shared, prompt])[:8192]
+        requests.append(serving.Request(index, prompt, int(rng.integers(64, 513)), int(arrivals[index] * 1e6)))
+    return requests
+
+
+def run_serving_arm(arguments, rank, world):
+    """One "step" = the whole trace.  `value` = generated tokens / makespan, measured end to end through the serving
+    loop (token ids in host memory in, sampled ids in host memory out, every step synchronised), so `e2e` is the same
+    number.  Each rank serves its own trace (replicas)."""
+    import torch
+    import torch.distributed as dist
+
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    entry.load_package()
+    from lfm25_inference_b200 import model as lfm_model
+    from lfm25_inference_b200 import serving
+
+    slots, max_sequence = 64, 8192 + 512 + 16
+    pages = slots * ((max_sequence + 15) // 16) // 2 + 4096      # half of the worst case plus the radix budget
+    stream = torch.cuda.Stream(device=device)
+    with torch.cuda.stream(stream):
+        model = lfm_model.RandomModel(4 + rank, device, pages, slots)
+        engine = serving.ServingEngine(model, device, max_slots=slots, max_sequence_tokens=max_sequence,
+                                       max_prefill_tokens=512, radix_pages=4096, checkpoint_capacity=128,
+                                       use_fp8=not arguments.no_fp8)
+        engine.calibrate()
+        for _ in range(max(arguments.warmup, 1)):                   # short warm-up traces (plans, attributes)
+            serving.run_trace(engine, serving_trace(100 + rank, 8, 1000.0))
+        engine.stats = {key: 0 if not isinstance(value, float) else 0.0 for key, value in engine.stats.items()}
+        if world > 1:
+            dist.barrier()
+        with ClockSampler(local_rank) as sampler:
+            result = serving.run_trace(engine, serving_trace(4 + rank, arguments.requests, arguments.rate))
+        clocks = sampler.summary()
+        makespan_ms = result["makespan_us"] / 1e3
+    (makespan_ms,) = max_over_ranks([makespan_ms], device, world)
+    if rank == 0:
+        finished = result["requests"]
+        ttft = np.array([entry_["ttft_us"] for entry_ in finished]) / 1e3
+        tpot = np.array([entry_["tpot_us"] for entry_ in finished if entry_["tpot_us"] > 0]) / 1e3
+        generated = sum(entry_["generated"] for entry_ in finished)
+        prompt_tokens = sum(entry_["prompt_len"] for entry_ in finished)
+        stats, prefix = result["stats"], result["prefix_cache"]
+        value = generated * world / (makespan_ms * 1e-3)
+        line = {
+            "metric": SERVING_METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": 1,
+            "warmup": arguments.warmup, "ms_per_step": makespan_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16" if arguments.no_fp8 else "bf16+e4m3", "data": "synthetic",
+            "config": {"workload": SERVING_WORKLOAD, "requests": arguments.requests, "rate_per_s": arguments.rate,
+                       "request_slots": slots, "maximum_prefill_tokens": 512, "page_size": 16,
+                       "prompt_sigma": 1.0, "replicas": world, "step": "eager launches, one host sync per step"},
+            "requests_per_s": len(finished) * world / (makespan_ms * 1e-3),
+            "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+            "ttft_p50_ms": float(np.percentile(ttft, 50)), "ttft_p95_ms": float(np.percentile(ttft, 95)),
+            "tpot_p50_ms": float(np.percentile(tpot, 50)), "tpot_p95_ms": float(np.percentile(tpot, 95)),
+            "engine_steps": stats["steps"], "mixed_steps": stats["mixed_steps"], "decode_steps": stats["decode_steps"],
+            "gpu_busy_frac": stats["gpu_ms"] / makespan_ms,
+            "prefix_cache": {"hits": prefix["hits"], "misses": prefix["misses"],
+                             "reused_prompt_tokens": stats["reused_tokens"],
+                             "reused_frac": stats["reused_tokens"] / max(prompt_tokens, 1)},
+            "cost_curves_ms": engine.calibration,
+            "roofline": None, "cpu_baseline": None,
+            "e2e": {"value": value, "unit": "tok/s",
+                    "h2d_bytes_per_step": 4 * (prompt_tokens + generated) * 3 // max(stats["steps"], 1),
+                    "d2h_bytes_per_step": 4 * slots, "steps": stats["steps"]},
+            "gpu_launches": None, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    engine.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     arguments = parse_arguments()
     rank = int(os.environ.get("RANK", 0))
@@ -834,6 +934,11 @@ def main():
             run_step_reference_arm(arguments, rank)
         else:
             run_step_arm(arguments, rank, world)
+        return
+    if arguments.workload == "serving":
+        if arguments.impl == "reference":
+            raise SystemExit("--impl reference times the decode workloads")
+        run_serving_arm(arguments, rank, world)
         return
     if arguments.workload == "prefill":
         if arguments.impl == "reference":

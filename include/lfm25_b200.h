@@ -456,6 +456,12 @@ typedef struct lfm25_ragged_batch {
     size_t block_table_rows;
     size_t num_tokens;
     size_t num_segments;
+    /* Extension: the first num_decode_segments segments are single-token decode segments (segment_offsets[i] == i
+     * for i <= num_decode_segments, which is how Scheduler::schedule orders its work: decodes first).  Their
+     * attention then runs in the decode kernel (KV-axis splits chosen from max_decode_context_tokens, the longest
+     * context among them) and only the remaining segments in the hybrid kernel.  0: everything in the hybrid kernel. */
+    size_t num_decode_segments;
+    size_t max_decode_context_tokens;
 } lfm25_ragged_batch;
 /* An executor for steps of up to maximum_tokens tokens (<= 8192) in up to maximum_segments sequences (<= 256):
  * lfm25_decode_executor_create is the case maximum_tokens == maximum_segments. */

@@ -86,7 +86,8 @@ class RaggedBatch(ctypes.Structure):
                 ("segment_slots", ctypes.c_void_p), ("output_rows", ctypes.c_void_p),
                 ("block_tables", ctypes.c_void_p), ("block_table_stride", ctypes.c_size_t),
                 ("block_table_rows", ctypes.c_size_t), ("num_tokens", ctypes.c_size_t),
-                ("num_segments", ctypes.c_size_t)]
+                ("num_segments", ctypes.c_size_t), ("num_decode_segments", ctypes.c_size_t),
+                ("max_decode_context_tokens", ctypes.c_size_t)]
 
 
 class PrefixCacheSnapshot(ctypes.Structure):

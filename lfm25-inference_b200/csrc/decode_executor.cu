@@ -423,7 +423,47 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                 RegionTimer timer(self, LFM25_REGION_APPEND);
                 LFM25_TRY(lfm25_qk_norm_rope_kv_write_decode(stream, &post));
             }
-            {
+            const size_t decode_tokens = batch->num_decode_segments;
+            const lfm25_slice tables_slice =
+                slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
+            if (decode_tokens > 0) {
+                // the leading single-token segments: the decode kernel (pages split over warps and, for long
+                // contexts, over CTAs) instead of one 16-row tile per token
+                RegionTimer timer(self, LFM25_REGION_ATTENTION);
+                const size_t splits = lfm25_splitk_decode_splits(decode_tokens, batch->max_decode_context_tokens, 16);
+                lfm25_splitk_ragged_attention_launch decode;
+                decode.page_size = 16;
+                decode.query = slice_of(self->query, decode_tokens * kQueryWidth);
+                decode.key_cache = post.key_cache;
+                decode.value_cache = post.value_cache;
+                decode.block_tables = tables_slice;
+                decode.request_slots = slice_of(batch->request_slots, decode_tokens);
+                decode.position_ids = slice_of(batch->positions, decode_tokens);
+                decode.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
+                decode.output = slice_of(self->post_operator, decode_tokens * kHidden);
+                decode.num_tokens = decode_tokens;
+                decode.num_pages = model->num_pages;
+                decode.block_table_stride = batch->block_table_stride;
+                decode.num_splits = splits;
+                if (splits > 1) {
+                    LFM25_TRY(lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &decode));
+                } else {
+                    lfm25_fast_ragged_attention_launch unsplit;
+                    unsplit.page_size = 16;
+                    unsplit.query = decode.query;
+                    unsplit.key_cache = decode.key_cache;
+                    unsplit.value_cache = decode.value_cache;
+                    unsplit.block_tables = decode.block_tables;
+                    unsplit.request_slots = decode.request_slots;
+                    unsplit.position_ids = decode.position_ids;
+                    unsplit.output = decode.output;
+                    unsplit.num_tokens = decode_tokens;
+                    unsplit.num_pages = model->num_pages;
+                    unsplit.block_table_stride = batch->block_table_stride;
+                    LFM25_TRY(lfm25_paged_ragged_attention_fast_lfm2_bf16(stream, &unsplit));
+                }
+            }
+            if (decode_tokens < segments) {
                 RegionTimer timer(self, LFM25_REGION_ATTENTION);
                 lfm25_hybrid_attention_launch attention;
                 attention.page_size = 16;
@@ -432,16 +472,16 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                 attention.current_value = slice_of(nullptr, 0);
                 attention.key_cache = post.key_cache;
                 attention.value_cache = post.value_cache;
-                attention.block_tables = slice_of(batch->block_tables,
-                                                  batch->block_table_stride * batch->block_table_rows);
+                attention.block_tables = tables_slice;
                 attention.request_slots = slice_of(batch->request_slots, tokens);
                 attention.position_ids = post.position_ids;
-                attention.segment_offsets = slice_of(batch->segment_offsets, segments + 1);
+                // segment offsets are absolute token indices, so the remaining segments are simply a later start
+                attention.segment_offsets = slice_of(batch->segment_offsets + decode_tokens, segments - decode_tokens + 1);
                 attention.output = slice_of(self->post_operator, tokens * kHidden);
                 attention.num_tokens = tokens;
                 attention.num_pages = model->num_pages;
                 attention.block_table_stride = batch->block_table_stride;
-                attention.num_segments = segments;
+                attention.num_segments = segments - decode_tokens;
                 attention.query_token_stride = 0;
                 attention.kv_token_stride = 0;
                 LFM25_TRY(lfm25_hybrid_ragged_attention_lfm2_bf16(stream, &attention));
@@ -688,6 +728,10 @@ int32_t lfm25_decode_executor_forward_ragged(lfm25_decode_executor* self, const 
     if (batch->num_segments == 0 || batch->num_segments > self->maximum_rows ||
         batch->num_segments > batch->num_tokens) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "ragged step segment count exceeds workspace");
+    }
+    if (batch->num_decode_segments > batch->num_segments ||
+        (batch->num_decode_segments > 0 && batch->max_decode_context_tokens == 0)) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "ragged step decode-segment count is inconsistent");
     }
     if (model->num_layers == 0 || model->layers == nullptr || model->embedding == nullptr ||
         model->final_norm == nullptr || model->inv_freq == nullptr) {

@@ -199,6 +199,15 @@ class DecodeBatch:
             self.num_tokens, max_context_tokens)
 
 
+def leading_decode_segments(batch) -> tuple[int, int]:
+    """(number of leading single-token segments of a `workloads.MixedStepBatch`, longest context among them)."""
+    count = 0
+    while count < batch.num_segments and batch.chunks[count] == 1:
+        count += 1
+    context = int(batch.prefixes[:count].max()) + 1 if count else 0
+    return count, context
+
+
 class RaggedBatch:
     """Device-resident metadata of a step that mixes prefill chunks and decode tokens
     (a `workloads.MixedStepBatch` plus the token ids)."""
@@ -217,11 +226,12 @@ class RaggedBatch:
         self.num_tokens = batch.num_tokens
         self.num_segments = batch.num_segments
         self.physical_slots = torch.zeros(self.num_tokens, dtype=torch.int64, device=device)
+        decode_segments, decode_context = leading_decode_segments(batch)
         self.struct = _abi.RaggedBatch(
             self.token_ids.data_ptr(), self.positions.data_ptr(), self.request_slots.data_ptr(),
             self.physical_slots.data_ptr(), self.segment_offsets.data_ptr(), self.segment_slots.data_ptr(),
             self.output_rows.data_ptr(), self.block_tables.data_ptr(), batch.block_tables.shape[1],
-            batch.block_tables.shape[0], self.num_tokens, self.num_segments)
+            batch.block_tables.shape[0], self.num_tokens, self.num_segments, decode_segments, decode_context)
 
 
 class DecodeExecutor:

@@ -219,7 +219,7 @@ class ServingEngine:
             self.d_token_ids.data_ptr(), self.d_positions.data_ptr(), self.d_request_slots.data_ptr(),
             self.d_physical_slots.data_ptr(), self.d_segment_offsets.data_ptr(), self.d_segment_slots.data_ptr(),
             self.d_output_rows.data_ptr(), self.d_tables.data_ptr(), self.pages_per_slot, self.max_slots, tokens,
-            segments)
+            segments, *lfm_model.leading_decode_segments(batch))
         self.blaslt.bind_current_stream()
         if segments == tokens:
             # pure decode: the decode executor's path (fused append + attention, split-K policy)

@@ -24,10 +24,13 @@ def compare_logits(got_bits, want_bits, use_fp8):
     assert cosine >= (0.99 if use_fp8 else 0.999)
 
 
+@pytest.mark.parametrize("prefixes,chunks", [([0, 20, 7, 33], [19, 1, 5, 1]),       # all segments in the hybrid kernel
+                                             ([20, 33, 0, 7], [1, 1, 19, 5])])      # decode segments first: routed
 @pytest.mark.parametrize("use_fp8", [False, True])
-def test_mixed_step_against_the_oracle(device, use_fp8):
+def test_mixed_step_against_the_oracle(device, use_fp8, prefixes, chunks):
     pages = 32
-    batch = workloads.mixed_step_batch(3, [0, 20, 7, 33], [19, 1, 5, 1], pages)
+    batch = workloads.mixed_step_batch(3, prefixes, chunks, pages)
+    assert lfm_model.leading_decode_segments(batch)[0] == (2 if chunks[0] == 1 else 0)
     model = lfm_model.RandomModel(3, device, pages, batch.num_segments)
     model.fill_caches(4)
     rng = np.random.default_rng(3)
