@@ -228,6 +228,79 @@ def run_reference_arm(arguments, rank):
 # ------------------------------------------------------------------------------------ GPU arm
 
 
+def config0_latency(device):
+    """BASELINE config 0: one sequence, context 40 after the append (39 cached + 1 new), 3 pages of a 64-page pool.
+    80 KB of KV: latency-bound, so what is reported is microseconds per decode step of one attention layer, GPU-side,
+    from a CUDA graph of 64 repetitions: raw append + attention (two launches), the one-kernel decode, and -- when
+    the reference's kernels were built -- its one-kernel decode (the path config 0 takes there) and its append +
+    attention pair."""
+    import torch
+    from lfm25_inference_b200 import ops, workloads
+    c0 = workloads.single_step_c0(0)
+
+    def bf16(bits):
+        return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16).copy()).view(torch.bfloat16).to(device)
+
+    def u32(values):
+        return torch.from_numpy(np.ascontiguousarray(values, dtype=np.uint32).view(np.int32).copy()).to(device)
+
+    arena = ops.PagedKvArena(torch.zeros((64, 8, 16, 64), dtype=torch.bfloat16, device=device),
+                             torch.zeros((64, 8, 16, 64), dtype=torch.bfloat16, device=device))
+    arena.write_lfm2(bf16(c0["cached_key"]), bf16(c0["cached_value"]), torch.from_numpy(c0["cached_slots"]).to(device))
+    query, key, value = bf16(c0["query"]), bf16(c0["new_key"]), bf16(c0["new_value"])
+    slot, position = torch.from_numpy(c0["new_slot"]).to(device), u32(c0["position"])
+    table, request_slot = u32(c0["block_table"]), u32(c0["request_slot"])
+    ones, inv_freq = torch.ones(64, dtype=torch.bfloat16, device=device), torch.from_numpy(_inv_freq()).to(device)
+    output = torch.zeros_like(query)
+    inputs = ops.FastRaggedAttentionInput(query, arena, table, 3, request_slot, position)
+
+    def two_launches():
+        arena.write_lfm2(key, value, slot)
+        ops.paged_ragged_attention_fast_lfm2_bf16_into(inputs, output)
+
+    def one_kernel():
+        ops.fused_ragged_paged_attention_decode_lfm2_bf16_into(query, key, value, ones, ones, inv_freq, position, slot,
+                                                               arena, table, 3, request_slot, 1e-5, output)
+
+    calls = {"append_plus_attention_us": two_launches, "one_kernel_decode_us": one_kernel}
+    try:
+        from oracle import refkernels
+        if refkernels.available():
+            scratch = query.clone()
+            calls["reference_append_plus_attention_us"] = lambda: (
+                refkernels.kv_cache_write(key, value, arena.key, arena.value, slot),
+                refkernels.paged_ragged_attention_fast(query, arena.key, arena.value, table, request_slot, position,
+                                                       output))
+            calls["reference_qk_append_plus_attention_us"] = lambda: (
+                refkernels.qk_norm_rope_kv_write_decode(scratch, key, value, ones, ones, inv_freq, position, slot,
+                                                        arena.key, arena.value, 1e-5),
+                refkernels.paged_ragged_attention_fast(scratch, arena.key, arena.value, table, request_slot, position,
+                                                       output))
+    except Exception:                      # the comparison is optional
+        pass
+    result = {}
+    stream = torch.cuda.Stream(device=device)
+    for name, call in calls.items():
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                call()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(64):
+                    call()
+            graph.replay()
+            stream.synchronize()
+            begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            for _ in range(5):
+                graph.replay()
+            finish.record()
+            stream.synchronize()
+            result[name] = begin.elapsed_time(finish) * 1e3 / (5 * 64)
+    return result
+
+
 def run_gpu_arm(arguments, rank, world):
     import torch
     import torch.distributed as dist
@@ -378,6 +451,12 @@ def run_gpu_arm(arguments, rank, world):
             reference_kernels = {"error": str(error)[:120]}
 
     total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
+    config0 = None
+    if rank == 0:
+        try:
+            config0 = config0_latency(device)
+        except Exception as error:           # an extra; the metric does not depend on it
+            config0 = {"error": str(error)[:160]}
 
     if rank == 0:
         hbm_peak, peak_kind = peaks()
@@ -412,6 +491,7 @@ def run_gpu_arm(arguments, rank, world):
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": launches_per_step * steps,
             "reference_kernels_same_gpu": reference_kernels,
+            "config0_single_step_latency": config0,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
