@@ -960,7 +960,6 @@ def run_serving_arm(arguments, rank, world):
         engine.calibrate()
         for _ in range(max(arguments.warmup, 1)):                   # short warm-up traces (plans, attributes)
             serving.run_trace(engine, serving_trace(100 + rank, 8, 1000.0))
-        engine.stats = {key: 0 if not isinstance(value, float) else 0.0 for key, value in engine.stats.items()}
         if world > 1:
             dist.barrier()
         with ClockSampler(local_rank) as sampler:
@@ -982,7 +981,7 @@ def run_serving_arm(arguments, rank, world):
             "vs_baseline": None, "dtype": "bf16" if arguments.no_fp8 else "bf16+e4m3", "data": "synthetic",
             "config": {"workload": SERVING_WORKLOAD, "requests": arguments.requests, "rate_per_s": arguments.rate,
                        "request_slots": slots, "maximum_prefill_tokens": 512, "page_size": 16,
-                       "prompt_sigma": 1.0, "replicas": world, "step": "eager launches, one host sync per step"},
+                       "prompt_sigma": 1.0, "replicas": world, "step": "native engine loop, eager launches, one host sync per step"},
             "requests_per_s": len(finished) * world / (makespan_ms * 1e-3),
             "prompt_tokens": prompt_tokens, "generated_tokens": generated,
             "ttft_p50_ms": float(np.percentile(ttft, 50)), "ttft_p95_ms": float(np.percentile(ttft, 95)),
@@ -990,9 +989,9 @@ def run_serving_arm(arguments, rank, world):
             "engine_steps": stats["steps"], "mixed_steps": stats["mixed_steps"], "decode_steps": stats["decode_steps"],
             "gpu_busy_frac": stats["gpu_ms"] / makespan_ms,
             "prefix_cache": {"hits": prefix["hits"], "misses": prefix["misses"],
-                             "reused_prompt_tokens": stats["reused_tokens"],
-                             "reused_frac": stats["reused_tokens"] / max(prompt_tokens, 1)},
-            "cost_curves_ms": engine.calibration,
+                             "reused_prompt_tokens": stats["reused_prompt_tokens"],
+                             "reused_frac": stats["reused_prompt_tokens"] / max(prompt_tokens, 1)},
+            "cost_curves_ms": engine.predicted_ms(),
             "roofline": None, "cpu_baseline": None,
             "e2e": {"value": value, "unit": "tok/s",
                     "h2d_bytes_per_step": 4 * (prompt_tokens + generated) * 3 // max(stats["steps"], 1),

@@ -301,7 +301,9 @@ void lfm25_blaslt_destroy(lfm25_blaslt* handle);
 /* Rebinds the handle to another stream (the reference binds at construction only; work already enqueued on the
  * old stream that uses the workspace must have been ordered before new work by the caller). */
 int32_t lfm25_blaslt_set_stream(lfm25_blaslt* handle, void* stream);
-size_t lfm25_blaslt_workspace_size(const lfm25_blaslt* handle); /* BlasLt::workspace_size */
+size_t lfm25_blaslt_workspace_size(const lfm25_blaslt* handle);
+/* The stream the handle is bound to. */
+void* lfm25_blaslt_stream(const lfm25_blaslt* handle); /* BlasLt::workspace_size */
 int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                        const lfm25_fp8_linear_config* config);
 /* Replaces BlasLt::linear_bf16 (src/cuda/blaslt/mod.rs:113-186): out[M,N] = x[M,K] * weight[N,K]^T in bf16 with
@@ -691,6 +693,55 @@ int32_t lfm25_dispatcher_assign(lfm25_dispatcher* dispatcher, uint64_t prefix_ha
 void lfm25_dispatcher_complete(lfm25_dispatcher* dispatcher, size_t replica, uint64_t tokens);
 void lfm25_dispatcher_mark_failed(lfm25_dispatcher* dispatcher, size_t replica);
 uint64_t lfm25_dispatcher_load(const lfm25_dispatcher* dispatcher, size_t replica);
+
+/* The GPU-owner loop of continuous batching (src/engine/serving/radix_owner.rs:101-708 with RequestSlots /
+ * SequenceRequest, src/scheduler/{slots,request}.rs): request slots, admission with prefix reuse, planning, mixed
+ * prefill / decode steps, token bookkeeping, built from the parts above.  One engine per GPU, driven from one host
+ * thread; `model` and `blaslt` must outlive it.  lfm25_engine_calibrate measures the planner's cost curves on the
+ * idle engine (needed once before the first step).  lfm25_engine_step admits what fits, plans and runs one step on
+ * the handle's stream, synchronises once and reports the tokens it produced: one event per sequence that got a
+ * token (events needs room for max_slots entries); gpu_ms (may be NULL) is the step's GPU time.  Greedy sampling. */
+typedef struct lfm25_engine lfm25_engine;
+typedef struct lfm25_engine_config {
+    size_t max_slots;             /* concurrent sequences, <= 256 and <= model->num_request_slots */
+    size_t max_sequence_tokens;   /* prompt + generated tokens per sequence */
+    size_t max_prefill_tokens;    /* per step (the planner's maximum_prefill_tokens) */
+    size_t radix_pages;           /* page budget of the prefix index */
+    size_t checkpoint_capacity;   /* convolution-state checkpoints */
+    uint32_t use_fp8;
+    uint64_t ttft_slo_us;
+    uint64_t tpot_slo_us;
+    double step_budget_ms;
+} lfm25_engine_config;
+typedef struct lfm25_engine_event {
+    uint64_t request_id;
+    uint64_t time_us;             /* now_us of the step + its GPU time */
+    uint32_t token;
+    uint32_t finished;            /* the request produced its last token and left its slot */
+    uint32_t reused_tokens;       /* prompt tokens this request took from the prefix index */
+} lfm25_engine_event;
+typedef struct lfm25_engine_stats {
+    uint64_t steps;
+    uint64_t decode_steps;
+    uint64_t mixed_steps;
+    uint64_t generated_tokens;
+    uint64_t prefill_tokens;
+    uint64_t reused_prompt_tokens;
+    double gpu_ms;
+} lfm25_engine_stats;
+int32_t lfm25_engine_create(lfm25_blaslt* blaslt, const lfm25_model* model, const lfm25_engine_config* config,
+                            lfm25_engine** out);
+void lfm25_engine_destroy(lfm25_engine* engine);
+int32_t lfm25_engine_calibrate(lfm25_engine* engine);
+const lfm25_cost_model* lfm25_engine_cost_model(const lfm25_engine* engine);
+int32_t lfm25_engine_submit(lfm25_engine* engine, uint64_t request_id, const uint32_t* prompt, size_t prompt_len,
+                            size_t max_new_tokens, uint64_t arrival_us);
+int32_t lfm25_engine_step(lfm25_engine* engine, uint64_t now_us, lfm25_engine_event* events, size_t events_capacity,
+                          size_t* num_events, float* gpu_ms);
+size_t lfm25_engine_active(const lfm25_engine* engine);
+size_t lfm25_engine_queued(const lfm25_engine* engine);
+void lfm25_engine_get_stats(const lfm25_engine* engine, lfm25_engine_stats* stats, lfm25_kv_pool_snapshot* pool,
+                            lfm25_prefix_cache_snapshot* prefix);
 
 #ifdef __cplusplus
 }

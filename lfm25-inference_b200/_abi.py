@@ -121,6 +121,25 @@ class BatchPlan(ctypes.Structure):
                 ("prefill_tokens", ctypes.c_size_t), ("work_count", ctypes.c_size_t)]
 
 
+class EngineConfig(ctypes.Structure):
+    _fields_ = [("max_slots", ctypes.c_size_t), ("max_sequence_tokens", ctypes.c_size_t),
+                ("max_prefill_tokens", ctypes.c_size_t), ("radix_pages", ctypes.c_size_t),
+                ("checkpoint_capacity", ctypes.c_size_t), ("use_fp8", ctypes.c_uint32),
+                ("ttft_slo_us", ctypes.c_uint64), ("tpot_slo_us", ctypes.c_uint64),
+                ("step_budget_ms", ctypes.c_double)]
+
+
+class EngineEvent(ctypes.Structure):
+    _fields_ = [("request_id", ctypes.c_uint64), ("time_us", ctypes.c_uint64), ("token", ctypes.c_uint32),
+                ("finished", ctypes.c_uint32), ("reused_tokens", ctypes.c_uint32)]
+
+
+class EngineStats(ctypes.Structure):
+    _fields_ = [("steps", ctypes.c_uint64), ("decode_steps", ctypes.c_uint64), ("mixed_steps", ctypes.c_uint64),
+                ("generated_tokens", ctypes.c_uint64), ("prefill_tokens", ctypes.c_uint64),
+                ("reused_prompt_tokens", ctypes.c_uint64), ("gpu_ms", ctypes.c_double)]
+
+
 class Fp8Site(ctypes.Structure):
     _fields_ = [("data", ctypes.c_void_p), ("activation_quantize", ctypes.c_float),
                 ("activation_dequantize", ctypes.c_float), ("weight_dequantize", ctypes.c_float)]
@@ -191,6 +210,7 @@ PROTOTYPES = {
     "lfm25_blaslt_destroy": (None, [ctypes.c_void_p]),
     "lfm25_blaslt_set_stream": (ctypes.c_int32, [ctypes.c_void_p, _stream]),
     "lfm25_blaslt_workspace_size": (_size, [ctypes.c_void_p]),
+    "lfm25_blaslt_stream": (ctypes.c_void_p, [ctypes.c_void_p]),
     "lfm25_blaslt_linear_fp8_scaled": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _P(Fp8LinearConfig)]),
     "lfm25_blaslt_linear_bf16": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_embedding_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, _size]),
@@ -239,6 +259,18 @@ PROTOTYPES = {
     "lfm25_block_tables_data": (_P(ctypes.c_uint32), [ctypes.c_void_p]),
     "lfm25_schedule_decode": (_size, [_P(ctypes.c_uint32), _P(ctypes.c_uint64), _P(ctypes.c_uint32), _size,
                                       ctypes.c_uint64, _P(ctypes.c_uint32), _P(_size)]),
+    "lfm25_engine_create": (ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(EngineConfig), _P(ctypes.c_void_p)]),
+    "lfm25_engine_destroy": (None, [ctypes.c_void_p]),
+    "lfm25_engine_calibrate": (ctypes.c_int32, [ctypes.c_void_p]),
+    "lfm25_engine_cost_model": (ctypes.c_void_p, [ctypes.c_void_p]),
+    "lfm25_engine_submit": (
+        ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint64, _P(ctypes.c_uint32), _size, _size, ctypes.c_uint64]),
+    "lfm25_engine_step": (
+        ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint64, _P(EngineEvent), _size, _P(_size),
+                         _P(ctypes.c_float)]),
+    "lfm25_engine_active": (_size, [ctypes.c_void_p]),
+    "lfm25_engine_queued": (_size, [ctypes.c_void_p]),
+    "lfm25_engine_get_stats": (None, [ctypes.c_void_p, _P(EngineStats), _P(KvPoolSnapshot), _P(PrefixCacheSnapshot)]),
     "lfm25_cost_model_create": (
         ctypes.c_int32, [_P(CostPoint), _size, _P(CostPoint), _size, _P(CostPoint), _size, _size,
                          _P(ctypes.c_void_p)]),

@@ -871,6 +871,8 @@ int32_t lfm25_blaslt_set_stream(lfm25_blaslt* handle, void* stream) {
     return LFM25_OK;
 }
 
+void* lfm25_blaslt_stream(const lfm25_blaslt* handle) { return handle != nullptr ? handle->stream : nullptr; }
+
 size_t lfm25_blaslt_workspace_size(const lfm25_blaslt* handle) {
     return handle != nullptr ? handle->library_workspace_bytes : 0;
 }

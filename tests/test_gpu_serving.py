@@ -36,7 +36,7 @@ def test_trace_completes_and_reuses_prefixes(device):
         rng = np.random.default_rng(5)
         shared = rng.integers(0, lfm_model.VOCAB, size=64).astype(np.uint32)
         requests = make_requests(rng, 12, shared)
-        free_before = engine.allocator.snapshot()["free_pages"]
+        free_before = engine.snapshot()["pool"]["free_pages"]
         result = serving.run_trace(engine, requests)
         by_id = {entry["request_id"]: entry for entry in result["requests"]}
         assert sorted(by_id) == list(range(12))
@@ -49,8 +49,8 @@ def test_trace_completes_and_reuses_prefixes(device):
         assert any(entry["reused_tokens"] >= 64 for entry in result["requests"])
         assert result["stats"]["mixed_steps"] > 0 and result["stats"]["decode_steps"] > 0
         # everything returned: free slots, no reservation left, pages free except those the radix index pinned
-        assert engine.active() == 0 and len(engine.free_slots) == 8
-        snapshot = engine.allocator.snapshot()
+        assert engine.active() == 0 and engine.queued() == 0
+        snapshot = engine.snapshot()["pool"]
         assert snapshot["reserved_pages"] == 0
         assert snapshot["free_pages"] == free_before - snapshot["cached_pages"]
         assert ops.device_status()[0] == 0
