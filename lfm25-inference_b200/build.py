@@ -13,8 +13,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUTPUT = os.path.join(HERE, "liblfm25_b200.so")
 SOURCES = ["api.cu", "attention.cu", "kv_cache.cu", "fp8_elementwise.cu", "fp8_gemm_stream.cu", "fp8_gemm_umma.cu",
-           "attention_static_scratch.cu", "hybrid_attention.cu", "model_ops.cu", "cublaslt_bf16.cu", "decode_executor.cu", "host_runtime.cu", "prefix_cache.cu", "scheduler.cu", "serving_engine.cu"]
-HEADERS = ["common.cuh", "kernels.h", "tensor_map.h", "blaslt_handle.h", "launch.h", os.path.join("..", "..", "include", "lfm25_b200.h")]
+           "attention_static_scratch.cu", "hybrid_attention.cu", "hybrid_attention_umma.cu", "model_ops.cu", "cublaslt_bf16.cu", "decode_executor.cu", "host_runtime.cu", "prefix_cache.cu", "scheduler.cu", "serving_engine.cu"]
+HEADERS = ["common.cuh", "kernels.h", "tensor_map.h", "tcgen05.cuh", "blaslt_handle.h", "launch.h", os.path.join("..", "..", "include", "lfm25_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--use_fast_math=false", "-Xcompiler", "-fPIC", "-shared", "-cudart", "static", "-ldl",

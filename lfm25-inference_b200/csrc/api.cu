@@ -552,6 +552,16 @@ int32_t lfm25_hybrid_ragged_attention_lfm2_bf16(void* stream, const lfm25_hybrid
     args.query_token_stride = query_stride;
     args.kv_token_stride = kv_stride;
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    // LFM25_HYBRID_ATTENTION = umma | mma selects the tcgen05 kernel (32 tokens per CTA) or the mma.sync kernel
+    // (16 tokens per CTA)
+    const char* choice = getenv("LFM25_HYBRID_ATTENTION");
+    const bool umma_possible = (reinterpret_cast<uintptr_t>(l.query.ptr) & 15) == 0 && query_stride % 8 == 0;
+    bool use_umma = false;
+    if (choice != nullptr && strcmp(choice, "umma") == 0) use_umma = true;
+    if (use_umma && umma_possible) {
+        return cuda_result(lfm25::launch_hybrid_attention_umma(static_cast<cudaStream_t>(stream), args),
+                           "hybrid ragged attention launch failed");
+    }
     return cuda_result(lfm25::launch_hybrid_ragged_attention(static_cast<cudaStream_t>(stream), args),
                        "hybrid ragged attention launch failed");
 }

@@ -32,6 +32,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.h"
+#include "tcgen05.cuh"
 #include "tensor_map.h"
 
 namespace lfm25 {
@@ -62,16 +63,6 @@ struct UmmaParams {
     float alpha;
 };
 
-__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address) {
-    // K-major operand, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart
-    uint64_t descriptor = static_cast<uint64_t>((address & 0x3ffff) >> 4);
-    descriptor |= static_cast<uint64_t>(1) << 16;            // leading byte offset (unused with swizzle)
-    descriptor |= static_cast<uint64_t>(1024 >> 4) << 32;    // stride byte offset between 8-row groups
-    descriptor |= static_cast<uint64_t>(1) << 46;            // descriptor version of sm_100
-    descriptor |= static_cast<uint64_t>(2) << 61;            // SWIZZLE_128B
-    return descriptor;
-}
-
 template <bool BF16>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
                                      uint32_t accumulate) {
@@ -96,17 +87,6 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
     }
 }
 
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tcgen05_fence_before() {
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after() {
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-
 // ---- thread-block cluster helpers (split-K partners exchange partial tiles through distributed shared memory)
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n"
@@ -117,16 +97,6 @@ __device__ __forceinline__ uint32_t cluster_rank() {
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
     return rank;
 }
-__device__ __forceinline__ void tmem_load16(uint32_t address, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, "
-        "%15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(address));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
 template <bool BF16>
 __global__ void __launch_bounds__(kThreads, 2)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_constant__ CUtensorMap x_map,

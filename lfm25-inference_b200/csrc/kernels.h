@@ -59,6 +59,9 @@ struct HybridAttentionLaunch {
     size_t kv_token_stride = 8 * 64;
 };
 cudaError_t launch_hybrid_ragged_attention(cudaStream_t stream, const HybridAttentionLaunch& launch);
+// The same function on tcgen05 / TMEM, 32 tokens x 4 heads per CTA (hybrid_attention_umma.cu); needs the query
+// 16-byte aligned with a token stride that is a multiple of 8 elements.
+cudaError_t launch_hybrid_attention_umma(cudaStream_t stream, const HybridAttentionLaunch& launch);
 
 cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const void* value, void* key_cache,
                                   void* value_cache, const int64_t* slot_mapping, size_t num_tokens,

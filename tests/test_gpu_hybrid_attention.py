@@ -14,6 +14,13 @@ from oracle import oracle, refkernels
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["mma", "umma"], autouse=True)
+def kernel_choice(request, monkeypatch):
+    """Every case runs through both kernels: mma.sync (16 tokens per CTA) and tcgen05 (32 tokens per CTA)."""
+    monkeypatch.setenv("LFM25_HYBRID_ATTENTION", request.param)
+    return request.param
+
+
 def run_hybrid(case, device, from_cache=False, packed=False, sentinel=None, positions=None, tables=None):
     key_cache, value_cache = case["key_cache"], case["value_cache"]
     if from_cache:
