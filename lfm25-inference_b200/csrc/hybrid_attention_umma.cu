@@ -9,10 +9,13 @@
 //   warp 1      allocates 256 TMEM columns; one thread issues, per stage, S = Q K^T (4 x tcgen05.mma kind::f16, both
 //               operands K-major from shared memory, fp32 accumulator S in TMEM) and, once the softmax warps have put
 //               the weights back, PV = P V (one MMA per 16 keys: A = bf16 P read from TMEM, B = the V rows as an
-//               MN-major operand -- the page layout [key][dim] needs no transposition)
+//               MN-major operand -- the page layout [key][dim] needs no transposition).  S / P and PV are double
+//               buffered in TMEM and S of the next stage is issued before this stage's weights are awaited, so the
+//               tensor core works while the softmax warps do
 //   warps 2-5   one thread per row: tcgen05.ld S (two passes: row maximum, then weights), causal mask, exp2 online
-//               softmax without any shuffle, bf16 P written to TMEM with tcgen05.st, and O (64 fp32 registers per
-//               thread) <- O * rescale + PV read back from TMEM
+//               softmax without any shuffle, bf16 P written over the S columns it came from with tcgen05.st, and
+//               O (64 fp32 registers per thread) <- (O + PV of the previous stage) * rescale, one stage late, so that
+//               the PV product is never waited for
 //
 // Keys that do not exist or may not be read are masked by assignment, and their V rows are cleared in shared memory
 // before the PV MMA (a zero weight times a stale NaN pattern is NaN).  Every mbarrier wait is bounded; a wait that
@@ -35,16 +38,15 @@ constexpr uint32_t kTileRows = kTokensPerTile * kQPerKv;     // 128 = UMMA M
 constexpr uint32_t kUmmaThreads = 192;
 constexpr uint32_t kUmmaStages = 4;
 constexpr uint32_t kPagesPerStage = 4;                       // 64 keys per stage
-constexpr uint32_t kKeysPerStage = kPagesPerStage * kPageSize;
 constexpr uint32_t kPageBytes = kPageSize * kHeadDim * 2;    // one K or V tile of 16 keys: 2048 B
 constexpr uint32_t kHalfStageBytes = kPagesPerStage * kPageBytes;   // the K rows (or the V rows) of a stage
 constexpr uint32_t kStageBytesUmma = 2 * kHalfStageBytes;
 constexpr uint32_t kQBytes = kTileRows * kHeadDim * 2;       // 16 KiB
 constexpr uint32_t kUmmaSmem = kQBytes + kUmmaStages * kStageBytesUmma + 256 + 1024;
 constexpr uint32_t kTmemColumns = 256;
-constexpr uint32_t kColumnS = 0;      // 64 fp32 columns
-constexpr uint32_t kColumnP = 64;     // 32 columns of packed bf16 pairs
-constexpr uint32_t kColumnPV = 128;   // 64 fp32 columns
+constexpr uint32_t kColumnS = 0;      // two buffers of 64 fp32 columns; the bf16 P of a stage overwrites the first
+                                      // 32 columns of the S buffer it was computed from
+constexpr uint32_t kColumnPV = 128;   // two buffers of 64 fp32 columns
 
 struct UmmaAttentionParams {
     __nv_bfloat16* output;
@@ -158,10 +160,10 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
     const uint32_t bar_full = smem_u32(control);
     const uint32_t bar_empty = bar_full + 8 * kUmmaStages;
     const uint32_t bar_q = bar_empty + 8 * kUmmaStages;
-    const uint32_t bar_s = bar_q + 8;
-    const uint32_t bar_p = bar_s + 8;
-    const uint32_t bar_pv = bar_p + 8;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(control + 8 * (2 * kUmmaStages + 4));
+    const uint32_t bar_s = bar_q + 8;      // [2]: S of an even / odd stage is complete
+    const uint32_t bar_p = bar_s + 16;     // [2]: its weights are in TMEM
+    const uint32_t bar_pv = bar_p + 16;    // [2]: its PV product is complete
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(control + 8 * (2 * kUmmaStages + 7));
     volatile uint32_t* flags = tmem_slot + 1;   // [0] unassigned page met, [1] abort
 
     if (threadIdx.x == 0) {
@@ -173,9 +175,11 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
             mbar_init(bar_empty + 8 * stage, 1);
         }
         mbar_init(bar_q, 1);
-        mbar_init(bar_s, 1);
-        mbar_init(bar_p, 4);
-        mbar_init(bar_pv, 1);
+        for (uint32_t buffer = 0; buffer < 2; ++buffer) {
+            mbar_init(bar_s + 8 * buffer, 1);
+            mbar_init(bar_p + 8 * buffer, 4);
+            mbar_init(bar_pv + 8 * buffer, 1);
+        }
         flags[0] = 0;
         flags[1] = 0;
         fence_barrier_init();
@@ -269,33 +273,47 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
                 record_wait_timeout(p.status, kTagHybridAttention, (blockIdx.x << 2) | 2);
             }
             const uint64_t q_desc = smem_descriptor(q_base);
-            for (uint32_t macro = 0; macro < macro_tiles && ok; ++macro) {
+            // S = Q K^T of one stage into S buffer (macro & 1); needs the stage's K rows
+            auto issue_scores = [&](uint32_t macro) -> bool {
                 const uint32_t stage = macro % kUmmaStages;
                 const uint32_t count = min(kPagesPerStage, total_tiles - macro * kPagesPerStage);
                 if (flags[1] || !mbar_wait_bounded(bar_full + 8 * stage, (macro / kUmmaStages) & 1)) {
-                    ok = false;
-                    break;
+                    return false;
                 }
                 tcgen05_fence_after();
-                const uint32_t k_address = ring + stage * kStageBytesUmma;
-                const uint64_t k_desc = smem_descriptor(k_address);
+                const uint64_t k_desc = smem_descriptor(ring + stage * kStageBytesUmma);
                 const uint32_t idesc_qk = idesc_common | (((count * kPageSize) >> 3) << 17);
+                const uint32_t target = tmem_base + kColumnS + (macro & 1) * 64;
 #pragma unroll
                 for (uint32_t ks = 0; ks < 4; ++ks) {   // 16 dims = 32 bytes inside the swizzle row per step
-                    umma_bf16_ss(tmem_base + kColumnS, q_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks);
+                    umma_bf16_ss(target, q_desc + ks * 2, k_desc + ks * 2, idesc_qk, ks);
                 }
-                umma_commit(bar_s);
-                if (flags[1] || !mbar_wait_bounded(bar_p, macro & 1)) {
+                umma_commit(bar_s + 8 * (macro & 1));
+                return true;
+            };
+            ok = ok && macro_tiles > 0 && issue_scores(0);
+            for (uint32_t macro = 0; macro < macro_tiles && ok; ++macro) {
+                const uint32_t stage = macro % kUmmaStages;
+                const uint32_t count = min(kPagesPerStage, total_tiles - macro * kPagesPerStage);
+                const uint32_t buffer = macro & 1;
+                // the next stage's scores first: the tensor core computes them while this stage's softmax runs.
+                // Their buffer is free: its previous weights were consumed by the PV product issued before, and MMAs
+                // execute in issue order.
+                if (macro + 1 < macro_tiles && !issue_scores(macro + 1)) {
+                    ok = false;
+                    break;
+                }
+                if (flags[1] || !mbar_wait_bounded(bar_p + 8 * buffer, (macro >> 1) & 1)) {
                     ok = false;
                     break;
                 }
                 tcgen05_fence_after();
-                const uint64_t v_desc = smem_descriptor(k_address + kHalfStageBytes);
+                const uint64_t v_desc = smem_descriptor(ring + stage * kStageBytesUmma + kHalfStageBytes);
                 for (uint32_t step = 0; step < count; ++step) {   // 16 keys per step: 8 packed columns of P, 2 KiB of V
-                    umma_bf16_ts(tmem_base + kColumnPV, tmem_base + kColumnP + step * 8, v_desc + step * (kPageBytes >> 4),
-                                 idesc_pv, step);
+                    umma_bf16_ts(tmem_base + kColumnPV + buffer * 64, tmem_base + kColumnS + buffer * 64 + step * 8,
+                                 v_desc + step * (kPageBytes >> 4), idesc_pv, step);
                 }
-                umma_commit(bar_pv);
+                umma_commit(bar_pv + 8 * buffer);
                 umma_commit(bar_empty + 8 * stage);
             }
             if (!ok && !flags[1]) {
@@ -326,61 +344,143 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
             out[dim] = 0.0f;
         }
         bool ok = true;
+        // O <- (O + PV of stage `macro`) * factor: the PV product is folded in one stage late
+        auto fold = [&](uint32_t macro, float factor) -> bool {
+            const bool ready = !flags[1] && mbar_wait_bounded(bar_pv + 8 * (macro & 1), (macro >> 1) & 1);
+            if (!__all_sync(0xffffffffu, ready)) {
+                return false;
+            }
+            tcgen05_fence_after();
+            const uint32_t source = lane_address + kColumnPV + (macro & 1) * 64;
+            const bool unchanged = __all_sync(0xffffffffu, factor == 1.0f);   // no row of this warp moved its maximum
+#pragma unroll
+            for (uint32_t half = 0; half < 2; ++half) {
+                uint32_t raw[2][16];
+                tmem_load16_nowait(source + half * 32, raw[0]);
+                tmem_load16_nowait(source + half * 32 + 16, raw[1]);
+                tmem_load_wait();
+                if (unchanged) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        out[half * 32 + j] += __uint_as_float(raw[j >> 4][j & 15]);
+                    }
+                } else {
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        out[half * 32 + j] = (out[half * 32 + j] + __uint_as_float(raw[j >> 4][j & 15])) * factor;
+                    }
+                }
+            }
+            return true;
+        };
         for (uint32_t macro = 0; macro < macro_tiles; ++macro) {
             const uint32_t stage = macro % kUmmaStages;
             const uint32_t first_tile = macro * kPagesPerStage;
             const uint32_t count = min(kPagesPerStage, total_tiles - first_tile);
-            ok = !flags[1] && mbar_wait_bounded(bar_s, macro & 1);
+            const uint32_t buffer = macro & 1;
+            ok = !flags[1] && mbar_wait_bounded(bar_s + 8 * buffer, (macro >> 1) & 1);
             if (!__all_sync(0xffffffffu, ok)) {
                 ok = false;
                 break;
             }
             tcgen05_fence_after();
-            // last key of each 16-key tile this row may see (below the tile's first key: nothing)
-            int64_t limit[kPagesPerStage];
-            int64_t first_key[kPagesPerStage];
+            const uint32_t scores = lane_address + kColumnS + buffer * 64;
+            // The common stage: four full tiles of consecutive keys, all of them visible to every row of this warp.
+            const int64_t stage_first = tile_first_key(first_tile);
+            const bool regular = count == kPagesPerStage &&
+                                 tile_first_key(first_tile + kPagesPerStage - 1) == stage_first + 3 * kPageSize &&
+                                 tile_last_key(first_tile) >= stage_first + kPageSize - 1 &&
+                                 tile_last_key(first_tile + kPagesPerStage - 1) >= stage_first + 4 * kPageSize - 1;
+            const bool fast = __all_sync(0xffffffffu, regular && row_position >= stage_first + 4 * kPageSize - 1);
             bool clear_values = false;
+            float rescale;
+            float new_max;
+            float stage_sum = 0.0f;
+            if (fast) {
+                float maximum = -INFINITY;
+#pragma unroll
+                for (uint32_t half = 0; half < 2; ++half) {
+                    uint32_t raw[2][16];
+                    tmem_load16_nowait(scores + half * 32, raw[0]);
+                    tmem_load16_nowait(scores + half * 32 + 16, raw[1]);
+                    tmem_load_wait();
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; ++j) {
+                        maximum = fmaxf(maximum, __uint_as_float(raw[j >> 4][j & 15]));
+                    }
+                }
+                new_max = fmaxf(running_max, maximum);
+                rescale = fast_exp2((running_max - new_max) * kScaleLog2);
+                const float offset = -new_max * kScaleLog2;
+#pragma unroll
+                for (uint32_t half = 0; half < 2; ++half) {
+                    uint32_t raw[2][16];
+                    tmem_load16_nowait(scores + half * 32, raw[0]);
+                    tmem_load16_nowait(scores + half * 32 + 16, raw[1]);
+                    tmem_load_wait();
+                    uint32_t packed[16];
+#pragma unroll
+                    for (uint32_t j = 0; j < 32; j += 2) {
+                        const float w0 = fast_exp2(fmaf(__uint_as_float(raw[j >> 4][j & 15]), kScaleLog2, offset));
+                        const float w1 = fast_exp2(fmaf(__uint_as_float(raw[j >> 4][(j & 15) + 1]), kScaleLog2, offset));
+                        packed[j / 2] = pack_bf16x2(w0, w1);
+                        stage_sum += w0 + w1;   // unrounded here: the rounding of 64 weights averages out
+                    }
+                    tmem_store16(scores + half * 16, packed);
+                }
+            } else {
+            // how many keys of each 16-key tile this row may see (its keys are consecutive from the tile's first)
+            int32_t visible[kPagesPerStage];
 #pragma unroll
             for (uint32_t sub = 0; sub < kPagesPerStage; ++sub) {
                 const uint32_t tile = first_tile + sub;
-                first_key[sub] = tile_first_key(tile);
-                const int64_t exists = sub < count ? tile_last_key(tile) : first_key[sub] - 1;
-                limit[sub] = row_position < exists ? row_position : exists;
-                clear_values = clear_values || (sub < count && exists < first_key[sub] + kPageSize - 1);
+                const int64_t first = tile_first_key(tile);
+                const int64_t exists = sub < count ? tile_last_key(tile) : first - 1;
+                const int64_t limit = row_position < exists ? row_position : exists;
+                const int64_t seen = limit - first + 1;
+                visible[sub] = seen < 0 ? 0 : (seen > static_cast<int64_t>(kPageSize) ? static_cast<int32_t>(kPageSize)
+                                                                                      : static_cast<int32_t>(seen));
+                clear_values = clear_values || (sub < count && exists < first + kPageSize - 1);
             }
             // pass 1: row maximum of the masked scores
             float maximum = -INFINITY;
 #pragma unroll
-            for (uint32_t sub = 0; sub < kPagesPerStage; ++sub) {
-                uint32_t raw[16];
-                tmem_load16(lane_address + kColumnS + sub * 16, raw);
+            for (uint32_t half = 0; half < 2; ++half) {
+                uint32_t raw[2][16];
+                tmem_load16_nowait(scores + half * 32, raw[0]);
+                tmem_load16_nowait(scores + half * 32 + 16, raw[1]);
+                tmem_load_wait();
 #pragma unroll
-                for (uint32_t j = 0; j < 16; ++j) {
-                    if (first_key[sub] + j <= limit[sub]) {
-                        maximum = fmaxf(maximum, __uint_as_float(raw[j]));
+                for (uint32_t part = 0; part < 2; ++part) {
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j) {
+                        if (static_cast<int32_t>(j) < visible[half * 2 + part]) {
+                            maximum = fmaxf(maximum, __uint_as_float(raw[part][j]));
+                        }
                     }
                 }
             }
-            const float new_max = fmaxf(running_max, maximum);
+            new_max = fmaxf(running_max, maximum);
             const float base = new_max == -INFINITY ? 0.0f : new_max;
-            const float rescale = fast_exp2((running_max - base) * kScaleLog2);
+            rescale = fast_exp2((running_max - base) * kScaleLog2);
             const float offset = -base * kScaleLog2;
-            // pass 2: weights, rounded to bf16 and stored as the A operand of the PV product
-            float stage_sum = 0.0f;
+            // pass 2: weights, rounded to bf16, written over the scores they came from as the A operand of P V
 #pragma unroll
             for (uint32_t half = 0; half < 2; ++half) {
+                uint32_t raw[2][16];
+                tmem_load16_nowait(scores + half * 32, raw[0]);
+                tmem_load16_nowait(scores + half * 32 + 16, raw[1]);
+                tmem_load_wait();
                 uint32_t packed[16];
 #pragma unroll
                 for (uint32_t part = 0; part < 2; ++part) {
-                    const uint32_t sub = half * 2 + part;
-                    uint32_t raw[16];
-                    tmem_load16(lane_address + kColumnS + sub * 16, raw);
+                    const int32_t seen = visible[half * 2 + part];
 #pragma unroll
                     for (uint32_t j = 0; j < 16; j += 2) {
-                        const float w0 = first_key[sub] + j <= limit[sub]
-                                             ? fast_exp2(fmaf(__uint_as_float(raw[j]), kScaleLog2, offset)) : 0.0f;
-                        const float w1 = first_key[sub] + j + 1 <= limit[sub]
-                                             ? fast_exp2(fmaf(__uint_as_float(raw[j + 1]), kScaleLog2, offset)) : 0.0f;
+                        const float w0 = static_cast<int32_t>(j) < seen
+                                             ? fast_exp2(fmaf(__uint_as_float(raw[part][j]), kScaleLog2, offset)) : 0.0f;
+                        const float w1 = static_cast<int32_t>(j + 1) < seen
+                                             ? fast_exp2(fmaf(__uint_as_float(raw[part][j + 1]), kScaleLog2, offset)) : 0.0f;
                         const uint32_t pair = pack_bf16x2(w0, w1);
                         packed[part * 8 + j / 2] = pair;
                         // the denominator sums the same bf16-rounded weights that multiply V
@@ -388,7 +488,8 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
                         stage_sum += rounded.x + rounded.y;
                     }
                 }
-                tmem_store16(lane_address + kColumnP + half * 16, packed);
+                tmem_store16(scores + half * 16, packed);
+            }
             }
             tmem_store_wait();
             if (clear_values) {
@@ -397,7 +498,7 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
 #pragma unroll
                 for (uint32_t sub = 0; sub < kPagesPerStage; ++sub) {
                     const int64_t exists = tile_last_key(first_tile + sub);
-                    const int64_t key = first_key[sub] + (softmax_thread >> 3);
+                    const int64_t key = tile_first_key(first_tile + sub) + (softmax_thread >> 3);
                     if (sub < count && key > exists) {
                         asm volatile("st.shared.v4.u32 [%0], {%1, %1, %1, %1};" ::"r"(
                                          v_base + sub * kPageBytes + (softmax_thread >> 3) * 128 + (softmax_thread & 7) * 16),
@@ -410,25 +511,21 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(bar_p);
+                mbar_arrive(bar_p + 8 * buffer);
+            }
+            // fold in the previous stage's PV product (it was computed with the previous maximum): both it and
+            // the accumulator move to the new maximum together
+            if (macro > 0) {
+                if (!fold(macro - 1, rescale)) {
+                    ok = false;
+                    break;
+                }
             }
             running_sum = fmaf(running_sum, rescale, stage_sum);
             running_max = new_max;
-            ok = !flags[1] && mbar_wait_bounded(bar_pv, macro & 1);
-            if (!__all_sync(0xffffffffu, ok)) {
-                ok = false;
-                break;
-            }
-            tcgen05_fence_after();
-#pragma unroll
-            for (uint32_t chunk = 0; chunk < kHeadDim / 16; ++chunk) {
-                uint32_t raw[16];
-                tmem_load16(lane_address + kColumnPV + chunk * 16, raw);
-#pragma unroll
-                for (uint32_t j = 0; j < 16; ++j) {
-                    out[chunk * 16 + j] = fmaf(out[chunk * 16 + j], rescale, __uint_as_float(raw[j]));
-                }
-            }
+        }
+        if (ok && macro_tiles > 0) {
+            ok = fold(macro_tiles - 1, 1.0f);
         }
         if (!ok && lane == 0 && !flags[1]) {
             flags[1] = 1;
