@@ -754,8 +754,9 @@ def run_prefill_arm(arguments, rank, world):
     """One step = one mixed step of the executor holding eight 512-token prefill chunks (the chunk size the
     reference's planner prefers, src/scheduler/planner.rs:201) whose sequences already have 0..3584 tokens in the
     paged cache: 4096 tokens per step, BF16 at every site (the step is above the FP8 batch limit, as in the
-    reference).  `roofline` is the hybrid attention kernel: tensor-core flops 4 * 2048 * sum(position + 1) per launch
-    over its CUDA-event time in an instrumented pass, against the measured dense BF16 peak."""
+    reference).  `roofline` is the mixed-step attention kernel (tcgen05 / TMEM): tensor-core flops
+    4 * 2048 * sum(position + 1) per launch over its CUDA-event time in an instrumented pass, against the measured
+    dense BF16 peak."""
     import torch
     import torch.distributed as dist
 
@@ -871,7 +872,7 @@ def run_prefill_arm(arguments, rank, world):
             "regions_eager_ms_per_step": {name: ms / profile_steps for name, (ms, _) in regions.items()},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
                          "frac": achieved / tensor_peak, "traffic": None, "peak_source": peak_source,
-                         "kernel": "hybrid_ragged_attention_kernel (one attention layer, mma.sync path)",
+                         "kernel": "hybrid_attention_umma_kernel (one attention layer; tcgen05 / TMEM)",
                          "algorithmic_flops_per_launch": attention_flops},
             "cpu_baseline": cpu,
             "e2e": {"value": batch.num_tokens * e2e_steps * world / (e2e_ms * 1e-3), "unit": "tok/s",

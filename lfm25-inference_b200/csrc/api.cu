@@ -552,12 +552,14 @@ int32_t lfm25_hybrid_ragged_attention_lfm2_bf16(void* stream, const lfm25_hybrid
     args.query_token_stride = query_stride;
     args.kv_token_stride = kv_stride;
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
-    // LFM25_HYBRID_ATTENTION = umma | mma selects the tcgen05 kernel (32 tokens per CTA) or the mma.sync kernel
-    // (16 tokens per CTA)
+    // Two kernels: tcgen05 / TMEM with 32 tokens x 4 heads per CTA (191 us per layer on eight 512-token chunks) and
+    // mma.sync with 16 tokens per CTA (326 us there, but less padding on short segments).  The tcgen05 kernel takes
+    // the step when its segments average at least 16 tokens; LFM25_HYBRID_ATTENTION = umma | mma forces one.
     const char* choice = getenv("LFM25_HYBRID_ATTENTION");
     const bool umma_possible = (reinterpret_cast<uintptr_t>(l.query.ptr) & 15) == 0 && query_stride % 8 == 0;
-    bool use_umma = false;
+    bool use_umma = l.num_tokens >= 16 * l.num_segments;
     if (choice != nullptr && strcmp(choice, "umma") == 0) use_umma = true;
+    if (choice != nullptr && strcmp(choice, "mma") == 0) use_umma = false;
     if (use_umma && umma_possible) {
         return cuda_result(lfm25::launch_hybrid_attention_umma(static_cast<cudaStream_t>(stream), args),
                            "hybrid ragged attention launch failed");

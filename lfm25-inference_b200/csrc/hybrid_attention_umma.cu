@@ -397,7 +397,9 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
             float new_max;
             float stage_sum = 0.0f;
             if (fast) {
-                float maximum = -INFINITY;
+                // four independent chains for the maximum and for the sum: the 64 values of a row would otherwise
+                // form one dependent chain per pass
+                float lane_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                 for (uint32_t half = 0; half < 2; ++half) {
                     uint32_t raw[2][16];
@@ -406,12 +408,14 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
                     tmem_load_wait();
 #pragma unroll
                     for (uint32_t j = 0; j < 32; ++j) {
-                        maximum = fmaxf(maximum, __uint_as_float(raw[j >> 4][j & 15]));
+                        lane_max[j & 3] = fmaxf(lane_max[j & 3], __uint_as_float(raw[j >> 4][j & 15]));
                     }
                 }
+                const float maximum = fmaxf(fmaxf(lane_max[0], lane_max[1]), fmaxf(lane_max[2], lane_max[3]));
                 new_max = fmaxf(running_max, maximum);
                 rescale = fast_exp2((running_max - new_max) * kScaleLog2);
                 const float offset = -new_max * kScaleLog2;
+                float lane_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (uint32_t half = 0; half < 2; ++half) {
                     uint32_t raw[2][16];
@@ -424,10 +428,11 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
                         const float w0 = fast_exp2(fmaf(__uint_as_float(raw[j >> 4][j & 15]), kScaleLog2, offset));
                         const float w1 = fast_exp2(fmaf(__uint_as_float(raw[j >> 4][(j & 15) + 1]), kScaleLog2, offset));
                         packed[j / 2] = pack_bf16x2(w0, w1);
-                        stage_sum += w0 + w1;   // unrounded here: the rounding of 64 weights averages out
+                        lane_sum[(j >> 1) & 3] += w0 + w1;   // unrounded here: the rounding of 64 weights averages out
                     }
                     tmem_store16(scores + half * 16, packed);
                 }
+                stage_sum = (lane_sum[0] + lane_sum[1]) + (lane_sum[2] + lane_sum[3]);
             } else {
             // how many keys of each 16-key tile this row may see (its keys are consecutive from the tile's first)
             int32_t visible[kPagesPerStage];
