@@ -684,6 +684,14 @@ def run_step_arm(arguments, rank, world):
         if ops.device_status()[0] != 0:
             raise RuntimeError("a bounded wait ran out inside the benchmark")
 
+        # ---- the whole step assembled from the reference's kernels and cuBLASLt, replayed from a CUDA graph ----
+        if rank == 0 and reference_kernels is not None and "error" not in reference_kernels:
+            try:
+                reference_kernels.update(reference_kernel_step(model, device_batch, stream, use_fp8))
+                reference_kernels["ours_step_ms"] = float(np.median(step_ms))
+            except Exception as error:
+                reference_kernels["step_error"] = str(error)[:160]
+
     total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
 
     if rank == 0:
@@ -735,6 +743,38 @@ def run_step_arm(arguments, rank, world):
     blaslt.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def reference_kernel_step(model, device_batch, stream, use_fp8, repeats=16):
+    """Times the decode step as the reference runs it -- its own kernels (oracle/_ref, compiled for sm_100a from
+    the reference's sources) with cuBLASLt GEMMs between them, in the order of src/model/decode_executor.rs:183-443
+    -- on this benchmark's weights, caches and metadata.  The sequence is replayed from a CUDA graph, so the
+    figure has no launch or host overhead in it (the reference launches eagerly and synchronises every step): it is
+    the floor of the reference's step time on this GPU.  Runs last: it overwrites the caches' newest rows."""
+    import torch
+    from oracle import refstep
+
+    step = refstep.ReferenceKernelStep(model, device_batch.num_tokens, use_fp8=use_fp8)
+    arguments_ = (device_batch.token_ids, device_batch.positions, device_batch.request_slots,
+                  device_batch.physical_slots, device_batch.block_tables)
+    step.forward(*arguments_)                      # eager once: creates the scale tensors, warms cuBLASLt up
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        step.forward(*arguments_)
+    for _ in range(3):
+        graph.replay()
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(repeats + 1)]
+    stream.synchronize()
+    marks[0].record()
+    for index in range(repeats):
+        graph.replay()
+        marks[index + 1].record()
+    stream.synchronize()
+    times = [marks[i].elapsed_time(marks[i + 1]) for i in range(repeats)]
+    return {"step_ms_graph_replay": float(np.median(times)), "step_launches": step.launches,
+            "step_note": "reference kernels + cuBLASLt (torch.matmul / torch._scaled_mm) in the reference's op order, "
+                         "CUDA graph replay: no launch or host overhead, which the reference's own loop has"}
 
 
 def _inv_freq():

@@ -63,6 +63,7 @@ struct AttentionParams {
     __nv_bfloat16* key_cache;
     __nv_bfloat16* value_cache;
     float eps;
+    uint32_t kv_evict_first;  // nonzero: the K/V page loads carry the L2 evict-first hint
 };
 
 // FUSED == false: the query is already normalised and rotated and the newest K/V row is already in the cache.
@@ -154,6 +155,9 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     auto table_entry = [&](uint32_t iteration) -> uint32_t {
         return __ldg(table + first_page + warp + iteration * kWarps);
     };
+    // every page is read by exactly one warp of one CTA in a step: mark the stream as the first to leave L2, so
+    // that it does not displace the weights that the step's GEMMs have had fetched ahead
+    const uint64_t stream_policy = l2_evict_first_policy();
     auto issue = [&](uint32_t stage, uint32_t entry) {
         if (entry >= p.num_pages) {
             // An unassigned or out-of-range page: keep the pipeline uniform by reading page 0,
@@ -165,8 +169,13 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         const uint32_t bar = bars + stage * 8;
         const uint32_t dst = ring + stage * kStageBytes;
         mbar_arrive_expect_tx(bar, kStageBytes);
-        tma_load_2d(dst, &key_map, bar, 0, row);
-        tma_load_2d(dst + kPageTileBytes, &value_map, bar, 0, row);
+        if (p.kv_evict_first != 0) {
+            tma_load_2d_hint(dst, &key_map, bar, 0, row, stream_policy);
+            tma_load_2d_hint(dst + kPageTileBytes, &value_map, bar, 0, row, stream_policy);
+        } else {
+            tma_load_2d(dst, &key_map, bar, 0, row);
+            tma_load_2d(dst + kPageTileBytes, &value_map, bar, 0, row);
+        }
     };
     if (lane == 0) {
         const uint32_t prologue = my_pages < kStages ? my_pages : kStages;
@@ -558,6 +567,11 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.key_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(launch.key_cache));
     params.value_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(launch.value_cache));
     params.eps = launch.eps;
+    static const bool evict_first = [] {
+        const char* value = getenv("LFM25_KV_EVICT_FIRST");      // on unless set to 0
+        return value == nullptr || strcmp(value, "0") != 0;
+    }();
+    params.kv_evict_first = evict_first ? 1 : 0;
     const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
     cudaError_t status = launch_kernel(kernel, static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream, 1,
                                        key_map, value_map, params);

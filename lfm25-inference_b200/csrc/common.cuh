@@ -131,6 +131,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map
         : "memory");
 }
 
+// The same load with an L2 eviction-priority hint: a policy from l2_evict_first_policy() marks the lines as the
+// first to be replaced, for data that is read once (a KV stream), so that it does not push reusable lines out.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tensor_map, uint32_t bar, int32_t x,
+                                                 int32_t y, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
+
 // ------------------------------------------------------------------ tensor-core helpers
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t address, uint32_t& r0, uint32_t& r1, uint32_t& r2,

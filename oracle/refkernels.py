@@ -155,3 +155,31 @@ def short_conv_segmented(projected, weight, states, segment_offsets, segment_slo
     _launch("short_conv", "short_conv_segmented_lfm2_bf16", blocks,
             [projected, weight, states, segment_offsets, segment_slots, output, _sz(segments), _sz(hidden),
              _sz(states.shape[0])])
+
+
+def embedding(token_ids, weight, output) -> None:
+    """kernels/embedding.cu `embedding_bf16`, one block per token (src/cuda/kernels/embedding.rs:39-62)."""
+    tokens = token_ids.numel()
+    _launch("embedding", "embedding_bf16", tokens,
+            [token_ids, weight, output, _sz(tokens), _sz(weight.shape[0]), _sz(weight.shape[1])])
+
+
+def rms_norm(values, weight, output, eps: float) -> None:
+    """kernels/rms_norm.cu `rms_norm_bf16`, one block per row (src/cuda/kernels/rms_norm.rs:65-92)."""
+    rows, width = values.shape
+    _launch("rms_norm", "rms_norm_bf16", rows, [values, weight, output, _sz(rows), _sz(width), ctypes.c_float(eps)])
+
+
+def residual_rms_norm(residual, update, weight, residual_output, normalized_output, eps: float) -> None:
+    """kernels/rms_norm.cu `residual_rms_norm_bf16` (src/cuda/kernels/rms_norm.rs:94-128)."""
+    rows, width = residual.shape
+    _launch("rms_norm", "residual_rms_norm_bf16", rows,
+            [residual, update, weight, residual_output, normalized_output, _sz(rows), _sz(width),
+             ctypes.c_float(eps)])
+
+
+def argmax_rows(values, output) -> None:
+    """kernels/sampling.cu `argmax_rows_bf16`, one block per row: the path the reference's dispatch takes for
+    more than 16 rows (src/ops/sampling_dispatch.rs:17-60, src/cuda/kernels/sampling.rs:50-71)."""
+    rows, columns = values.shape
+    _launch("sampling", "argmax_rows_bf16", rows, [values, output, _sz(rows), _sz(columns)])

@@ -111,3 +111,54 @@ def test_graph_replay_matches_eager_steps(device):
         assert np.array_equal(a, b)
     # each step feeds the previous step's sampled ids: the histories must not be constant by construction
     assert ops.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("use_fp8", [False, True])
+def test_one_step_against_the_reference_kernels(device, use_fp8):
+    """The same step assembled from the reference's own kernels (compiled for this GPU) and cuBLASLt, on a second
+    model with the same seed: logits within the end-to-end bound used against the CPU restatement, the appended
+    K rows within the reference's own tolerance for its fast path."""
+    from oracle import refkernels, refstep
+    if not refkernels.available():
+        pytest.skip("oracle/_ref holds no compiled reference kernels")
+    tokens, pages = 16, 128                                # cuBLASLt's FP8 GEMM wants the batch in multiples of 16
+    batch = workloads.ragged_decode_batch(11, tokens, 5, 90, pages, 3)
+    token_ids = np.random.default_rng(11).integers(0, lfm_model.VOCAB, size=tokens).astype(np.uint32)
+    ours, theirs = (lfm_model.RandomModel(7, device, pages, tokens) for _ in range(2))
+    ours.fill_caches(8)
+    theirs.fill_caches(8)
+    blaslt = ops.BlasLt()
+    executor = lfm_model.DecodeExecutor(blaslt, tokens)
+    device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0), token_ids,
+                                         int(batch.contexts.max()) + 4)
+    executor.forward(ours, device_batch, use_fp8=use_fp8, advance=False)
+    got = oracle.bf16_to_f32(executor.logits(tokens)).astype(np.float64)
+    got_sampled = executor.sampled(tokens)
+
+    reference = refstep.ReferenceKernelStep(theirs, tokens, use_fp8=use_fp8)
+    slots = torch.from_numpy(batch.physical_slots(0).astype(np.int64)).to(device)
+    reference.forward(device_batch.token_ids, device_batch.positions, device_batch.request_slots, slots,
+                      device_batch.block_tables)
+    torch.cuda.synchronize()
+    want = oracle.bf16_to_f32(bits_of(reference.logits)).astype(np.float64)
+    want_sampled = reference.sampled.cpu().numpy().view(np.uint32)
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= (0.15 if use_fp8 else 0.05) * scale
+    cosine = (got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want))
+    assert cosine >= (0.99 if use_fp8 else 0.999)
+    # greedy ids agree wherever the reference's top two logits are further apart than the bound
+    ordered = np.sort(want, axis=1)
+    decided = ordered[:, -1] - ordered[:, -2] > 2 * np.abs(got - want).max(axis=1)
+    assert np.array_equal(got_sampled[decided], want_sampled[decided])
+    for mine, other in zip(ours.layers, theirs.layers):
+        if mine.is_attention:
+            a = oracle.bf16_to_f32(bits_of(mine.tensors["key_cache"])).astype(np.float64)
+            b = oracle.bf16_to_f32(bits_of(other.tensors["key_cache"])).astype(np.float64)
+            assert np.abs(a - b).max() <= (0.15 if use_fp8 else 0.05) * max(1.0, np.abs(b).max())
+        else:
+            a = oracle.bf16_to_f32(bits_of(mine.tensors["conv_state"])).astype(np.float64)
+            b = oracle.bf16_to_f32(bits_of(other.tensors["conv_state"])).astype(np.float64)
+            assert np.abs(a - b).max() <= (0.15 if use_fp8 else 0.05) * max(1.0, np.abs(b).max())
+    assert ops.device_status()[0] == 0
+    executor.close()
+    blaslt.close()
