@@ -44,7 +44,7 @@ constexpr uint32_t kBlockK = 128;   // bytes of K per stage = one swizzle row
 constexpr uint32_t kUmmaK = 32;     // K of one tcgen05.mma with 8-bit operands
 constexpr uint32_t kThreads = 192;
 constexpr uint32_t kMaxStages = 8;
-constexpr uint32_t kSmemBudget = 200 * 1024;   // one CTA per SM
+constexpr uint32_t kSmemBudget = 200 * 1024;   // upper bound of the ring of one CTA
 constexpr uint32_t kSmemBudgetShared = 98 * 1024;  // two CTAs per SM: one drains its tile while the other streams
 constexpr uint32_t kWeightTileBytes = kTileN * kBlockK;
 
@@ -61,7 +61,29 @@ struct UmmaParams {
     uint32_t splits;         // CTAs of a cluster that share one weight tile, each with its own K range
     uint32_t tmem_columns;   // power of two >= max(32, m_pad)
     float alpha;
+    uint32_t timeline_slot;  // only read by the instrumented build (LFM25_UMMA_TIMELINE)
 };
+
+// Instrumented build only: per CTA, the SM cycle counter at the points of the kernel's critical path (and the global
+// timer at entry and exit), for the two most recent launches.  Compiled out by default.
+#ifdef LFM25_UMMA_TIMELINE
+constexpr uint32_t kTimelineCtas = 512;
+constexpr uint32_t kTimelineMarks = 10;
+__device__ unsigned long long g_umma_timeline[2][kTimelineCtas][kTimelineMarks];
+__device__ __forceinline__ void timeline_mark(const UmmaParams& p, uint32_t mark) {
+    if (blockIdx.x < kTimelineCtas) {
+        g_umma_timeline[p.timeline_slot & 1][blockIdx.x][mark] = static_cast<unsigned long long>(clock64());
+    }
+}
+__device__ __forceinline__ void timeline_global(const UmmaParams& p, uint32_t mark) {
+    if (blockIdx.x < kTimelineCtas) {
+        g_umma_timeline[p.timeline_slot & 1][blockIdx.x][mark] = global_timer_ns();
+    }
+}
+#else
+__device__ __forceinline__ void timeline_mark(const UmmaParams&, uint32_t) {}
+__device__ __forceinline__ void timeline_global(const UmmaParams&, uint32_t) {}
+#endif
 
 template <bool BF16>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -116,7 +138,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(control + 16 * kMaxStages + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
 
+    if (threadIdx.x == 0) {
+        timeline_mark(p, 0);
+        timeline_global(p, 8);
+    }
     pdl_launch_dependents();
+    // K range of this split: the first (k_blocks % splits) splits take one block more
+    const uint32_t k_share = p.k_blocks / p.splits;
+    const uint32_t k_extra = p.k_blocks % p.splits;
+    const uint32_t k_count = k_share + (split < k_extra ? 1u : 0u);
+    const uint32_t k_block0 = split * k_share + (split < k_extra ? split : k_extra);
+    const uint32_t ahead = k_count < p.stages ? k_count : p.stages;
+    const int32_t tile_row = static_cast<int32_t>(tile * kTileN);
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&weight_map);
         tma_prefetch_descriptor(&x_map);
@@ -128,6 +161,16 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
         *abort_flag = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
+        // The weight tiles are constants: the first ring of them is requested right here -- before the TMEM
+        // allocation, the CTA-wide barrier and the dependency wait -- so the stream is flowing while the rest of
+        // the CTA sets up and the predecessor kernel drains.  The activation tiles, which the predecessor
+        // writes, follow after the wait and complete the same barriers.
+        for (uint32_t block = 0; block < ahead; ++block) {
+            const uint32_t bar = bar_full + 8 * block;
+            mbar_arrive_expect_tx(bar, stage_bytes);
+            tma_load_2d(smem_base + block * stage_bytes, &weight_map, bar,
+                        static_cast<int32_t>((k_block0 + block) * kBlockK), tile_row);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -140,27 +183,12 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-
-    // K range of this split: the first (k_blocks % splits) splits take one block more
-    const uint32_t k_share = p.k_blocks / p.splits;
-    const uint32_t k_extra = p.k_blocks % p.splits;
-    const uint32_t k_count = k_share + (split < k_extra ? 1u : 0u);
-    const uint32_t k_block0 = split * k_share + (split < k_extra ? split : k_extra);
+    if (threadIdx.x == 0) timeline_mark(p, 1);
 
     if (warp == 0) {
         if (lane == 0) {
-            // The weight tiles are constants: the first ring of them is requested before the dependency wait, so
-            // the stream is already flowing while the predecessor kernel drains.  The activation tiles, which the
-            // predecessor writes, follow after the wait and complete the same barriers.
-            const uint32_t ahead = k_count < p.stages ? k_count : p.stages;
-            const int32_t tile_row = static_cast<int32_t>(tile * kTileN);
-            for (uint32_t block = 0; block < ahead; ++block) {
-                const uint32_t bar = bar_full + 8 * block;
-                mbar_arrive_expect_tx(bar, stage_bytes);
-                tma_load_2d(smem_base + block * stage_bytes, &weight_map, bar,
-                            static_cast<int32_t>((k_block0 + block) * kBlockK), tile_row);
-            }
             pdl_wait();
+            timeline_mark(p, 2);
             for (uint32_t block = 0; block < ahead; ++block) {
                 tma_load_2d(smem_base + block * stage_bytes + kWeightTileBytes, &x_map, bar_full + 8 * block,
                             static_cast<int32_t>((k_block0 + block) * kBlockK), 0);
@@ -196,6 +224,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                     break;
                 }
                 tcgen05_fence_after();
+                if (block == 0) timeline_mark(p, 3);
                 const uint32_t a_address = smem_base + stage * stage_bytes;
                 const uint64_t a_desc = smem_descriptor(a_address);
                 const uint64_t b_desc = smem_descriptor(a_address + kWeightTileBytes);
@@ -209,6 +238,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             if (ok) {
                 umma_commit(bar_accumulator);
             }
+            timeline_mark(p, 4);
         }
     } else {
         // ---- epilogue: 4 warps, each owns the 32 TMEM lanes of its quadrant (warp id modulo 4) ----
@@ -220,6 +250,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 3);
         }
         tcgen05_fence_after();
+        if (warp == 2 && lane == 0) timeline_mark(p, 5);
         const uint32_t lane_address = tmem_base + ((quadrant * 32) << 16);
         if (p.splits == 1) {
             if (ready) {
@@ -266,6 +297,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             }
         }
     }
+    if (warp == 2 && lane == 0) timeline_mark(p, 6);
     if (p.splits > 1) {
         // Split K, step 2 of 2: after the cluster barrier (release / acquire at cluster scope, and the partners are
         // the only readers) CTA q of the cluster finishes batch columns [q, q+1) * ceil(m / splits): it adds the
@@ -310,6 +342,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
 
     tcgen05_fence_before();
     __syncthreads();
+    if (threadIdx.x == 0) {
+        timeline_mark(p, 7);
+        timeline_global(p, 9);
+    }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_columns)
                      : "memory");
@@ -394,8 +430,29 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
             }
         }
     }
+    if (const char* forced = getenv("LFM25_UMMA_SPLITS")) {      // tuning override: a split count to try as is
+        const uint32_t candidate = static_cast<uint32_t>(atoi(forced));
+        if (exchange != nullptr && candidate >= 1 && candidate <= 8 && k_blocks_total / candidate >= 2 &&
+            static_cast<size_t>(tiles) * candidate * m_pad * kTileN * 4 <= exchange_bytes &&
+            (can_share || tiles * candidate <= 148)) {
+            splits = candidate;
+        }
+    }
     const bool share_sm = can_share && (splits > 1 || tiles > 148);
-    uint32_t stages = (share_sm ? kSmemBudgetShared : kSmemBudget) / stage_bytes;
+    // Ring size.  Measured on the decode shapes, a deeper ring than about 98 KiB does not pay even with one CTA per
+    // SM (Gate/Up at 1..32 rows: 9.9 us with 11 stages, 9.1 with 8, 8.5 with 5): a CTA that leaves half of the
+    // shared memory free lets the CTA of the next kernel in the stream move in beside it and request its own first
+    // ring of weights before the dependency resolves, which is worth more than bytes in flight.  Four stages are the
+    // floor (128 rows: 4 x 32 KiB).
+    uint32_t budget = kSmemBudgetShared;
+    if (!share_sm && 4 * stage_bytes > budget) {
+        budget = 4 * stage_bytes < kSmemBudget ? 4 * stage_bytes : kSmemBudget;
+    }
+    if (const char* forced = getenv("LFM25_UMMA_SMEM_KB")) {      // tuning override: ring bytes per CTA
+        const uint32_t candidate = static_cast<uint32_t>(atoi(forced)) * 1024u;
+        if (candidate >= 2 * stage_bytes && candidate <= kSmemBudget) budget = candidate;
+    }
+    uint32_t stages = budget / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     const uint32_t k_blocks_least = k_blocks_total / splits;
     if (stages > k_blocks_least) stages = k_blocks_least;
@@ -417,6 +474,8 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
     params.tmem_columns = 32;
     while (params.tmem_columns < m_pad) params.tmem_columns *= 2;
     params.alpha = alpha;
+    static uint32_t launches = 0;
+    params.timeline_slot = launches++;
 
     const cudaError_t attribute_status = cudaFuncSetAttribute(
         gemm_umma_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
@@ -428,6 +487,13 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
 }
 
 }  // namespace
+
+#ifdef LFM25_UMMA_TIMELINE
+// Instrumented build only: copies the marks of the two most recent launches, [2][512][10] 64-bit words.
+extern "C" int lfm25_debug_umma_timeline(unsigned long long* host) {
+    return static_cast<int>(cudaMemcpyFromSymbol(host, g_umma_timeline, sizeof(g_umma_timeline)));
+}
+#endif
 
 cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
                                  size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,
