@@ -88,6 +88,60 @@ def sweep_bf16(arguments, ops, device, hbm_peak):
     blaslt.close()
 
 
+TIMELINE_MARKS = ["entry", "setup_done", "dependency_released", "first_stage_full", "last_mma_committed",
+                  "accumulator_ready", "epilogue_stored", "end"]
+
+
+def timeline(arguments, ops, abi, device):
+    """Per-launch breakdown of the tcgen05 GEMM from the instrumented build: a graph of 16 launches over the weight
+    ring; the marks of the last two launches (SM cycle counter per CTA, anchored by the global timer at CTA entry) are
+    printed as min / mean / max nanoseconds since the first CTA entry of the earlier launch."""
+    import ctypes
+
+    import numpy as np
+
+    generator = torch.Generator(device=device).manual_seed(2)
+    blaslt = ops.BlasLt()
+    for name, n, k in SHAPES:
+        if arguments.shapes and name not in arguments.shapes:
+            continue
+        copies = max(2, (RING_BYTES + n * k - 1) // (n * k))
+        codes = (torch.randn((n, k), generator=generator, device=device) * 8).clamp(-448, 448).to(
+            torch.float8_e4m3fn).view(torch.uint8)
+        ring = [codes.clone() for _ in range(copies)]
+        for m in arguments.ms:
+            x = (torch.randn((m, k), generator=generator, device=device) * 8).to(torch.float8_e4m3fn).view(torch.uint8)
+            out = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+
+            def ours(index, ring=ring, out=out, x=x):
+                blaslt.bind_current_stream()
+                blaslt.linear_fp8_scaled(x, ring[index % len(ring)], out, 1.0)
+
+            per_launch = time_launches(ours, 16, replays=1)
+            marks = np.zeros((2, 512, 10), dtype=np.uint64)
+            code = abi.library().lfm25_debug_umma_timeline(marks.ctypes.data_as(ctypes.POINTER(ctypes.c_ulonglong)))
+            if code != 0:
+                raise RuntimeError(f"timeline read failed with CUDA error {code}")
+            launches = []
+            for slot in range(2):
+                used = marks[slot][:, 0] != 0
+                if used.any():
+                    t = marks[slot][used].astype(np.int64)
+                    since_entry = (t[:, 0:8] - t[:, 0:1]) / arguments.sm_mhz * 1e3      # cycles -> ns
+                    launches.append((int(t[:, 8].min()), t[:, 8:9] + since_entry, t[:, 9]))
+            launches.sort(key=lambda item: item[0])
+            line = {"shape": name, "m": m, "us_per_launch": per_launch, "launches": []}
+            for first_entry, absolute, exits in launches:
+                origin = launches[0][0]
+                line["launches"].append({
+                    "ctas": int(absolute.shape[0]),
+                    **{mark: [float(absolute[:, index].min() - origin), float(absolute[:, index].mean() - origin),
+                              float(absolute[:, index].max() - origin)] for index, mark in enumerate(TIMELINE_MARKS)},
+                    "exit_global_timer": [int(exits.min() - origin), int(exits.max() - origin)]})
+            print(json.dumps(line), flush=True)
+        del ring
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--dtype", choices=["e4m3", "bf16"], default="e4m3")
@@ -98,13 +152,24 @@ def main():
                         help="kernel paths to time: auto, stream, umma (sets LFM25_FP8_GEMM_PATH)")
     parser.add_argument("--handle", action="store_true", help="call through a BlasLt handle (allows split-K)")
     parser.add_argument("--shapes", nargs="+", default=None, help="only these sites (gate_up, down, lm_head, ...)")
+    parser.add_argument("--timeline", action="store_true",
+                        help="per-launch breakdown from the instrumented build (python lfm25-inference_b200/build.py "
+                             "--timeline makes liblfm25_b200_timeline.so)")
+    parser.add_argument("--sm-mhz", type=float, default=1965.0, help="SM clock used to turn cycle marks into ns")
     arguments = parser.parse_args()
     entry.load_package()
+    if arguments.timeline:
+        from lfm25_inference_b200 import _abi
+        _abi.LIBRARY_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "liblfm25_b200_timeline.so")
     from lfm25_inference_b200 import ops
 
     device = torch.device("cuda:0")
     peak_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     hbm_peak = json.load(open(peak_path))["hbm_gbs"] if os.path.exists(peak_path) else 6650.0
+    if arguments.timeline:
+        from lfm25_inference_b200 import _abi
+        timeline(arguments, ops, _abi, device)
+        return
     if arguments.dtype == "bf16":
         sweep_bf16(arguments, ops, device, hbm_peak)
         return
