@@ -70,6 +70,9 @@ def parse_arguments():
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     parser.add_argument("--requests", type=int, default=192, help="serving workload: requests in the trace")
     parser.add_argument("--rate", type=float, default=32.0, help="serving workload: Poisson arrival rate, requests/s")
+    parser.add_argument("--admission-control", action="store_true",
+                        help="serving workload: reject requests whose predicted TTFT / TPOT break the SLOs (the "
+                             "reference's admission) instead of queueing them")
     arguments = parser.parse_args()
     if arguments.steps <= 0:
         arguments.steps = {"step": 256, "attention": 1024, "prefill": 16, "serving": 1}[arguments.workload]
@@ -997,7 +1000,8 @@ def run_serving_arm(arguments, rank, world):
         model = lfm_model.RandomModel(4 + rank, device, pages, slots)
         engine = serving.ServingEngine(model, device, max_slots=slots, max_sequence_tokens=max_sequence,
                                        max_prefill_tokens=512, radix_pages=4096, checkpoint_capacity=128,
-                                       use_fp8=not arguments.no_fp8)
+                                       use_fp8=not arguments.no_fp8,
+                                       admission_control=arguments.admission_control)
         engine.calibrate()
         for _ in range(max(arguments.warmup, 1)):                   # short warm-up traces (plans, attributes)
             serving.run_trace(engine, serving_trace(100 + rank, 8, 1000.0))
@@ -1009,7 +1013,11 @@ def run_serving_arm(arguments, rank, world):
         makespan_ms = result["makespan_us"] / 1e3
     (makespan_ms,) = max_over_ranks([makespan_ms], device, world)
     if rank == 0:
-        finished = result["requests"]
+        rejected = [entry_ for entry_ in result["requests"] if entry_["rejected"]]
+        finished = [entry_ for entry_ in result["requests"] if not entry_["rejected"]]
+        reasons = {}
+        for entry_ in rejected:
+            reasons[entry_["rejected"]] = reasons.get(entry_["rejected"], 0) + 1
         ttft = np.array([entry_["ttft_us"] for entry_ in finished]) / 1e3
         tpot = np.array([entry_["tpot_us"] for entry_ in finished if entry_["tpot_us"] > 0]) / 1e3
         generated = sum(entry_["generated"] for entry_ in finished)
@@ -1024,6 +1032,8 @@ def run_serving_arm(arguments, rank, world):
                        "request_slots": slots, "maximum_prefill_tokens": 512, "page_size": 16,
                        "prompt_sigma": 1.0, "replicas": world, "step": "native engine loop, eager launches, one host sync per step"},
             "requests_per_s": len(finished) * world / (makespan_ms * 1e-3),
+            "admission_control": bool(arguments.admission_control), "rejected_requests": len(rejected),
+            "rejected_by_reason": reasons,
             "prompt_tokens": prompt_tokens, "generated_tokens": generated,
             "ttft_p50_ms": float(np.percentile(ttft, 50)), "ttft_p95_ms": float(np.percentile(ttft, 95)),
             "tpot_p50_ms": float(np.percentile(tpot, 50)), "tpot_p95_ms": float(np.percentile(tpot, 95)),

@@ -712,13 +712,27 @@ typedef struct lfm25_engine_config {
     uint64_t ttft_slo_us;
     uint64_t tpot_slo_us;
     double step_budget_ms;
+    /* SLO admission (admit_request_radix, src/engine/serving/radix_owner.rs:549-708).  0: a request that does not
+     * fit yet waits in the queue, in order (back-pressure).  1: every queued request is decided at the next step,
+     * admitted or rejected with one of the LFM25_REJECT_* reasons, as the reference answers "overloaded". */
+    uint32_t admission_control;
+    size_t interactive_prompt_limit;   /* longest admitted prompt when admission_control is on; 0 = no limit */
 } lfm25_engine_config;
+/* Why a request was turned away (lfm25_engine_event.rejected), in the order the reference checks them. */
+#define LFM25_REJECT_NONE 0u
+#define LFM25_REJECT_SEQUENCE_CAPACITY 1u /* prompt + new tokens exceed max_sequence_tokens */
+#define LFM25_REJECT_PROMPT_LIMIT 2u      /* prompt longer than interactive_prompt_limit */
+#define LFM25_REJECT_DECODE_BUDGET 3u     /* predicted decode step with one more sequence >= step budget or TPOT SLO */
+#define LFM25_REJECT_TTFT 4u              /* time already waited + predicted prefill queue >= TTFT SLO */
+#define LFM25_REJECT_SLOTS 5u             /* no free request slot */
+#define LFM25_REJECT_KV_PAGES 6u          /* the page reservation for the whole sequence failed */
 typedef struct lfm25_engine_event {
     uint64_t request_id;
     uint64_t time_us;             /* now_us of the step + its GPU time */
     uint32_t token;
     uint32_t finished;            /* the request produced its last token and left its slot */
     uint32_t reused_tokens;       /* prompt tokens this request took from the prefix index */
+    uint32_t rejected;            /* LFM25_REJECT_*: nonzero = the request was not admitted (token 0, finished 1) */
 } lfm25_engine_event;
 typedef struct lfm25_engine_stats {
     uint64_t steps;
@@ -728,6 +742,7 @@ typedef struct lfm25_engine_stats {
     uint64_t prefill_tokens;
     uint64_t reused_prompt_tokens;
     double gpu_ms;
+    uint64_t rejected_requests;
 } lfm25_engine_stats;
 int32_t lfm25_engine_create(lfm25_blaslt* blaslt, const lfm25_model* model, const lfm25_engine_config* config,
                             lfm25_engine** out);

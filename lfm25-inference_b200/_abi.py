@@ -126,18 +126,20 @@ class EngineConfig(ctypes.Structure):
                 ("max_prefill_tokens", ctypes.c_size_t), ("radix_pages", ctypes.c_size_t),
                 ("checkpoint_capacity", ctypes.c_size_t), ("use_fp8", ctypes.c_uint32),
                 ("ttft_slo_us", ctypes.c_uint64), ("tpot_slo_us", ctypes.c_uint64),
-                ("step_budget_ms", ctypes.c_double)]
+                ("step_budget_ms", ctypes.c_double), ("admission_control", ctypes.c_uint32),
+                ("interactive_prompt_limit", ctypes.c_size_t)]
 
 
 class EngineEvent(ctypes.Structure):
     _fields_ = [("request_id", ctypes.c_uint64), ("time_us", ctypes.c_uint64), ("token", ctypes.c_uint32),
-                ("finished", ctypes.c_uint32), ("reused_tokens", ctypes.c_uint32)]
+                ("finished", ctypes.c_uint32), ("reused_tokens", ctypes.c_uint32), ("rejected", ctypes.c_uint32)]
 
 
 class EngineStats(ctypes.Structure):
     _fields_ = [("steps", ctypes.c_uint64), ("decode_steps", ctypes.c_uint64), ("mixed_steps", ctypes.c_uint64),
                 ("generated_tokens", ctypes.c_uint64), ("prefill_tokens", ctypes.c_uint64),
-                ("reused_prompt_tokens", ctypes.c_uint64), ("gpu_ms", ctypes.c_double)]
+                ("reused_prompt_tokens", ctypes.c_uint64), ("gpu_ms", ctypes.c_double),
+                ("rejected_requests", ctypes.c_uint64)]
 
 
 class Fp8Site(ctypes.Structure):

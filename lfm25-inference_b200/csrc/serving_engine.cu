@@ -201,10 +201,38 @@ int32_t clear_conv_state(lfm25_engine* self, size_t slot) {
 // admit_request_radix (src/engine/serving/radix_owner.rs:549-708): a free slot, the longest reusable checkpointed
 // prefix (at most the last full page before the final prompt token, so that the forward pass still yields logits),
 // a page reservation for the rest of the sequence, convolution states restored from the checkpoint or cleared.
-int32_t admit(lfm25_engine* self) {
-    while (!self->queue.empty() && !self->free_slots.empty()) {
+// With admission control (the reference's behaviour) every queued request is decided now: the checks run in the
+// reference's order and a request that fails one leaves the queue with a rejection event; `rejections` holds at
+// most `rejection_capacity` of them per call, the rest of the queue waits for the next step.  Without admission
+// control a request that does not fit yet stays at the head of the queue.
+int32_t admit(lfm25_engine* self, uint64_t now_us, lfm25_engine_event* rejections, size_t rejection_capacity,
+              size_t* rejected) {
+    const bool control = self->config.admission_control != 0;
+    auto reject = [&](const Pending& request, uint32_t reason) {
+        lfm25_engine_event& event = rejections[(*rejected)++];
+        event.request_id = request.request_id;
+        event.time_us = now_us;
+        event.token = 0;
+        event.finished = 1;
+        event.reused_tokens = 0;
+        event.rejected = reason;
+        self->stats.rejected_requests += 1;
+        self->queue.pop_front();
+    };
+    while (!self->queue.empty() && (control ? *rejected < rejection_capacity : !self->free_slots.empty())) {
         Pending& request = self->queue.front();
         const size_t limit = reusable_limit(request.prompt.size());
+        if (control) {
+            if (request.prompt.size() + request.max_new_tokens > self->config.max_sequence_tokens) {
+                reject(request, LFM25_REJECT_SEQUENCE_CAPACITY);
+                continue;
+            }
+            if (self->config.interactive_prompt_limit != 0 &&
+                request.prompt.size() > self->config.interactive_prompt_limit) {
+                reject(request, LFM25_REJECT_PROMPT_LIMIT);
+                continue;
+            }
+        }
         size_t pages_found = 0;
         uint32_t checkpoint = 0;
         int64_t matched = 0;
@@ -215,8 +243,45 @@ int32_t admit(lfm25_engine* self) {
             if (matched < 0) return static_cast<int32_t>(matched);
         }
         const size_t total_tokens = request.prompt.size() + request.max_new_tokens;
+        if (control) {
+            // one more decoding sequence must keep the predicted decode step inside the step budget and the TPOT
+            // SLO, and the prefill work queued in front of this prompt must leave its first token inside the TTFT SLO
+            size_t decode_count = 1;
+            size_t maximum_context = total_tokens;
+            double prefill_queue_ms =
+                lfm25_cost_model_predict_prefill_ms(self->cost, request.prompt.size() - static_cast<size_t>(matched));
+            for (const Slot& other : self->slots) {
+                if (other.phase == LFM25_PHASE_DECODING) {
+                    decode_count += 1;
+                    maximum_context = std::max(maximum_context, other.tokens.size());
+                } else if (other.phase == LFM25_PHASE_QUEUED_PREFILL) {
+                    prefill_queue_ms += lfm25_cost_model_predict_prefill_ms(self->cost, other.prompt_len - other.prefilled);
+                }
+            }
+            const double decode_ms =
+                lfm25_cost_model_predict_decode_ms(self->cost, decode_count, maximum_context, self->config.use_fp8);
+            if (decode_ms >= self->config.step_budget_ms ||
+                decode_ms * 1000.0 >= static_cast<double>(self->config.tpot_slo_us)) {
+                reject(request, LFM25_REJECT_DECODE_BUDGET);
+                continue;
+            }
+            const double waited_ms =
+                now_us > request.arrival_us ? static_cast<double>(now_us - request.arrival_us) / 1000.0 : 0.0;
+            if (waited_ms + prefill_queue_ms >= static_cast<double>(self->config.ttft_slo_us) / 1000.0) {
+                reject(request, LFM25_REJECT_TTFT);
+                continue;
+            }
+            if (self->free_slots.empty()) {
+                reject(request, LFM25_REJECT_SLOTS);
+                continue;
+            }
+        }
         const size_t needed_pages = (total_tokens + kPage - 1) / kPage - static_cast<size_t>(matched) / kPage;
         if (lfm25_kv_allocator_try_reserve_pages(self->allocator, needed_pages) < 0) {
+            if (control) {
+                reject(request, LFM25_REJECT_KV_PAGES);
+                continue;
+            }
             return LFM25_OK;   // back-pressure: the queue keeps its order
         }
         if (limit > 0) {       // the admission lookup proper: counts the hit or the miss
@@ -476,7 +541,9 @@ int32_t lfm25_engine_submit(lfm25_engine* self, uint64_t request_id, const uint3
         return lfm25::report_error(LFM25_ERR_NULL_POINTER, "engine submit received a null argument");
     }
     if (prompt_len == 0) return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "request prompt is empty");
-    if (max_new_tokens == 0 || prompt_len + max_new_tokens > self->pages_per_slot * kPage) {
+    if (max_new_tokens == 0) return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "request asks for no tokens");
+    // with admission control an oversized request is answered by a rejection event at the next step
+    if (self->config.admission_control == 0 && prompt_len + max_new_tokens > self->pages_per_slot * kPage) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "request exceeds fixed token capacity");
     }
     self->queue.push_back({request_id, std::vector<uint32_t>(prompt, prompt + prompt_len), max_new_tokens, arrival_us});
@@ -488,15 +555,19 @@ int32_t lfm25_engine_step(lfm25_engine* self, uint64_t now_us, lfm25_engine_even
     if (self == nullptr || num_events == nullptr || (events == nullptr && events_capacity > 0)) {
         return lfm25::report_error(LFM25_ERR_NULL_POINTER, "engine step received a null argument");
     }
-    if (events_capacity < self->config.max_slots) {
-        return lfm25::report_error(LFM25_ERR_BUFFER_TOO_SMALL, "event buffer smaller than the request slots");
+    if (events_capacity < self->config.max_slots * (self->config.admission_control != 0 ? 2 : 1)) {
+        return lfm25::report_error(LFM25_ERR_BUFFER_TOO_SMALL,
+                                   "event buffer smaller than the request slots (twice that with admission control)");
     }
     if (self->cost == nullptr) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "calibrate the engine before its first step");
     }
     *num_events = 0;
     if (gpu_ms != nullptr) *gpu_ms = 0.0f;
-    ENGINE_TRY(admit(self));
+    // rejections go first into the event buffer; the step's token events (at most one per slot) follow them
+    size_t rejected = 0;
+    ENGINE_TRY(admit(self, now_us, events, events_capacity - self->config.max_slots, &rejected));
+    *num_events = rejected;
 
     for (size_t index = 0; index < self->slots.size(); ++index) {
         const Slot& slot = self->slots[index];
@@ -574,7 +645,7 @@ int32_t lfm25_engine_step(lfm25_engine* self, uint64_t now_us, lfm25_engine_even
         self->stats.mixed_steps += 1;
     }
     self->stats.gpu_ms += elapsed;
-    size_t produced = 0;
+    size_t produced = rejected;
     for (size_t index = 0; index < plan.work_count; ++index) {
         const lfm25_scheduled_work& item = self->work[index];
         Slot& slot = self->slots[item.slot];
@@ -600,6 +671,7 @@ int32_t lfm25_engine_step(lfm25_engine* self, uint64_t now_us, lfm25_engine_even
         event.token = token;
         event.finished = finished ? 1u : 0u;
         event.reused_tokens = static_cast<uint32_t>(slot.reused_tokens);
+        event.rejected = LFM25_REJECT_NONE;
         event.time_us = done_us;
         if (finished) {
             release(self, item.slot);

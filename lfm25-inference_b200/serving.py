@@ -20,6 +20,10 @@ from . import model as lfm_model
 from ._abi import check, library
 
 
+# lfm25_engine_event.rejected (include/lfm25_b200.h, LFM25_REJECT_*)
+REJECT_REASONS = {1: "sequence_capacity", 2: "prompt_limit", 3: "decode_budget", 4: "ttft", 5: "slots", 6: "kv_pages"}
+
+
 @dataclass
 class Request:
     request_id: int
@@ -34,16 +38,21 @@ class ServingEngine:
     def __init__(self, model: lfm_model.RandomModel, device, max_slots: int = 64, max_sequence_tokens: int = 8704,
                  max_prefill_tokens: int = 512, radix_pages: int = 4096, checkpoint_capacity: int = 64,
                  use_fp8: bool = True, ttft_slo_us: int = 400_000, tpot_slo_us: int = 50_000,
-                 step_budget_ms: float = 40.0):
+                 step_budget_ms: float = 40.0, admission_control: bool = False, interactive_prompt_limit: int = 0):
+        """`admission_control`: decide every queued request at the next step, admitting it or rejecting it with a
+        reason (the reference's admit_request_radix, src/engine/serving/radix_owner.rs:549-708); off, a request that
+        does not fit yet waits in the queue."""
         self.model, self.device, self.max_slots = model, device, max_slots
         self.blaslt = ops.BlasLt()
         self.blaslt.bind_current_stream()
         config = _abi.EngineConfig(max_slots, max_sequence_tokens, max_prefill_tokens, radix_pages,
-                                   checkpoint_capacity, int(use_fp8), ttft_slo_us, tpot_slo_us, step_budget_ms)
+                                   checkpoint_capacity, int(use_fp8), ttft_slo_us, tpot_slo_us, step_budget_ms,
+                                   int(admission_control), interactive_prompt_limit)
         self._handle = ctypes.c_void_p()
         check(library().lfm25_engine_create(self.blaslt._handle, model.struct, ctypes.byref(config),
                                             ctypes.byref(self._handle)))
-        self._events = (_abi.EngineEvent * max_slots)()
+        self._capacity = 2 * max_slots
+        self._events = (_abi.EngineEvent * self._capacity)()
         self._count = ctypes.c_size_t(0)
         self._gpu_ms = ctypes.c_float(0.0)
 
@@ -68,11 +77,12 @@ class ServingEngine:
 
     def step(self, now_us: int):
         """Admits, plans and runs one step.  Returns (events, gpu_ms); an event is
-        (request_id, token, finished, time_us, reused_tokens)."""
-        check(library().lfm25_engine_step(self._handle, now_us, self._events, self.max_slots,
+        (request_id, token, finished, time_us, reused_tokens, rejected): `rejected` is 0 for a token and one of the
+        REJECT_* reasons for a request that admission control turned away."""
+        check(library().lfm25_engine_step(self._handle, now_us, self._events, self._capacity,
                                           ctypes.byref(self._count), ctypes.byref(self._gpu_ms)))
-        events = [(int(e.request_id), int(e.token), bool(e.finished), int(e.time_us), int(e.reused_tokens))
-                  for e in self._events[:self._count.value]]
+        events = [(int(e.request_id), int(e.token), bool(e.finished), int(e.time_us), int(e.reused_tokens),
+                   int(e.rejected)) for e in self._events[:self._count.value]]
         return events, float(self._gpu_ms.value)
 
     def active(self) -> int:
@@ -105,7 +115,7 @@ def run_trace(engine: ServingEngine, requests: list[Request]) -> dict:
     pending = sorted(requests, key=lambda request: request.arrival_us)
     records = {request.request_id: {"request_id": request.request_id, "prompt_len": len(request.prompt),
                                     "arrival_us": request.arrival_us, "times_us": [], "tokens": [],
-                                    "reused_tokens": 0} for request in pending}
+                                    "reused_tokens": 0, "rejected": None} for request in pending}
     origin = time.perf_counter()
     skipped_us = 0
     cursor = 0
@@ -120,8 +130,11 @@ def run_trace(engine: ServingEngine, requests: list[Request]) -> dict:
             engine.submit(pending[cursor])
             cursor += 1
         events, _ = engine.step(now_us)
-        for request_id, token, _, time_us, reused in events:
+        for request_id, token, _, time_us, reused, rejected in events:
             record = records[request_id]
+            if rejected:
+                record["rejected"] = REJECT_REASONS.get(rejected, str(rejected))
+                continue
             record["times_us"].append(time_us)
             record["tokens"].append(token)
             record["reused_tokens"] = reused

@@ -11,10 +11,10 @@ from lfm25_inference_b200 import ops, serving
 pytestmark = pytest.mark.gpu
 
 
-def build_engine(device, pages=512, slots=8):
+def build_engine(device, pages=512, slots=8, radix_pages=128, **options):
     model = lfm_model.RandomModel(13, device, pages, slots)
     engine = serving.ServingEngine(model, device, max_slots=slots, max_sequence_tokens=640, max_prefill_tokens=128,
-                                   radix_pages=128, checkpoint_capacity=16, use_fp8=False)
+                                   radix_pages=radix_pages, checkpoint_capacity=16, use_fp8=False, **options)
     engine.calibrate()
     return model, engine
 
@@ -64,3 +64,63 @@ def test_trace_completes_and_reuses_prefixes(device):
         assert agree >= 1          # the first token comes from the same prompt; later ones may diverge at a near-tie
         engine.close()
         alone.close()
+
+
+def prompt_of(rng, length):
+    return rng.integers(0, lfm_model.VOCAB, size=length).astype(np.uint32)
+
+
+def test_admission_control_rejects_with_the_reference_reasons(device):
+    """admit_request_radix (src/engine/serving/radix_owner.rs:549-708): with admission control every queued request
+    is decided at the next step, in the reference's order of checks; rejected requests leave nothing behind."""
+    with torch.cuda.stream(torch.cuda.Stream()):
+        rng = np.random.default_rng(17)
+        model, engine = build_engine(device, slots=2, admission_control=True, interactive_prompt_limit=300)
+        requests = [serving.Request(0, prompt_of(rng, 50), 4, 0),
+                    serving.Request(1, prompt_of(rng, 600), 100, 0),      # 700 tokens > 640
+                    serving.Request(2, prompt_of(rng, 400), 4, 0),        # prompt over the interactive limit
+                    serving.Request(3, prompt_of(rng, 60), 4, 0),
+                    serving.Request(4, prompt_of(rng, 40), 4, 0)]         # both slots taken by 0 and 3
+        result = serving.run_trace(engine, requests)
+        by_id = {entry["request_id"]: entry for entry in result["requests"]}
+        assert by_id[1]["rejected"] == "sequence_capacity" and by_id[1]["generated"] == 0
+        assert by_id[2]["rejected"] == "prompt_limit"
+        assert by_id[4]["rejected"] == "slots"
+        for request_id in (0, 3):
+            assert by_id[request_id]["rejected"] is None and by_id[request_id]["generated"] == 4
+        assert result["stats"]["rejected_requests"] == 3
+        assert engine.active() == 0 and engine.queued() == 0
+        assert engine.snapshot()["pool"]["reserved_pages"] == 0
+        engine.close()
+
+        # a decode step predicted over the TPOT SLO, then a first token predicted over the TTFT SLO
+        model, engine = build_engine(device, slots=2, admission_control=True, tpot_slo_us=1)
+        result = serving.run_trace(engine, [serving.Request(0, prompt_of(rng, 50), 4, 0)])
+        assert result["requests"][0]["rejected"] == "decode_budget"
+        engine.close()
+        model, engine = build_engine(device, slots=2, admission_control=True, ttft_slo_us=1)
+        result = serving.run_trace(engine, [serving.Request(0, prompt_of(rng, 50), 4, 0)])
+        assert result["requests"][0]["rejected"] == "ttft"
+        engine.close()
+
+        # the page reservation of the whole sequence: 38 pages each against a pool of 64
+        model, engine = build_engine(device, pages=64, slots=4, radix_pages=16, admission_control=True)
+        result = serving.run_trace(engine, [serving.Request(0, prompt_of(rng, 300), 300, 0),
+                                            serving.Request(1, prompt_of(rng, 300), 300, 0)])
+        by_id = {entry["request_id"]: entry for entry in result["requests"]}
+        assert by_id[0]["rejected"] is None and by_id[0]["generated"] == 300
+        assert by_id[1]["rejected"] == "kv_pages"
+        assert ops.device_status()[0] == 0
+        engine.close()
+
+
+def test_without_admission_control_the_queue_waits(device):
+    """Back-pressure: the same overload as above is served in order instead of being turned away."""
+    with torch.cuda.stream(torch.cuda.Stream()):
+        rng = np.random.default_rng(19)
+        model, engine = build_engine(device, slots=2)
+        requests = [serving.Request(index, prompt_of(rng, 40 + index), 4, 0) for index in range(5)]
+        result = serving.run_trace(engine, requests)
+        assert all(entry["rejected"] is None and entry["generated"] == 4 for entry in result["requests"])
+        assert result["stats"]["rejected_requests"] == 0
+        engine.close()
