@@ -661,15 +661,15 @@ def run_step_arm(arguments, rank, world):
                 reference_kernels = {"error": str(error)[:120]}
 
         # ---- end to end: host metadata in, sampled ids out, every step ----
-        host_meta = {name: getattr(device_batch, name).cpu().pin_memory()
-                     for name in ("token_ids", "positions", "request_slots")}
+        host_block = device_batch.step_metadata.cpu().pin_memory()       # token ids | positions | request slots
+        host_meta = {"token_ids": host_block[:STEP_SEQUENCES],
+                     "positions": host_block[STEP_SEQUENCES:2 * STEP_SEQUENCES]}
         host_sampled = torch.empty(STEP_SEQUENCES, dtype=torch.int32).pin_memory()
-        h2d_bytes = sum(t.numel() * t.element_size() for t in host_meta.values())
+        h2d_bytes = host_block.numel() * host_block.element_size()
         d2h_bytes = host_sampled.numel() * host_sampled.element_size()
 
         def served_step():
-            for name, tensor in host_meta.items():
-                getattr(device_batch, name).copy_(tensor, non_blocking=True)
+            device_batch.step_metadata.copy_(host_block, non_blocking=True)     # one upload per step
             executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=False)
             executor.download_sampled(host_sampled)
             stream.synchronize()                   # the serving loop needs the ids (EOS, streaming) before it goes on

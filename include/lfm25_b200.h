@@ -306,6 +306,17 @@ size_t lfm25_blaslt_workspace_size(const lfm25_blaslt* handle);
 void* lfm25_blaslt_stream(const lfm25_blaslt* handle); /* BlasLt::workspace_size */
 int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                        const lfm25_fp8_linear_config* config);
+/* The packed Gate/Up FP8 linear with the gated activation in its epilogue: one launch for
+ * linear_decode_prequantized_fp8_into on the Gate/Up site + silu_mul_packed_bf16_to_e4m3_into (or
+ * silu_mul_packed_bf16_into when `e4m3_output` is 0) of the decode step (src/model/decode_executor.rs:378-402,
+ * kernels/silu_mul.cu:68-133).  `weight` [config->n = 2 * intermediate, config->k] E4M3 with the gate rows first,
+ * `activation` [config->m, intermediate]: E4M3 codes of bf16(silu(bf16(gate)) * bf16(up)) * activation_scale, or
+ * that bf16 value.  Same bits as the two-launch route (the projections are rounded to bf16 before the activation).
+ * LFM25_ERR_UNSUPPORTED when the shape is outside the tensor-core kernel (n % 128, k % 128, m <= 256, 16-byte
+ * aligned buffers): the caller then takes the two-launch route. */
+int32_t lfm25_blaslt_linear_fp8_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight,
+                                         lfm25_slice activation, const lfm25_fp8_linear_config* config,
+                                         float activation_scale, uint32_t e4m3_output);
 /* Replaces BlasLt::linear_bf16 (src/cuda/blaslt/mod.rs:113-186): out[M,N] = x[M,K] * weight[N,K]^T in bf16 with
  * fp32 accumulation, through cuBLASLt (opened lazily; plans cached per shape), as the reference does for the
  * sites that are not promoted to FP8. */

@@ -214,6 +214,8 @@ PROTOTYPES = {
     "lfm25_blaslt_workspace_size": (_size, [ctypes.c_void_p]),
     "lfm25_blaslt_stream": (ctypes.c_void_p, [ctypes.c_void_p]),
     "lfm25_blaslt_linear_fp8_scaled": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _P(Fp8LinearConfig)]),
+    "lfm25_blaslt_linear_fp8_silu_mul": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _P(Fp8LinearConfig),
+                                                          ctypes.c_float, ctypes.c_uint32]),
     "lfm25_blaslt_linear_bf16": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_embedding_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_rms_norm_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, ctypes.c_float]),

@@ -937,4 +937,48 @@ int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm2
     return linear_fp8_dispatch(handle->stream, x, weight, out, config, handle->exchange, handle->exchange_bytes);
 }
 
+int32_t lfm25_blaslt_linear_fp8_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight,
+                                         lfm25_slice activation, const lfm25_fp8_linear_config* config,
+                                         float activation_scale, uint32_t e4m3_output) {
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
+    LFM25_ENSURE(config != nullptr, LFM25_ERR_NULL_POINTER, "FP8 linear config is null");
+    const size_t m = config->m;
+    const size_t n = config->n;
+    const size_t k = config->k;
+    LFM25_ENSURE(m > 0 && n > 0 && k > 0, LFM25_ERR_INVALID_ARGUMENT, "gated FP8 linear is empty");
+    LFM25_ENSURE(n % 2 == 0, LFM25_ERR_INVALID_ARGUMENT, "packed Gate/Up width must be even, got %zu", n);
+    LFM25_ENSURE(config->scale_mode == LFM25_FP8_SCALE_TENSORWIDE, LFM25_ERR_UNSUPPORTED,
+                 "Block32 (MXFP8) scaling is not built; use the tensor-wide mode");
+    LFM25_ENSURE(std::isfinite(config->output_scale) && config->output_scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                 "FP8 output scale must be finite and positive");
+    LFM25_ENSURE(std::isfinite(activation_scale) && activation_scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                 "activation scale must be finite and positive");
+    size_t x_required = 0;
+    size_t weight_required = 0;
+    size_t out_required = 0;
+    LFM25_ENSURE(checked_mul(m, k, &x_required), LFM25_ERR_OVERFLOW, "gated FP8 linear input size overflow");
+    LFM25_ENSURE(checked_mul(n, k, &weight_required), LFM25_ERR_OVERFLOW, "gated FP8 linear weight size overflow");
+    LFM25_ENSURE(checked_mul(m, n / 2, &out_required), LFM25_ERR_OVERFLOW, "gated FP8 linear output size overflow");
+    LFM25_ENSURE(x.len >= x_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "gated FP8 linear input storage too small: required=%zu, actual=%zu", x_required, x.len);
+    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "gated FP8 linear weight storage too small: required=%zu, actual=%zu", weight_required, weight.len);
+    LFM25_ENSURE(activation.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "gated FP8 linear output storage too small: required=%zu, actual=%zu", out_required,
+                 activation.len);
+    LFM25_ENSURE(x.ptr && weight.ptr && activation.ptr, LFM25_ERR_NULL_POINTER,
+                 "gated FP8 linear received a null device pointer");
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
+                           reinterpret_cast<uintptr_t>(activation.ptr)) &
+                          15) == 0;
+    LFM25_ENSURE(aligned && lfm25::fp8_gemm_umma_gated_supports(m, n, k), LFM25_ERR_UNSUPPORTED,
+                 "gated FP8 linear: shape or alignment outside the tensor-core kernel");
+    unsigned int* status_words = device_status_pointer();
+    LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(lfm25::launch_fp8_gemm_umma_gated(handle->stream, x.ptr, weight.ptr, activation.ptr, m, n, k,
+                                                         config->output_scale, activation_scale, e4m3_output != 0,
+                                                         status_words),
+                       "gated FP8 linear launch failed");
+}
+
 }  // extern "C"

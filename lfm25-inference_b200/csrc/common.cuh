@@ -148,6 +148,21 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const void* tenso
         : "memory");
 }
 
+// ------------------------------------------------------------------ E4M3 and SiLU (shared by the element-wise
+// kernels and the GEMM epilogue that fuses them, so that both produce the same bits)
+
+// two floats -> two E4M3 codes (round to nearest even, saturate to +-448); `low` lands in the low byte
+__device__ __forceinline__ uint16_t e4m3x2(float low, float high) {
+    uint16_t codes;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(codes) : "f"(low), "f"(high));
+    return codes;
+}
+
+// kernels/silu_mul.cu:7-9
+__device__ __forceinline__ float silu(float x) {
+    return x / (1.0f + __expf(-x));
+}
+
 // ------------------------------------------------------------------ tensor-core helpers
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t address, uint32_t& r0, uint32_t& r1, uint32_t& r2,

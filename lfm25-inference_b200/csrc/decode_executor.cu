@@ -300,6 +300,55 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
         }
         if (status != cudaSuccess) return cuda_failure(status, "residual_rms_norm launch failed");
 
+        // An FP8 Gate/Up whose shape the tensor-core kernel takes runs with SiLU(gate) * up in its epilogue: the
+        // packed projection is never written, and the activation arrives as the Down site's E4M3 codes or as bf16.
+        static const bool fuse_gate = [] {
+            const char* value = getenv("LFM25_FUSED_SILU");
+            return value == nullptr || strcmp(value, "0") != 0;
+        }();
+        const bool down_fp8 = use_fp8 && layer.down.fp8.data != nullptr;
+        bool gate_fused = false;
+        if (fuse_gate && gate_up_fp8 && layer.gate_up.n == 2 * kFfn && (down_fp8 || layer.down.bf16 != nullptr)) {
+            RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
+            lfm25_fp8_linear_config config;
+            config.m = tokens;
+            config.n = 2 * kFfn;
+            config.k = kHidden;
+            config.scale_mode = LFM25_FP8_SCALE_TENSORWIDE;
+            config.output_scale = layer.gate_up.fp8.activation_dequantize * layer.gate_up.fp8.weight_dequantize;
+            // the codes of the normalised rows are in fp8_input; the activation's codes go to `activated` (the Down
+            // GEMM reads them from there), the bf16 activation too
+            const int32_t rc = lfm25_blaslt_linear_fp8_silu_mul(
+                self->blaslt, slice_of(self->fp8_input, tokens * kHidden),
+                slice_of(layer.gate_up.fp8.data, 2 * kFfn * kHidden),
+                slice_of(self->activated, down_fp8 ? tokens * kFfn * 2 : tokens * kFfn), &config,
+                down_fp8 ? layer.down.fp8.activation_quantize : 1.0f, down_fp8 ? 1u : 0u);
+            if (rc == LFM25_OK) {
+                gate_fused = true;
+            } else if (rc != LFM25_ERR_UNSUPPORTED) {
+                return rc;
+            }
+        }
+        if (gate_fused) {
+            if (down_fp8) {
+                RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
+                lfm25_fp8_linear_config config;
+                config.m = tokens;
+                config.n = kHidden;
+                config.k = kFfn;
+                config.scale_mode = LFM25_FP8_SCALE_TENSORWIDE;
+                config.output_scale = layer.down.fp8.activation_dequantize * layer.down.fp8.weight_dequantize;
+                LFM25_TRY(lfm25_blaslt_linear_fp8_scaled(self->blaslt, slice_of(self->activated, tokens * kFfn),
+                                                         slice_of(layer.down.fp8.data, kHidden * kFfn),
+                                                         slice_of(self->operator_output, tokens * kHidden), &config));
+            } else {
+                RegionTimer timer(self, LFM25_REGION_BF16_LINEAR);
+                LFM25_TRY(lfm25_blaslt_linear_bf16(self->blaslt, slice_of(self->activated, tokens * kFfn),
+                                                   slice_of(layer.down.bf16, kHidden * kFfn),
+                                                   slice_of(self->operator_output, tokens * kHidden), tokens, kHidden,
+                                                   kFfn));
+            }
+        } else {
         LFM25_TRY(linear_decode(self, layer.gate_up, self->normalized, self->wide, tokens, use_fp8, gate_up_fp8));
         if (use_fp8 && layer.down.fp8.data != nullptr) {
             RegionTimer timer(self, LFM25_REGION_FP8_LINEAR);
@@ -326,6 +375,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                                                slice_of(layer.down.bf16, kHidden * kFfn),
                                                slice_of(self->operator_output, tokens * kHidden), tokens, kHidden,
                                                kFfn));
+        }
         }
 
         const bool last_layer = index + 1 == model->num_layers;

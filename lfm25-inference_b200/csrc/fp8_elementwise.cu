@@ -20,18 +20,8 @@ namespace {
 
 constexpr uint32_t kThreads = 256;
 
-__device__ __forceinline__ uint16_t e4m3x2(float low, float high) {
-    uint16_t codes;
-    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(codes) : "f"(low), "f"(high));
-    return codes;
-}
-
 __device__ __forceinline__ uint8_t e4m3x1(float value) {
     return static_cast<uint8_t>(e4m3x2(value, 0.0f) & 0xffu);
-}
-
-__device__ __forceinline__ float silu(float x) {
-    return x / (1.0f + __expf(-x));
 }
 
 // 8 bf16 -> 8 codes

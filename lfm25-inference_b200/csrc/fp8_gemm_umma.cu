@@ -62,6 +62,13 @@ struct UmmaParams {
     uint32_t tmem_columns;   // power of two >= max(32, m_pad)
     float alpha;
     uint32_t timeline_slot;  // only read by the instrumented build (LFM25_UMMA_TIMELINE)
+    // Gated mode (packed Gate/Up weights [2 * intermediate, K], gate rows first): a tile is 64 gate rows and the 64
+    // up rows that belong to them, and the epilogue writes act = bf16(silu(bf16(gate)) * bf16(up)) -- as E4M3 codes
+    // of act * gated_scale when gated_e4m3 is set -- instead of the two projections.  0 = plain GEMM.
+    uint32_t intermediate;
+    uint32_t gated_e4m3;
+    float gated_scale;
+    void* gated_out;         // [m, intermediate] E4M3 codes or bf16
 };
 
 // Instrumented build only: per CTA, the SM cycle counter at the points of the kernel's critical path (and the global
@@ -149,7 +156,18 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
     const uint32_t k_count = k_share + (split < k_extra ? 1u : 0u);
     const uint32_t k_block0 = split * k_share + (split < k_extra ? split : k_extra);
     const uint32_t ahead = k_count < p.stages ? k_count : p.stages;
-    const int32_t tile_row = static_cast<int32_t>(tile * kTileN);
+    const bool gated = p.intermediate != 0;
+    const int32_t tile_row = static_cast<int32_t>(tile * (gated ? kTileN / 2 : kTileN));
+    // the weight tile of one K block: one 128-row box, or in gated mode two 64-row boxes (gate rows, up rows)
+    auto load_weights = [&](uint32_t dst, uint32_t bar, int32_t k_offset) {
+        if (gated) {
+            tma_load_2d(dst, &weight_map, bar, k_offset, tile_row);
+            tma_load_2d(dst + kWeightTileBytes / 2, &weight_map, bar, k_offset,
+                        tile_row + static_cast<int32_t>(p.intermediate));
+        } else {
+            tma_load_2d(dst, &weight_map, bar, k_offset, tile_row);
+        }
+    };
     if (threadIdx.x == 0) {
         tma_prefetch_descriptor(&weight_map);
         tma_prefetch_descriptor(&x_map);
@@ -168,8 +186,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
         for (uint32_t block = 0; block < ahead; ++block) {
             const uint32_t bar = bar_full + 8 * block;
             mbar_arrive_expect_tx(bar, stage_bytes);
-            tma_load_2d(smem_base + block * stage_bytes, &weight_map, bar,
-                        static_cast<int32_t>((k_block0 + block) * kBlockK), tile_row);
+            load_weights(smem_base + block * stage_bytes, bar, static_cast<int32_t>((k_block0 + block) * kBlockK));
         }
     }
     if (warp == 1) {
@@ -204,7 +221,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                 const uint32_t dst = smem_base + stage * stage_bytes;
                 const int32_t k_offset = static_cast<int32_t>((k_block0 + block) * kBlockK);
                 mbar_arrive_expect_tx(bar, stage_bytes);
-                tma_load_2d(dst, &weight_map, bar, k_offset, tile_row);
+                load_weights(dst, bar, k_offset);
                 tma_load_2d(dst + kWeightTileBytes, &x_map, bar, k_offset, 0);
             }
         }
@@ -252,7 +269,64 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
         tcgen05_fence_after();
         if (warp == 2 && lane == 0) timeline_mark(p, 5);
         const uint32_t lane_address = tmem_base + ((quadrant * 32) << 16);
-        if (p.splits == 1) {
+        if (gated) {
+            // Rows 0-63 of the tile are gate rows, rows 64-127 the matching up rows.  Every thread rounds its row to
+            // bf16 (what the unfused route stores as the packed projection) into staged[column][128 rows]; after a
+            // barrier of the four epilogue warps a thread takes 16 consecutive outputs of one batch column.
+            uint8_t* staged = smem;
+            if (ready) {
+                for (uint32_t column0 = 0; column0 < p.m_pad; column0 += 16) {
+                    uint32_t raw[16];
+                    tmem_load16(lane_address + column0, raw);
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j) {
+                        reinterpret_cast<__nv_bfloat16*>(staged + (column0 + j) * 256)[quadrant * 32 + lane] =
+                            __float2bfloat16_rn(__uint_as_float(raw[j]) * p.alpha);
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!*abort_flag) {
+                const uint32_t worker = threadIdx.x - 64;     // 0..127 over the four epilogue warps
+                const uint32_t part = worker & 3;             // 16 of the tile's 64 outputs
+                for (uint32_t batch = worker >> 2; batch < p.m; batch += 32) {
+                    const uint4* gate_raw = reinterpret_cast<const uint4*>(staged + batch * 256 + part * 32);
+                    const uint4* up_raw = reinterpret_cast<const uint4*>(staged + batch * 256 + 128 + part * 32);
+                    __align__(16) __nv_bfloat162 hidden[8];
+#pragma unroll
+                    for (uint32_t half = 0; half < 2; ++half) {
+                        const uint4 g4 = gate_raw[half];
+                        const uint4 u4 = up_raw[half];
+                        const __nv_bfloat162* g = reinterpret_cast<const __nv_bfloat162*>(&g4);
+                        const __nv_bfloat162* u = reinterpret_cast<const __nv_bfloat162*>(&u4);
+#pragma unroll
+                        for (uint32_t pair = 0; pair < 4; ++pair) {
+                            const float2 gv = __bfloat1622float2(g[pair]);
+                            const float2 uv = __bfloat1622float2(u[pair]);
+                            hidden[half * 4 + pair] = __floats2bfloat162_rn(silu(gv.x) * uv.x, silu(gv.y) * uv.y);
+                        }
+                    }
+                    const size_t element = static_cast<size_t>(batch) * p.intermediate + tile * 64 + part * 16;
+                    if (p.gated_e4m3) {
+                        uint32_t packed[4];
+#pragma unroll
+                        for (uint32_t word = 0; word < 4; ++word) {
+                            const float2 a = __bfloat1622float2(hidden[word * 2]);
+                            const float2 b = __bfloat1622float2(hidden[word * 2 + 1]);
+                            packed[word] =
+                                static_cast<uint32_t>(e4m3x2(a.x * p.gated_scale, a.y * p.gated_scale)) |
+                                (static_cast<uint32_t>(e4m3x2(b.x * p.gated_scale, b.y * p.gated_scale)) << 16);
+                        }
+                        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.gated_out) + element) =
+                            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    } else {
+                        uint4* target = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.gated_out) + element);
+                        target[0] = *reinterpret_cast<const uint4*>(&hidden[0]);
+                        target[1] = *reinterpret_cast<const uint4*>(&hidden[4]);
+                    }
+                }
+            }
+        } else if (p.splits == 1) {
             if (ready) {
                 // Transpose through this warp's slice of the (now idle) pipeline memory so that the global stores
                 // are 16 bytes wide: staged[column][32 rows] as bf16, then lane -> (column l/4, 8 rows l%4).
@@ -396,15 +470,28 @@ uint32_t resident_clusters(uint32_t size) {
 }
 
 // `k_bytes` is the length of a weight / activation row in bytes (K for E4M3, 2 K for BF16).
+// Gated mode of a launch: where the activation goes and how it is encoded (see UmmaParams).
+struct GatedOutput {
+    void* out;
+    float code_scale;
+    bool e4m3;
+};
+
 template <bool BF16>
 cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m, size_t n,
-                        size_t k_bytes, float alpha, void* exchange, size_t exchange_bytes, unsigned int* status) {
+                        size_t k_bytes, float alpha, void* exchange, size_t exchange_bytes, unsigned int* status,
+                        const GatedOutput* gated = nullptr) {
     const uint32_t m_pad = static_cast<uint32_t>((m + 15) / 16 * 16);
     CUtensorMap weight_map;
     CUtensorMap x_map;
-    if (!make_swizzled_2d_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, weight, n, k_bytes, kTileN) ||
+    // gated: n = 2 * intermediate packed rows, fetched as two 64-row boxes per tile
+    if (!make_swizzled_2d_map(&weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, weight, n, k_bytes,
+                              gated != nullptr ? kTileN / 2 : kTileN) ||
         !make_swizzled_2d_map(&x_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, m, k_bytes, m_pad)) {
         return cudaErrorInvalidValue;
+    }
+    if (gated != nullptr) {
+        exchange = nullptr;      // the fused epilogue needs whole sums in one CTA: K is not split
     }
     const uint32_t tiles = static_cast<uint32_t>(n / kTileN);
     const uint32_t k_blocks_total = static_cast<uint32_t>(k_bytes / kBlockK);
@@ -476,6 +563,10 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
     params.alpha = alpha;
     static uint32_t launches = 0;
     params.timeline_slot = launches++;
+    params.intermediate = gated != nullptr ? static_cast<uint32_t>(n / 2) : 0;
+    params.gated_e4m3 = gated != nullptr && gated->e4m3 ? 1u : 0u;
+    params.gated_scale = gated != nullptr ? gated->code_scale : 1.0f;
+    params.gated_out = gated != nullptr ? gated->out : nullptr;
 
     const cudaError_t attribute_status = cudaFuncSetAttribute(
         gemm_umma_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
@@ -499,6 +590,17 @@ cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void*
                                  size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,
                                  unsigned int* status) {
     return launch_umma<false>(stream, x, weight, out, m, n, k, alpha, exchange, exchange_bytes, status);
+}
+
+bool fp8_gemm_umma_gated_supports(size_t m, size_t n, size_t k) {
+    return fp8_gemm_umma_supports(m, n, k) && (n / 2) % (kTileN / 2) == 0 && n % 2 == 0;
+}
+
+cudaError_t launch_fp8_gemm_umma_gated(cudaStream_t stream, const void* x, const void* weight, void* activation,
+                                       size_t m, size_t n, size_t k, float alpha, float code_scale, bool e4m3,
+                                       unsigned int* status) {
+    const GatedOutput gated = {activation, code_scale, e4m3};
+    return launch_umma<false>(stream, x, weight, nullptr, m, n, k, alpha, nullptr, 0, status, &gated);
 }
 
 cudaError_t launch_bf16_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,

@@ -99,6 +99,12 @@ cudaError_t launch_fp8_gemm_generic(cudaStream_t stream, const void* x, const vo
                                     size_t n, size_t k, float alpha);
 
 bool fp8_gemm_umma_supports(size_t m, size_t n, size_t k);
+// Packed Gate/Up GEMM with SiLU(gate) * up in the epilogue: `weight` [n = 2 * intermediate, k] (gate rows first),
+// `activation` [m, n / 2] as E4M3 codes of the bf16 activation times `code_scale`, or as bf16.
+bool fp8_gemm_umma_gated_supports(size_t m, size_t n, size_t k);
+cudaError_t launch_fp8_gemm_umma_gated(cudaStream_t stream, const void* x, const void* weight, void* activation,
+                                       size_t m, size_t n, size_t k, float alpha, float code_scale, bool e4m3,
+                                       unsigned int* status);
 // `exchange` (may be null: K is then not split) is scratch for split-K partial tiles, owned by the caller and
 // used by one stream at a time; kUmmaExchangeBytes covers every supported shape.
 constexpr size_t kUmmaExchangeBytes = 148u * 256u * 128u * 4u;

@@ -188,10 +188,16 @@ class DecodeBatch:
             return torch.from_numpy(np.ascontiguousarray(values, dtype=np.uint32).view(np.int32).copy()).to(device)
 
         self.block_tables = u32(block_tables)
-        self.request_slots = u32(request_slots)
-        self.positions = u32(positions)
-        self.token_ids = u32(token_ids)
         self.num_tokens = int(len(positions))
+        # token ids | positions | request slots in one allocation: a serving loop that supplies them from the host
+        # uploads the step's metadata with one copy (the reference packs its slab the same way,
+        # src/scheduler/batch.rs:26-53)
+        self.step_metadata = u32(np.concatenate([np.asarray(token_ids, dtype=np.uint32),
+                                                 np.asarray(positions, dtype=np.uint32),
+                                                 np.asarray(request_slots, dtype=np.uint32)]))
+        self.token_ids = self.step_metadata[:self.num_tokens]
+        self.positions = self.step_metadata[self.num_tokens:2 * self.num_tokens]
+        self.request_slots = self.step_metadata[2 * self.num_tokens:]
         self.physical_slots = torch.zeros(self.num_tokens, dtype=torch.int64, device=device)
         self.struct = _abi.DecodeBatch(
             self.token_ids.data_ptr(), self.positions.data_ptr(), self.request_slots.data_ptr(),

@@ -303,6 +303,18 @@ class BlasLt:
         check(library().lfm25_blaslt_linear_fp8_scaled(self._handle, _slice(x_codes), _slice(weight_codes),
                                                        _slice(output), config))
 
+    def linear_fp8_silu_mul(self, x_codes, weight_codes, activation, output_scale: float,
+                            activation_scale: float = 1.0) -> None:
+        """Packed Gate/Up FP8 linear with SiLU(gate) * up in the epilogue (one launch for
+        src/model/decode_executor.rs:378-402): `activation` [M, N/2] is uint8 (E4M3 codes of the activation times
+        `activation_scale`) or bfloat16."""
+        m, k = x_codes.shape
+        config = _abi.Fp8LinearConfig(m, weight_codes.shape[0], k, _abi.FP8_SCALE_TENSORWIDE, output_scale)
+        self.bind_current_stream()
+        check(library().lfm25_blaslt_linear_fp8_silu_mul(self._handle, _slice(x_codes), _slice(weight_codes),
+                                                         _slice(activation), config, activation_scale,
+                                                         1 if activation.dtype == torch.uint8 else 0))
+
     def bind_current_stream(self) -> None:
         stream = _stream()
         if stream != self._bound_stream:

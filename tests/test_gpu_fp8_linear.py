@@ -158,3 +158,51 @@ def test_shape_checks(device):
         ops.linear_fp8_scaled_into(x, w, out, 0.0)
     with pytest.raises(Lfm25Error, match="Block32"):
         ops.linear_fp8_scaled_into(x, w, out, 1.0, scale_mode=1)
+
+
+@pytest.mark.parametrize("e4m3_output", [True, False])
+@pytest.mark.parametrize("m", [1, 5, 16, 33, 128, 200, 256])
+@pytest.mark.parametrize("intermediate,k", [(8192, 2048), (256, 512), (64, 128)])
+def test_gated_linear_equals_linear_then_silu_mul(device, monkeypatch, m, intermediate, k, e4m3_output):
+    """The packed Gate/Up linear with SiLU(gate) * up in its epilogue: bit for bit what the same GEMM kernel followed
+    by the SiLU * Up kernel produces (src/model/decode_executor.rs:378-402 as two launches), and within the FP8
+    tolerance of the oracle's restatement of those two ops."""
+    monkeypatch.setenv("LFM25_FP8_GEMM_PATH", "umma")          # the two-launch route through the same GEMM kernel
+    _, x_codes, w_codes, (_, xd), (_, wd) = quantised_problem(m * 7 + intermediate + k, m, 2 * intermediate, k)
+    x_device, w_device = codes_tensor(x_codes, device), codes_tensor(w_codes, device)
+    activation_scale = 448.0 / 6.0
+    blaslt = ops.BlasLt()
+    packed = torch.zeros((m, 2 * intermediate), dtype=torch.bfloat16, device=device)
+    ops.linear_fp8_scaled_into(x_device, w_device, packed, xd * wd)
+    if e4m3_output:
+        want = torch.zeros((m, intermediate), dtype=torch.uint8, device=device)
+        ops.silu_mul_packed_bf16_to_e4m3_into(packed, want, activation_scale)
+        got = torch.full((m, intermediate), 0x55, dtype=torch.uint8, device=device)
+        blaslt.linear_fp8_silu_mul(x_device, w_device, got, xd * wd, activation_scale)
+        assert np.array_equal(got.cpu().numpy(), want.cpu().numpy())
+    else:
+        want = torch.zeros((m, intermediate), dtype=torch.bfloat16, device=device)
+        ops.silu_mul_packed_bf16_into(packed, want)
+        got = torch.zeros((m, intermediate), dtype=torch.bfloat16, device=device)
+        blaslt.linear_fp8_silu_mul(x_device, w_device, got, xd * wd)
+        assert np.array_equal(bits_of(got), bits_of(want))
+        # against the oracle: projections from the same codes, then its SiLU * Up
+        projected = oracle.linear_fp8(x_codes, w_codes, xd * wd)
+        activated, _ = oracle.silu_mul_packed(projected, 1.0)
+        assert_close_bf16(bits_of(got), activated, atol=2e-2, rtol=2e-2)
+    assert ops.device_status()[0] == 0
+    blaslt.close()
+
+
+def test_gated_linear_shape_checks(device):
+    blaslt = ops.BlasLt()
+    x = torch.zeros((4, 128), dtype=torch.uint8, device=device)
+    weight = torch.zeros((2 * 96, 128), dtype=torch.uint8, device=device)      # 96 outputs: not a multiple of 64
+    out = torch.zeros((4, 96), dtype=torch.uint8, device=device)
+    with pytest.raises(Lfm25Error):
+        blaslt.linear_fp8_silu_mul(x, weight, out, 1.0, 1.0)
+    weight = torch.zeros((2 * 64, 128), dtype=torch.uint8, device=device)
+    small = torch.zeros((4, 32), dtype=torch.uint8, device=device)             # output storage too small
+    with pytest.raises(Lfm25Error):
+        blaslt.linear_fp8_silu_mul(x, weight, small, 1.0, 1.0)
+    blaslt.close()
