@@ -356,13 +356,18 @@ def run_gpu_arm(arguments, rank, world):
         return ops.FastRaggedAttentionInput(query, arena, block_tables, batch.stride, request_slots,
                                             inputs["positions"])
 
-    def attend(attention_inputs):
-        if splits > 1:
-            ops.paged_ragged_attention_splitk_lfm2_bf16_into(attention_inputs, partials, splits, output)
-        else:
-            ops.paged_ragged_attention_fast_lfm2_bf16_into(attention_inputs, output)
+    token_order = torch.zeros(SEQUENCES, dtype=torch.int32, device=device)
 
-    launches_per_step = 2 + (1 if splits > 1 else 0)   # append, attention, (merge)
+    def attend(attention_inputs):
+        # the CTAs start on the longest contexts (ordered on the device, every step)
+        ops.context_order_desc_into(attention_inputs.position_ids, token_order)
+        if splits > 1:
+            ops.paged_ragged_attention_splitk_lfm2_bf16_into(attention_inputs, partials, splits, output,
+                                                             token_order=token_order)
+        else:
+            ops.paged_ragged_attention_fast_lfm2_bf16_into(attention_inputs, output, token_order=token_order)
+
+    launches_per_step = 3 + (1 if splits > 1 else 0)   # append, context order, attention, (merge)
 
     for step in range(arguments.warmup):
         attend(decode_step(episode[step % EPISODE], episode[step % EPISODE]["query"]))

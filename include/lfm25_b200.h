@@ -132,8 +132,16 @@ typedef struct lfm25_fast_ragged_attention_launch {
     size_t num_tokens;
     size_t num_pages;
     size_t block_table_stride;
+    /* Extension (no counterpart in the reference's launch struct): optional u32 [num_tokens] permutation of the
+     * tokens.  CTAs are handed out in this order; listing the longest contexts first (lfm25_context_order_desc)
+     * keeps the tail of the grid short on ragged batches.  Results do not depend on it.  ptr NULL = as given. */
+    lfm25_slice token_order;
 } lfm25_fast_ragged_attention_launch;
 int32_t lfm25_paged_ragged_attention_fast_lfm2_bf16(void* stream, const lfm25_fast_ragged_attention_launch* launch);
+/* order[r] = index of the token with the r-th largest position (ties: lower index first), for the `token_order`
+ * field of the decode attention launches.  At most 2048 tokens.  No counterpart in the reference, whose kernels take
+ * the batch in the order given. */
+int32_t lfm25_context_order_desc(void* stream, lfm25_slice position_ids, size_t num_tokens, lfm25_slice order);
 
 /* Replaces SplitKRaggedAttentionLaunch + launch_splitk_ragged_lfm2_bf16
  * (src/cuda/kernels/attention_async_fast.rs:28-42, :343-437; kernels
@@ -153,6 +161,7 @@ typedef struct lfm25_splitk_ragged_attention_launch {
     size_t num_pages;
     size_t block_table_stride;
     size_t num_splits;         /* 2..=8 */
+    lfm25_slice token_order;   /* optional, as in lfm25_fast_ragged_attention_launch */
 } lfm25_splitk_ragged_attention_launch;
 int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream, const lfm25_splitk_ragged_attention_launch* launch);
 
@@ -205,6 +214,7 @@ typedef struct lfm25_fused_ragged_decode_launch {
      * ([num_tokens, 3072] = q | k | v).  0 = dense (2048 and 512). */
     size_t query_token_stride;
     size_t kv_token_stride;
+    lfm25_slice token_order;   /* optional, as in lfm25_fast_ragged_attention_launch */
 } lfm25_fused_ragged_decode_launch;
 int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
                                                             const lfm25_fused_ragged_decode_launch* launch);

@@ -56,10 +56,10 @@ PagedAttentionLaunch = _launch_struct("PagedAttentionLaunch", [
     "#num_tokens", "#num_pages"])
 FastRaggedAttentionLaunch = _launch_struct("FastRaggedAttentionLaunch", [
     "#page_size", "query", "key_cache", "value_cache", "block_tables", "request_slots", "position_ids",
-    "output", "#num_tokens", "#num_pages", "#block_table_stride"])
+    "output", "#num_tokens", "#num_pages", "#block_table_stride", "token_order"])
 SplitKRaggedAttentionLaunch = _launch_struct("SplitKRaggedAttentionLaunch", [
     "#page_size", "query", "key_cache", "value_cache", "block_tables", "request_slots", "position_ids",
-    "partials", "output", "#num_tokens", "#num_pages", "#block_table_stride", "#num_splits"])
+    "partials", "output", "#num_tokens", "#num_pages", "#block_table_stride", "#num_splits", "token_order"])
 
 
 
@@ -182,7 +182,7 @@ FusedRaggedDecodeLaunch = _launch_struct("FusedRaggedDecodeLaunch", [
     "#page_size", "query_raw", "key_raw", "value_raw", "query_norm", "key_norm", "inv_freq", "key_cache",
     "value_cache", "position_ids", "slot_mapping", "output", "#num_tokens", "#num_pages", ("eps", ctypes.c_float),
     "block_tables", "request_slots", "#block_table_stride", "partials", "#num_splits", "#query_token_stride",
-    "#kv_token_stride"])
+    "#kv_token_stride", "token_order"])
 
 HybridAttentionLaunch = _launch_struct("HybridAttentionLaunch", [
     "#page_size", "query", "current_key", "current_value", "key_cache", "value_cache", "block_tables", "request_slots",
@@ -198,6 +198,7 @@ PROTOTYPES = {
     "lfm25_qk_norm_rope_kv_write_decode": (ctypes.c_int32, [_stream, _P(QkPostprocessLaunch)]),
     "lfm25_paged_attention_fast_lfm2_bf16": (ctypes.c_int32, [_stream, _P(PagedAttentionLaunch)]),
     "lfm25_paged_ragged_attention_fast_lfm2_bf16": (ctypes.c_int32, [_stream, _P(FastRaggedAttentionLaunch)]),
+    "lfm25_context_order_desc": (ctypes.c_int32, [_stream, Slice, _size, Slice]),
     "lfm25_paged_ragged_attention_splitk_lfm2_bf16": (ctypes.c_int32, [_stream, _P(SplitKRaggedAttentionLaunch)]),
     "lfm25_paged_ragged_attention_splitk_static_lfm2_bf16": (
         ctypes.c_int32, [_stream, _P(FastRaggedAttentionLaunch), _size]),

@@ -335,6 +335,33 @@ int32_t lfm25_paged_attention_fast_lfm2_bf16(void* stream, const lfm25_paged_att
                        "fast-exp attention launch failed");
 }
 
+namespace {
+// The optional token order of a decode attention launch: null, or at least num_tokens entries.
+int32_t take_token_order(const lfm25_slice& order, size_t num_tokens, const uint32_t** out) {
+    *out = nullptr;
+    if (order.ptr == nullptr) {
+        return LFM25_OK;
+    }
+    LFM25_ENSURE(order.len >= num_tokens, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "token order too small: required=%zu, actual=%zu", num_tokens, order.len);
+    *out = static_cast<const uint32_t*>(order.ptr);
+    return LFM25_OK;
+}
+}  // namespace
+
+int32_t lfm25_context_order_desc(void* stream, lfm25_slice position_ids, size_t num_tokens, lfm25_slice order) {
+    LFM25_ENSURE(num_tokens > 0 && num_tokens <= lfm25::kMaxOrderTokens, LFM25_ERR_INVALID_ARGUMENT,
+                 "context order takes 1..=%zu tokens, got %zu", lfm25::kMaxOrderTokens, num_tokens);
+    LFM25_ENSURE(position_ids.ptr != nullptr && order.ptr != nullptr, LFM25_ERR_NULL_POINTER,
+                 "context order received a null device pointer");
+    LFM25_ENSURE(position_ids.len >= num_tokens && order.len >= num_tokens, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "context order buffers too small for %zu tokens", num_tokens);
+    return cuda_result(lfm25::launch_context_order(static_cast<cudaStream_t>(stream),
+                                                   static_cast<const uint32_t*>(position_ids.ptr), num_tokens,
+                                                   static_cast<uint32_t*>(order.ptr)),
+                       "context order launch failed");
+}
+
 int32_t lfm25_paged_ragged_attention_fast_lfm2_bf16(void* stream, const lfm25_fast_ragged_attention_launch* launch) {
     LFM25_ENSURE(launch != nullptr, LFM25_ERR_NULL_POINTER, "fast-exp ragged attention launch is null");
     const lfm25_fast_ragged_attention_launch& l = *launch;
@@ -359,6 +386,10 @@ int32_t lfm25_paged_ragged_attention_fast_lfm2_bf16(void* stream, const lfm25_fa
     args.block_table_stride = l.block_table_stride;
     args.block_table_rows = l.block_tables.len / l.block_table_stride;
     args.num_splits = 1;
+    {
+        const int32_t order_status = take_token_order(l.token_order, l.num_tokens, &args.token_order);
+        if (order_status != LFM25_OK) return order_status;
+    }
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
     return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
                        "fast-exp ragged attention launch failed");
@@ -399,6 +430,10 @@ int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream,
     args.block_table_stride = l.block_table_stride;
     args.block_table_rows = l.block_tables.len / l.block_table_stride;
     args.num_splits = static_cast<uint32_t>(l.num_splits);
+    {
+        const int32_t order_status = take_token_order(l.token_order, l.num_tokens, &args.token_order);
+        if (order_status != LFM25_OK) return order_status;
+    }
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
     return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
                        "split-K ragged attention launch failed");
@@ -473,6 +508,10 @@ int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
     args.eps = l.eps;
     args.query_token_stride = query_stride;
     args.kv_token_stride = kv_stride;
+    {
+        const int32_t order_status = take_token_order(l.token_order, l.num_tokens, &args.token_order);
+        if (order_status != LFM25_OK) return order_status;
+    }
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
     return cuda_result(lfm25::launch_ragged_decode_attention(static_cast<cudaStream_t>(stream), args),
                        "fused ragged decode launch failed");

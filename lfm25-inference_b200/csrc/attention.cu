@@ -64,6 +64,7 @@ struct AttentionParams {
     __nv_bfloat16* value_cache;
     float eps;
     uint32_t kv_evict_first;  // nonzero: the K/V page loads carry the L2 evict-first hint
+    const uint32_t* token_order;  // optional permutation: which token the r-th group of CTAs takes
 };
 
 // FUSED == false: the query is already normalised and rotated and the newest K/V row is already in the cache.
@@ -85,8 +86,13 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     const uint32_t splits = p.num_splits;
     const uint32_t split = blockIdx.x % splits;
     const uint32_t item = blockIdx.x / splits;
-    const uint32_t token = item / kKvHeads;
     const uint32_t kv_head = item % kKvHeads;
+    if (item / kKvHeads >= p.num_tokens) {
+        return;
+    }
+    // CTAs start in block order: with an order that lists the longest contexts first the short ones fill the end of
+    // the grid, and the last wave does not wait for a few long sequences.  An entry outside the batch is a no-op.
+    const uint32_t token = p.token_order != nullptr ? p.token_order[item / kKvHeads] : item / kKvHeads;
     if (token >= p.num_tokens) {
         return;
     }
@@ -572,6 +578,7 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
         return value == nullptr || strcmp(value, "0") != 0;
     }();
     params.kv_evict_first = evict_first ? 1 : 0;
+    params.token_order = launch.token_order;
     const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
     cudaError_t status = launch_kernel(kernel, static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream, 1,
                                        key_map, value_map, params);

@@ -94,5 +94,6 @@ extern "C" int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(
     full.num_pages = launch->num_pages;
     full.block_table_stride = launch->block_table_stride;
     full.num_splits = num_splits;
+    full.token_order = launch->token_order;
     return lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &full);
 }

@@ -50,6 +50,7 @@ struct lfm25_decode_executor {
     float* partials;
     uint32_t* sampled;
     void* head_input;      // [maximum_rows, 2048]: the rows that go to the LM head in a mixed step
+    uint32_t* token_order; // [maximum_rows]: the step's tokens, longest context first (written by the metadata kernel)
     // opt-in region timing (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): CUDA-event pairs
     // around every op of an eager step, summed per region
     bool profiling = false;
@@ -146,11 +147,13 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
     cudaStream_t stream = self->blaslt->stream;
     const size_t tokens = batch->num_tokens;
     cudaError_t status = cudaSuccess;
+    const bool ordered = tokens <= 256;   // the metadata kernel orders the tokens only when one CTA covers the batch
     {
     RegionTimer timer(self, LFM25_REGION_OTHER);
     status = lfm25::launch_decode_metadata(
         stream, batch->token_ids, batch->positions, batch->request_slots, batch->block_tables, self->sampled,
-        batch->physical_slots, tokens, batch->block_table_stride, batch->block_table_rows, model->num_pages, advance);
+        batch->physical_slots, tokens, batch->block_table_stride, batch->block_table_rows, model->num_pages, advance,
+        self->token_order);
     if (status != cudaSuccess) return cuda_failure(status, "step metadata launch failed");
     status = lfm25::launch_embedding_bf16(stream, batch->token_ids, model->embedding, self->hidden, tokens, kVocab,
                                           kHidden);
@@ -236,6 +239,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 fused.num_splits = splits;
                 fused.query_token_stride = 0;
                 fused.kv_token_stride = 0;
+                fused.token_order = slice_of(ordered ? self->token_order : nullptr, ordered ? tokens : 0);
                 if (packed_qkv) {
                     uint16_t* packed_rows = static_cast<uint16_t*>(self->wide);
                     const size_t span = (tokens - 1) * kPackedWidth;
@@ -267,10 +271,12 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             attention.num_pages = model->num_pages;
             attention.block_table_stride = batch->block_table_stride;
             attention.num_splits = splits;
+            attention.token_order = slice_of(ordered ? self->token_order : nullptr, ordered ? tokens : 0);
             if (splits > 1) {
                 LFM25_TRY(lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &attention));
             } else {
                 lfm25_fast_ragged_attention_launch unsplit;
+                unsplit.token_order = attention.token_order;
                 unsplit.page_size = 16;
                 unsplit.query = attention.query;
                 unsplit.key_cache = attention.key_cache;
@@ -495,6 +501,7 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                 decode.num_pages = model->num_pages;
                 decode.block_table_stride = batch->block_table_stride;
                 decode.num_splits = splits;
+                decode.token_order = slice_of(nullptr, 0);
                 if (splits > 1) {
                     LFM25_TRY(lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &decode));
                 } else {
@@ -510,6 +517,7 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                     unsplit.num_tokens = decode_tokens;
                     unsplit.num_pages = model->num_pages;
                     unsplit.block_table_stride = batch->block_table_stride;
+                    unsplit.token_order = slice_of(nullptr, 0);
                     LFM25_TRY(lfm25_paged_ragged_attention_fast_lfm2_bf16(stream, &unsplit));
                 }
             }
@@ -655,16 +663,17 @@ int32_t lfm25_decode_executor_create_ragged(lfm25_blaslt* blaslt, size_t maximum
     self->maximum_rows = maximum_segments;
     const size_t b = maximum_tokens;
     const size_t r = maximum_segments;
-    const size_t sizes[14] = {
+    const size_t sizes[15] = {
         b * kHidden * 2, b * kHidden * 2, b * kHidden * 2, b * kHidden * 2,         // hidden .. operator_output
         b * kQueryWidth * 2, b * kKvWidth * 2, b * kKvWidth * 2,                    // query, key, value
         b * 2 * kFfn * 2, b * kFfn * 2, r * kVocab * 2,                             // wide, activated, logits
         b * kFfn,                                                                   // fp8_input
         lfm25_splitk_workspace_elements(r) * sizeof(float), r * sizeof(uint32_t),   // partials, sampled
-        r * kHidden * 2};                                                           // head_input
+        r * kHidden * 2,                                                            // head_input
+        r * sizeof(uint32_t)};                                                      // token_order
     size_t total = 0;
-    size_t offsets[14];
-    for (int index = 0; index < 14; ++index) {
+    size_t offsets[15];
+    for (int index = 0; index < 15; ++index) {
         offsets[index] = total;
         total += (sizes[index] + 255) & ~static_cast<size_t>(255);
     }
@@ -677,11 +686,11 @@ int32_t lfm25_decode_executor_create_ragged(lfm25_blaslt* blaslt, size_t maximum
         return cuda_failure(status, "failed to allocate decode scratch");
     }
     unsigned char* base = static_cast<unsigned char*>(self->allocation);
-    void** fields[14] = {&self->hidden, &self->normalized, &self->post_operator, &self->operator_output, &self->query,
+    void** fields[15] = {&self->hidden, &self->normalized, &self->post_operator, &self->operator_output, &self->query,
                          &self->key, &self->value, &self->wide, &self->activated, &self->logits, &self->fp8_input,
                          reinterpret_cast<void**>(&self->partials), reinterpret_cast<void**>(&self->sampled),
-                         &self->head_input};
-    for (int index = 0; index < 14; ++index) {
+                         &self->head_input, reinterpret_cast<void**>(&self->token_order)};
+    for (int index = 0; index < 15; ++index) {
         *fields[index] = base + offsets[index];
     }
     *out = self;

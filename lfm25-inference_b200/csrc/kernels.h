@@ -33,8 +33,14 @@ struct AttentionLaunch {
     float eps = 0.0f;
     size_t query_token_stride = 32 * 64;   // elements between tokens of `query`
     size_t kv_token_stride = 8 * 64;       // elements between tokens of key_raw / value_raw
+    // optional permutation of the tokens: CTAs are handed out in this order (longest context first evens out the
+    // tail of the grid); nullptr = as given
+    const uint32_t* token_order = nullptr;
 };
 cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionLaunch& launch);
+// order[r] = index of the token with the r-th largest position (ties by index); at most kMaxOrderTokens tokens
+constexpr size_t kMaxOrderTokens = 2048;
+cudaError_t launch_context_order(cudaStream_t stream, const uint32_t* positions, size_t num_tokens, uint32_t* order);
 
 // Attention of a mixed prefill / decode step (hybrid_attention.cu).  `current_key` == nullptr: every key up to a
 // token's position is read from the cache; otherwise the segment's own tokens come from current_key / current_value.
@@ -135,7 +141,8 @@ cudaError_t launch_argmax_rows_bf16(cudaStream_t stream, const void* logits, uin
 cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uint32_t* positions,
                                    const uint32_t* request_slots, const uint32_t* block_tables, const uint32_t* sampled,
                                    int64_t* physical_slots, size_t num_tokens, size_t block_table_stride,
-                                   size_t block_table_rows, size_t num_pages, bool advance);
+                                   size_t block_table_rows, size_t num_pages, bool advance,
+                                   uint32_t* token_order = nullptr);
 
 bool bf16_gemm_umma_supports(size_t m, size_t n, size_t k);
 cudaError_t launch_bf16_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,

@@ -300,29 +300,68 @@ __global__ void __launch_bounds__(kRowThreads)
 decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ positions,
                        const uint32_t* __restrict__ request_slots, const uint32_t* __restrict__ block_tables,
                        const uint32_t* __restrict__ sampled, int64_t* __restrict__ physical_slots, size_t num_tokens,
-                       size_t block_table_stride, size_t block_table_rows, size_t num_pages, uint32_t advance) {
+                       size_t block_table_stride, size_t block_table_rows, size_t num_pages, uint32_t advance,
+                       uint32_t* __restrict__ token_order) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ uint32_t step_positions[kRowThreads];
     const size_t token = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (token >= num_tokens) {
-        return;
+    uint32_t position = 0;
+    if (token < num_tokens) {
+        position = positions[token];
+        if (advance) {
+            position += 1;
+            positions[token] = position;
+            token_ids[token] = sampled[token];
+        }
+        const size_t row = request_slots[token];
+        int64_t slot = -1;
+        const size_t page_index = position / kPageSize;
+        if (row < block_table_rows && page_index < block_table_stride) {
+            const uint32_t page = block_tables[row * block_table_stride + page_index];
+            if (page < num_pages) {
+                slot = static_cast<int64_t>(page) * kPageSize + position % kPageSize;
+            }
+        }
+        physical_slots[token] = slot;
     }
-    uint32_t position = positions[token];
-    if (advance) {
-        position += 1;
-        positions[token] = position;
-        token_ids[token] = sampled[token];
-    }
-    const size_t row = request_slots[token];
-    int64_t slot = -1;
-    const size_t page_index = position / kPageSize;
-    if (row < block_table_rows && page_index < block_table_stride) {
-        const uint32_t page = block_tables[row * block_table_stride + page_index];
-        if (page < num_pages) {
-            slot = static_cast<int64_t>(page) * kPageSize + position % kPageSize;
+    // Optional (single-CTA launches only): the tokens ordered by context length, longest first, for the attention
+    // kernel to hand its CTAs out in -- rank by counting, at most 256 x 256 comparisons.
+    if (token_order != nullptr && gridDim.x == 1) {
+        step_positions[threadIdx.x] = position;
+        __syncthreads();
+        if (token < num_tokens) {
+            uint32_t rank = 0;
+            for (uint32_t other = 0; other < num_tokens; ++other) {
+                const uint32_t theirs = step_positions[other];
+                rank += (theirs > position || (theirs == position && other < threadIdx.x)) ? 1u : 0u;
+            }
+            token_order[rank] = static_cast<uint32_t>(token);
         }
     }
-    physical_slots[token] = slot;
+}
+
+// order[r] = index of the token with the r-th largest position (ties: lower index first).  One CTA; the positions sit
+// in shared memory and every thread ranks its tokens by counting.
+constexpr uint32_t kOrderThreads = 1024;
+__global__ void __launch_bounds__(kOrderThreads)
+context_order_kernel(const uint32_t* __restrict__ positions, uint32_t num_tokens, uint32_t* __restrict__ order) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ uint32_t held[kMaxOrderTokens];
+    for (uint32_t token = threadIdx.x; token < num_tokens; token += blockDim.x) {
+        held[token] = positions[token];
+    }
+    __syncthreads();
+    for (uint32_t token = threadIdx.x; token < num_tokens; token += blockDim.x) {
+        const uint32_t mine = held[token];
+        uint32_t rank = 0;
+        for (uint32_t other = 0; other < num_tokens; ++other) {
+            const uint32_t theirs = held[other];
+            rank += (theirs > mine || (theirs == mine && other < token)) ? 1u : 0u;
+        }
+        order[rank] = token;
+    }
 }
 
 }  // namespace
@@ -463,9 +502,19 @@ cudaError_t launch_argmax_rows_bf16(cudaStream_t stream, const void* logits, uin
 cudaError_t launch_decode_metadata(cudaStream_t stream, uint32_t* token_ids, uint32_t* positions,
                                    const uint32_t* request_slots, const uint32_t* block_tables, const uint32_t* sampled,
                                    int64_t* physical_slots, size_t num_tokens, size_t block_table_stride,
-                                   size_t block_table_rows, size_t num_pages, bool advance) {
-    return launch_kernel(decode_metadata_kernel, static_cast<unsigned int>((num_tokens + kRowThreads - 1) / kRowThreads), kRowThreads, 0, stream, 1, token_ids, positions, request_slots, block_tables, sampled, physical_slots,
-                                       num_tokens, block_table_stride, block_table_rows, num_pages, advance ? 1u : 0u);
+                                   size_t block_table_rows, size_t num_pages, bool advance, uint32_t* token_order) {
+    const unsigned int blocks = static_cast<unsigned int>((num_tokens + kRowThreads - 1) / kRowThreads);
+    return launch_kernel(decode_metadata_kernel, blocks, kRowThreads, 0, stream, 1, token_ids, positions,
+                         request_slots, block_tables, sampled, physical_slots, num_tokens, block_table_stride,
+                         block_table_rows, num_pages, advance ? 1u : 0u, blocks == 1 ? token_order : nullptr);
+}
+
+cudaError_t launch_context_order(cudaStream_t stream, const uint32_t* positions, size_t num_tokens, uint32_t* order) {
+    if (num_tokens == 0 || num_tokens > kMaxOrderTokens) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_kernel(context_order_kernel, 1, kOrderThreads, 0, stream, 1, positions,
+                         static_cast<uint32_t>(num_tokens), order);
 }
 
 cudaError_t launch_short_conv_segmented(cudaStream_t stream, const void* projected, const void* weight, void* states,

@@ -142,13 +142,27 @@ def _validate_ragged_input(inputs: FastRaggedAttentionInput) -> int:
     return num_tokens
 
 
-def paged_ragged_attention_fast_lfm2_bf16_into(inputs: FastRaggedAttentionInput, output: torch.Tensor) -> None:
+def _order_slice(token_order, num_tokens: int) -> Slice:
+    if token_order is None:
+        return Slice(None, 0)
+    _ensure(token_order.numel() >= num_tokens, "token order shorter than the batch")
+    return _slice(token_order)
+
+
+def context_order_desc_into(position_ids: torch.Tensor, order: torch.Tensor) -> None:
+    """order[r] = index of the token with the r-th largest position: the `token_order` of the decode attention ops
+    (their CTAs then start on the longest contexts).  No counterpart in the reference."""
+    check(library().lfm25_context_order_desc(_stream(), _slice(position_ids), position_ids.numel(), _slice(order)))
+
+
+def paged_ragged_attention_fast_lfm2_bf16_into(inputs: FastRaggedAttentionInput, output: torch.Tensor,
+                                               token_order=None) -> None:
     """Reference: src/ops/attention_async_fast.rs:123-152."""
     num_tokens = _validate_ragged_input(inputs)
     launch = _abi.FastRaggedAttentionLaunch(
         inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
         _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(output),
-        num_tokens, inputs.arena.num_pages, inputs.block_table_stride)
+        num_tokens, inputs.arena.num_pages, inputs.block_table_stride, _order_slice(token_order, num_tokens))
     check(library().lfm25_paged_ragged_attention_fast_lfm2_bf16(_stream(), launch))
 
 
@@ -159,21 +173,22 @@ def paged_ragged_attention_fast_lfm2_bf16(inputs: FastRaggedAttentionInput) -> t
 
 
 def paged_ragged_attention_splitk_lfm2_bf16_into(inputs: FastRaggedAttentionInput, partials: torch.Tensor,
-                                                 num_splits: int, output: torch.Tensor) -> None:
+                                                 num_splits: int, output: torch.Tensor, token_order=None) -> None:
     """Reference: src/ops/attention_async_fast.rs:154-197."""
     _ensure(2 <= num_splits <= SPLITK_MAX_SPLITS, f"split-K attention requires 2..={SPLITK_MAX_SPLITS} splits")
     num_tokens = _validate_ragged_input(inputs)
     launch = _abi.SplitKRaggedAttentionLaunch(
         inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
         _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(partials),
-        _slice(output), num_tokens, inputs.arena.num_pages, inputs.block_table_stride, num_splits)
+        _slice(output), num_tokens, inputs.arena.num_pages, inputs.block_table_stride, num_splits,
+        _order_slice(token_order, num_tokens))
     check(library().lfm25_paged_ragged_attention_splitk_lfm2_bf16(_stream(), launch))
 
 
 def fused_ragged_paged_attention_decode_lfm2_bf16_into(query_raw, key_raw, value_raw, query_norm, key_norm, inv_freq,
                                                        position_ids, slot_mapping, arena: PagedKvArena, block_tables,
                                                        block_table_stride: int, request_slots, eps: float, output,
-                                                       partials=None, num_splits: int = 1) -> None:
+                                                       partials=None, num_splits: int = 1, token_order=None) -> None:
     """One-kernel decode: QK-norm + RoPE + paged KV append + attention
     (reference: src/ops/attention_fused.rs:95-153); optionally split over the KV axis.  The three projections may
     be row-strided views (columns of one packed [N, 3072] GEMM output); the last two dimensions must be dense."""
@@ -193,7 +208,8 @@ def fused_ragged_paged_attention_decode_lfm2_bf16_into(query_raw, key_raw, value
         _slice(inv_freq), _slice(arena.key), _slice(arena.value), _slice(position_ids), _slice(slot_mapping),
         _slice(output), num_tokens, arena.num_pages, eps, _slice(block_tables), _slice(request_slots),
         block_table_stride, _slice(partials) if partials is not None else empty, num_splits,
-        query_raw.stride(0) if num_tokens > 1 else 0, key_raw.stride(0) if num_tokens > 1 else 0)
+        query_raw.stride(0) if num_tokens > 1 else 0, key_raw.stride(0) if num_tokens > 1 else 0,
+        _order_slice(token_order, num_tokens))
     check(library().lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(_stream(), launch))
 
 
@@ -238,7 +254,7 @@ def paged_ragged_attention_splitk_static_lfm2_bf16_into(inputs: FastRaggedAttent
     launch = _abi.FastRaggedAttentionLaunch(
         inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
         _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(output),
-        num_tokens, inputs.arena.num_pages, inputs.block_table_stride)
+        num_tokens, inputs.arena.num_pages, inputs.block_table_stride, Slice(None, 0))
     check(library().lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(_stream(), launch, num_splits))
 
 

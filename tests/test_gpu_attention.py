@@ -235,3 +235,52 @@ def test_full_size_ragged_batch_properties(device):
                                                 inputs.request_slots, inputs.position_ids)
     assert np.array_equal(bits_of(ops.paged_ragged_attention_fast_lfm2_bf16(moved_inputs)), unsplit)
     assert ops.device_status()[0] == 0
+
+
+def test_context_order_is_a_stable_descending_sort(device):
+    rng = np.random.default_rng(31)
+    for count in (1, 2, 64, 257, 2048):
+        positions = rng.integers(0, 50, size=count).astype(np.uint32)        # many ties
+        order = torch.full((count,), 0x7fffffff, dtype=torch.int32, device=device)
+        ops.context_order_desc_into(to_u32(positions, device), order)
+        want = np.argsort(-positions.astype(np.int64), kind="stable")
+        assert np.array_equal(order.cpu().numpy(), want)
+    with pytest.raises(Lfm25Error):
+        ops.context_order_desc_into(torch.zeros(2049, dtype=torch.int32, device=device),
+                                    torch.zeros(2049, dtype=torch.int32, device=device))
+
+
+def test_token_order_changes_no_result(device):
+    """The optional token order only changes which CTA takes which token: outputs are bit-identical for the
+    longest-first order, for a random permutation, and without one; an entry outside the batch is a no-op."""
+    case = cases.random_ragged_case(12, 37, 5, 1500, 8192)
+    inputs = upload(case, device)
+    tokens = case["query"].shape[0]
+    plain = bits_of(ops.paged_ragged_attention_fast_lfm2_bf16(inputs))
+    longest_first = torch.zeros(tokens, dtype=torch.int32, device=device)
+    ops.context_order_desc_into(inputs.position_ids, longest_first)
+    shuffled = to_u32(np.random.default_rng(12).permutation(tokens).astype(np.uint32), device)
+    partials = torch.empty((ops.splitk_workspace_elements(tokens),), dtype=torch.float32, device=device)
+    plain_split = torch.zeros_like(inputs.query)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, partials, 4, plain_split)
+    for order in (longest_first, shuffled):
+        output = torch.zeros_like(inputs.query)
+        ops.paged_ragged_attention_fast_lfm2_bf16_into(inputs, output, token_order=order)
+        assert np.array_equal(bits_of(output), plain)
+        output = torch.zeros_like(inputs.query)
+        ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, partials, 4, output, token_order=order)
+        assert np.array_equal(bits_of(output), bits_of(plain_split))
+    # one entry points outside the batch: that group of CTAs does nothing, the token it displaced keeps the fill
+    broken = shuffled.clone()
+    victim = int(broken[5])
+    broken[5] = tokens + 3
+    output = torch.full_like(inputs.query, 7.0)
+    ops.paged_ragged_attention_fast_lfm2_bf16_into(inputs, output, token_order=broken)
+    got = bits_of(output)
+    untouched = bits_of(torch.full((1,), 7.0, dtype=torch.bfloat16))[0]
+    assert np.all(got[victim] == untouched)
+    keep = np.arange(tokens) != victim
+    assert np.array_equal(got[keep], plain[keep])
+    with pytest.raises(Lfm25Error):
+        ops.paged_ragged_attention_fast_lfm2_bf16_into(inputs, output, token_order=shuffled[:tokens - 1])
+    assert ops.device_status()[0] == 0
