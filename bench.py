@@ -70,6 +70,8 @@ def parse_arguments():
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     parser.add_argument("--requests", type=int, default=192, help="serving workload: requests in the trace")
     parser.add_argument("--rate", type=float, default=32.0, help="serving workload: Poisson arrival rate, requests/s")
+    parser.add_argument("--skip-reference-kernels", action="store_true",
+                        help="leave out the comparison runs of the reference project's own kernels")
     parser.add_argument("--admission-control", action="store_true",
                         help="serving workload: reject requests whose predicted TTFT / TPOT break the SLOs (the "
                              "reference's admission) instead of queueing them")
@@ -643,7 +645,7 @@ def run_step_arm(arguments, rank, world):
 
         # ---- the reference project's own attention kernels (rebuilt for sm_100a) on the same cache and metadata ----
         reference_kernels = None
-        if rank == 0:
+        if rank == 0 and not arguments.skip_reference_kernels:
             try:
                 from oracle import refkernels
                 if refkernels.available():

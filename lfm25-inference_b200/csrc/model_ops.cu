@@ -296,6 +296,26 @@ argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, uint32_t* __restric
 // (src/model/lfm2_base.rs:371-378), or -1 when the request slot, the position or the table entry is not valid
 // (the append kernels skip negative slots).  With `advance` the kernel first moves every sequence on by one
 // token: token id <- the id sampled by the previous step, position <- position + 1.  No host round trip.
+// How many entries of `held` come before (`mine`, `index`) in descending order of value, ties by index.  `held` is
+// 16-byte aligned and padded with zeros up to a multiple of four entries: a zero behind the batch is never larger
+// than a value and never has a smaller index, so it is not counted.
+__device__ __forceinline__ uint32_t rank_descending(const uint32_t* held, uint32_t count, uint32_t index,
+                                                    uint32_t mine) {
+    uint32_t rank = 0;
+    const uint4* quads = reinterpret_cast<const uint4*>(held);
+    const uint32_t groups = (count + 3) / 4;
+#pragma unroll 4
+    for (uint32_t group = 0; group < groups; ++group) {
+        const uint4 q = quads[group];
+        const uint32_t base = group * 4;
+        rank += (q.x > mine || (q.x == mine && base + 0 < index)) ? 1u : 0u;
+        rank += (q.y > mine || (q.y == mine && base + 1 < index)) ? 1u : 0u;
+        rank += (q.z > mine || (q.z == mine && base + 2 < index)) ? 1u : 0u;
+        rank += (q.w > mine || (q.w == mine && base + 3 < index)) ? 1u : 0u;
+    }
+    return rank;
+}
+
 __global__ void __launch_bounds__(kRowThreads)
 decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ positions,
                        const uint32_t* __restrict__ request_slots, const uint32_t* __restrict__ block_tables,
@@ -304,7 +324,7 @@ decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ 
                        uint32_t* __restrict__ token_order) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ uint32_t step_positions[kRowThreads];
+    __shared__ __align__(16) uint32_t step_positions[kRowThreads];
     const size_t token = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     uint32_t position = 0;
     if (token < num_tokens) {
@@ -328,15 +348,11 @@ decode_metadata_kernel(uint32_t* __restrict__ token_ids, uint32_t* __restrict__ 
     // Optional (single-CTA launches only): the tokens ordered by context length, longest first, for the attention
     // kernel to hand its CTAs out in -- rank by counting, at most 256 x 256 comparisons.
     if (token_order != nullptr && gridDim.x == 1) {
-        step_positions[threadIdx.x] = position;
+        step_positions[threadIdx.x] = position;      // 0 beyond the batch: never counted (see rank_descending)
         __syncthreads();
         if (token < num_tokens) {
-            uint32_t rank = 0;
-            for (uint32_t other = 0; other < num_tokens; ++other) {
-                const uint32_t theirs = step_positions[other];
-                rank += (theirs > position || (theirs == position && other < threadIdx.x)) ? 1u : 0u;
-            }
-            token_order[rank] = static_cast<uint32_t>(token);
+            token_order[rank_descending(step_positions, static_cast<uint32_t>(num_tokens), threadIdx.x, position)] =
+                static_cast<uint32_t>(token);
         }
     }
 }
@@ -348,19 +364,13 @@ __global__ void __launch_bounds__(kOrderThreads)
 context_order_kernel(const uint32_t* __restrict__ positions, uint32_t num_tokens, uint32_t* __restrict__ order) {
     pdl_launch_dependents();
     pdl_wait();
-    __shared__ uint32_t held[kMaxOrderTokens];
-    for (uint32_t token = threadIdx.x; token < num_tokens; token += blockDim.x) {
-        held[token] = positions[token];
+    __shared__ __align__(16) uint32_t held[kMaxOrderTokens];
+    for (uint32_t token = threadIdx.x; token < ((num_tokens + 3) & ~3u); token += blockDim.x) {
+        held[token] = token < num_tokens ? positions[token] : 0u;
     }
     __syncthreads();
     for (uint32_t token = threadIdx.x; token < num_tokens; token += blockDim.x) {
-        const uint32_t mine = held[token];
-        uint32_t rank = 0;
-        for (uint32_t other = 0; other < num_tokens; ++other) {
-            const uint32_t theirs = held[other];
-            rank += (theirs > mine || (theirs == mine && other < token)) ? 1u : 0u;
-        }
-        order[rank] = token;
+        order[rank_descending(held, num_tokens, token, held[token])] = token;
     }
 }
 
