@@ -55,9 +55,11 @@ struct lfm25_decode_executor {
     // around every op of an eager step, summed per region
     bool profiling = false;
     std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> marks;
-    // captured step, one per batch size
+    // captured steps: one per (batch size, attention split count, flags, buffers); a serving loop walks through many
+    // batch sizes, so the table is large and the least recently used entry is recycled
     struct Captured {
         size_t num_tokens = 0;
+        size_t splits = 0;
         uint32_t use_fp8 = 0;
         uint32_t advance = 0;
         const void* model_layers = nullptr;
@@ -65,7 +67,9 @@ struct lfm25_decode_executor {
         bool warmed = false;
         cudaGraphExec_t exec = nullptr;
         size_t kernel_nodes = 0;
-    } captured[8];
+        uint64_t last_used = 0;
+    } captured[96];
+    uint64_t graph_clock = 0;
     size_t last_graph_kernel_nodes = 0;   // of the graph launched most recently
 };
 
@@ -807,35 +811,40 @@ int32_t lfm25_decode_executor_forward_ragged(lfm25_decode_executor* self, const 
 int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm25_model* model,
                                          const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance) {
     LFM25_TRY(validate(self, model, batch));
+    // the split count of the attention launches is decided on the host from the longest context, so it is part of
+    // what a captured step is valid for
+    const size_t splits = lfm25_splitk_decode_splits(batch->num_tokens, batch->max_context_tokens, 16);
     lfm25_decode_executor::Captured* entry = nullptr;
     for (auto& candidate : self->captured) {
-        if (candidate.num_tokens == batch->num_tokens && candidate.use_fp8 == use_fp8 &&
+        if (candidate.num_tokens == batch->num_tokens && candidate.splits == splits && candidate.use_fp8 == use_fp8 &&
             candidate.advance == advance && candidate.model_layers == model->layers && candidate.token_ids == batch->token_ids) {
             entry = &candidate;
             break;
         }
     }
     if (entry == nullptr) {
-        // take a free entry, or recycle the first one
+        // take a free entry, or recycle the least recently used one
         for (auto& candidate : self->captured) {
             if (candidate.num_tokens == 0) {
                 entry = &candidate;
                 break;
             }
-        }
-        if (entry == nullptr) {
-            entry = &self->captured[0];
-            if (entry->exec != nullptr) {
-                cudaGraphExecDestroy(entry->exec);
+            if (entry == nullptr || candidate.last_used < entry->last_used) {
+                entry = &candidate;
             }
+        }
+        if (entry->exec != nullptr) {
+            cudaGraphExecDestroy(entry->exec);
         }
         *entry = lfm25_decode_executor::Captured();
         entry->num_tokens = batch->num_tokens;
+        entry->splits = splits;
         entry->use_fp8 = use_fp8;
         entry->advance = advance;
         entry->model_layers = model->layers;
         entry->token_ids = batch->token_ids;
     }
+    entry->last_used = ++self->graph_clock;
     cudaStream_t stream = self->blaslt->stream;
     if (stream == nullptr || stream == cudaStreamLegacy) {
         return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT,

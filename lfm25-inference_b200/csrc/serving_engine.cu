@@ -87,6 +87,7 @@ struct lfm25_engine {
     uint32_t* h_sampled = nullptr;   // pinned
     size_t meta_words = 0;
     bool tables_dirty = true;
+    bool graph_decode = true;        // LFM25_ENGINE_GRAPH=0: pure decode steps launch eagerly
     cudaEvent_t start = nullptr;
     cudaEvent_t stop = nullptr;
     lfm25_engine_stats stats{};
@@ -169,6 +170,11 @@ int32_t enqueue_step(lfm25_engine* self, const StepShape& shape) {
         batch.block_table_rows = self->config.max_slots;
         batch.num_tokens = tokens;
         batch.max_context_tokens = decode_context;
+        // a pure decode step replays the captured step of its batch size (the first two steps of a size run eagerly
+        // and capture); the metadata was uploaded above, so the step does not advance it on the device
+        if (self->graph_decode) {
+            return lfm25_decode_executor_step_graph(self->executor, self->model, &batch, self->config.use_fp8, 0);
+        }
         return lfm25_decode_executor_forward(self->executor, self->model, &batch, self->config.use_fp8, 0);
     }
     lfm25_ragged_batch batch;
@@ -385,6 +391,13 @@ int32_t lfm25_engine_create(lfm25_blaslt* blaslt, const lfm25_model* model, cons
     self->config = *config;
     self->pages_per_slot = (config->max_sequence_tokens + kPage - 1) / kPage;
     self->max_tokens = config->max_slots + config->max_prefill_tokens;
+    {
+        // graph replay needs a stream of its own (capture is not possible on the legacy default stream)
+        const char* graph_switch = getenv("LFM25_ENGINE_GRAPH");
+        cudaStream_t bound = static_cast<cudaStream_t>(lfm25_blaslt_stream(blaslt));
+        self->graph_decode = (graph_switch == nullptr || strcmp(graph_switch, "0") != 0) && bound != nullptr &&
+                             bound != cudaStreamLegacy;
+    }
     for (uint32_t layer = 0; layer < model->num_layers; ++layer) {
         if (!model->layers[layer].is_attention) self->conv_layers.push_back(layer);
     }
@@ -461,6 +474,14 @@ int32_t lfm25_engine_calibrate(lfm25_engine* self) {
             return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "calibrate needs an idle engine");
         }
     }
+    // the curves are measured with eager launches: a first replay would put the capture inside the timed step
+    const bool graph_decode = self->graph_decode;
+    self->graph_decode = false;
+    struct Restore {
+        lfm25_engine* engine;
+        bool value;
+        ~Restore() { engine->graph_decode = value; }
+    } restore{self, graph_decode};
     std::vector<lfm25_cost_point> decode_points;
     std::vector<lfm25_cost_point> prefill_points;
     std::vector<uint32_t> table(self->config.max_slots * self->pages_per_slot);
