@@ -620,14 +620,24 @@ size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_toke
     if (num_tokens == 0 || page_size != 16) {
         return 1;
     }
-    // A B200 keeps 148 SMs x 3 CTAs = 444 (token, KV head, split) items resident.  Split until
-    // about four waves of items exist (measured on 64 ragged sequences: 1/2/4/8 splits give
-    // 109/103/96/96 us), but never below 8 pages (128 tokens) per split.
+    // A B200 keeps 148 SMs x 3 CTAs = 444 (token, KV head, split) items resident, and the callers hand the CTAs out
+    // longest context first, so a little more than one wave of items is enough.  Measured on the full decode step
+    // (contexts 128..4096, splits -> ms per step): 8 sequences 2/4/8 -> 0.766/0.727/0.725; 16: 2/4/8 ->
+    // 0.788/0.750/0.782; 32: 1/2/4/8 -> 0.943/0.874/0.883/0.925; 48: 1/2/4 -> 1.002/0.957/0.992; 64: 1/2/4 ->
+    // 1.050/1.030/1.066; 96: 1/2 -> 1.197/1.229; 128: 1/2/3/4 -> 1.336/1.377/1.404/1.441.  With contexts up to 8192
+    // (64 sequences, attention alone, 1/2/4/8 -> 113/100/99/105 us) one more doubling pays.  Never below 8 pages
+    // (128 tokens) per split.
+    if (const char* forced = getenv("LFM25_DECODE_SPLITS")) {      // tuning override: 1..8
+        const long value = atol(forced);
+        if (value >= 1 && value <= 8) return static_cast<size_t>(value);
+    }
     const size_t pages = (maximum_context_tokens + page_size - 1) / page_size;
-    const size_t base_items = num_tokens * 8;
-    size_t splits = 1;
-    while (splits < 8 && base_items * splits < 1776 && pages / (splits * 2) >= 8) {
-        splits *= 2;
+    size_t splits = num_tokens <= 8 ? 8 : (num_tokens <= 24 ? 4 : (num_tokens <= 80 ? 2 : 1));
+    if (num_tokens > 24 && num_tokens <= 80 && maximum_context_tokens > 6144) {
+        splits = 4;
+    }
+    while (splits > 1 && pages / splits < 8) {
+        splits /= 2;
     }
     return splits;
 }

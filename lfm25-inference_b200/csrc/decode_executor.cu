@@ -445,6 +445,16 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                                              tokens, kHidden, model->norm_eps);
         if (status != cudaSuccess) return cuda_failure(status, "rms_norm launch failed");
     }
+    // the leading decode tokens go through the decode attention kernel: order them longest context first, once per
+    // step, for all attention layers
+    const size_t leading_decodes = batch->num_decode_segments;
+    const bool decodes_ordered = leading_decodes > 1 && leading_decodes <= lfm25::kMaxOrderTokens &&
+                                 leading_decodes <= self->maximum_rows;
+    if (decodes_ordered) {
+        RegionTimer timer(self, LFM25_REGION_OTHER);
+        status = lfm25::launch_context_order(stream, batch->positions, leading_decodes, self->token_order);
+        if (status != cudaSuccess) return cuda_failure(status, "context order launch failed");
+    }
     for (uint32_t index = 0; index < model->num_layers; ++index) {
         const lfm25_layer& layer = model->layers[index];
         if (!layer.is_attention) {
@@ -505,7 +515,8 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                 decode.num_pages = model->num_pages;
                 decode.block_table_stride = batch->block_table_stride;
                 decode.num_splits = splits;
-                decode.token_order = slice_of(nullptr, 0);
+                decode.token_order = slice_of(decodes_ordered ? self->token_order : nullptr,
+                                              decodes_ordered ? decode_tokens : 0);
                 if (splits > 1) {
                     LFM25_TRY(lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &decode));
                 } else {
@@ -521,7 +532,7 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                     unsplit.num_tokens = decode_tokens;
                     unsplit.num_pages = model->num_pages;
                     unsplit.block_table_stride = batch->block_table_stride;
-                    unsplit.token_order = slice_of(nullptr, 0);
+                    unsplit.token_order = decode.token_order;
                     LFM25_TRY(lfm25_paged_ragged_attention_fast_lfm2_bf16(stream, &unsplit));
                 }
             }

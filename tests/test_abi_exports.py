@@ -135,9 +135,13 @@ def test_workspace_and_split_policy():
     assert splits(0, 8192, 16) == 1            # src/ops/splitk_policy.rs:20-22
     assert splits(1, 100, 16) == 1             # short contexts never split
     assert splits(1, 8192, 16) == 8            # one long sequence: as many splits as allowed
-    assert splits(64, 8192, 16) == 4           # 512 items: two doublings reach four waves of resident CTAs
-    assert splits(128, 4096, 16) == 2
+    assert splits(64, 8192, 16) == 4           # 512 items of up to 8192 tokens: four splits
+    assert splits(64, 4096, 16) == 2
+    assert splits(32, 4096, 16) == 2
+    assert splits(16, 4096, 16) == 4
+    assert splits(128, 4096, 16) == 1          # 1024 items, handed out longest first: no split
     assert splits(256, 8192, 16) == 1          # enough items without splitting
+    assert splits(8, 256, 16) == 2             # never below 8 pages per split
     assert splits(4, 8192, 32) == 1            # page size 32 is not built
     for tokens in (1, 2, 8, 16, 32, 64, 128):
         for context in (16, 512, 2048, 8192):
