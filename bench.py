@@ -676,10 +676,9 @@ def run_step_arm(arguments, rank, world):
         d2h_bytes = host_sampled.numel() * host_sampled.element_size()
 
         def served_step():
-            device_batch.step_metadata.copy_(host_block, non_blocking=True)     # one upload per step
-            executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=False)
-            executor.download_sampled(host_sampled)
-            stream.synchronize()                   # the serving loop needs the ids (EOS, streaming) before it goes on
+            # upload of the metadata block, replay of the captured step, download of the ids and the synchronisation
+            # the serving loop needs (EOS, streaming) before it goes on: one call into the library
+            executor.serve_step(model, device_batch, host_block, host_sampled, use_fp8=use_fp8)
             host_meta["token_ids"].copy_(host_sampled)
             host_meta["positions"] += 1
 

@@ -504,6 +504,14 @@ int32_t lfm25_decode_executor_forward_ragged(lfm25_decode_executor* executor, co
  * launches ~170 kernels and synchronises the host every step (src/engine/serving/radix_owner.rs:230-259). */
 int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* executor, const lfm25_model* model,
                                          const lfm25_decode_batch* batch, uint32_t use_fp8, uint32_t advance);
+/* One decode step as a serving loop runs it, in one call: uploads the step's metadata from pinned host memory
+ * (`host_metadata`: token ids | positions | request slots, 3 * num_tokens u32; one copy when the batch's three device
+ * arrays are adjacent in that order, three copies otherwise), replays the captured step (advance = 0), downloads the
+ * sampled ids to `host_sampled` (num_tokens u32, pinned) and synchronises the stream: the sequence of
+ * src/engine/serving/radix_owner.rs:230-259 (update_segments, forward, enqueue_sampled_download, synchronise). */
+int32_t lfm25_decode_executor_serve_step(lfm25_decode_executor* executor, const lfm25_model* model,
+                                         const lfm25_decode_batch* batch, uint32_t use_fp8,
+                                         const uint32_t* host_metadata, uint32_t* host_sampled);
 /* Kernel nodes of the CUDA graph that the last lfm25_decode_executor_step_graph call replayed (0 before the first
  * replay): the number of GPU kernels one step launches, this library's and cuBLASLt's together. */
 size_t lfm25_decode_executor_graph_kernels(const lfm25_decode_executor* executor);

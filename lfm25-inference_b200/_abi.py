@@ -242,6 +242,9 @@ PROTOTYPES = {
         ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
     "lfm25_decode_executor_step_graph": (
         ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
+    "lfm25_decode_executor_serve_step": (
+        ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_void_p,
+                         ctypes.c_void_p]),
     "lfm25_decode_executor_profile": (
         ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint32, _P(ctypes.c_float), _P(ctypes.c_uint32)]),
     "lfm25_decode_executor_download_sampled": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_void_p, _size]),

@@ -903,6 +903,38 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
     return LFM25_OK;
 }
 
+int32_t lfm25_decode_executor_serve_step(lfm25_decode_executor* self, const lfm25_model* model,
+                                         const lfm25_decode_batch* batch, uint32_t use_fp8,
+                                         const uint32_t* host_metadata, uint32_t* host_sampled) {
+    LFM25_TRY(validate(self, model, batch));
+    if (host_metadata == nullptr || host_sampled == nullptr) {
+        return lfm25::report_error(LFM25_ERR_NULL_POINTER, "served step received a null host buffer");
+    }
+    cudaStream_t stream = self->blaslt->stream;
+    const size_t tokens = batch->num_tokens;
+    const size_t bytes = tokens * sizeof(uint32_t);
+    cudaError_t status;
+    if (batch->positions == batch->token_ids + tokens && batch->request_slots == batch->positions + tokens) {
+        status = cudaMemcpyAsync(batch->token_ids, host_metadata, 3 * bytes, cudaMemcpyHostToDevice, stream);
+    } else {
+        status = cudaMemcpyAsync(batch->token_ids, host_metadata, bytes, cudaMemcpyHostToDevice, stream);
+        if (status == cudaSuccess) {
+            status = cudaMemcpyAsync(batch->positions, host_metadata + tokens, bytes, cudaMemcpyHostToDevice, stream);
+        }
+        if (status == cudaSuccess) {
+            status = cudaMemcpyAsync(const_cast<uint32_t*>(batch->request_slots), host_metadata + 2 * tokens, bytes,
+                                     cudaMemcpyHostToDevice, stream);
+        }
+    }
+    if (status != cudaSuccess) return cuda_failure(status, "step metadata upload failed");
+    LFM25_TRY(lfm25_decode_executor_step_graph(self, model, batch, use_fp8, 0));
+    status = cudaMemcpyAsync(host_sampled, self->sampled, bytes, cudaMemcpyDeviceToHost, stream);
+    if (status == cudaSuccess) {
+        status = cudaStreamSynchronize(stream);
+    }
+    return status == cudaSuccess ? LFM25_OK : cuda_failure(status, "served step failed");
+}
+
 size_t lfm25_decode_executor_graph_kernels(const lfm25_decode_executor* self) {
     return self != nullptr ? self->last_graph_kernel_nodes : 0;
 }

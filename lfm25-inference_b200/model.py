@@ -269,6 +269,19 @@ class DecodeExecutor:
         check(library().lfm25_decode_executor_step_graph(self._handle, model.struct, batch.struct, int(use_fp8),
                                                          int(advance)))
 
+    def serve_step(self, model: RandomModel, batch: DecodeBatch, host_metadata: torch.Tensor,
+                   host_sampled: torch.Tensor, use_fp8: bool = True) -> None:
+        """One served step in one call: `host_metadata` (pinned int32 [3 * tokens]: token ids | positions | request
+        slots) goes to the device, the captured step replays, the sampled ids land in `host_sampled` (pinned int32
+        [tokens]) and the stream is synchronised (src/engine/serving/radix_owner.rs:230-259)."""
+        if not (host_metadata.is_pinned() and host_sampled.is_pinned()):
+            raise ValueError("served step needs pinned host buffers")
+        if host_metadata.numel() < 3 * batch.num_tokens or host_sampled.numel() < batch.num_tokens:
+            raise ValueError("served step host buffers are too small")
+        self.blaslt.bind_current_stream()
+        check(library().lfm25_decode_executor_serve_step(self._handle, model.struct, batch.struct, int(use_fp8),
+                                                         host_metadata.data_ptr(), host_sampled.data_ptr()))
+
     def graph_kernels(self) -> int:
         """GPU kernels per step in the graph that the last step_graph call replayed (0 before the first replay)."""
         return int(library().lfm25_decode_executor_graph_kernels(self._handle))

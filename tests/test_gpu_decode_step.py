@@ -162,3 +162,39 @@ def test_one_step_against_the_reference_kernels(device, use_fp8):
     assert ops.device_status()[0] == 0
     executor.close()
     blaslt.close()
+
+
+def test_served_step_equals_upload_replay_download(device):
+    """lfm25_decode_executor_serve_step is upload + captured step + download + synchronise in one call."""
+    tokens, pages, steps = 6, 64, 4
+    batch, token_ids = small_batch(device, 21, tokens, pages, steps)
+
+    def run(served):
+        with torch.cuda.stream(torch.cuda.Stream()):
+            model = lfm_model.RandomModel(5, device, pages, 8)
+            model.fill_caches(6)
+            blaslt = ops.BlasLt()
+            executor = lfm_model.DecodeExecutor(blaslt, 8)
+            device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0),
+                                                 token_ids, int(batch.contexts.max()) + steps + 1)
+            host_block = device_batch.step_metadata.cpu().pin_memory()
+            host_sampled = torch.zeros(tokens, dtype=torch.int32).pin_memory()
+            history = []
+            for _ in range(steps):
+                if served:
+                    executor.serve_step(model, device_batch, host_block, host_sampled)
+                else:
+                    device_batch.step_metadata.copy_(host_block, non_blocking=True)
+                    executor.forward(model, device_batch, use_fp8=True, advance=False)
+                    executor.download_sampled(host_sampled)
+                    torch.cuda.current_stream().synchronize()
+                history.append(host_sampled.numpy().copy())
+                host_block[:tokens].copy_(host_sampled)
+                host_block[tokens:2 * tokens] += 1
+            executor.close()
+            blaslt.close()
+            return history
+
+    for a, b in zip(run(False), run(True)):
+        assert np.array_equal(a, b)
+    assert ops.device_status()[0] == 0
