@@ -58,6 +58,26 @@ const char* lfm25_version(void);
  */
 int32_t lfm25_device_status(void* stream, uint32_t out[4]);
 
+/*
+ * Process-wide switches, in the place of the reference's environment-driven feature toggles
+ * (LFM25_* variables read in src/model/lfm2_base.rs and src/engine/serving/radix_owner.rs).  Each switch has a
+ * default, may be preset by the environment variable LFM25_<NAME> (read once) and changed at run time here; a
+ * change applies to launches issued afterwards and is not recorded in CUDA graphs that are already captured.
+ *   pdl, fused_append, fused_silu, kv_evict_first, engine_graph        0 | 1 (default 1)
+ *   fused_silu_bf16        0 | 1 (default 0): SiLU * Up in the epilogue of a BF16 Gate/Up linear as well
+ *   hybrid_attention       0 auto | 1 umma | 2 mma
+ *   fp8_gemm_path          0 auto | 1 stream | 2 umma (weight-major) | 3 generic | 4 rows (batch-major)
+ *   bf16_gemm              0 auto | 1 umma (weight-major) | 2 cublaslt | 3 rows (batch-major)
+ *   decode_splits          0 auto | 1..8
+ *   wait_limit_ns          limit of every bounded device-side wait, default 1000000000
+ *   wait_selftest_drop     0 | 1: a self-test of the bounded waits -- kernels with a TMA ring arm one barrier
+ *                          whose copy they never issue, so that the wait runs out after wait_limit_ns; the kernel
+ *                          then records the event (lfm25_device_status), stores nothing and returns normally
+ * Unknown names and values out of range are refused with LFM25_ERR_INVALID_ARGUMENT.
+ */
+int32_t lfm25_set_option(const char* name, int64_t value);
+int32_t lfm25_get_option(const char* name, int64_t* value);
+
 /* ------------------------------------------------------------------------------------------
  * Paged KV append
  * ------------------------------------------------------------------------------------------ */
@@ -328,10 +348,47 @@ int32_t lfm25_blaslt_linear_fp8_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lf
                                          lfm25_slice activation, const lfm25_fp8_linear_config* config,
                                          float activation_scale, uint32_t e4m3_output);
 /* Replaces BlasLt::linear_bf16 (src/cuda/blaslt/mod.rs:113-186): out[M,N] = x[M,K] * weight[N,K]^T in bf16 with
- * fp32 accumulation, through cuBLASLt (opened lazily; plans cached per shape), as the reference does for the
+ * fp32 accumulation.  This library's tcgen05 kernels take the call where they measured ahead on the decode step;
+ * elsewhere it goes through cuBLASLt (opened lazily; plans cached per shape), as the reference does for the
  * sites that are not promoted to FP8. */
 int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out, size_t m,
                                  size_t n, size_t k);
+/* The BF16 packed Gate/Up linear with the gated activation in its epilogue, for the layers whose Gate/Up site is
+ * not promoted to FP8: linear_decode_into + silu_mul_packed_bf16_into (or ..._to_e4m3_into when `e4m3_output` is
+ * set, for an FP8 Down site) of the decode step in one launch (src/model/decode_executor.rs:378-402,
+ * kernels/silu_mul.cu:13-133).  `weight` [n = 2 * intermediate, k] bf16 with the gate rows first, `activation`
+ * [m, intermediate]; same bits as the two-launch route.  LFM25_ERR_UNSUPPORTED outside the tensor-core kernel
+ * (m <= 256, intermediate % 8 == 0, k % 64 == 0, 16-byte aligned buffers). */
+int32_t lfm25_blaslt_linear_bf16_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight,
+                                          lfm25_slice activation, size_t m, size_t n, size_t k,
+                                          float activation_scale, uint32_t e4m3_output);
+
+/* Kernel and tile choice of the linears of one handle, in the place of the algorithm selection a cuBLASLt caller
+ * has (cublasLtMatmulAlgoGetHeuristic in src/cuda/blaslt/plan.rs): every field 0 = the library's choice.
+ * `kernel`: 1 weight-streaming mma.sync kernel (E4M3, M <= 8), 2 weight-major tcgen05 kernel, 3 generic kernel
+ * (E4M3) / cuBLASLt (BF16), 4 batch-major tcgen05 kernel.  The other fields apply to the batch-major kernel:
+ * weight rows per CTA (a multiple of 16 up to 256), K splits (1..8), ring slots (<= 12), warps that issue
+ * tcgen05.mma (1, 2 or 4), CTAs per SM the tile count is fitted to (1 or 2), shared-memory budget per CTA in bytes,
+ * batch slices (1..8 CTAs that share a weight tile, each with a part of the batch rows).
+ * A choice the shape does not allow is ignored.  Passing NULL restores the defaults.  bench.py --workload gemm
+ * uses it to sweep. */
+typedef struct lfm25_gemm_tuning {
+    uint32_t kernel;
+    uint32_t n_tile;
+    uint32_t splits;
+    uint32_t stages;
+    uint32_t issuers;
+    uint32_t ctas_per_sm;
+    uint32_t shared_memory_bytes;
+    uint32_t batch_slices;
+} lfm25_gemm_tuning;
+int32_t lfm25_blaslt_set_gemm_tuning(lfm25_blaslt* handle, const lfm25_gemm_tuning* tuning);
+/* What the batch-major kernel would launch for a problem under the handle's tuning (the counterpart of reading back
+ * a cuBLASLt heuristic result): out = {n_tile, K splits, tiles, ring slots, issuing warps, CTAs per SM,
+ * shared-memory bytes per CTA, batch slices}.  `k_bytes` is the row length in bytes (K for E4M3, 2 K for BF16); for
+ * the gated form `n` is the intermediate width.  Launches nothing. */
+int32_t lfm25_blaslt_gemm_plan(const lfm25_blaslt* handle, size_t m, size_t n, size_t k_bytes, uint32_t gated,
+                               uint32_t out[8]);
 
 /* ------------------------------------------------------------------------------------------
  * Remaining ops of the decode step
@@ -497,7 +554,8 @@ int32_t lfm25_decode_executor_create_ragged(lfm25_blaslt* blaslt, size_t maximum
  * reference does above its maximum FP8 batch. */
 int32_t lfm25_decode_executor_forward_ragged(lfm25_decode_executor* executor, const lfm25_model* model,
                                              const lfm25_ragged_batch* batch, uint32_t use_fp8);
-/* The same step replayed from a CUDA graph captured per (batch size, model, batch buffers, flags): the first call
+/* The same step replayed from a CUDA graph captured per (batch size, flags, every value the step bakes in -- see
+ * lfm25_decode_executor_graph_captures): the first call
  * of a bucket runs eagerly, the second captures, later ones only launch the graph.  With advance != 0 the step
  * feeds itself (ids and positions move on the device); with advance == 0 the caller refreshes the metadata
  * buffers between steps.  The handle must be bound to a non-default stream.  No counterpart in the reference, which
@@ -515,6 +573,11 @@ int32_t lfm25_decode_executor_serve_step(lfm25_decode_executor* executor, const 
 /* Kernel nodes of the CUDA graph that the last lfm25_decode_executor_step_graph call replayed (0 before the first
  * replay): the number of GPU kernels one step launches, this library's and cuBLASLt's together. */
 size_t lfm25_decode_executor_graph_kernels(const lfm25_decode_executor* executor);
+/* How many steps this executor has captured so far.  A captured step is replayed only while everything it baked in
+ * is unchanged: batch size, split count, flags, every pointer, stride and row count of the batch, the model's page
+ * count and every pointer, shape and scale inside model->layers, the library's switches and the handle's stream and
+ * tuning; any change makes the next call run eagerly once and capture again. */
+size_t lfm25_decode_executor_graph_captures(const lfm25_decode_executor* executor);
 /* Opt-in region timing of eager steps (the reference's ModelProfileRecorder, src/model/profile.rs:84-253): while
  * enabled, every op of lfm25_decode_executor_forward is bracketed by CUDA events.  A call with region_ms != NULL
  * synchronises, returns the milliseconds and op counts accumulated per region since the last collection, and then

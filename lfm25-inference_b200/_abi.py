@@ -73,6 +73,16 @@ class Fp8LinearConfig(ctypes.Structure):
                 ("scale_mode", ctypes.c_uint32), ("output_scale", ctypes.c_float)]
 
 
+class GemmTuning(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_uint32), ("n_tile", ctypes.c_uint32), ("splits", ctypes.c_uint32),
+                ("stages", ctypes.c_uint32), ("issuers", ctypes.c_uint32),
+                ("ctas_per_sm", ctypes.c_uint32), ("shared_memory_bytes", ctypes.c_uint32),
+                ("batch_slices", ctypes.c_uint32)]
+
+
+GEMM_KERNEL_AUTO, GEMM_KERNEL_STREAM, GEMM_KERNEL_WEIGHT_MAJOR, GEMM_KERNEL_LIBRARY, GEMM_KERNEL_BATCH_MAJOR = range(5)
+
+
 class DecodeBatch(ctypes.Structure):
     _fields_ = [("token_ids", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("request_slots", ctypes.c_void_p),
                 ("physical_slots", ctypes.c_void_p), ("block_tables", ctypes.c_void_p),
@@ -218,6 +228,13 @@ PROTOTYPES = {
     "lfm25_blaslt_linear_fp8_silu_mul": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _P(Fp8LinearConfig),
                                                           ctypes.c_float, ctypes.c_uint32]),
     "lfm25_blaslt_linear_bf16": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _size, _size, _size]),
+    "lfm25_blaslt_linear_bf16_silu_mul": (ctypes.c_int32, [ctypes.c_void_p, Slice, Slice, Slice, _size, _size, _size,
+                                                           ctypes.c_float, ctypes.c_uint32]),
+    "lfm25_blaslt_set_gemm_tuning": (ctypes.c_int32, [ctypes.c_void_p, _P(GemmTuning)]),
+    "lfm25_blaslt_gemm_plan": (ctypes.c_int32, [ctypes.c_void_p, _size, _size, _size, ctypes.c_uint32,
+                                                _P(ctypes.c_uint32)]),
+    "lfm25_set_option": (ctypes.c_int32, [ctypes.c_char_p, ctypes.c_int64]),
+    "lfm25_get_option": (ctypes.c_int32, [ctypes.c_char_p, _P(ctypes.c_int64)]),
     "lfm25_embedding_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, _size]),
     "lfm25_rms_norm_bf16": (ctypes.c_int32, [_stream, Slice, Slice, Slice, _size, _size, ctypes.c_float]),
     "lfm25_residual_rms_norm_bf16": (
@@ -238,6 +255,7 @@ PROTOTYPES = {
         ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(RaggedBatch), ctypes.c_uint32]),
     "lfm25_decode_executor_destroy": (None, [ctypes.c_void_p]),
     "lfm25_decode_executor_graph_kernels": (ctypes.c_size_t, [ctypes.c_void_p]),
+    "lfm25_decode_executor_graph_captures": (ctypes.c_size_t, [ctypes.c_void_p]),
     "lfm25_decode_executor_forward": (
         ctypes.c_int32, [ctypes.c_void_p, _P(Model), _P(DecodeBatch), ctypes.c_uint32, ctypes.c_uint32]),
     "lfm25_decode_executor_step_graph": (

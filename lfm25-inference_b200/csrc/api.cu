@@ -14,6 +14,7 @@
 #include "blaslt_handle.h"
 #include "common.cuh"
 #include "kernels.h"
+#include "options.h"
 
 namespace {
 
@@ -123,14 +124,18 @@ int32_t validate_ragged_common(size_t page_size, const lfm25_slice& query, const
 
 // Validation of Fp8MatmulKey::new + BlasLt::linear_fp8_scaled (src/cuda/blaslt/fp8.rs:23-40,
 // src/cuda/blaslt/mod.rs:222-262), then the choice of kernel:
-//   M <= 256, N % 128 == 0, K % 128 == 0   tcgen05 / TMEM kernel (K split over a thread-block cluster when there
-//                                          are few tiles and the caller is a handle with an exchange buffer)
+//   through a handle, N % 16 == 0, K % 128 == 0, M in the range where it measured ahead (see rows_preferred)
+//                                          batch-major tcgen05 kernel (gemm_rows_umma.cu)
+//   M <= 256, N % 128 == 0, K % 128 == 0   weight-major tcgen05 kernel (K split over a thread-block cluster when
+//                                          there are few tiles and the caller is a handle with an exchange buffer)
 //   M <= 8 otherwise, or few tiles without a handle   weight-streaming mma.sync kernel
 //   anything else                          generic kernel
-// LFM25_FP8_GEMM_PATH = stream | umma | generic overrides the choice where the shape allows (for measurements).
-// `exchange` is the split-K scratch of a BlasLt handle; the handle-free entry point passes null and never splits K.
+// The option fp8_gemm_path = stream | umma | generic | rows overrides the choice where the shape allows.
+// `handle` is null for the handle-free entry point, which has no exchange buffer and never splits K.
 int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
-                            const lfm25_fp8_linear_config* config, void* exchange, size_t exchange_bytes) {
+                            const lfm25_fp8_linear_config* config, const lfm25_blaslt* handle) {
+    void* exchange = handle != nullptr ? handle->exchange : nullptr;
+    const size_t exchange_bytes = handle != nullptr ? handle->exchange_bytes : 0;
     LFM25_ENSURE(config != nullptr, LFM25_ERR_NULL_POINTER, "FP8 linear config is null");
     const size_t m = config->m;
     const size_t n = config->n;
@@ -171,19 +176,29 @@ int32_t linear_fp8_dispatch(cudaStream_t stream, lfm25_slice x, lfm25_slice weig
     // (LM head at M = 1: 24.1 against 29.2 us), i.e. with at least 100 weight tiles or with an exchange buffer to
     // split K through; without either (few tiles, handle-free call) small batches stay on the streaming kernel.
     const bool umma_occupies = umma_ok && (n / 128 >= 100 || exchange != nullptr);
-    enum { kStream, kUmma, kGeneric } path = kGeneric;
-    if (umma_occupies || (umma_ok && !(stream_ok && m <= 8))) {
+    const bool rows_ok = aligned && lfm25::gemm_rows_supports(m, n, k);
+    enum { kStream, kUmma, kGeneric, kRows } path = kGeneric;
+    if (rows_ok && handle != nullptr && lfm25::fp8_rows_preferred(m, n, k)) {
+        path = kRows;
+    } else if (umma_occupies || (umma_ok && !(stream_ok && m <= 8))) {
         path = kUmma;
     } else if (stream_ok) {
         path = kStream;
     }
-    if (const char* forced = getenv("LFM25_FP8_GEMM_PATH")) {
-        if (strcmp(forced, "stream") == 0 && stream_ok) path = kStream;
-        if (strcmp(forced, "umma") == 0 && umma_ok) path = kUmma;
-        if (strcmp(forced, "generic") == 0) path = kGeneric;
-    }
+    const int64_t forced = handle != nullptr && handle->tuning_kernel != 0 ? handle->tuning_kernel
+                                                                           : lfm25::option(lfm25::kOptFp8GemmPath);
+    if (forced == lfm25::kPathStream && stream_ok) path = kStream;
+    if (forced == lfm25::kPathUmma && umma_ok) path = kUmma;
+    if (forced == lfm25::kPathGeneric) path = kGeneric;
+    if (forced == lfm25::kPathRows && rows_ok) path = kRows;
     cudaError_t status;
-    if (path == kStream) {
+    if (path == kRows) {
+        unsigned int* status_words = device_status_pointer();
+        LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+        status = lfm25::launch_fp8_gemm_rows(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale,
+                                             exchange, exchange_bytes, status_words,
+                                             handle != nullptr ? handle->tuning : lfm25::GemmRowsTuning());
+    } else if (path == kStream) {
         status = lfm25::launch_fp8_gemm_stream(stream, x.ptr, weight.ptr, out.ptr, m, n, k, config->output_scale);
     } else if (path == kUmma) {
         unsigned int* status_words = device_status_pointer();
@@ -593,12 +608,12 @@ int32_t lfm25_hybrid_ragged_attention_lfm2_bf16(void* stream, const lfm25_hybrid
     LFM25_ENSURE(args.status != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
     // Two kernels: tcgen05 / TMEM with 32 tokens x 4 heads per CTA (191 us per layer on eight 512-token chunks) and
     // mma.sync with 16 tokens per CTA (326 us there, but less padding on short segments).  The tcgen05 kernel takes
-    // the step when its segments average at least 16 tokens; LFM25_HYBRID_ATTENTION = umma | mma forces one.
-    const char* choice = getenv("LFM25_HYBRID_ATTENTION");
+    // the step when its segments average at least 16 tokens; the option hybrid_attention = umma | mma forces one.
+    const int64_t choice = lfm25::option(lfm25::kOptHybridAttention);
     const bool umma_possible = (reinterpret_cast<uintptr_t>(l.query.ptr) & 15) == 0 && query_stride % 8 == 0;
     bool use_umma = l.num_tokens >= 16 * l.num_segments;
-    if (choice != nullptr && strcmp(choice, "umma") == 0) use_umma = true;
-    if (choice != nullptr && strcmp(choice, "mma") == 0) use_umma = false;
+    if (choice == 1) use_umma = true;
+    if (choice == 2) use_umma = false;
     if (use_umma && umma_possible) {
         return cuda_result(lfm25::launch_hybrid_attention_umma(static_cast<cudaStream_t>(stream), args),
                            "hybrid ragged attention launch failed");
@@ -627,9 +642,9 @@ size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_toke
     // 1.050/1.030/1.066; 96: 1/2 -> 1.197/1.229; 128: 1/2/3/4 -> 1.336/1.377/1.404/1.441.  With contexts up to 8192
     // (64 sequences, attention alone, 1/2/4/8 -> 113/100/99/105 us) one more doubling pays.  Never below 8 pages
     // (128 tokens) per split.
-    if (const char* forced = getenv("LFM25_DECODE_SPLITS")) {      // tuning override: 1..8
-        const long value = atol(forced);
-        if (value >= 1 && value <= 8) return static_cast<size_t>(value);
+    const int64_t forced = lfm25::option(lfm25::kOptDecodeSplits);   // 0 = by the table below
+    if (forced >= 1 && forced <= 8) {
+        return static_cast<size_t>(forced);
     }
     const size_t pages = (maximum_context_tokens + page_size - 1) / page_size;
     size_t splits = num_tokens <= 8 ? 8 : (num_tokens <= 24 ? 4 : (num_tokens <= 80 ? 2 : 1));
@@ -889,7 +904,7 @@ int32_t lfm25_decode_step_metadata(void* stream, const lfm25_decode_batch* batch
 
 int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                 const lfm25_fp8_linear_config* config) {
-    return linear_fp8_dispatch(static_cast<cudaStream_t>(stream), x, weight, out, config, nullptr, 0);
+    return linear_fp8_dispatch(static_cast<cudaStream_t>(stream), x, weight, out, config, nullptr);
 }
 
 int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out) {
@@ -952,20 +967,37 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
     LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear weight storage too small");
     LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear output storage too small");
     LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "linear received a null device pointer");
-    // Batches of up to 32 rows go to this library's tcgen05 kernel where it supports the shape (N % 128 == 0,
-    // K % 64 == 0): with programmatic dependent launch and the weight prefetch it is ahead of cuBLASLt there
-    // (measured on the whole step: 12 % at 1 row, 8 % at 8 rows, 2 % at 32 rows), and behind it at 128 rows.
-    // LFM25_BF16_GEMM = umma | cublaslt forces one of the two (for measurements).
-    const char* bf16_path = getenv("LFM25_BF16_GEMM");
+    // Which kernel: this library's tcgen05 kernels where they measured ahead of cuBLASLt on the step (the
+    // weight-major one up to 32 rows where N % 128 == 0 and K % 64 == 0, the batch-major one where
+    // bf16_rows_preferred says so), cuBLASLt otherwise, as the reference does.  The option bf16_gemm (or the
+    // handle's tuning) = umma | cublaslt | rows forces one.
     const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
                            reinterpret_cast<uintptr_t>(out.ptr)) &
                           15) == 0;
-    bool own_kernel = m <= 32;
-    if (bf16_path != nullptr && strcmp(bf16_path, "umma") == 0) own_kernel = true;
-    if (bf16_path != nullptr && strcmp(bf16_path, "cublaslt") == 0) own_kernel = false;
-    if (own_kernel && aligned && lfm25::bf16_gemm_umma_supports(m, n, k)) {
+    const bool umma_ok = aligned && lfm25::bf16_gemm_umma_supports(m, n, k);
+    const bool rows_ok = aligned && lfm25::gemm_rows_supports(m, n, k * 2);
+    enum { kLibrary, kUmma, kRows } path = kLibrary;
+    if (rows_ok && lfm25::bf16_rows_preferred(m, n, k)) {
+        path = kRows;
+    } else if (umma_ok && m <= 32) {
+        path = kUmma;
+    }
+    int64_t forced = lfm25::option(lfm25::kOptBf16Gemm);
+    if (handle->tuning_kernel == lfm25::kPathUmma) forced = lfm25::kBf16Umma;
+    if (handle->tuning_kernel == lfm25::kPathRows) forced = lfm25::kBf16Rows;
+    if (handle->tuning_kernel == lfm25::kPathGeneric) forced = lfm25::kBf16CublasLt;
+    if (forced == lfm25::kBf16Umma && umma_ok) path = kUmma;
+    if (forced == lfm25::kBf16Rows && rows_ok) path = kRows;
+    if (forced == lfm25::kBf16CublasLt) path = kLibrary;
+    if (path != kLibrary) {
         unsigned int* status_words = device_status_pointer();
         LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+        if (path == kRows) {
+            return cuda_result(
+                lfm25::launch_bf16_gemm_rows(handle->stream, x.ptr, weight.ptr, out.ptr, m, n, k, handle->exchange,
+                                             handle->exchange_bytes, status_words, handle->tuning),
+                "BF16 linear launch failed");
+        }
         return cuda_result(
             lfm25::launch_bf16_gemm_umma(handle->stream, x.ptr, weight.ptr, out.ptr, m, n, k, handle->exchange,
                                          handle->exchange_bytes, status_words),
@@ -980,10 +1012,87 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
         "cuBLASLt BF16 matmul failed");
 }
 
+int32_t lfm25_blaslt_set_gemm_tuning(lfm25_blaslt* handle, const lfm25_gemm_tuning* tuning) {
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
+    if (tuning == nullptr) {
+        handle->tuning_kernel = 0;
+        handle->tuning = lfm25::GemmRowsTuning();
+        return LFM25_OK;
+    }
+    LFM25_ENSURE(tuning->kernel <= 4, LFM25_ERR_INVALID_ARGUMENT, "unknown GEMM kernel %u", tuning->kernel);
+    LFM25_ENSURE(tuning->n_tile % 16 == 0 && tuning->n_tile <= 256, LFM25_ERR_INVALID_ARGUMENT,
+                 "n_tile must be a multiple of 16 up to 256, got %u", tuning->n_tile);
+    LFM25_ENSURE(tuning->splits <= 8 && tuning->stages <= 12 && tuning->ctas_per_sm <= 2 && tuning->batch_slices <= 8 &&
+                     (tuning->issuers == 0 || tuning->issuers == 1 || tuning->issuers == 2 || tuning->issuers == 4),
+                 LFM25_ERR_INVALID_ARGUMENT, "GEMM tuning value out of range");
+    handle->tuning_kernel = tuning->kernel;
+    handle->tuning.n_tile = tuning->n_tile;
+    handle->tuning.splits = tuning->splits;
+    handle->tuning.stages = tuning->stages;
+    handle->tuning.issuers = tuning->issuers;
+    handle->tuning.slices = tuning->batch_slices;
+    handle->tuning.ctas_per_sm = tuning->ctas_per_sm;
+    handle->tuning.smem_bytes = tuning->shared_memory_bytes;
+    return LFM25_OK;
+}
+
+int32_t lfm25_blaslt_gemm_plan(const lfm25_blaslt* handle, size_t m, size_t n, size_t k_bytes, uint32_t gated,
+                               uint32_t out[8]) {
+    LFM25_ENSURE(handle != nullptr && out != nullptr, LFM25_ERR_NULL_POINTER, "GEMM plan query received a null argument");
+    LFM25_ENSURE(lfm25::gemm_rows_supports(m, gated != 0 ? 2 * n : n, k_bytes), LFM25_ERR_UNSUPPORTED,
+                 "shape outside the batch-major kernel");
+    const lfm25::GemmRowsPlan plan =
+        lfm25::gemm_rows_plan(m, n, k_bytes, gated != 0, handle->exchange_bytes, handle->tuning);
+    LFM25_ENSURE(plan.valid, LFM25_ERR_UNSUPPORTED, "no valid plan for this shape and tuning");
+    out[0] = plan.n_tile;
+    out[1] = plan.splits;
+    out[2] = plan.tiles;
+    out[3] = plan.stages;
+    out[4] = plan.issuers;
+    out[5] = plan.ctas_per_sm;
+    out[6] = plan.smem_bytes;
+    out[7] = plan.slices;
+    return LFM25_OK;
+}
+
+int32_t lfm25_blaslt_linear_bf16_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight,
+                                          lfm25_slice activation, size_t m, size_t n, size_t k,
+                                          float activation_scale, uint32_t e4m3_output) {
+    LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
+    LFM25_ENSURE(m > 0 && n > 0 && k > 0, LFM25_ERR_INVALID_ARGUMENT, "gated BF16 linear is empty");
+    LFM25_ENSURE(n % 2 == 0, LFM25_ERR_INVALID_ARGUMENT, "packed Gate/Up width must be even, got %zu", n);
+    LFM25_ENSURE(std::isfinite(activation_scale) && activation_scale > 0.0f, LFM25_ERR_INVALID_ARGUMENT,
+                 "activation scale must be finite and positive");
+    size_t x_required = 0;
+    size_t weight_required = 0;
+    size_t out_required = 0;
+    LFM25_ENSURE(checked_mul(m, k, &x_required) && checked_mul(n, k, &weight_required) &&
+                     checked_mul(m, n / 2, &out_required),
+                 LFM25_ERR_OVERFLOW, "gated BF16 linear size overflow");
+    LFM25_ENSURE(x.len >= x_required, LFM25_ERR_BUFFER_TOO_SMALL, "gated BF16 linear input storage too small");
+    LFM25_ENSURE(weight.len >= weight_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "gated BF16 linear weight storage too small");
+    LFM25_ENSURE(activation.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                 "gated BF16 linear output storage too small");
+    LFM25_ENSURE(x.ptr && weight.ptr && activation.ptr, LFM25_ERR_NULL_POINTER,
+                 "gated BF16 linear received a null device pointer");
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
+                           reinterpret_cast<uintptr_t>(activation.ptr)) &
+                          15) == 0;
+    LFM25_ENSURE(aligned && (n / 2) % 8 == 0 && lfm25::gemm_rows_supports(m, n, k * 2), LFM25_ERR_UNSUPPORTED,
+                 "gated BF16 linear: shape or alignment outside the tensor-core kernel");
+    unsigned int* status_words = device_status_pointer();
+    LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    return cuda_result(
+        lfm25::launch_bf16_gemm_rows_gated(handle->stream, x.ptr, weight.ptr, activation.ptr, m, n / 2, k,
+                                           activation_scale, e4m3_output != 0, status_words, handle->tuning),
+        "gated BF16 linear launch failed");
+}
+
 int32_t lfm25_blaslt_linear_fp8_scaled(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                        const lfm25_fp8_linear_config* config) {
     LFM25_ENSURE(handle != nullptr, LFM25_ERR_NULL_POINTER, "BlasLt handle is null");
-    return linear_fp8_dispatch(handle->stream, x, weight, out, config, handle->exchange, handle->exchange_bytes);
+    return linear_fp8_dispatch(handle->stream, x, weight, out, config, handle);
 }
 
 int32_t lfm25_blaslt_linear_fp8_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight,
@@ -1020,10 +1129,23 @@ int32_t lfm25_blaslt_linear_fp8_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lf
     const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
                            reinterpret_cast<uintptr_t>(activation.ptr)) &
                           15) == 0;
-    LFM25_ENSURE(aligned && lfm25::fp8_gemm_umma_gated_supports(m, n, k), LFM25_ERR_UNSUPPORTED,
-                 "gated FP8 linear: shape or alignment outside the tensor-core kernel");
+    const bool umma_ok = aligned && lfm25::fp8_gemm_umma_gated_supports(m, n, k);
+    const bool rows_ok = aligned && (n / 2) % 8 == 0 && lfm25::gemm_rows_supports(m, n, k);
+    LFM25_ENSURE(umma_ok || rows_ok, LFM25_ERR_UNSUPPORTED,
+                 "gated FP8 linear: shape or alignment outside the tensor-core kernels");
     unsigned int* status_words = device_status_pointer();
     LFM25_ENSURE(status_words != nullptr, LFM25_ERR_CUDA, "device status words are not reachable");
+    bool use_rows = rows_ok && (!umma_ok || lfm25::fp8_gated_rows_preferred(m, n / 2, k));
+    const int64_t forced = handle->tuning_kernel != 0 ? handle->tuning_kernel : lfm25::option(lfm25::kOptFp8GemmPath);
+    if (forced == lfm25::kPathRows && rows_ok) use_rows = true;
+    if (forced == lfm25::kPathUmma && umma_ok) use_rows = false;
+    if (use_rows) {
+        return cuda_result(
+            lfm25::launch_fp8_gemm_rows_gated(handle->stream, x.ptr, weight.ptr, activation.ptr, m, n / 2, k,
+                                              config->output_scale, activation_scale, e4m3_output != 0, status_words,
+                                              handle->tuning),
+            "gated FP8 linear launch failed");
+    }
     return cuda_result(lfm25::launch_fp8_gemm_umma_gated(handle->stream, x.ptr, weight.ptr, activation.ptr, m, n, k,
                                                          config->output_scale, activation_scale, e4m3_output != 0,
                                                          status_words),

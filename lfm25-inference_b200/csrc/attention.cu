@@ -22,6 +22,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.h"
+#include "options.h"
 #include "qk_norm_rope.cuh"
 #include "tensor_map.h"
 
@@ -64,6 +65,8 @@ struct AttentionParams {
     __nv_bfloat16* value_cache;
     float eps;
     uint32_t kv_evict_first;  // nonzero: the K/V page loads carry the L2 evict-first hint
+    uint32_t selftest_drop;   // self-test of the bounded wait: warp 0 arms its first barrier and issues no copy for it
+    uint64_t wait_limit_ns;   // limit of every mbarrier wait
     const uint32_t* token_order;  // optional permutation: which token the r-th group of CTAs takes
 };
 
@@ -164,6 +167,7 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     // every page is read by exactly one warp of one CTA in a step: mark the stream as the first to leave L2, so
     // that it does not displace the weights that the step's GEMMs have had fetched ahead
     const uint64_t stream_policy = l2_evict_first_policy();
+    bool dropped = false;
     auto issue = [&](uint32_t stage, uint32_t entry) {
         if (entry >= p.num_pages) {
             // An unassigned or out-of-range page: keep the pipeline uniform by reading page 0,
@@ -175,6 +179,10 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         const uint32_t bar = bars + stage * 8;
         const uint32_t dst = ring + stage * kStageBytes;
         mbar_arrive_expect_tx(bar, kStageBytes);
+        if (p.selftest_drop != 0 && warp == 0 && !dropped) {
+            dropped = true;   // nothing will complete this barrier: the wait below has to run out
+            return;
+        }
         if (p.kv_evict_first != 0) {
             tma_load_2d_hint(dst, &key_map, bar, 0, row, stream_policy);
             tma_load_2d_hint(dst + kPageTileBytes, &value_map, bar, 0, row, stream_policy);
@@ -318,7 +326,7 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         const uint32_t stage = iteration % kStages;
         const uint32_t parity = (iteration / kStages) & 1;
         const uint32_t bar = bars + stage * 8;
-        const bool ready = mbar_wait_bounded(bar, parity);
+        const bool ready = mbar_wait_bounded(bar, parity, p.wait_limit_ns);
         if (!__all_sync(0xffffffffu, ready)) {
             timed_out = true;
             failed_iteration = iteration;
@@ -424,7 +432,7 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         // shared memory is released, then report and discard the result.
         for (uint32_t pending = failed_iteration; pending < my_pages && pending < failed_iteration + kStages;
              ++pending) {
-            (void)mbar_wait_bounded(bars + (pending % kStages) * 8, (pending / kStages) & 1);
+            (void)mbar_wait_bounded(bars + (pending % kStages) * 8, (pending / kStages) & 1, p.wait_limit_ns);
         }
         if (lane == 0) {
             record_wait_timeout(p.status, kTagAttention, blockIdx.x);
@@ -573,11 +581,9 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.key_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(launch.key_cache));
     params.value_cache = static_cast<__nv_bfloat16*>(const_cast<void*>(launch.value_cache));
     params.eps = launch.eps;
-    static const bool evict_first = [] {
-        const char* value = getenv("LFM25_KV_EVICT_FIRST");      // on unless set to 0
-        return value == nullptr || strcmp(value, "0") != 0;
-    }();
-    params.kv_evict_first = evict_first ? 1 : 0;
+    params.kv_evict_first = option(kOptKvEvictFirst) != 0 ? 1 : 0;
+    params.wait_limit_ns = wait_limit_ns();
+    params.selftest_drop = wait_selftest_drop() ? 1 : 0;
     params.token_order = launch.token_order;
     const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
     cudaError_t status = launch_kernel(kernel, static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream, 1,

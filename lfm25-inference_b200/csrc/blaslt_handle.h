@@ -5,6 +5,9 @@
 
 #include <cuda_runtime.h>
 #include <stddef.h>
+#include <stdint.h>
+
+#include "kernels.h"
 
 namespace lfm25 {
 struct CublasLtBf16;
@@ -22,4 +25,8 @@ struct lfm25_blaslt {
     void* exchange;                 // split-K partial tiles of the tcgen05 GEMM; one stream at a time
     size_t exchange_bytes;
     lfm25::CublasLtBf16* cublaslt;  // null until the first BF16 linear
+    // lfm25_blaslt_set_gemm_tuning: which kernel the linears of this handle take (0 = the library's choice; the
+    // values of lfm25::GemmPath) and the tile parameters of the batch-major kernel (0 = the library's choice)
+    int64_t tuning_kernel = 0;
+    lfm25::GemmRowsTuning tuning;
 };

@@ -27,7 +27,13 @@ constexpr uint32_t kPageTileBytes = kPageSize * kHeadDim * 2;  // 2048
 // trapping or spinning for ever; the host reads the words with lfm25_device_status().  The
 // words live in one translation unit (api.cu); kernels receive their device address.
 //   [0] number of waits that ran out   [1] kernel tag of the last one   [2] detail (stage / item)
-enum StatusTag : uint32_t { kTagAttention = 1, kTagGemmStream = 2, kTagGemmUmma = 3, kTagHybridAttention = 4 };
+enum StatusTag : uint32_t {
+    kTagAttention = 1,
+    kTagGemmStream = 2,
+    kTagGemmUmma = 3,
+    kTagHybridAttention = 4,
+    kTagGemmRows = 5
+};
 __device__ __forceinline__ void record_wait_timeout(unsigned int* status, uint32_t tag, uint32_t detail) {
     atomicAdd(&status[0], 1u);
     status[1] = tag;
@@ -89,27 +95,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return done != 0;
 }
 
-// Waits for a phase of an mbarrier for at most about one second of wall time.  Returns false when
-// the limit is reached (the caller records the failure and unwinds); it never spins without bound.
+// Waits for a phase of an mbarrier for at most about `limit_ns` of wall time (one second unless the host set another
+// limit, see wait_limit_ns() in options.h).  Returns false when the limit is reached (the caller records the
+// failure and unwinds); it never spins without bound.  The bound is kept on the SM's cycle counter, which is cheap
+// to read (a wait that misses its first probe must not pay for a slow timer before it probes again): the SM clock
+// never exceeds 2 GHz, so 2 * limit_ns cycles last at least limit_ns and at most a few times longer.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
-__device__ __forceinline__ uint64_t global_timer_ns() {
-    uint64_t now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    return now;
-}
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) {
         return true;
     }
-    const uint64_t start = global_timer_ns();
+    const long long start = clock64();
+    const long long limit_cycles = static_cast<long long>(limit_ns) * 2;
     for (;;) {
 #pragma unroll 1
-        for (uint32_t spin = 0; spin < 64; ++spin) {
+        for (uint32_t spin = 0; spin < 32; ++spin) {
             if (mbar_try_wait(bar, parity)) {
                 return true;
             }
         }
-        if (global_timer_ns() - start > kWaitLimitNs) {
+        if (clock64() - start > limit_cycles) {
             return false;
         }
     }

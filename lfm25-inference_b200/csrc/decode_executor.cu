@@ -19,6 +19,7 @@
 #include "../../include/lfm25_b200.h"
 #include "blaslt_handle.h"
 #include "kernels.h"
+#include "options.h"
 
 namespace {
 
@@ -62,8 +63,7 @@ struct lfm25_decode_executor {
         size_t splits = 0;
         uint32_t use_fp8 = 0;
         uint32_t advance = 0;
-        const void* model_layers = nullptr;
-        const void* token_ids = nullptr;
+        uint64_t signature = 0;   // of everything else the graph bakes in, see step_signature()
         bool warmed = false;
         cudaGraphExec_t exec = nullptr;
         size_t kernel_nodes = 0;
@@ -71,6 +71,7 @@ struct lfm25_decode_executor {
     } captured[96];
     uint64_t graph_clock = 0;
     size_t last_graph_kernel_nodes = 0;   // of the graph launched most recently
+    size_t graph_captures = 0;            // captures made so far
 };
 
 namespace {
@@ -93,6 +94,88 @@ struct RegionTimer {
         }
     }
 };
+
+// A captured step bakes in every kernel argument: all pointers of the batch (token ids, positions, slots, block
+// tables, their stride and row count), the page count inside the TMA tensor maps, and every weight, norm, state and
+// cache pointer, shape and scale of the model -- the contents of model->layers, not just its address.  The
+// signature hashes all of them (and the switches that change which kernels a step launches), so a caller who
+// regrows a block table, resizes the pool or swaps weights under the same array gets a fresh capture instead of a
+// replay of stale arguments.
+struct Fnv1a {
+    uint64_t state = 1469598103934665603ull;
+    void word(uint64_t value) { state = (state ^ value) * 1099511628211ull; }
+    template <typename Value>
+    void add(const Value& value) {   // values of up to 8 bytes are mixed in one step, longer ones word by word
+        static_assert(sizeof(Value) % 4 == 0, "hashed fields are 4-byte multiples");
+        const unsigned char* cursor = reinterpret_cast<const unsigned char*>(&value);
+        for (size_t offset = 0; offset < sizeof(Value); offset += 4) {
+            uint32_t part;
+            memcpy(&part, cursor + offset, 4);
+            word(part);
+        }
+    }
+    void linear(const lfm25_linear_weights& weights) {
+        add(weights.bf16);
+        add(weights.fp8.data);
+        add(weights.fp8.activation_quantize);
+        add(weights.fp8.activation_dequantize);
+        add(weights.fp8.weight_dequantize);
+        add(weights.n);
+        add(weights.k);
+    }
+};
+
+uint64_t step_signature(const lfm25_decode_executor* self, const lfm25_model* model, const lfm25_decode_batch* batch) {
+    Fnv1a hash;
+    hash.add(batch->token_ids);
+    hash.add(batch->positions);
+    hash.add(batch->request_slots);
+    hash.add(batch->physical_slots);
+    hash.add(batch->block_tables);
+    hash.add(batch->block_table_stride);
+    hash.add(batch->block_table_rows);
+    hash.add(model->num_layers);
+    hash.add(model->layers);
+    hash.add(model->embedding);
+    hash.add(model->lm_head_fp8.data);
+    hash.add(model->lm_head_fp8.activation_quantize);
+    hash.add(model->lm_head_fp8.activation_dequantize);
+    hash.add(model->lm_head_fp8.weight_dequantize);
+    hash.add(model->final_norm);
+    hash.add(model->inv_freq);
+    hash.add(model->norm_eps);
+    hash.add(model->num_pages);
+    hash.add(model->num_request_slots);
+    for (uint32_t index = 0; index < model->num_layers; ++index) {
+        const lfm25_layer& layer = model->layers[index];
+        hash.add(layer.is_attention);
+        hash.add(layer.operator_norm);
+        hash.add(layer.ffn_norm);
+        hash.linear(layer.conv_input);
+        hash.add(layer.conv_kernel);
+        hash.linear(layer.conv_output);
+        hash.add(layer.conv_state);
+        hash.linear(layer.query);
+        hash.linear(layer.key);
+        hash.linear(layer.value);
+        hash.linear(layer.output);
+        hash.add(layer.query_norm);
+        hash.add(layer.key_norm);
+        hash.add(layer.key_cache);
+        hash.add(layer.value_cache);
+        hash.linear(layer.gate_up);
+        hash.linear(layer.down);
+    }
+    for (int which = 0; which < lfm25::kOptCount; ++which) {
+        if (which != lfm25::kOptEngineGraph) {
+            hash.add(lfm25::option(static_cast<lfm25::Option>(which)));
+        }
+    }
+    hash.add(self->blaslt->tuning_kernel);
+    hash.add(self->blaslt->tuning);
+    hash.add(self->blaslt->stream);
+    return hash.state;
+}
 
 int32_t cuda_failure(cudaError_t status, const char* what) {
     char message[200];
@@ -179,8 +262,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             LFM25_TRY(linear_decode(self, layer.conv_output, self->post_operator, self->operator_output, tokens,
                                     use_fp8));
         } else {
-            const char* fused_switch = getenv("LFM25_FUSED_APPEND");
-            const bool fused_append = fused_switch == nullptr || strcmp(fused_switch, "0") != 0;
+            const bool fused_append = lfm25::option(lfm25::kOptFusedAppend) != 0;
             // One GEMM for the three projections when their BF16 matrices are adjacent in memory (q | k | v rows of
             // one [3072, 2048] allocation): the outputs then sit side by side in `wide`, [tokens, 3072], which only
             // the one-kernel attention reads (it takes token strides).
@@ -312,10 +394,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
 
         // An FP8 Gate/Up whose shape the tensor-core kernel takes runs with SiLU(gate) * up in its epilogue: the
         // packed projection is never written, and the activation arrives as the Down site's E4M3 codes or as bf16.
-        static const bool fuse_gate = [] {
-            const char* value = getenv("LFM25_FUSED_SILU");
-            return value == nullptr || strcmp(value, "0") != 0;
-        }();
+        const bool fuse_gate = lfm25::option(lfm25::kOptFusedSilu) != 0;
         const bool down_fp8 = use_fp8 && layer.down.fp8.data != nullptr;
         bool gate_fused = false;
         if (fuse_gate && gate_up_fp8 && layer.gate_up.n == 2 * kFfn && (down_fp8 || layer.down.bf16 != nullptr)) {
@@ -332,6 +411,21 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 self->blaslt, slice_of(self->fp8_input, tokens * kHidden),
                 slice_of(layer.gate_up.fp8.data, 2 * kFfn * kHidden),
                 slice_of(self->activated, down_fp8 ? tokens * kFfn * 2 : tokens * kFfn), &config,
+                down_fp8 ? layer.down.fp8.activation_quantize : 1.0f, down_fp8 ? 1u : 0u);
+            if (rc == LFM25_OK) {
+                gate_fused = true;
+            } else if (rc != LFM25_ERR_UNSUPPORTED) {
+                return rc;
+            }
+        }
+        if (!gate_fused && fuse_gate && !gate_up_fp8 && layer.gate_up.bf16 != nullptr && layer.gate_up.n == 2 * kFfn &&
+            layer.gate_up.k == kHidden && (down_fp8 || layer.down.bf16 != nullptr) &&
+            lfm25::option(lfm25::kOptFusedSiluBf16) != 0) {
+            // the same fusion for a Gate/Up site that stays in BF16 (batch-major tcgen05 kernel)
+            RegionTimer timer(self, LFM25_REGION_BF16_LINEAR);
+            const int32_t rc = lfm25_blaslt_linear_bf16_silu_mul(
+                self->blaslt, slice_of(self->normalized, tokens * kHidden), slice_of(layer.gate_up.bf16, 2 * kFfn * kHidden),
+                slice_of(self->activated, down_fp8 ? tokens * kFfn * 2 : tokens * kFfn), tokens, 2 * kFfn, kHidden,
                 down_fp8 ? layer.down.fp8.activation_quantize : 1.0f, down_fp8 ? 1u : 0u);
             if (rc == LFM25_OK) {
                 gate_fused = true;
@@ -825,10 +919,11 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
     // the split count of the attention launches is decided on the host from the longest context, so it is part of
     // what a captured step is valid for
     const size_t splits = lfm25_splitk_decode_splits(batch->num_tokens, batch->max_context_tokens, 16);
+    const uint64_t signature = step_signature(self, model, batch);
     lfm25_decode_executor::Captured* entry = nullptr;
     for (auto& candidate : self->captured) {
         if (candidate.num_tokens == batch->num_tokens && candidate.splits == splits && candidate.use_fp8 == use_fp8 &&
-            candidate.advance == advance && candidate.model_layers == model->layers && candidate.token_ids == batch->token_ids) {
+            candidate.advance == advance && candidate.signature == signature) {
             entry = &candidate;
             break;
         }
@@ -852,8 +947,7 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
         entry->splits = splits;
         entry->use_fp8 = use_fp8;
         entry->advance = advance;
-        entry->model_layers = model->layers;
-        entry->token_ids = batch->token_ids;
+        entry->signature = signature;
     }
     entry->last_used = ++self->graph_clock;
     cudaStream_t stream = self->blaslt->stream;
@@ -896,6 +990,7 @@ int32_t lfm25_decode_executor_step_graph(lfm25_decode_executor* self, const lfm2
         status = cudaGraphInstantiate(&entry->exec, graph, 0);
         cudaGraphDestroy(graph);
         if (status != cudaSuccess) return cuda_failure(status, "graph instantiation failed");
+        ++self->graph_captures;
     }
     const cudaError_t status = cudaGraphLaunch(entry->exec, stream);
     if (status != cudaSuccess) return cuda_failure(status, "graph launch failed");
@@ -937,6 +1032,10 @@ int32_t lfm25_decode_executor_serve_step(lfm25_decode_executor* self, const lfm2
 
 size_t lfm25_decode_executor_graph_kernels(const lfm25_decode_executor* self) {
     return self != nullptr ? self->last_graph_kernel_nodes : 0;
+}
+
+size_t lfm25_decode_executor_graph_captures(const lfm25_decode_executor* self) {
+    return self != nullptr ? self->graph_captures : 0;
 }
 
 }  // extern "C"

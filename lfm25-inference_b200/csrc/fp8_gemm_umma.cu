@@ -10,7 +10,9 @@
 //            per stage a 128 x 128 B weight tile and the M_pad x 128 B activation tile of the same K block
 //   warp 1   allocates TMEM; one thread issues 4 tcgen05.mma per stage (K = 32 each) into a
 //            128-lane x M_pad-column fp32 accumulator and releases the stage with tcgen05.commit
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (thread = weight row, registers = batch columns),
+//   warp 6   a second issuer with an accumulator of its own: the two take alternate K blocks (one thread issues an
+//            MMA every ~180 cycles whatever its shape, which is 4 KiB of weights, about an SM's share of HBM)
+//   warps 2-5  epilogue: tcgen05.ld the accumulators (thread = weight row, registers = batch columns), add them,
 //            scale, round to bf16, transpose through shared memory and store 16 bytes per lane
 //
 // The op is bound by the weight stream (N*K bytes) for every batch size here, so what matters is the number
@@ -32,6 +34,7 @@
 #include "common.cuh"
 #include "kernels.h"
 #include "launch.h"
+#include "options.h"
 #include "tcgen05.cuh"
 #include "tensor_map.h"
 
@@ -42,7 +45,7 @@ namespace {
 constexpr uint32_t kTileN = 128;    // weight rows per CTA = UMMA M
 constexpr uint32_t kBlockK = 128;   // bytes of K per stage = one swizzle row
 constexpr uint32_t kUmmaK = 32;     // K of one tcgen05.mma with 8-bit operands
-constexpr uint32_t kThreads = 192;
+constexpr uint32_t kThreads = 224;    // producer, issuer, 4 epilogue warps, second issuer
 constexpr uint32_t kMaxStages = 8;
 constexpr uint32_t kSmemBudget = 200 * 1024;   // upper bound of the ring of one CTA
 constexpr uint32_t kSmemBudgetShared = 98 * 1024;  // two CTAs per SM: one drains its tile while the other streams
@@ -59,9 +62,12 @@ struct UmmaParams {
     uint32_t data_bytes;     // shared memory in front of the control block: the stages, or the parked tile
     uint32_t k_blocks;       // 128-byte K blocks in total; split s takes the s-th of `splits` near-equal ranges
     uint32_t splits;         // CTAs of a cluster that share one weight tile, each with its own K range
-    uint32_t tmem_columns;   // power of two >= max(32, m_pad)
+    uint32_t tmem_columns;   // power of two >= max(32, issuers * accumulator_columns)
+    uint32_t issuers;        // issuing warps (1 or 2): issuer i takes K blocks i, i + issuers, ... into accumulator i
+    uint32_t accumulator_columns;   // TMEM columns between the two accumulators
     float alpha;
-    uint32_t timeline_slot;  // only read by the instrumented build (LFM25_UMMA_TIMELINE)
+    uint32_t drop_block;     // self-test: the copy of this K block is armed but never issued
+    uint64_t wait_limit_ns;  // limit of every mbarrier wait
     // Gated mode (packed Gate/Up weights [2 * intermediate, K], gate rows first): a tile is 64 gate rows and the 64
     // up rows that belong to them, and the epilogue writes act = bf16(silu(bf16(gate)) * bf16(up)) -- as E4M3 codes
     // of act * gated_scale when gated_e4m3 is set -- instead of the two projections.  0 = plain GEMM.
@@ -70,27 +76,6 @@ struct UmmaParams {
     float gated_scale;
     void* gated_out;         // [m, intermediate] E4M3 codes or bf16
 };
-
-// Instrumented build only: per CTA, the SM cycle counter at the points of the kernel's critical path (and the global
-// timer at entry and exit), for the two most recent launches.  Compiled out by default.
-#ifdef LFM25_UMMA_TIMELINE
-constexpr uint32_t kTimelineCtas = 512;
-constexpr uint32_t kTimelineMarks = 10;
-__device__ unsigned long long g_umma_timeline[2][kTimelineCtas][kTimelineMarks];
-__device__ __forceinline__ void timeline_mark(const UmmaParams& p, uint32_t mark) {
-    if (blockIdx.x < kTimelineCtas) {
-        g_umma_timeline[p.timeline_slot & 1][blockIdx.x][mark] = static_cast<unsigned long long>(clock64());
-    }
-}
-__device__ __forceinline__ void timeline_global(const UmmaParams& p, uint32_t mark) {
-    if (blockIdx.x < kTimelineCtas) {
-        g_umma_timeline[p.timeline_slot & 1][blockIdx.x][mark] = global_timer_ns();
-    }
-}
-#else
-__device__ __forceinline__ void timeline_mark(const UmmaParams&, uint32_t) {}
-__device__ __forceinline__ void timeline_global(const UmmaParams&, uint32_t) {}
-#endif
 
 template <bool BF16>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
@@ -113,6 +98,23 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
             "}\n" ::"r"(tmem_d),
             "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
             : "memory");
+    }
+}
+
+// 16 consecutive columns of this thread's TMEM lane, summed over the issuers' accumulators (as fp32 bit patterns)
+__device__ __forceinline__ void load_accumulators16(uint32_t address, uint32_t issuers, uint32_t stride,
+                                                    uint32_t (&raw)[16]) {
+    if (issuers == 1) {
+        tmem_load16(address, raw);
+        return;
+    }
+    uint32_t other[16];
+    tmem_load16_nowait(address, raw);
+    tmem_load16_nowait(address + stride, other);
+    tmem_load_wait();
+#pragma unroll
+    for (uint32_t j = 0; j < 16; ++j) {
+        raw[j] = __float_as_uint(__uint_as_float(raw[j]) + __uint_as_float(other[j]));
     }
 }
 
@@ -144,11 +146,8 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
     const uint32_t bar_accumulator = bar_empty + 8 * kMaxStages;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(control + 16 * kMaxStages + 8);
     volatile uint32_t* abort_flag = tmem_slot + 1;
+    volatile uint32_t* partner_abort = tmem_slot + 2;   // set by a split-K partner that gave up
 
-    if (threadIdx.x == 0) {
-        timeline_mark(p, 0);
-        timeline_global(p, 8);
-    }
     pdl_launch_dependents();
     // K range of this split: the first (k_blocks % splits) splits take one block more
     const uint32_t k_share = p.k_blocks / p.splits;
@@ -175,8 +174,9 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             mbar_init(bar_full + 8 * stage, 1);
             mbar_init(bar_empty + 8 * stage, 1);
         }
-        mbar_init(bar_accumulator, 1);
+        mbar_init(bar_accumulator, p.issuers);
         *abort_flag = 0;
+        *partner_abort = 0;
         fence_barrier_init();
         fence_proxy_async_smem();
         // The weight tiles are constants: the first ring of them is requested right here -- before the TMEM
@@ -186,9 +186,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
         for (uint32_t block = 0; block < ahead; ++block) {
             const uint32_t bar = bar_full + 8 * block;
             mbar_arrive_expect_tx(bar, stage_bytes);
+            if (block == p.drop_block) {
+                continue;   // self-test: nothing completes this barrier, the bounded wait on it has to run out
+            }
             load_weights(smem_base + block * stage_bytes, bar, static_cast<int32_t>((k_block0 + block) * kBlockK));
         }
     }
+    __syncwarp();
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(const_cast<uint32_t*>(tmem_slot))),
@@ -200,19 +204,17 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    if (threadIdx.x == 0) timeline_mark(p, 1);
 
     if (warp == 0) {
         if (lane == 0) {
             pdl_wait();
-            timeline_mark(p, 2);
             for (uint32_t block = 0; block < ahead; ++block) {
                 tma_load_2d(smem_base + block * stage_bytes + kWeightTileBytes, &x_map, bar_full + 8 * block,
                             static_cast<int32_t>((k_block0 + block) * kBlockK), 0);
             }
             for (uint32_t block = ahead; block < k_count; ++block) {
                 const uint32_t stage = block % p.stages;
-                if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1)) {
+                if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1, p.wait_limit_ns)) {
                     *abort_flag = 1;
                     record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 1);
                     break;
@@ -225,49 +227,54 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                 tma_load_2d(dst + kWeightTileBytes, &x_map, bar, k_offset, 0);
             }
         }
-    } else if (warp == 1) {
-        if (lane == 0) {
+        __syncwarp();   // whole warps reach the CTA barriers below
+    } else if (warp == 1 || warp == 6) {
+        // One thread issues a tcgen05.mma every ~180 cycles whatever its shape, i.e. 4 KiB of weights per 180 cycles:
+        // about an SM's share of HBM and no more.  A second issuing warp with an accumulator of its own runs at the
+        // same rate beside it, so the K blocks alternate between the two (the slot count is even: a slot always
+        // belongs to the same issuer, which therefore sees every phase of its barrier).
+        const uint32_t issuer = warp == 1 ? 0u : 1u;
+        if (lane == 0 && issuer < p.issuers) {
             // instruction descriptor: D = f32, A = B = E4M3 (format 0) or BF16 (format 1), both K-major,
             // N = m_pad, M = 128
             const uint32_t formats = BF16 ? ((1u << 7) | (1u << 10)) : 0u;
             const uint32_t idesc = (1u << 4) | formats | ((p.m_pad >> 3) << 17) | ((kTileN >> 4) << 24);
+            const uint32_t accumulator = tmem_base + issuer * p.accumulator_columns;
             bool ok = true;
-            for (uint32_t block = 0; block < k_count && ok; ++block) {
+            for (uint32_t block = issuer; block < k_count; block += p.issuers) {
                 const uint32_t stage = block % p.stages;
-                if (*abort_flag || !mbar_wait_bounded(bar_full + 8 * stage, (block / p.stages) & 1)) {
+                if (!mbar_wait_bounded(bar_full + 8 * stage, (block / p.stages) & 1, p.wait_limit_ns)) {
+                    if (!*abort_flag) record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 2);
                     *abort_flag = 1;
-                    record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 2);
                     ok = false;
                     break;
                 }
-                tcgen05_fence_after();
-                if (block == 0) timeline_mark(p, 3);
                 const uint32_t a_address = smem_base + stage * stage_bytes;
                 const uint64_t a_desc = smem_descriptor(a_address);
                 const uint64_t b_desc = smem_descriptor(a_address + kWeightTileBytes);
 #pragma unroll
                 for (uint32_t step = 0; step < kBlockK / kUmmaK; ++step) {
                     // advancing 32 bytes inside the swizzle row = +2 in the (address >> 4) field
-                    umma<BF16>(tmem_base, a_desc + step * 2, b_desc + step * 2, idesc, (block | step) != 0 ? 1u : 0u);
+                    umma<BF16>(accumulator, a_desc + step * 2, b_desc + step * 2, idesc,
+                               (block != issuer || step != 0) ? 1u : 0u);
                 }
                 umma_commit(bar_empty + 8 * stage);
             }
             if (ok) {
                 umma_commit(bar_accumulator);
             }
-            timeline_mark(p, 4);
         }
+        __syncwarp();   // whole warps reach the CTA barriers below
     } else {
         // ---- epilogue: 4 warps, each owns the 32 TMEM lanes of its quadrant (warp id modulo 4) ----
         const uint32_t quadrant = warp & 3;
         pdl_wait();   // the output buffer may still be read by an earlier kernel until the dependency resolves
-        const bool ready = __all_sync(0xffffffffu, !*abort_flag && mbar_wait_bounded(bar_accumulator, 0));
+        const bool ready = __all_sync(0xffffffffu, !*abort_flag && mbar_wait_bounded(bar_accumulator, 0, p.wait_limit_ns));
         if (!ready && lane == 0) {
             *abort_flag = 1;
             record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 3);
         }
         tcgen05_fence_after();
-        if (warp == 2 && lane == 0) timeline_mark(p, 5);
         const uint32_t lane_address = tmem_base + ((quadrant * 32) << 16);
         if (gated) {
             // Rows 0-63 of the tile are gate rows, rows 64-127 the matching up rows.  Every thread rounds its row to
@@ -277,7 +284,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             if (ready) {
                 for (uint32_t column0 = 0; column0 < p.m_pad; column0 += 16) {
                     uint32_t raw[16];
-                    tmem_load16(lane_address + column0, raw);
+                    load_accumulators16(lane_address + column0, p.issuers, p.accumulator_columns, raw);
 #pragma unroll
                     for (uint32_t j = 0; j < 16; ++j) {
                         reinterpret_cast<__nv_bfloat16*>(staged + (column0 + j) * 256)[quadrant * 32 + lane] =
@@ -333,7 +340,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                 uint8_t* staged = smem + quadrant * (p.m_pad * 64);
                 for (uint32_t column0 = 0; column0 < p.m_pad; column0 += 16) {
                     uint32_t raw[16];
-                    tmem_load16(lane_address + column0, raw);
+                    load_accumulators16(lane_address + column0, p.issuers, p.accumulator_columns, raw);
 #pragma unroll
                     for (uint32_t j = 0; j < 16; ++j) {
                         reinterpret_cast<__nv_bfloat16*>(staged + (column0 + j) * 64)[lane] =
@@ -360,7 +367,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                               quadrant * 32 + lane;
                 for (uint32_t column0 = 0; column0 < p.m; column0 += 16) {
                     uint32_t raw[16];
-                    tmem_load16(lane_address + column0, raw);
+                    load_accumulators16(lane_address + column0, p.issuers, p.accumulator_columns, raw);
 #pragma unroll
                     for (uint32_t j = 0; j < 16; ++j) {
                         if (column0 + j < p.m) {
@@ -371,16 +378,24 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             }
         }
     }
-    if (warp == 2 && lane == 0) timeline_mark(p, 6);
     if (p.splits > 1) {
         // Split K, step 2 of 2: after the cluster barrier (release / acquire at cluster scope, and the partners are
         // the only readers) CTA q of the cluster finishes batch columns [q, q+1) * ceil(m / splits): it adds the
         // partials in rank order (reproducible, no atomics) and stores bf16.  A warp covers the 128 rows of one
         // column with 16-byte loads; the loads of all ranks are in flight together.
-        __syncwarp();
+        // A CTA that gave up tells its partners first (a word in each partner's shared memory), so that nobody
+        // stores a sum with a term missing.
+        __syncthreads();
+        if (threadIdx.x < p.splits && *abort_flag) {
+            uint32_t remote;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                         : "=r"(remote)
+                         : "r"(smem_u32(const_cast<uint32_t*>(partner_abort))), "r"(threadIdx.x));
+            asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(1u) : "memory");
+        }
         tcgen05_fence_before();
         cluster_sync_all();
-        if (warp >= 2 && !*abort_flag) {
+        if (warp >= 2 && warp <= 5 && !*abort_flag && !*partner_abort) {
             const uint32_t columns = (p.m + p.splits - 1) / p.splits;
             const uint32_t row4 = lane * 4;
             const float* partials = p.exchange + static_cast<size_t>(tile) * p.splits * p.m_pad * kTileN + row4;
@@ -416,10 +431,6 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
 
     tcgen05_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0) {
-        timeline_mark(p, 7);
-        timeline_global(p, 9);
-    }
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(p.tmem_columns)
                      : "memory");
@@ -517,14 +528,6 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
             }
         }
     }
-    if (const char* forced = getenv("LFM25_UMMA_SPLITS")) {      // tuning override: a split count to try as is
-        const uint32_t candidate = static_cast<uint32_t>(atoi(forced));
-        if (exchange != nullptr && candidate >= 1 && candidate <= 8 && k_blocks_total / candidate >= 2 &&
-            static_cast<size_t>(tiles) * candidate * m_pad * kTileN * 4 <= exchange_bytes &&
-            (can_share || tiles * candidate <= 148)) {
-            splits = candidate;
-        }
-    }
     const bool share_sm = can_share && (splits > 1 || tiles > 148);
     // Ring size.  Measured on the decode shapes, a deeper ring than about 98 KiB does not pay even with one CTA per
     // SM (Gate/Up at 1..32 rows: 9.9 us with 11 stages, 9.1 with 8, 8.5 with 5): a CTA that leaves half of the
@@ -535,14 +538,15 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
     if (!share_sm && 4 * stage_bytes > budget) {
         budget = 4 * stage_bytes < kSmemBudget ? 4 * stage_bytes : kSmemBudget;
     }
-    if (const char* forced = getenv("LFM25_UMMA_SMEM_KB")) {      // tuning override: ring bytes per CTA
-        const uint32_t candidate = static_cast<uint32_t>(atoi(forced)) * 1024u;
-        if (candidate >= 2 * stage_bytes && candidate <= kSmemBudget) budget = candidate;
-    }
     uint32_t stages = budget / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     const uint32_t k_blocks_least = k_blocks_total / splits;
     if (stages > k_blocks_least) stages = k_blocks_least;
+    // two issuing warps when an even ring still has four slots or more (measured: with two slots the second issuer
+    // costs more than it gives) and two accumulators fit the tensor memory that one of two CTAs on an SM may take
+    const uint32_t accumulator_columns = (m_pad + 31) / 32 * 32;
+    uint32_t issuers = (stages - stages % 2 >= 4 && 2 * accumulator_columns <= (share_sm ? 256u : 512u)) ? 2u : 1u;
+    if (issuers == 2) stages -= stages % 2;
     uint32_t data_bytes = stages * stage_bytes;
     if (data_bytes < m_pad * 256) data_bytes = m_pad * 256;   // bf16 staging of the epilogue: 4 warps x m_pad x 64 B
     const uint32_t smem_bytes = data_bytes + kControlBytes;
@@ -558,33 +562,39 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
     params.data_bytes = data_bytes;
     params.k_blocks = k_blocks_total;
     params.splits = splits;
+    params.issuers = issuers;
+    params.accumulator_columns = accumulator_columns;
     params.tmem_columns = 32;
-    while (params.tmem_columns < m_pad) params.tmem_columns *= 2;
+    while (params.tmem_columns < issuers * accumulator_columns) params.tmem_columns *= 2;
     params.alpha = alpha;
-    static uint32_t launches = 0;
-    params.timeline_slot = launches++;
+    params.drop_block = wait_selftest_drop() ? 0u : 0xffffffffu;
+    params.wait_limit_ns = wait_limit_ns();
     params.intermediate = gated != nullptr ? static_cast<uint32_t>(n / 2) : 0;
     params.gated_e4m3 = gated != nullptr && gated->e4m3 ? 1u : 0u;
     params.gated_scale = gated != nullptr ? gated->code_scale : 1.0f;
     params.gated_out = gated != nullptr ? gated->out : nullptr;
 
-    const cudaError_t attribute_status = cudaFuncSetAttribute(
-        gemm_umma_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes));
-    if (attribute_status != cudaSuccess) {
-        return attribute_status;
+    // The dynamic shared-memory limit of the kernel is set once per device to the largest size any launch uses, so
+    // that no launch depends on what an earlier one (or the occupancy query above) left behind.
+    static bool granted[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+        return cudaErrorInvalidDevice;
+    }
+    if (!granted[device]) {
+        const cudaError_t attribute_status =
+            cudaFuncSetAttribute(gemm_umma_kernel<BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemBudget + kControlBytes));
+        if (attribute_status != cudaSuccess) {
+            return attribute_status;
+        }
+        granted[device] = true;
     }
     return launch_kernel(gemm_umma_kernel<BF16>, tiles * splits, kThreads, smem_bytes, stream, splits, weight_map,
                          x_map, params);
 }
 
 }  // namespace
-
-#ifdef LFM25_UMMA_TIMELINE
-// Instrumented build only: copies the marks of the two most recent launches, [2][512][10] 64-bit words.
-extern "C" int lfm25_debug_umma_timeline(unsigned long long* host) {
-    return static_cast<int>(cudaMemcpyFromSymbol(host, g_umma_timeline, sizeof(g_umma_timeline)));
-}
-#endif
 
 cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
                                  size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,

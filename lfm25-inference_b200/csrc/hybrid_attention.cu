@@ -463,6 +463,7 @@ hybrid_ragged_attention_kernel(const __grid_constant__ CUtensorMap key_map, cons
         }
         return;
     }
+    __syncwarp();      // the producer ran its loop on one lane: whole warps reach the CTA barrier
     __syncthreads();   // producer warp: matches the barrier of the compute warps
 }
 

@@ -555,6 +555,10 @@ hybrid_attention_umma_kernel(const __grid_constant__ CUtensorMap query_map, cons
         }
     }
 
+    // the producer and MMA warps ran their loops on one lane: the warp meets again here, so that the CTA barrier
+    // below is reached by whole warps (a barrier reached by part of a warp is not defined behaviour, and it was seen
+    // to let the early lanes through before the late one arrived)
+    __syncwarp();
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 1) {

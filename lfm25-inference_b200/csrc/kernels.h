@@ -118,6 +118,46 @@ cudaError_t launch_fp8_gemm_umma(cudaStream_t stream, const void* x, const void*
                                  size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,
                                  unsigned int* status);
 
+// Batch-major tcgen05 GEMM (gemm_rows_umma.cu): the batch on the TMEM lanes, a tile of n_tile weight rows as the
+// N operand.  A tuning field that is 0 is chosen by gemm_rows_plan().
+struct GemmRowsTuning {
+    uint32_t n_tile = 0;       // weight rows per CTA, a multiple of 16 up to 256
+    uint32_t splits = 0;       // K splits (cluster size), 1..8
+    uint32_t stages = 0;       // ring slots (one 128-byte K block of activations and weights each), <= 12
+    uint32_t issuers = 0;      // warps that issue tcgen05.mma, each into an accumulator of its own: 1, 2 or 4
+    uint32_t slices = 0;       // CTAs that share a weight tile, each with 1 / slices of the batch rows: 1..8
+    uint32_t ctas_per_sm = 0;  // 1 or 2: which wave size the tile count is fitted to
+    uint32_t smem_bytes = 0;   // shared-memory budget of one CTA
+};
+struct GemmRowsPlan {
+    uint32_t n_tile, splits, tiles, a_tiles, a_rows, slices, slice_rows, stages, issuers, ctas_per_sm;
+    uint32_t stage_bytes, control_offset, smem_bytes;
+    bool valid;
+};
+// `k_bytes`: length of a weight / activation row in bytes (K for E4M3, 2 K for BF16); `n`: output features, for
+// the gated form the intermediate width
+bool gemm_rows_supports(size_t m, size_t n, size_t k_bytes);
+GemmRowsPlan gemm_rows_plan(size_t m, size_t n, size_t k_bytes, bool gated, size_t exchange_bytes,
+                            const GemmRowsTuning& tuning);
+// Where the batch-major kernel measured ahead of the other routes (the weight-major tcgen05 kernel, cuBLASLt)
+bool fp8_rows_preferred(size_t m, size_t n, size_t k);
+bool bf16_rows_preferred(size_t m, size_t n, size_t k);
+bool fp8_gated_rows_preferred(size_t m, size_t intermediate, size_t k);
+cudaError_t launch_fp8_gemm_rows(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                 size_t n, size_t k, float alpha, void* exchange, size_t exchange_bytes,
+                                 unsigned int* status, const GemmRowsTuning& tuning);
+// packed Gate/Up weights [2 * intermediate, k] (gate rows first); activation [m, intermediate] as E4M3 codes of the
+// bf16 activation times code_scale, or as bf16
+cudaError_t launch_fp8_gemm_rows_gated(cudaStream_t stream, const void* x, const void* weight, void* activation,
+                                       size_t m, size_t intermediate, size_t k, float alpha, float code_scale,
+                                       bool e4m3, unsigned int* status, const GemmRowsTuning& tuning);
+cudaError_t launch_bf16_gemm_rows(cudaStream_t stream, const void* x, const void* weight, void* out, size_t m,
+                                  size_t n, size_t k, void* exchange, size_t exchange_bytes, unsigned int* status,
+                                  const GemmRowsTuning& tuning);
+cudaError_t launch_bf16_gemm_rows_gated(cudaStream_t stream, const void* x, const void* weight, void* activation,
+                                        size_t m, size_t intermediate, size_t k, float code_scale, bool e4m3,
+                                        unsigned int* status, const GemmRowsTuning& tuning);
+
 cudaError_t launch_embedding_bf16(cudaStream_t stream, const uint32_t* token_ids, const void* table, void* out,
                                   size_t num_tokens, size_t vocab_size, size_t hidden);
 cudaError_t launch_rms_norm_bf16(cudaStream_t stream, const void* x, const void* weight, void* out, size_t rows,

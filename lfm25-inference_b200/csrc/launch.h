@@ -1,17 +1,14 @@
 // Kernel launch helper: every kernel of the library goes through cudaLaunchKernelEx with the programmatic
-// stream-serialisation attribute (see pdl_wait() in common.cuh), unless LFM25_PDL=0 is set in the environment.
+// stream-serialisation attribute (see pdl_wait() in common.cuh), unless the option `pdl` is 0.
 #pragma once
 
 #include <cuda_runtime.h>
-#include <stdlib.h>
-#include <string.h>
+
+#include "options.h"
 
 namespace lfm25 {
 
-inline bool pdl_enabled() {
-    const char* value = getenv("LFM25_PDL");
-    return value == nullptr || strcmp(value, "0") != 0;
-}
+inline bool pdl_enabled() { return option(kOptPdl) != 0; }
 
 template <typename... Parameters, typename... Arguments>
 cudaError_t launch_kernel(void (*kernel)(Parameters...), unsigned int blocks, unsigned int threads, size_t shared_bytes,

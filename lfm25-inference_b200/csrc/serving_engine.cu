@@ -22,6 +22,7 @@
 
 #include "../../include/lfm25_b200.h"
 #include "kernels.h"
+#include "options.h"
 
 namespace {
 
@@ -393,9 +394,8 @@ int32_t lfm25_engine_create(lfm25_blaslt* blaslt, const lfm25_model* model, cons
     self->max_tokens = config->max_slots + config->max_prefill_tokens;
     {
         // graph replay needs a stream of its own (capture is not possible on the legacy default stream)
-        const char* graph_switch = getenv("LFM25_ENGINE_GRAPH");
         cudaStream_t bound = static_cast<cudaStream_t>(lfm25_blaslt_stream(blaslt));
-        self->graph_decode = (graph_switch == nullptr || strcmp(graph_switch, "0") != 0) && bound != nullptr &&
+        self->graph_decode = lfm25::option(lfm25::kOptEngineGraph) != 0 && bound != nullptr &&
                              bound != cudaStreamLegacy;
     }
     for (uint32_t layer = 0; layer < model->num_layers; ++layer) {

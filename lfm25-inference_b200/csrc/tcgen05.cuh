@@ -45,6 +45,12 @@ __device__ __forceinline__ void tmem_load16_nowait(uint32_t address, uint32_t (&
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(address));
 }
+// 8 consecutive 32-bit columns of this thread's TMEM lane, without the wait
+__device__ __forceinline__ void tmem_load8_nowait(uint32_t address, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(address));
+}
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // 16 consecutive 32-bit columns of this thread's TMEM lane <- registers

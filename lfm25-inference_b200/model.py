@@ -286,6 +286,10 @@ class DecodeExecutor:
         """GPU kernels per step in the graph that the last step_graph call replayed (0 before the first replay)."""
         return int(library().lfm25_decode_executor_graph_kernels(self._handle))
 
+    def graph_captures(self) -> int:
+        """Steps captured so far; a change of anything a captured step baked in makes the next call capture again."""
+        return int(library().lfm25_decode_executor_graph_captures(self._handle))
+
     REGIONS = ("attention", "append", "fp8_linear", "bf16_linear", "other")
 
     def profile(self, enable: bool, collect: bool = False):

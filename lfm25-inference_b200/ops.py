@@ -347,6 +347,33 @@ class BlasLt:
         check(library().lfm25_blaslt_linear_bf16(self._handle, _slice(x), _slice(weight), _slice(output), rows,
                                                  weight.shape[0], k))
 
+    def linear_bf16_silu_mul(self, x: torch.Tensor, weight: torch.Tensor, activation: torch.Tensor,
+                             activation_scale: float = 1.0) -> None:
+        """Packed BF16 Gate/Up linear with SiLU(gate) * up in the epilogue; `activation` [M, N/2] is uint8 (E4M3
+        codes of the activation times `activation_scale`) or bfloat16."""
+        k = x.shape[-1]
+        _ensure(weight.dim() == 2 and weight.shape[1] == k, "linear K mismatch")
+        rows = x.numel() // k
+        self.bind_current_stream()
+        check(library().lfm25_blaslt_linear_bf16_silu_mul(self._handle, _slice(x), _slice(weight), _slice(activation),
+                                                          rows, weight.shape[0], k, activation_scale,
+                                                          1 if activation.dtype == torch.uint8 else 0))
+
+    def set_gemm_tuning(self, kernel: int = 0, n_tile: int = 0, splits: int = 0, stages: int = 0, issuers: int = 0,
+                        ctas_per_sm: int = 0, shared_memory_bytes: int = 0, batch_slices: int = 0) -> None:
+        """Kernel and tile choice of this handle's linears (0 = the library's choice); no arguments = defaults."""
+        tuning = _abi.GemmTuning(kernel, n_tile, splits, stages, issuers, ctas_per_sm, shared_memory_bytes,
+                                 batch_slices)
+        check(library().lfm25_blaslt_set_gemm_tuning(self._handle, tuning))
+
+    def gemm_plan(self, m: int, n: int, k_bytes: int, gated: bool = False) -> dict:
+        """The batch-major kernel's launch plan for a problem under this handle's tuning."""
+        import ctypes
+        out = (ctypes.c_uint32 * 8)()
+        check(library().lfm25_blaslt_gemm_plan(self._handle, m, n, k_bytes, 1 if gated else 0, out))
+        names = ("n_tile", "splits", "tiles", "stages", "issuers", "ctas_per_sm", "smem_bytes", "batch_slices")
+        return dict(zip(names, (int(value) for value in out)))
+
     def close(self) -> None:
         if self._handle:
             library().lfm25_blaslt_destroy(self._handle)
@@ -429,6 +456,18 @@ def gather_rows_bf16_into(values, row_indices, output) -> None:
 def argmax_rows_bf16_into(logits: torch.Tensor, sampled: torch.Tensor) -> None:
     check(library().lfm25_argmax_rows_bf16(_stream(), _slice(logits), _slice(sampled), logits.shape[0],
                                            logits.shape[1]))
+
+
+def set_option(name: str, value: int) -> None:
+    """Process-wide switch of the library (include/lfm25_b200.h: lfm25_set_option)."""
+    check(library().lfm25_set_option(name.encode(), int(value)))
+
+
+def get_option(name: str) -> int:
+    import ctypes
+    value = ctypes.c_int64()
+    check(library().lfm25_get_option(name.encode(), ctypes.byref(value)))
+    return int(value.value)
 
 
 def device_status() -> tuple[int, int, int, int]:

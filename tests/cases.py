@@ -143,3 +143,44 @@ def short_conv_segmented_case(seed=31, hidden=256):
                 states=workloads.bf16_normal(rng, (7, hidden, 2)),
                 segment_offsets=np.concatenate([[0], np.cumsum(chunks)]).astype(np.uint32),
                 segment_slots=np.array([3, 0, 9, 6, 1], dtype=np.uint32))      # slot 9 is beyond the table: skipped
+
+
+# The E4M3 decode GEMM sites at the batch sizes of the sweep (the reference's FP8 call sites,
+# src/model/decode_executor.rs:35-76 with the shapes of src/model/lfm2.rs): 15 points.
+FP8_GEMM_SITES = {"gate_up": (16384, 2048), "down": (2048, 8192), "lm_head": (65536, 2048)}
+FP8_GEMM_BATCHES = (1, 8, 32, 128, 256)
+FP8_GEMM_BLOCK = 512          # weight rows generated from one seed
+FP8_GEMM_SAMPLE = 32          # rows sampled from the head of each of four blocks: 128 output columns
+FP8_WEIGHT_CLIP = 0.1         # static weight scale c_w (5 sigma of N(0, 0.02)); values beyond it saturate
+FP8_ACTIVATION_CLIP = 5.0     # static activation scale c_x
+
+
+def fp8_gemm_weight_block(site, block):
+    """E4M3 codes of weight rows [block * 512, block * 512 + 512) of a site: N(0, 0.02) quantised with c_w = 0.1.
+    Every block has its own seed, so a test that checks a sample of the output columns only builds those rows."""
+    n, k = FP8_GEMM_SITES[site]
+    rng = np.random.default_rng([17, sorted(FP8_GEMM_SITES).index(site), block])
+    weights = workloads.bf16_normal(rng, (min(FP8_GEMM_BLOCK, n - block * FP8_GEMM_BLOCK), k), std=0.02)
+    return oracle.quantize_bf16_e4m3(weights, oracle.scalar_scale(FP8_WEIGHT_CLIP)[0])
+
+
+def fp8_gemm_sample_blocks(site):
+    blocks = FP8_GEMM_SITES[site][0] // FP8_GEMM_BLOCK
+    return [0, blocks // 3, (2 * blocks) // 3, blocks - 1]
+
+
+def fp8_gemm_point(site, m):
+    """(activation codes [m, k], output scale d_x * d_w, sampled output columns) of one point of the sweep."""
+    n, k = FP8_GEMM_SITES[site]
+    rng = np.random.default_rng([19, sorted(FP8_GEMM_SITES).index(site), m])
+    x_quantize, x_dequantize = oracle.scalar_scale(FP8_ACTIVATION_CLIP)
+    x_codes = oracle.quantize_bf16_e4m3(workloads.bf16_normal(rng, (m, k)), x_quantize)
+    columns = np.concatenate([np.arange(block * FP8_GEMM_BLOCK, block * FP8_GEMM_BLOCK + FP8_GEMM_SAMPLE)
+                              for block in fp8_gemm_sample_blocks(site)])
+    return x_codes, x_dequantize * oracle.scalar_scale(FP8_WEIGHT_CLIP)[1], columns
+
+
+def fp8_gemm_sampled_weights(site):
+    """The weight rows of the sampled output columns, [128, k]."""
+    return np.concatenate([fp8_gemm_weight_block(site, block)[:FP8_GEMM_SAMPLE]
+                           for block in fp8_gemm_sample_blocks(site)])

@@ -25,6 +25,26 @@ def device():
     return torch.device("cuda:0")
 
 
+@pytest.fixture
+def library_option():
+    """Sets process-wide switches of the library (lfm25_set_option) for one test and restores them afterwards."""
+    from lfm25_inference_b200 import ops
+    before = {}
+
+    def set_option(name: str, value: int) -> None:
+        before.setdefault(name, ops.get_option(name))
+        ops.set_option(name, value)
+
+    yield set_option
+    for name, value in before.items():
+        ops.set_option(name, value)
+
+
+FP8_GEMM_PATHS = {"auto": 0, "stream": 1, "umma": 2, "generic": 3, "rows": 4}
+BF16_GEMM_PATHS = {"auto": 0, "umma": 1, "cublaslt": 2, "rows": 3}
+HYBRID_ATTENTION_KERNELS = {"auto": 0, "umma": 1, "mma": 2}
+
+
 def to_bf16(bits: np.ndarray, device):
     """uint16 bit patterns -> torch.bfloat16 tensor on `device`."""
     import torch

@@ -1,5 +1,7 @@
 """Generates tests/golden/reference_b200.npz: outputs of the reference project's own, unmodified CUDA kernels
-(compiled for sm_100a into oracle/_ref/*.cubin by `make -C oracle ref`) on the inputs of tests/cases.py.
+(compiled for sm_100a into oracle/_ref/*.cubin by `make -C oracle ref`) on the inputs of tests/cases.py, and of
+cuBLASLt's E4M3 GEMM -- the library the reference calls for its FP8 linears (src/cuda/blaslt/mod.rs:212-298),
+here through torch._scaled_mm -- on the 15 points of the decode GEMM sweep (a sample of 128 output columns each).
 
 Run on a B200:   python tests/golden/make_golden.py <output.npz>
 The fixture pins the CPU oracle (tests/test_oracle_golden.py runs without a GPU) to what the reference
@@ -42,9 +44,28 @@ def attention_outputs(case, device, splits=()):
     return out
 
 
+def cublaslt_fp8_outputs(device):
+    """fp8_<site>_<m>: bf16 bits [m, 128] of cuBLASLt's E4M3 GEMM on the sampled columns of cases.fp8_gemm_point.
+    cuBLASLt wants both GEMM extents in multiples of 16, so smaller batches are padded with zero rows."""
+    out = {}
+    one = torch.ones((), device=device)
+    for site in cases.FP8_GEMM_SITES:
+        weights = torch.from_numpy(cases.fp8_gemm_sampled_weights(site)).to(device).view(torch.float8_e4m3fn)
+        for m in cases.FP8_GEMM_BATCHES:
+            x_codes, scale, _ = cases.fp8_gemm_point(site, m)
+            padded = np.zeros(((m + 15) // 16 * 16, x_codes.shape[1]), dtype=np.uint8)
+            padded[:m] = x_codes
+            activations = torch.from_numpy(padded).to(device).view(torch.float8_e4m3fn)
+            result = torch._scaled_mm(activations, weights.t(), scale_a=one * scale, scale_b=one,
+                                      out_dtype=torch.bfloat16)
+            out[f"fp8_{site}_{m}"] = bits_of(result[:m])
+    return out
+
+
 def main(path):
     device = torch.device("cuda:0")
     golden = {}
+    golden.update(cublaslt_fp8_outputs(device))
     for context in cases.SINGLE_CONTEXTS:
         for name, bits in attention_outputs(cases.single_context_case(context), device).items():
             golden[f"single{context}_{name}"] = bits

@@ -3,11 +3,15 @@
 The op is Y = bf16(output_scale * Xq Wq^T) on E4M3 codes with fp32 accumulation.  Every product of two E4M3
 values is exact in fp32 and only the order of the fp32 sum differs between implementations, so the tolerance
 against the fp64 oracle on the same codes is |y - y*| <= 2e-2 + 1e-2 |y*| and cosine >= 0.9999."""
+import os
+
 import numpy as np
 import pytest
 import torch
 
-from conftest import assert_close_bf16, assert_within_oracle, bits_of, to_bf16
+import cases
+
+from conftest import FP8_GEMM_PATHS, assert_close_bf16, assert_within_oracle, bits_of, to_bf16
 from lfm25_inference_b200 import Lfm25Error, ops, workloads
 from oracle import oracle
 
@@ -58,14 +62,14 @@ def test_stream_path_against_oracle(device, m, n, k):
     assert np.abs(oracle.bf16_to_f32(got) - want).max() <= np.abs(exact).max() * 2 ** -7
 
 
-@pytest.mark.parametrize("path", ["umma", "stream"])
+@pytest.mark.parametrize("path", ["umma", "stream", "rows"])
 @pytest.mark.parametrize("m", [1, 9, 16, 17, 31, 32, 48, 64, 100, 128, 129, 200, 256])
 @pytest.mark.parametrize("n,k", [(128, 128), (256, 1024), (2048, 2048), (512, 8192)])
-def test_kernel_paths_against_oracle(device, monkeypatch, path, m, n, k):
-    """Both fast kernels on the shapes they accept (the environment variable only selects among valid paths)."""
+def test_kernel_paths_against_oracle(device, library_option, path, m, n, k):
+    """The fast kernels on the shapes they accept (the option only selects among valid paths)."""
     if path == "stream" and m > 8:
         pytest.skip("the streaming kernel covers M <= 8")
-    monkeypatch.setenv("LFM25_FP8_GEMM_PATH", path)
+    library_option("fp8_gemm_path", FP8_GEMM_PATHS[path])
     _, x_codes, w_codes, (_, xd), (_, wd) = quantised_problem(m * 31 + n + k, m, n, k)
     got = run_linear(x_codes, w_codes, xd * wd, device)
     _, exact = oracle.linear_fp8(x_codes, w_codes, xd * wd, want_exact=True)
@@ -75,17 +79,17 @@ def test_kernel_paths_against_oracle(device, monkeypatch, path, m, n, k):
     assert ops.device_status()[0] == 0
 
 
-def test_paths_agree_bit_for_bit_on_exact_sums(device, monkeypatch):
+def test_paths_agree_bit_for_bit_on_exact_sums(device, library_option):
     """With +-1.0 / +-0.5 codes every partial sum is exact in fp32, so all kernels must return identical bits."""
     rng = np.random.default_rng(4)
     choices = np.array([0x38, 0xB8, 0x30, 0xB0, 0x00], dtype=np.uint8)
     x = choices[rng.integers(0, 5, size=(24, 1024))]
     w = choices[rng.integers(0, 5, size=(256, 1024))]
     results = []
-    for path in ("generic", "stream", "umma"):
-        monkeypatch.setenv("LFM25_FP8_GEMM_PATH", path)
+    for path in ("generic", "stream", "umma", "rows"):
+        library_option("fp8_gemm_path", FP8_GEMM_PATHS[path])
         results.append(run_linear(x, w, 0.25, device))
-    assert np.array_equal(results[0], results[1]) and np.array_equal(results[0], results[2])
+    assert all(np.array_equal(results[0], other) for other in results[1:])
     assert np.array_equal(results[0], oracle.linear_fp8(x, w, 0.25))
 
 
@@ -163,11 +167,12 @@ def test_shape_checks(device):
 @pytest.mark.parametrize("e4m3_output", [True, False])
 @pytest.mark.parametrize("m", [1, 5, 16, 33, 128, 200, 256])
 @pytest.mark.parametrize("intermediate,k", [(8192, 2048), (256, 512), (64, 128)])
-def test_gated_linear_equals_linear_then_silu_mul(device, monkeypatch, m, intermediate, k, e4m3_output):
+@pytest.mark.parametrize("kernel", ["umma", "rows"])
+def test_gated_linear_equals_linear_then_silu_mul(device, library_option, kernel, m, intermediate, k, e4m3_output):
     """The packed Gate/Up linear with SiLU(gate) * up in its epilogue: bit for bit what the same GEMM kernel followed
     by the SiLU * Up kernel produces (src/model/decode_executor.rs:378-402 as two launches), and within the FP8
     tolerance of the oracle's restatement of those two ops."""
-    monkeypatch.setenv("LFM25_FP8_GEMM_PATH", "umma")          # the two-launch route through the same GEMM kernel
+    library_option("fp8_gemm_path", FP8_GEMM_PATHS[kernel])    # the two-launch route through the same GEMM kernel
     _, x_codes, w_codes, (_, xd), (_, wd) = quantised_problem(m * 7 + intermediate + k, m, 2 * intermediate, k)
     x_device, w_device = codes_tensor(x_codes, device), codes_tensor(w_codes, device)
     activation_scale = 448.0 / 6.0
@@ -197,12 +202,60 @@ def test_gated_linear_equals_linear_then_silu_mul(device, monkeypatch, m, interm
 def test_gated_linear_shape_checks(device):
     blaslt = ops.BlasLt()
     x = torch.zeros((4, 128), dtype=torch.uint8, device=device)
-    weight = torch.zeros((2 * 96, 128), dtype=torch.uint8, device=device)      # 96 outputs: not a multiple of 64
-    out = torch.zeros((4, 96), dtype=torch.uint8, device=device)
+    weight = torch.zeros((2 * 100, 128), dtype=torch.uint8, device=device)     # 100 outputs: not a multiple of 8
+    out = torch.zeros((4, 100), dtype=torch.uint8, device=device)
     with pytest.raises(Lfm25Error):
         blaslt.linear_fp8_silu_mul(x, weight, out, 1.0, 1.0)
     weight = torch.zeros((2 * 64, 128), dtype=torch.uint8, device=device)
     small = torch.zeros((4, 32), dtype=torch.uint8, device=device)             # output storage too small
     with pytest.raises(Lfm25Error):
         blaslt.linear_fp8_silu_mul(x, weight, small, 1.0, 1.0)
+    blaslt.close()
+
+
+@pytest.fixture(scope="module")
+def sweep_weights(device):
+    """Full weight matrices of the three sites (built block by block from their seeds), kept on the device."""
+    cache = {}
+
+    def get(site):
+        if site not in cache:
+            blocks = cases.FP8_GEMM_SITES[site][0] // cases.FP8_GEMM_BLOCK
+            host = np.concatenate([cases.fp8_gemm_weight_block(site, block) for block in range(blocks)])
+            cache[site] = codes_tensor(host, device)
+        return cache[site]
+
+    return get
+
+
+@pytest.mark.parametrize("m", cases.FP8_GEMM_BATCHES)
+@pytest.mark.parametrize("site", sorted(cases.FP8_GEMM_SITES))
+def test_sweep_points_against_cublaslt(device, sweep_weights, site, m):
+    """All 15 points of the decode GEMM sweep through a handle (the kernel the library picks for each) against
+    cuBLASLt's E4M3 GEMM -- the reference's BlasLt::linear_fp8_scaled (src/cuda/blaslt/mod.rs:212-298) -- (a) live,
+    on the same device buffers, every output element, and (b) from the committed fixture on a sample of columns.
+    Both sides round one fp32 sum of exact products to bf16, in different orders: |a - b| <= 2^-7 |b| (one bf16
+    step) + 2^-10 max|b| (the fp32 rounding of partial sums is relative to the largest terms, not to a result that
+    cancels to almost nothing)."""
+    x_codes, scale, columns = cases.fp8_gemm_point(site, m)
+    weights = sweep_weights(site)
+    n = weights.shape[0]
+    blaslt = ops.BlasLt()
+    out = torch.zeros((m, n), dtype=torch.bfloat16, device=device)
+    blaslt.linear_fp8_scaled(codes_tensor(x_codes, device), weights, out, scale)
+    got = bits_of(out)
+    padded = np.zeros(((m + 15) // 16 * 16, x_codes.shape[1]), dtype=np.uint8)
+    padded[:m] = x_codes
+    one = torch.ones((), device=device)
+    library = torch._scaled_mm(codes_tensor(padded, device).view(torch.float8_e4m3fn),
+                               weights.view(torch.float8_e4m3fn).t(), scale_a=one * scale, scale_b=one,
+                               out_dtype=torch.bfloat16)
+    want = bits_of(library[:m])
+    atol = float(np.abs(oracle.bf16_to_f32(want)).max()) * 2 ** -10
+    assert_close_bf16(got, want, atol, 2 ** -7)
+    golden_path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_b200.npz")
+    golden = np.load(golden_path)
+    if f"fp8_{site}_{m}" in golden.files:
+        assert_close_bf16(got[:, columns], golden[f"fp8_{site}_{m}"], atol, 2 ** -7)
+    assert ops.device_status()[0] == 0
     blaslt.close()

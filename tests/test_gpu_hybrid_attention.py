@@ -7,7 +7,7 @@ import pytest
 import torch
 
 import cases
-from conftest import assert_close_bf16, assert_within_oracle, bits_of, to_bf16, to_u32
+from conftest import HYBRID_ATTENTION_KERNELS, assert_close_bf16, assert_within_oracle, bits_of, to_bf16, to_u32
 from lfm25_inference_b200 import ops, workloads
 from oracle import oracle, refkernels
 
@@ -15,9 +15,9 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.fixture(params=["mma", "umma"], autouse=True)
-def kernel_choice(request, monkeypatch):
+def kernel_choice(request, library_option):
     """Every case runs through both kernels: mma.sync (16 tokens per CTA) and tcgen05 (32 tokens per CTA)."""
-    monkeypatch.setenv("LFM25_HYBRID_ATTENTION", request.param)
+    library_option("hybrid_attention", HYBRID_ATTENTION_KERNELS[request.param])
     return request.param
 
 

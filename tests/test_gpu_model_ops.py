@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import assert_close_bf16, bits_of, to_bf16, to_u32
+from conftest import BF16_GEMM_PATHS, assert_close_bf16, bits_of, to_bf16, to_u32
 from lfm25_inference_b200 import _abi, ops, workloads
 from lfm25_inference_b200._abi import check, library
 from oracle import oracle
@@ -169,8 +169,8 @@ def test_step_metadata_on_device(device):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (128, 512, 2048), (7, 6144, 2048), (128, 2048, 8192)])
-def test_bf16_linear_through_cublaslt(device, monkeypatch, m, n, k):
-    monkeypatch.setenv("LFM25_BF16_GEMM", "cublaslt")
+def test_bf16_linear_through_cublaslt(device, library_option, m, n, k):
+    library_option("bf16_gemm", BF16_GEMM_PATHS["cublaslt"])
     rng = np.random.default_rng(m + n)
     x = workloads.bf16_normal(rng, (m, k))
     weight = workloads.bf16_normal(rng, (n, k), std=0.02)
@@ -181,11 +181,14 @@ def test_bf16_linear_through_cublaslt(device, monkeypatch, m, n, k):
     blaslt.close()
 
 
+@pytest.mark.parametrize("kernel", ["umma", "rows"])
 @pytest.mark.parametrize("m,n,k", [(1, 2048, 2048), (128, 512, 2048), (7, 6144, 2048), (128, 2048, 8192),
-                                   (33, 16384, 2048), (256, 2048, 2048), (128, 65536, 2048)])
-def test_bf16_linear_through_tcgen05(device, monkeypatch, m, n, k):
-    """The BF16 sites of the step through this library's tcgen05 kernel (fp32 accumulation, one rounding)."""
-    monkeypatch.setenv("LFM25_BF16_GEMM", "umma")
+                                   (33, 16384, 2048), (256, 2048, 2048), (128, 65536, 2048), (33, 3072, 2048),
+                                   (128, 6144, 2048), (128, 16384, 2048), (128, 3072, 2048), (128, 2048, 2048)])
+def test_bf16_linear_through_tcgen05(device, library_option, kernel, m, n, k):
+    """The BF16 sites of the step through this library's tcgen05 kernels (fp32 accumulation, one rounding): the
+    weight-major one and the batch-major one, at the batch sizes of the headline step (33 and 128 rows) too."""
+    library_option("bf16_gemm", BF16_GEMM_PATHS[kernel])
     rng = np.random.default_rng(m + n + 1)
     x = workloads.bf16_normal(rng, (m, k))
     weight = workloads.bf16_normal(rng, (n, k), std=0.02)

@@ -102,3 +102,18 @@ def test_short_conv_segmented(golden):
                                               case["segment_slots"])
     assert np.array_equal(golden["conv_segmented_output"], output)
     assert np.array_equal(golden["conv_segmented_states"], states)
+
+
+@pytest.mark.parametrize("m", cases.FP8_GEMM_BATCHES)
+@pytest.mark.parametrize("site", sorted(cases.FP8_GEMM_SITES))
+def test_fp8_linear_against_cublaslt(golden, site, m):
+    """The oracle's FP8 linear against what cuBLASLt (the library behind the reference's BlasLt::linear_fp8_scaled,
+    src/cuda/blaslt/mod.rs:212-298) returned on a B200 for the 15 points of the decode sweep, on a sample of 128
+    output columns: both round one fp32 sum of exact products to bf16, so they agree to one bf16 step."""
+    key = f"fp8_{site}_{m}"
+    if key not in golden.files:
+        pytest.skip("fixture predates the cuBLASLt section of make_golden.py")
+    x_codes, scale, _ = cases.fp8_gemm_point(site, m)
+    ours = oracle.linear_fp8(x_codes, cases.fp8_gemm_sampled_weights(site), scale)
+    atol = float(np.abs(oracle.bf16_to_f32(ours)).max()) * 2 ** -10      # fp32 sums in another order
+    assert_close_bf16(golden[key], ours, atol, 2 ** -7)
