@@ -1,6 +1,7 @@
 """Benchmark of the decode hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload step|attention]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--workload step|attention|gemm|prefill|serving]
 
 Default workload `step` (one "step" = one decode step of the whole model): the LFM2.5-1.2B architecture with
 random-init weights under continuous batching -- 16 layers (6 GQA attention, 10 gated short-conv), hidden 2048,
@@ -16,8 +17,14 @@ Workload `attention` (one "step" = append + attention of one layer) is the ragge
 64 sequences, contexts seeded-uniform in [16, 8192], a 2^16-page pool, fused QK-norm + RoPE + paged append followed
 by ragged paged attention, in episodes of 16 positions.  Its KV GB/s is also reported inside the default line.
 
+Workload `gemm` is the decode GEMM sweep: the three E4M3 sites (packed Gate/Up 2048 -> 16384, Down 8192 -> 2048,
+LM head 2048 -> 65536) and the BF16 sites of the step at M in {1, 8, 32, 128, 256}, HBM-cold over a ring of weight
+copies of at least 512 MB, cuBLASLt on the same buffers beside every point, each against
+max(bytes / HBM peak, flops / tensor peak).  A compact table of its E4M3 half is part of the default line
+(`gemm_roofline`).
+
 `cpu_baseline` / `--impl reference`: the reference project is GPU-only, so the CPU arm is the multithreaded C
-restatement of its kernels (oracle/), timed on a bounded sample of the same step on the host's cores.
+restatement of its kernels (oracle/), timed on the same step (all 128 sequences, one step) on the host's cores.
 
 Multi-GPU: the path does not shard (the model and every sequence's KV fit one GPU), so N ranks are N independent
 engine replicas with different seeds; there is no collective on the data path, only the timing barrier.
@@ -55,7 +62,7 @@ STEP_POOL_PAGES = 32768
 def parse_arguments():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--workload", default="step", choices=["step", "attention", "prefill", "serving"])
+    parser.add_argument("--workload", default="step", choices=["step", "attention", "gemm", "prefill", "serving"])
     parser.add_argument("--steps", type=int, default=0, help="timed steps (default 256 for step, 1024 for attention)")
     parser.add_argument("--warmup", type=int, default=0, help="warm-up steps (default 8 / 32)")
     parser.add_argument("--no-fp8", action="store_true", help="step workload: run every site in BF16")
@@ -68,6 +75,8 @@ def parse_arguments():
                         help="step workload: sequences in the batch (the headline number needs the default)")
     parser.add_argument("--pool-pages", type=int, default=NUM_PAGES, help="pages in the K/V pool (same remark)")
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
+    parser.add_argument("--skip-gemm", action="store_true", help="step workload: omit the gemm_roofline table")
+    parser.add_argument("--gemm-dtype", default="all", choices=["all", "e4m3", "bf16"], help="gemm workload: which sites")
     parser.add_argument("--requests", type=int, default=192, help="serving workload: requests in the trace")
     parser.add_argument("--rate", type=float, default=32.0, help="serving workload: Poisson arrival rate, requests/s")
     parser.add_argument("--skip-reference-kernels", action="store_true",
@@ -77,9 +86,9 @@ def parse_arguments():
                              "reference's admission) instead of queueing them")
     arguments = parser.parse_args()
     if arguments.steps <= 0:
-        arguments.steps = {"step": 256, "attention": 1024, "prefill": 16, "serving": 1}[arguments.workload]
+        arguments.steps = {"step": 256, "attention": 1024, "prefill": 16, "serving": 1, "gemm": 64}[arguments.workload]
     if arguments.warmup <= 0:
-        arguments.warmup = {"step": 8, "attention": 32, "prefill": 3, "serving": 3}[arguments.workload]
+        arguments.warmup = {"step": 8, "attention": 32, "prefill": 3, "serving": 3, "gemm": 3}[arguments.workload]
     globals().update(SEQUENCES=arguments.sequences, NUM_PAGES=arguments.pool_pages,
                      STEP_SEQUENCES=arguments.step_sequences)
     return arguments
@@ -91,6 +100,33 @@ def peaks():
         with open(path) as handle:
             return float(json.load(handle)["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def tensor_peaks():
+    """(BF16 TFLOP/s, source): the measured cuBLAS rate for a kernel timed alone."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as handle:
+            return float(json.load(handle)["bf16_tflops"]), "measured"
+    return 1590.0, "fallback"
+
+
+# DRAM bytes over algorithmic bytes of the decode attention kernel, from the ncu capture summarised in
+# profiles/ragged_decode_attention_config1.md (dram__bytes_read.sum + dram__bytes_write.sum of a 16-sequence launch;
+# the traffic is the KV stream, which grows in proportion to the keys read).
+ATTENTION_TRAFFIC_FACTOR = 1.001
+
+
+def gather_over_ranks(values, device, world):
+    """Every rank's values, [world][len(values)] (the replicas are independent: no reduction is meaningful but max)."""
+    import torch
+    import torch.distributed as dist
+    tensor = torch.tensor(list(values), dtype=torch.float64, device=device)
+    if world == 1:
+        return [[float(value) for value in tensor.cpu()]]
+    gathered = [torch.zeros_like(tensor) for _ in range(world)]
+    dist.all_gather(gathered, tensor)
+    return [[float(value) for value in part.cpu()] for part in gathered]
 
 
 def max_over_ranks(values, device, world):
@@ -460,6 +496,22 @@ def run_gpu_arm(arguments, rank, world):
         except Exception as error:           # the comparison is optional; the metric does not depend on it
             reference_kernels = {"error": str(error)[:120]}
 
+    # the E4M3 half of the decode GEMM sweep, as a compact table in the line (rank 0 only; after the timed regions)
+    gemm_table = None
+    if rank == 0 and not arguments.skip_gemm:
+        try:
+            from lfm25_inference_b200 import gemm_sweep
+            fp8_peak = gemm_sweep.measure_fp8_peak(device)
+            with torch.cuda.stream(stream):
+                rows = gemm_sweep.sweep_fp8(ops, device, peaks()[0], fp8_peak, iterations=32, with_gated=False)
+            gemm_table = {"fp8_tensor_peak_tflops": round(fp8_peak, 1),
+                          "fp8_tensor_peak_source": "cuBLASLt E4M3 8192^3 measured in this run",
+                          "ring": "weight copies >= 512 MB per site (HBM-cold), CUDA graph of 32 launches x 5 replays",
+                          "points": gemm_sweep.compact(rows)}
+        except Exception as error:       # the table is an annex of the line; the metric does not depend on it
+            gemm_table = {"error": str(error)[:160]}
+
+    per_rank = gather_over_ranks([total_ms / steps, submit_seconds * 1e3 / steps], device, world)
     total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
     config0 = None
     if rank == 0:
@@ -492,7 +544,12 @@ def run_gpu_arm(arguments, rank, world):
             "kv_gbs": kv_bytes / attention_seconds / 1e9,
             "append_us": float(append_ms.mean()) * 1e3, "attention_us": float(attention_ms.mean()) * 1e3,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                         "frac": achieved / hbm_peak,
+                         "traffic": ATTENTION_TRAFFIC_FACTOR * (kv_bytes + other_bytes),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 16-sequence launch = "
+                                           "1.001 x its algorithmic bytes, scaled by the keys read "
+                                           "(profiles/ragged_decode_attention_config1.md)",
+                         "peak_source": peak_kind,
                          "kernel": "ragged_decode_attention_kernel" + (" + merge_splitk_kernel" if splits > 1 else ""),
                          "algorithmic_bytes_per_launch": kv_bytes + other_bytes},
             "cpu_baseline": {"value": cpu_tokens, "unit": "tok/s", "cores": threads, "kind": "port",
@@ -514,8 +571,7 @@ def run_gpu_arm(arguments, rank, world):
 
 def step_cpu_sample(model, batch, token_ids, use_fp8, sequences, repeats):
     """CPU oracle on `sequences` of the batch's sequences for one full decode step.  Returns (tok/s, s, text, threads)."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import step_oracle
+    from oracle import step_oracle
     from oracle import oracle
     oracle.use_all_cores()
     host = step_oracle.HostModel(model)
@@ -557,8 +613,8 @@ def run_step_reference_arm(arguments, rank):
     entry.load_package()
     device = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
     batch, model, token_ids = build_step_state(arguments, 3, device, 8)
-    sequences = arguments.cpu_sequences or 4
-    steps = max(1, min(arguments.steps, 3))
+    sequences = arguments.cpu_sequences or STEP_SEQUENCES
+    steps = 1
     tokens_per_s, seconds, description, threads = step_cpu_sample(model, batch, token_ids, not arguments.no_fp8,
                                                                   sequences, steps)
     line = {
@@ -615,8 +671,11 @@ def run_step_arm(arguments, rank, world):
         with ClockSampler(local_rank) as sampler:
             stream.synchronize()
             marks[0].record()
+            submit_seconds = 0.0
             for step in range(steps):
+                submit_start = time.perf_counter()
                 executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=True)
+                submit_seconds += time.perf_counter() - submit_start
                 marks[step + 1].record()
             stream.synchronize()
             total_ms = marks[0].elapsed_time(marks[steps])
@@ -654,15 +713,31 @@ def run_step_arm(arguments, rank, world):
                     output = torch.empty_like(query)
                     arguments_ = (query, layer.tensors["key_cache"], layer.tensors["value_cache"],
                                   device_batch.block_tables, device_batch.request_slots, device_batch.positions, output)
-                    refkernels.paged_ragged_attention_fast(*arguments_)
-                    stream.synchronize()
-                    begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    begin.record()
-                    for _ in range(3):
-                        refkernels.paged_ragged_attention_fast(*arguments_)
-                    finish.record()
-                    stream.synchronize()
-                    reference_kernels = {"attention_unsplit_us_per_layer": begin.elapsed_time(finish) / 3 * 1e3,
+                    def time_reference(function, launches=20):
+                        for _ in range(3):
+                            function()
+                        stream.synchronize()
+                        begin, finish = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        begin.record()
+                        for _ in range(launches):
+                            function()
+                        finish.record()
+                        stream.synchronize()
+                        return begin.elapsed_time(finish) / launches * 1e3
+
+                    # the reference's unsplit kernel and its split-K kernel + merge (attention_async_fast.cu:211-419)
+                    # under every split count its policy may pick; its better time is what this library is set against
+                    unsplit_us = time_reference(lambda: refkernels.paged_ragged_attention_fast(*arguments_))
+                    split_us = {}
+                    for count in (2, 4, 8):
+                        partials = torch.empty((STEP_SEQUENCES, 32, count, 66), dtype=torch.float32, device=device)
+                        split_us[count] = time_reference(
+                            lambda: refkernels.paged_ragged_attention_splitk(*arguments_[:-1], partials, output, count))
+                    best_split = min(split_us, key=split_us.get)
+                    reference_kernels = {"attention_unsplit_us_per_layer": unsplit_us,
+                                         "attention_splitk_us_per_layer": {str(k): v for k, v in split_us.items()},
+                                         "attention_best_us_per_layer": min(unsplit_us, split_us[best_split]),
+                                         "attention_note": "20 launches each after 3 warm-up launches, same cache and metadata",
                                          "ours_us_per_layer": attention_seconds * 1e6}
             except Exception as error:       # optional comparison; the metric does not depend on it
                 reference_kernels = {"error": str(error)[:120]}
@@ -712,13 +787,13 @@ def run_step_arm(arguments, rank, world):
             cpu_tokens, cpu_description, threads = None, "skipped", 0
         else:
             cpu_tokens, _, cpu_description, threads = step_cpu_sample(model, batch, token_ids, use_fp8,
-                                                                      arguments.cpu_sequences or 4, 2)
+                                                                      arguments.cpu_sequences or STEP_SEQUENCES, 1)
         per_step = {name: ops_count // profile_steps for name, (_, ops_count) in regions.items()}
         # GPU kernels per step, counted from the captured graph; the BF16 GEMMs of batches above 32 rows are
         # cuBLASLt's kernels (one per call), everything else is this library's
         graph_kernels = executor.graph_kernels()
-        forced = os.environ.get("LFM25_BF16_GEMM")
-        through_library = forced == "cublaslt" or (forced != "umma" and STEP_SEQUENCES > 32)
+        forced = ops.get_option("bf16_gemm")          # 0 auto | 1 umma | 2 cublaslt | 3 rows
+        through_library = forced == 2 or (forced == 0 and STEP_SEQUENCES > 32)
         library_launches = per_step["bf16_linear"] if through_library else 0
         launches = graph_kernels - library_launches
         line = {
@@ -745,6 +820,13 @@ def run_step_arm(arguments, rank, world):
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes, "steps": e2e_steps},
             "gpu_launches": launches * steps, "cublaslt_launches": library_launches * steps,
             "reference_kernels_same_gpu": reference_kernels,
+            "gemm_roofline": gemm_table,
+            "replicas": {"tok_s_sum_of_replicas": sum(STEP_SEQUENCES / (ms * 1e-3) for ms, _ in per_rank),
+                         "tok_s_from_slowest_replica": STEP_SEQUENCES * steps * world / (total_ms * 1e-3),
+                         "ms_per_step_per_rank": [round(ms, 4) for ms, _ in per_rank],
+                         "step_submit_cpu_ms_per_rank": [round(cpu, 4) for _, cpu in per_rank],
+                         "note": "independent replicas, no collective on the data path; `value` uses the slowest "
+                                 "replica's time, the sum adds each replica's own rate"},
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -784,6 +866,52 @@ def reference_kernel_step(model, device_batch, stream, use_fp8, repeats=16):
     return {"step_ms_graph_replay": float(np.median(times)), "step_launches": step.launches,
             "step_note": "reference kernels + cuBLASLt (torch.matmul / torch._scaled_mm) in the reference's op order, "
                          "CUDA graph replay: no launch or host overhead, which the reference's own loop has"}
+
+
+# ------------------------------------------------------------------------------------ decode GEMM sweep
+
+GEMM_METRIC = "decode GEMM microseconds per launch (E4M3 and BF16 sites, M in {1, 8, 32, 128, 256}, HBM-cold)"
+GEMM_WORKLOAD = "config2-decode-gemm-sweep"
+
+
+def run_gemm_arm(arguments, rank, world):
+    """Config 2: every point against max(bytes / HBM peak, flops / tensor peak), with cuBLASLt on the same buffers.
+    One JSON line; `value` is the geometric mean over the E4M3 points of cuBLASLt's time over this library's."""
+    import torch
+    if rank != 0:
+        return
+    torch.cuda.set_device(0)
+    device = torch.device("cuda", 0)
+    entry.load_package()
+    from lfm25_inference_b200 import gemm_sweep, ops
+    hbm_peak, peak_kind = peaks()
+    bf16_peak, _ = tensor_peaks()
+    fp8_peak = gemm_sweep.measure_fp8_peak(device)
+    rows = []
+    start = time.perf_counter()
+    with ClockSampler(0) as sampler:
+        if arguments.gemm_dtype in ("all", "e4m3"):
+            rows += gemm_sweep.sweep_fp8(ops, device, hbm_peak, fp8_peak, iterations=arguments.steps, with_quantise=True)
+        if arguments.gemm_dtype in ("all", "bf16"):
+            rows += gemm_sweep.sweep_bf16(ops, device, hbm_peak, bf16_peak, iterations=arguments.steps)
+    clocks = sampler.summary()
+    if ops.device_status()[0] != 0:
+        raise RuntimeError("a bounded wait ran out inside the benchmark")
+    ratios = [row["cublaslt_us"] / row["ours_us"] for row in rows if row["dtype"] == "e4m3" and "cublaslt_us" in row]
+    value = float(np.exp(np.mean(np.log(ratios)))) if ratios else None
+    launches = sum(arguments.steps * 5 for row in rows for key in row if key.startswith("ours") and key.endswith("_us"))
+    line = {
+        "metric": GEMM_METRIC, "value": value, "unit": "x cuBLASLt (geometric mean of time ratios, E4M3 points)",
+        "n_gpus": 1, "steps": arguments.steps, "warmup": 3, "ms_per_step": None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "e4m3 / bf16 operands, fp32 accumulation", "data": "synthetic",
+        "config": {"workload": GEMM_WORKLOAD, "batches": gemm_sweep.BATCHES,
+                   "l2": "weights rotate over >= 512 MB of distinct copies per site (four times the L2)"},
+        "peaks": {"hbm_gbs": hbm_peak, "hbm_source": peak_kind, "fp8_tflops": fp8_peak,
+                  "fp8_source": "cuBLASLt E4M3 8192^3 measured in this run", "bf16_tflops": bf16_peak},
+        "table": gemm_sweep.compact(rows), "rows": rows, "gpu_launches": launches, "clocks": clocks,
+        "seconds": time.perf_counter() - start,
+    }
+    print(json.dumps(line), flush=True)
 
 
 def _inv_freq():
@@ -939,8 +1067,7 @@ def run_prefill_arm(arguments, rank, world):
 
 def prefill_cpu_sample(model, batch, token_ids):
     """CPU oracle on a small mixed step of the same kind (one 64-token chunk on a 192-token prefix)."""
-    sys.path.insert(0, os.path.join(ROOT, "tests"))
-    import step_oracle
+    from oracle import step_oracle
     from lfm25_inference_b200 import workloads
     from oracle import oracle
     oracle.use_all_cores()
@@ -1070,6 +1197,11 @@ def main():
             run_step_reference_arm(arguments, rank)
         else:
             run_step_arm(arguments, rank, world)
+        return
+    if arguments.workload == "gemm":
+        if arguments.impl == "reference":
+            raise SystemExit("--impl reference times the decode workloads")
+        run_gemm_arm(arguments, rank, world)
         return
     if arguments.workload == "serving":
         if arguments.impl == "reference":

@@ -212,9 +212,11 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                 tma_load_2d(smem_base + block * stage_bytes + kWeightTileBytes, &x_map, bar_full + 8 * block,
                             static_cast<int32_t>((k_block0 + block) * kBlockK), 0);
             }
+            // (slot and phase are carried along: a division per K block is dozens of instructions on a lone thread)
+            uint32_t stage = 0;
+            uint32_t parity = 0;
             for (uint32_t block = ahead; block < k_count; ++block) {
-                const uint32_t stage = block % p.stages;
-                if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1, p.wait_limit_ns)) {
+                if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, parity, p.wait_limit_ns)) {
                     *abort_flag = 1;
                     record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 1);
                     break;
@@ -225,6 +227,10 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
                 mbar_arrive_expect_tx(bar, stage_bytes);
                 load_weights(dst, bar, k_offset);
                 tma_load_2d(dst + kWeightTileBytes, &x_map, bar, k_offset, 0);
+                if (++stage == p.stages) {
+                    stage = 0;
+                    parity ^= 1;
+                }
             }
         }
         __syncwarp();   // whole warps reach the CTA barriers below
@@ -241,24 +247,39 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
             const uint32_t idesc = (1u << 4) | formats | ((p.m_pad >> 3) << 17) | ((kTileN >> 4) << 24);
             const uint32_t accumulator = tmem_base + issuer * p.accumulator_columns;
             bool ok = true;
+            // slot, phase and descriptors are carried along instead of being derived from the block index: the loop of
+            // a lone thread is bound by its instruction count
+            constexpr uint64_t kDescriptorHigh = (static_cast<uint64_t>(1) << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+                                                 (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+            const uint32_t slot_step = p.issuers * stage_bytes;
+            const uint32_t ring_bytes = p.stages * stage_bytes;
+            uint32_t stage = issuer;                       // issuers <= stages and stages % issuers == 0
+            uint32_t slot = smem_base + issuer * stage_bytes;
+            uint32_t parity = 0;
+            uint32_t accumulate = 0;
             for (uint32_t block = issuer; block < k_count; block += p.issuers) {
-                const uint32_t stage = block % p.stages;
-                if (!mbar_wait_bounded(bar_full + 8 * stage, (block / p.stages) & 1, p.wait_limit_ns)) {
+                if (!mbar_wait_bounded(bar_full + 8 * stage, parity, p.wait_limit_ns)) {
                     if (!*abort_flag) record_wait_timeout(p.status, kTagGemmUmma, (blockIdx.x << 4) | 2);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                const uint32_t a_address = smem_base + stage * stage_bytes;
-                const uint64_t a_desc = smem_descriptor(a_address);
-                const uint64_t b_desc = smem_descriptor(a_address + kWeightTileBytes);
-#pragma unroll
-                for (uint32_t step = 0; step < kBlockK / kUmmaK; ++step) {
-                    // advancing 32 bytes inside the swizzle row = +2 in the (address >> 4) field
-                    umma<BF16>(accumulator, a_desc + step * 2, b_desc + step * 2, idesc,
-                               (block != issuer || step != 0) ? 1u : 0u);
-                }
+                const uint64_t a_desc = kDescriptorHigh | (slot >> 4);
+                const uint64_t b_desc = kDescriptorHigh | ((slot + kWeightTileBytes) >> 4);
+                // advancing 32 bytes inside the swizzle row = +2 in the (address >> 4) field
+                umma<BF16>(accumulator, a_desc, b_desc, idesc, accumulate);
+                umma<BF16>(accumulator, a_desc + 2, b_desc + 2, idesc, 1u);
+                umma<BF16>(accumulator, a_desc + 4, b_desc + 4, idesc, 1u);
+                umma<BF16>(accumulator, a_desc + 6, b_desc + 6, idesc, 1u);
                 umma_commit(bar_empty + 8 * stage);
+                accumulate = 1;
+                stage += p.issuers;
+                slot += slot_step;
+                if (stage >= p.stages) {
+                    stage -= p.stages;
+                    slot -= ring_bytes;
+                    parity ^= 1;
+                }
             }
             if (ok) {
                 umma_commit(bar_accumulator);

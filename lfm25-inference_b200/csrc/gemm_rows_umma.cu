@@ -229,8 +229,7 @@ gemm_rows_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gr
     const int32_t weight_row = static_cast<int32_t>(tile * (p.gated ? half : p.n_tile));
     const uint32_t ahead = k_count < p.stages ? k_count : p.stages;
     // a ring slot: [activation tile(s)][weight tile]
-    auto load_weights = [&](uint32_t block) {
-        const uint32_t stage = block % p.stages;
+    auto load_weights = [&](uint32_t block, uint32_t stage) {
         const uint32_t bar = bar_full + 8 * stage;
         const uint32_t dst = ring + stage * p.stage_bytes + x_bytes;
         const int32_t k_offset = static_cast<int32_t>((k_block0 + block) * kBlockK);
@@ -241,8 +240,7 @@ gemm_rows_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gr
             tma_load_2d(dst, &weight_map, bar, k_offset, weight_row);
         }
     };
-    auto load_activations = [&](uint32_t block) {
-        const uint32_t stage = block % p.stages;
+    auto load_activations = [&](uint32_t block, uint32_t stage) {
         const uint32_t bar = bar_full + 8 * stage;
         const uint32_t dst = ring + stage * p.stage_bytes;
         const int32_t k_offset = static_cast<int32_t>((k_block0 + block) * kBlockK);
@@ -269,7 +267,7 @@ gemm_rows_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gr
         for (uint32_t block = 0; block < ahead; ++block) {
             mbar_arrive_expect_tx(bar_full + 8 * block, p.stage_bytes);
             if (block != p.drop_block) {     // self-test: nothing completes the barrier of a dropped block
-                load_weights(block);
+                load_weights(block, block);
             }
         }
     }
@@ -287,20 +285,25 @@ gemm_rows_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gr
             pdl_wait();   // the activations are the predecessor's output
             for (uint32_t block = 0; block < ahead; ++block) {
                 if (block != p.drop_block) {
-                    load_activations(block);
+                    load_activations(block, block);
                 }
             }
+            // (slot and phase are carried along: a division per K block is dozens of instructions on a lone thread)
+            uint32_t stage = 0;
+            uint32_t parity = 0;
             for (uint32_t block = ahead; block < k_count; ++block) {
-                const uint32_t stage = block % p.stages;
-                if (*abort_flag ||
-                    !mbar_wait_bounded(bar_empty + 8 * stage, ((block / p.stages) - 1) & 1, p.wait_limit_ns)) {
+                if (*abort_flag || !mbar_wait_bounded(bar_empty + 8 * stage, parity, p.wait_limit_ns)) {
                     if (!*abort_flag) record_wait_timeout(p.status, kTagGemmRows, (blockIdx.x << 4) | 1);
                     *abort_flag = 1;
                     break;
                 }
                 mbar_arrive_expect_tx(bar_full + 8 * stage, p.stage_bytes);
-                load_weights(block);
-                load_activations(block);
+                load_weights(block, stage);
+                load_activations(block, stage);
+                if (++stage == p.stages) {
+                    stage = 0;
+                    parity ^= 1;
+                }
             }
         }
     } else if (warp < kFirstEpilogueWarp) {
@@ -314,32 +317,47 @@ gemm_rows_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gr
             bool ok = true;
             // The operands of a slot were written by TMA and announced through the slot's mbarrier, which is all the
             // ordering tcgen05.mma needs; the abort flag is only looked at when a wait runs out.
+            // slot, phase and descriptors are carried along instead of being derived from the block index: the loop of
+            // a lone thread is bound by its instruction count (a division alone is dozens of instructions)
+            constexpr uint64_t kDescriptorHigh = (static_cast<uint64_t>(1) << 16) | (static_cast<uint64_t>(1024 >> 4) << 32) |
+                                                 (static_cast<uint64_t>(1) << 46) | (static_cast<uint64_t>(2) << 61);
+            const uint32_t slot_step = p.issuers * p.stage_bytes;
+            const uint32_t ring_bytes = p.stages * p.stage_bytes;
+            uint32_t stage = issuer;                       // issuers <= stages and stages % issuers == 0
+            uint32_t slot = ring + issuer * p.stage_bytes;
+            uint32_t parity = 0;
+            uint32_t accumulate = 0;
             for (uint32_t block = issuer; block < k_count; block += p.issuers) {
-                const uint32_t stage = block % p.stages;
-                if (!mbar_wait_bounded(bar_full + 8 * stage, (block / p.stages) & 1, p.wait_limit_ns)) {
+                if (!mbar_wait_bounded(bar_full + 8 * stage, parity, p.wait_limit_ns)) {
                     if (!*abort_flag) record_wait_timeout(p.status, kTagGemmRows, (blockIdx.x << 4) | 2);
                     *abort_flag = 1;
                     ok = false;
                     break;
                 }
-                const uint32_t slot = ring + stage * p.stage_bytes;
-                const uint64_t a_desc = smem_descriptor(slot);
-                const uint64_t b_desc = smem_descriptor(slot + x_bytes);
-                const uint32_t accumulate = block != issuer ? 1u : 0u;
-#pragma unroll
-                for (uint32_t step = 0; step < kKSteps; ++step) {
-                    // advancing 32 bytes inside the swizzle row = +2 in the (address >> 4) field
-                    umma_rows<BF16>(accumulator, a_desc + step * 2, b_desc + step * 2, idesc, accumulate | step);
-                }
+                const uint64_t a_desc = kDescriptorHigh | (slot >> 4);
+                const uint64_t b_desc = kDescriptorHigh | ((slot + x_bytes) >> 4);
+                // advancing 32 bytes inside the swizzle row = +2 in the (address >> 4) field
+                umma_rows<BF16>(accumulator, a_desc, b_desc, idesc, accumulate);
+                umma_rows<BF16>(accumulator, a_desc + 2, b_desc + 2, idesc, 1u);
+                umma_rows<BF16>(accumulator, a_desc + 4, b_desc + 4, idesc, 1u);
+                umma_rows<BF16>(accumulator, a_desc + 6, b_desc + 6, idesc, 1u);
                 if (p.a_tiles == 2) {
-                    const uint64_t a_desc_second = smem_descriptor(slot + x_tile_bytes);
-#pragma unroll
-                    for (uint32_t step = 0; step < kKSteps; ++step) {
-                        umma_rows<BF16>(accumulator + p.accumulator_columns, a_desc_second + step * 2, b_desc + step * 2,
-                                        idesc, accumulate | step);
-                    }
+                    const uint64_t a_desc_second = kDescriptorHigh | ((slot + x_tile_bytes) >> 4);
+                    const uint32_t second = accumulator + p.accumulator_columns;
+                    umma_rows<BF16>(second, a_desc_second, b_desc, idesc, accumulate);
+                    umma_rows<BF16>(second, a_desc_second + 2, b_desc + 2, idesc, 1u);
+                    umma_rows<BF16>(second, a_desc_second + 4, b_desc + 4, idesc, 1u);
+                    umma_rows<BF16>(second, a_desc_second + 6, b_desc + 6, idesc, 1u);
                 }
                 umma_commit(bar_empty + 8 * stage);
+                accumulate = 1;
+                stage += p.issuers;
+                slot += slot_step;
+                if (stage >= p.stages) {
+                    stage -= p.stages;
+                    slot -= ring_bytes;
+                    parity ^= 1;
+                }
             }
             if (ok) {
                 umma_commit(bar_accumulator);

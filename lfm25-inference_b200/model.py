@@ -78,9 +78,13 @@ class LayerState:
 class RandomModel:
     """Random-init weights of the architecture plus per-layer caches, resident on `device`."""
 
-    def __init__(self, seed: int, device, num_pages: int, num_request_slots: int, fp8_policy: bool = True,
+    def __init__(self, seed: int, device, num_pages: int, num_request_slots: int, fp8_policy=True,
                  pack_qkv: bool = True):
-        """`pack_qkv`: the query, key and value matrices of a layer share one [3072, 2048] allocation (as a loader
+        """`fp8_policy`: True = the reference's promoted policy (the 16 sites of FP8_GATE_UP_LAYERS, FP8_DOWN_LAYERS and
+        the LM head), False = every site in BF16, or an `fp8_policy.Fp8PrecisionPolicy` loaded from a file in the
+        reference's schema: its enabled MLP / LM-head sites are promoted and its static activation scales are used
+        (the weight scales are taken from the random weights themselves: amax / 448).
+        `pack_qkv`: the query, key and value matrices of a layer share one [3072, 2048] allocation (as a loader
         that concatenates them would leave them), which lets the executor run the three projections as one GEMM;
         False keeps three separate allocations (three GEMMs, the reference's layout)."""
         self.device = device
@@ -93,6 +97,15 @@ class RandomModel:
 
         def ones(count):
             return torch.ones(count, dtype=torch.bfloat16, device=device)
+
+        loaded = fp8_policy if not isinstance(fp8_policy, bool) else None
+        gate_up_layers = loaded.layers_with("gate_up") if loaded else (FP8_GATE_UP_LAYERS if fp8_policy else ())
+        down_layers = loaded.layers_with("down") if loaded else (FP8_DOWN_LAYERS if fp8_policy else ())
+        head_promoted = loaded.lm_head_enabled() if loaded else bool(fp8_policy)
+
+        def activation_amax(site: str, default: float) -> float:
+            entry = loaded.site(site) if loaded else None
+            return entry.activation_scale.clip_amax if entry is not None else default
 
         self.embedding = normal(VOCAB, HIDDEN)
         self.final_norm = ones(HIDDEN)
@@ -126,14 +139,15 @@ class RandomModel:
                                                           device=device)
             layer.linears["gate_up"] = Linear(normal(2 * FFN, HIDDEN))
             layer.linears["down"] = Linear(normal(HIDDEN, FFN))
-            if fp8_policy and index in FP8_GATE_UP_LAYERS:
-                _promote(layer.linears["gate_up"], ACTIVATION_AMAX_NORMALIZED)
-            if fp8_policy and index in FP8_DOWN_LAYERS:
-                _promote(layer.linears["down"], ACTIVATION_AMAX_GATED)
+            if index in gate_up_layers:
+                _promote(layer.linears["gate_up"], activation_amax(f"layers.{index}.mlp.gate_up",
+                                                                   ACTIVATION_AMAX_NORMALIZED))
+            if index in down_layers:
+                _promote(layer.linears["down"], activation_amax(f"layers.{index}.mlp.down", ACTIVATION_AMAX_GATED))
             self.layers.append(layer)
         self.lm_head = Linear(self.embedding)
-        if fp8_policy:
-            _promote(self.lm_head, ACTIVATION_AMAX_NORMALIZED)
+        if head_promoted:
+            _promote(self.lm_head, activation_amax("lm_head", ACTIVATION_AMAX_NORMALIZED))
         self._build_struct()
 
     def _build_struct(self) -> None:

@@ -31,7 +31,8 @@ _size = ctypes.c_size_t
 def build() -> str:
     """Compile the oracle (and, where the reference tree is present, its kernels)."""
     subprocess.run(["make", "-C", _HERE, "all"], check=True, capture_output=True)
-    reference_root = os.environ.get("REFERENCE_ROOT", "/root/reference")
+    # the reference checkout: REFERENCE_ROOT, else a directory `reference` beside this repository
+    reference_root = os.environ.get("REFERENCE_ROOT") or os.path.normpath(os.path.join(_HERE, "..", "..", "reference"))
     if os.path.isdir(os.path.join(reference_root, "kernels")):
         subprocess.run(["make", "-C", _HERE, "ref", f"REFERENCE_ROOT={reference_root}"],
                        check=True, capture_output=True)

@@ -3,7 +3,7 @@ DecodeExecutor::forward_prepared, src/model/decode_executor.rs:183-443), built f
 TEST INFRASTRUCTURE ONLY."""
 import numpy as np
 
-from oracle import oracle
+from . import oracle
 
 
 def to_bits(tensor):

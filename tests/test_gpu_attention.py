@@ -91,7 +91,9 @@ def test_splitk_lengths_257_65(device):
         assert np.allclose(got[..., 0][live], want[..., 0][live], atol=1e-4, rtol=0)
         assert np.allclose(got[..., 1][live], want[..., 1][live], rtol=1e-2)
         assert np.allclose(got[..., 2:][live], want[..., 2:][live], atol=3e-2, rtol=1e-2)
-        assert np.array_equal(oracle.merge_splitk(got), oracle.merge_splitk(got))
+        # the oracle's merge of this library's records against its merge of its own records: same identity, so the
+        # bound is the one between the records
+        assert_close_bf16(oracle.merge_splitk(got), oracle.merge_splitk(want), 3e-2, 1e-2)
         assert_close_bf16(bits_of(output), oracle.merge_splitk(got), 1e-6, 2 ** -7)
 
 

@@ -8,7 +8,7 @@ from conftest import bits_of
 from lfm25_inference_b200 import model as lfm_model
 from lfm25_inference_b200 import ops, workloads
 from oracle import oracle
-import step_oracle
+from oracle import step_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -198,3 +198,149 @@ def test_served_step_equals_upload_replay_download(device):
     for a, b in zip(run(False), run(True)):
         assert np.array_equal(a, b)
     assert ops.device_status()[0] == 0
+
+
+HEADLINE_ROWS = 128
+
+
+def headline_batch(seed, steps):
+    """128 sequences with contexts of a few hundred tokens in a small page pool: the batch size of the benchmark's
+    headline configuration, where the step takes other branches than at 3 or 16 rows (cuBLASLt for the BF16 sites,
+    the gated Gate/Up in the batch-major tcgen05 kernel, unsplit attention in the device-built token order)."""
+    pages = 6144
+    batch = workloads.ragged_decode_batch(seed, HEADLINE_ROWS, 100, 500, pages, steps + 1)
+    token_ids = np.random.default_rng(seed).integers(0, lfm_model.VOCAB, size=HEADLINE_ROWS).astype(np.uint32)
+    return batch, token_ids, pages
+
+
+@pytest.mark.parametrize("use_fp8", [True, False])
+def test_headline_batch_against_the_reference_kernels(device, use_fp8):
+    """One eager step at 128 rows against the same step assembled from the reference's own kernels and cuBLASLt
+    (src/model/decode_executor.rs:183-443) on a twin model: logits within the end-to-end bound of the smaller cases,
+    greedy ids equal wherever the reference's top two logits are further apart than that bound, appended K rows and
+    convolution states within the same bound, no bounded wait expired."""
+    from oracle import refkernels, refstep
+    if not refkernels.available():
+        pytest.skip("oracle/_ref holds no compiled reference kernels")
+    batch, token_ids, pages = headline_batch(31, 2)
+    ours, theirs = (lfm_model.RandomModel(17, device, pages, HEADLINE_ROWS) for _ in range(2))
+    ours.fill_caches(18)
+    theirs.fill_caches(18)
+    blaslt = ops.BlasLt()
+    executor = lfm_model.DecodeExecutor(blaslt, HEADLINE_ROWS)
+    device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0), token_ids,
+                                         int(batch.contexts.max()) + 4)
+    executor.forward(ours, device_batch, use_fp8=use_fp8, advance=False)
+    got = oracle.bf16_to_f32(executor.logits(HEADLINE_ROWS)).astype(np.float64)
+    got_sampled = executor.sampled(HEADLINE_ROWS)
+    reference = refstep.ReferenceKernelStep(theirs, HEADLINE_ROWS, use_fp8=use_fp8)
+    slots = torch.from_numpy(batch.physical_slots(0).astype(np.int64)).to(device)
+    reference.forward(device_batch.token_ids, device_batch.positions, device_batch.request_slots, slots,
+                      device_batch.block_tables)
+    torch.cuda.synchronize()
+    want = oracle.bf16_to_f32(bits_of(reference.logits)).astype(np.float64)
+    want_sampled = reference.sampled.cpu().numpy().view(np.uint32)
+    bound = 0.15 if use_fp8 else 0.05
+    assert np.abs(got - want).max() <= bound * np.abs(want).max()
+    cosine = (got * want).sum() / (np.linalg.norm(got) * np.linalg.norm(want))
+    assert cosine >= (0.99 if use_fp8 else 0.999)
+    assert np.array_equal(got_sampled, oracle.argmax_rows_bf16(executor.logits(HEADLINE_ROWS)))
+    ordered = np.sort(want, axis=1)
+    decided = ordered[:, -1] - ordered[:, -2] > 2 * np.abs(got - want).max(axis=1)
+    assert decided.sum() >= HEADLINE_ROWS // 2
+    assert np.array_equal(got_sampled[decided], want_sampled[decided])
+    for mine, other in zip(ours.layers, theirs.layers):
+        name = "key_cache" if mine.is_attention else "conv_state"
+        a = oracle.bf16_to_f32(bits_of(mine.tensors[name])).astype(np.float64)
+        b = oracle.bf16_to_f32(bits_of(other.tensors[name])).astype(np.float64)
+        assert np.abs(a - b).max() <= bound * max(1.0, np.abs(b).max())
+    assert ops.device_status()[0] == 0
+    executor.close()
+    blaslt.close()
+
+
+def test_headline_batch_graph_replay_matches_eager_steps(device):
+    """Three self-feeding steps at 128 rows from the captured graph against the same steps launched eagerly on a twin
+    model: sampled ids of every step, final logits, positions, K caches and convolution states bit for bit."""
+    steps = 3
+    batch, token_ids, pages = headline_batch(33, steps)
+
+    def run(use_graph):
+        with torch.cuda.stream(torch.cuda.Stream()):
+            model = lfm_model.RandomModel(19, device, pages, HEADLINE_ROWS)
+            model.fill_caches(20)
+            blaslt = ops.BlasLt()
+            executor = lfm_model.DecodeExecutor(blaslt, HEADLINE_ROWS)
+            device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0),
+                                                 token_ids, int(batch.contexts.max()) + steps + 1)
+            history = []
+            executor.forward(model, device_batch, use_fp8=True, advance=False)
+            history.append(executor.sampled(HEADLINE_ROWS))
+            for _ in range(steps):
+                if use_graph:
+                    executor.step_graph(model, device_batch, use_fp8=True)
+                else:
+                    executor.forward(model, device_batch, use_fp8=True, advance=True)
+                history.append(executor.sampled(HEADLINE_ROWS))
+            captures = executor.graph_captures()
+            state = [executor.logits(HEADLINE_ROWS), device_batch.positions.cpu().numpy().view(np.uint32)]
+            state += [bits_of(layer.tensors["key_cache" if layer.is_attention else "conv_state"])
+                      for layer in model.layers]
+            torch.cuda.current_stream().synchronize()
+            executor.close()
+            blaslt.close()
+            return history, state, captures
+
+    eager_history, eager_state, _ = run(False)
+    graph_history, graph_state, captures = run(True)
+    assert captures == 1
+    for a, b in zip(eager_history, graph_history):
+        assert np.array_equal(a, b)
+    for a, b in zip(eager_state, graph_state):
+        assert np.array_equal(a, b)
+    assert np.array_equal(eager_state[1], batch.positions(0) + steps)
+    assert ops.device_status()[0] == 0
+
+
+def test_changed_batch_buffers_capture_again(device):
+    """A captured step bakes in every pointer and stride of the batch: after the block tables move to a wider
+    allocation (same contents, larger stride) under the same token-id buffer, the next calls run eagerly once and
+    capture again instead of replaying the stale graph, and the results stay those of the eager step."""
+    tokens, pages, steps = 6, 64, 8
+    batch, token_ids = small_batch(device, 41, tokens, pages, steps)
+    with torch.cuda.stream(torch.cuda.Stream()):
+        model = lfm_model.RandomModel(5, device, pages, 8)
+        model.fill_caches(6)
+        twin = lfm_model.RandomModel(5, device, pages, 8)
+        twin.fill_caches(6)
+        blaslt = ops.BlasLt()
+        executor = lfm_model.DecodeExecutor(blaslt, 8)
+        reference = lfm_model.DecodeExecutor(blaslt, 8)
+        context = int(batch.contexts.max()) + steps + 1
+        device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0),
+                                             token_ids, context)
+        twin_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0),
+                                           token_ids, context)
+        for _ in range(3):                                   # eager warm-up, capture, replay
+            executor.step_graph(model, device_batch, use_fp8=True)
+            reference.forward(twin, twin_batch, use_fp8=True, advance=True)
+        assert executor.graph_captures() == 1
+        assert np.array_equal(executor.sampled(tokens), reference.sampled(tokens))
+        # the tables move: twice the stride, unassigned tail entries, a new allocation
+        wide = np.full((batch.block_tables.shape[0], 2 * batch.block_tables.shape[1]), 0xFFFFFFFF, dtype=np.uint32)
+        wide[:, :batch.block_tables.shape[1]] = batch.block_tables
+        moved = torch.from_numpy(wide.view(np.int32).copy()).to(device)
+        device_batch.block_tables = moved
+        device_batch.struct.block_tables = moved.data_ptr()
+        device_batch.struct.block_table_stride = wide.shape[1]
+        for _ in range(3):
+            executor.step_graph(model, device_batch, use_fp8=True)
+            reference.forward(twin, twin_batch, use_fp8=True, advance=True)
+        assert executor.graph_captures() == 2
+        assert np.array_equal(executor.sampled(tokens), reference.sampled(tokens))
+        assert np.array_equal(device_batch.positions.cpu().numpy(), twin_batch.positions.cpu().numpy())
+        torch.cuda.current_stream().synchronize()
+        assert ops.device_status()[0] == 0
+        executor.close()
+        reference.close()
+        blaslt.close()

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-import step_oracle
+from oracle import step_oracle
 from conftest import bits_of
 from lfm25_inference_b200 import model as lfm_model
 from lfm25_inference_b200 import ops, workloads
