@@ -496,22 +496,6 @@ def run_gpu_arm(arguments, rank, world):
         except Exception as error:           # the comparison is optional; the metric does not depend on it
             reference_kernels = {"error": str(error)[:120]}
 
-    # the E4M3 half of the decode GEMM sweep, as a compact table in the line (rank 0 only; after the timed regions)
-    gemm_table = None
-    if rank == 0 and not arguments.skip_gemm:
-        try:
-            from lfm25_inference_b200 import gemm_sweep
-            fp8_peak = gemm_sweep.measure_fp8_peak(device)
-            with torch.cuda.stream(stream):
-                rows = gemm_sweep.sweep_fp8(ops, device, peaks()[0], fp8_peak, iterations=32, with_gated=False)
-            gemm_table = {"fp8_tensor_peak_tflops": round(fp8_peak, 1),
-                          "fp8_tensor_peak_source": "cuBLASLt E4M3 8192^3 measured in this run",
-                          "ring": "weight copies >= 512 MB per site (HBM-cold), CUDA graph of 32 launches x 5 replays",
-                          "points": gemm_sweep.compact(rows)}
-        except Exception as error:       # the table is an annex of the line; the metric does not depend on it
-            gemm_table = {"error": str(error)[:160]}
-
-    per_rank = gather_over_ranks([total_ms / steps, submit_seconds * 1e3 / steps], device, world)
     total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
     config0 = None
     if rank == 0:
@@ -776,6 +760,22 @@ def run_step_arm(arguments, rank, world):
             except Exception as error:
                 reference_kernels["step_error"] = str(error)[:160]
 
+    # the E4M3 half of the decode GEMM sweep, as a compact table in the line (rank 0 only; after the timed regions)
+    gemm_table = None
+    if rank == 0 and not arguments.skip_gemm:
+        try:
+            from lfm25_inference_b200 import gemm_sweep
+            fp8_peak = gemm_sweep.measure_fp8_peak(device)
+            with torch.cuda.stream(stream):
+                rows = gemm_sweep.sweep_fp8(ops, device, peaks()[0], fp8_peak, iterations=32, with_gated=False)
+            gemm_table = {"fp8_tensor_peak_tflops": round(fp8_peak, 1),
+                          "fp8_tensor_peak_source": "cuBLASLt E4M3 8192^3 measured in this run",
+                          "ring": "weight copies >= 512 MB per site (HBM-cold), CUDA graph of 32 launches x 5 replays",
+                          "points": gemm_sweep.compact(rows)}
+        except Exception as error:       # the table is an annex of the line; the metric does not depend on it
+            gemm_table = {"error": str(error)[:160]}
+
+    per_rank = gather_over_ranks([total_ms / steps, submit_seconds * 1e3 / steps], device, world)
     total_ms, e2e_ms = max_over_ranks([total_ms, e2e_seconds * 1e3], device, world)
 
     if rank == 0:
