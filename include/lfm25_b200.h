@@ -63,7 +63,10 @@ int32_t lfm25_device_status(void* stream, uint32_t out[4]);
  * (LFM25_* variables read in src/model/lfm2_base.rs and src/engine/serving/radix_owner.rs).  Each switch has a
  * default, may be preset by the environment variable LFM25_<NAME> (read once) and changed at run time here; a
  * change applies to launches issued afterwards and is not recorded in CUDA graphs that are already captured.
- *   pdl, fused_append, fused_silu, kv_evict_first, engine_graph        0 | 1 (default 1)
+ *   pdl, fused_silu, kv_evict_first, engine_graph                      0 | 1 (default 1)
+ *   fused_append           0 two launches | 1 one kernel | 2 auto (default): how the decode executor runs an
+ *                          attention layer -- QK-norm + RoPE + append as a kernel of their own before the attention
+ *                          kernel, or inside it; auto asks lfm25_decode_one_kernel_preferred()
  *   fused_silu_bf16        0 | 1 (default 0): SiLU * Up in the epilogue of a BF16 Gate/Up linear as well
  *   hybrid_attention       0 auto | 1 umma | 2 mma
  *   fp8_gemm_path          0 auto | 1 stream | 2 umma (weight-major) | 3 generic | 4 rows (batch-major)
@@ -279,6 +282,13 @@ size_t lfm25_splitk_workspace_elements(size_t maximum_tokens);
  * for a decode batch (1 = use the unsplit kernel).  Re-derived for B200: the reference's table
  * was measured on a 36-SM laptop part. */
 size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_tokens, size_t page_size);
+
+/* Replaces should_use_mok_one_kernel (src/ops/mok_dispatch.rs:7-27): 1 when a decode step of `batch_size`
+ * sequences with at most `context_tokens` cached tokens should run lfm25_fused_ragged_paged_attention_decode_lfm2_bf16
+ * (one kernel), 0 when it should run lfm25_qk_norm_rope_kv_write_decode followed by the attention kernel.  The
+ * thresholds are measured on a B200 (the table is in the definition); with the `pdl` switch off the reference's own
+ * thresholds apply.  Page sizes other than 16 answer 0. */
+int32_t lfm25_decode_one_kernel_preferred(size_t page_size, size_t context_tokens, size_t batch_size);
 
 /* ------------------------------------------------------------------------------------------
  * FP8 (E4M3) producers

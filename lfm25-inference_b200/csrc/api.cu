@@ -301,6 +301,9 @@ int32_t lfm25_qk_norm_rope_kv_write_decode(void* stream, const lfm25_qk_postproc
                  LFM25_ERR_NULL_POINTER, "fused QK postprocess received a null device pointer");
     lfm25::QkPostprocessArgs args;
     args.query = l.query.ptr;
+    args.query_out = l.query.ptr;
+    args.query_token_stride = 32 * 64;
+    args.kv_token_stride = 8 * 64;
     args.key = l.key.ptr;
     args.value = l.value.ptr;
     args.query_norm = l.query_norm.ptr;
@@ -655,6 +658,42 @@ size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_toke
         splits /= 2;
     }
     return splits;
+}
+
+int32_t lfm25_decode_one_kernel_preferred(size_t page_size, size_t context_tokens, size_t batch_size) {
+    if (page_size != 16 || batch_size == 0) {
+        return 0;
+    }
+    if (lfm25::option(lfm25::kOptPdl) == 0) {
+        // Without programmatic dependent launch the boundary between the append and the attention kernel costs a
+        // full launch gap, as it did where the reference measured its table (src/ops/mok_dispatch.rs:12-18).
+        return (context_tokens <= 16 || (context_tokens <= 32 && batch_size <= 32) ||
+                (context_tokens <= 64 && batch_size <= 8))
+                   ? 1
+                   : 0;
+    }
+    // Measured on a B200 inside the whole decode step (graph replay, 6 attention layers; microseconds per attention
+    // layer that the one kernel costs more (+) or less (-) than QK-norm + RoPE + append followed by attention):
+    //   sequences   ctx 16   ctx 64   ctx 128   ctx 512   ctx 2048   ctx 128..4096 (ragged)
+    //        1       +0.7     +0.4     +0.4      +0.4      +0.8       +0.8
+    //        4       +0.2     -0.2     -0.2      -0.3      -0.2       -0.4
+    //        8       +0.2     +0.3     +0.2      -0.1      +1.8       +1.8
+    //       16       -0.4     -0.6     -0.6      +2.0      +1.8       -1.5
+    //       32       -1.5     -0.9     -2.1      +2.4      +2.1       -2.2
+    //       64       +0.8     +1.2     +1.5      +3.6      +2.1       +2.5
+    //      128       +2.5     +2.3     +3.2      +2.5      +1.9       -0.7
+    // The dependent launch hides the boundary between the two kernels, so the one kernel wins only where its
+    // per-CTA prologue (norm, rotation and append before the first page can be read) is hidden as well: 16 to 32
+    // sequences with short contexts, and batches whose maximum context is long, which in serving means a ragged
+    // batch -- the CTAs are handed out longest context first, so the short sequences' prologues run in the shadow
+    // of the long ones.  (One attention layer alone, both routes in a graph of 32 repetitions, uniform contexts:
+    // two launches / one kernel = 10.2 / 14.2 us at 128 sequences x 16 tokens, 89.6 / 90.5 us at 128 x 2048,
+    // 5.0 / 5.1 us at 1 x 40.)
+    const bool mid_batch = batch_size >= 16 && batch_size <= 32;
+    const bool large_batch = batch_size > 64;
+    return ((mid_batch && (context_tokens <= 128 || context_tokens > 2048)) || (large_batch && context_tokens > 2048))
+               ? 1
+               : 0;
 }
 
 int32_t lfm25_quantize_bf16_e4m3(void* stream, lfm25_slice input, lfm25_slice output, size_t numel, float scale) {

@@ -262,12 +262,15 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             LFM25_TRY(linear_decode(self, layer.conv_output, self->post_operator, self->operator_output, tokens,
                                     use_fp8));
         } else {
-            const bool fused_append = lfm25::option(lfm25::kOptFusedAppend) != 0;
+            // 0 = two launches, 1 = one kernel, 2 = whichever the measured table prefers for this batch
+            const int64_t route = lfm25::option(lfm25::kOptFusedAppend);
+            const bool fused_append =
+                route == 2 ? lfm25_decode_one_kernel_preferred(16, batch->max_context_tokens, tokens) != 0 : route != 0;
             // One GEMM for the three projections when their BF16 matrices are adjacent in memory (q | k | v rows of
-            // one [3072, 2048] allocation): the outputs then sit side by side in `wide`, [tokens, 3072], which only
-            // the one-kernel attention reads (it takes token strides).
+            // one [3072, 2048] allocation): the outputs then sit side by side in `wide`, [tokens, 3072]; the one-kernel
+            // attention and the QK-norm + RoPE + append kernel both take token strides.
             const uint16_t* query_weight = static_cast<const uint16_t*>(layer.query.bf16);
-            const bool packed_qkv = fused_append && query_weight != nullptr &&
+            const bool packed_qkv = query_weight != nullptr &&
                                     !(use_fp8 && (layer.query.fp8.data || layer.key.fp8.data || layer.value.fp8.data)) &&
                                     layer.key.bf16 == query_weight + kQueryWidth * kHidden &&
                                     layer.value.bf16 == query_weight + (kQueryWidth + kKvWidth) * kHidden &&
@@ -337,7 +340,30 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 }
                 LFM25_TRY(lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(stream, &fused));
             } else {
-            {
+            if (packed_qkv) {
+                // the packed projection is read in place; the rotated query goes to the dense array attention reads
+                RegionTimer timer(self, LFM25_REGION_APPEND);
+                const uint16_t* packed_rows = static_cast<const uint16_t*>(self->wide);
+                lfm25::QkPostprocessArgs strided;
+                strided.query = packed_rows;
+                strided.query_out = self->query;
+                strided.query_token_stride = kPackedWidth;
+                strided.kv_token_stride = kPackedWidth;
+                strided.key = packed_rows + kQueryWidth;
+                strided.value = packed_rows + kQueryWidth + kKvWidth;
+                strided.query_norm = layer.query_norm;
+                strided.key_norm = layer.key_norm;
+                strided.inv_freq = static_cast<const float*>(model->inv_freq);
+                strided.position_ids = static_cast<const uint32_t*>(batch->positions);
+                strided.slot_mapping = static_cast<const int64_t*>(batch->physical_slots);
+                strided.key_cache = layer.key_cache;
+                strided.value_cache = layer.value_cache;
+                strided.num_tokens = tokens;
+                strided.num_pages = model->num_pages;
+                strided.eps = model->norm_eps;
+                const cudaError_t status = lfm25::launch_qk_norm_rope_kv_write_decode(stream, strided);
+                if (status != cudaSuccess) return cuda_failure(status, "QK postprocess launch failed");
+            } else {
                 RegionTimer timer(self, LFM25_REGION_APPEND);
                 LFM25_TRY(lfm25_qk_norm_rope_kv_write_decode(stream, &post));
             }

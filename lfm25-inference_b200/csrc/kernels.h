@@ -74,7 +74,10 @@ cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const vo
                                   size_t num_pages);
 
 struct QkPostprocessArgs {
-    void* query;
+    const void* query;            // [tokens] rows of 32 x 64, `query_token_stride` elements apart
+    void* query_out;              // dense [tokens, 32, 64]; may alias `query` when that is dense
+    size_t query_token_stride;
+    size_t kv_token_stride;       // of `key` and `value` rows (8 x 64 each)
     const void* key;
     const void* value;
     const void* query_norm;

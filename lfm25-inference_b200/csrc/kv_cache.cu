@@ -49,12 +49,15 @@ kv_cache_write_kernel(const uint4* __restrict__ key, const uint4* __restrict__ v
 }
 
 // One CTA per token, 10 warps: warps 0..7 each take 4 query heads, warps 8..9 each take 4 KV
-// heads (K normalised + rotated into the arena, V copied).  Every warp evaluates the 32 RoPE
+// heads (K normalised + rotated into the arena, V copied).  The three inputs take a token stride (in elements), so
+// they may be columns of one packed [tokens, 3072] projection; the rotated query goes to a dense [tokens, 32, 64]
+// array, which may be the input itself.  Every warp evaluates the 32 RoPE
 // coefficients of the token itself (one sincosf per lane), so the CTA needs no barrier.
 constexpr uint32_t kPostWarps = 10;
 __global__ void __launch_bounds__(kPostWarps * 32)
-qk_norm_rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ query, const __nv_bfloat16* __restrict__ key,
-                                    const __nv_bfloat16* __restrict__ value,
+qk_norm_rope_kv_write_decode_kernel(const __nv_bfloat16* query, __nv_bfloat16* query_out,
+                                    const __nv_bfloat16* __restrict__ key, const __nv_bfloat16* __restrict__ value,
+                                    size_t query_token_stride, size_t kv_token_stride,
                                     const __nv_bfloat16* __restrict__ query_norm,
                                     const __nv_bfloat16* __restrict__ key_norm, const float* __restrict__ inv_freq,
                                     const uint32_t* __restrict__ position_ids,
@@ -87,12 +90,13 @@ qk_norm_rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ query, const __n
         const __nv_bfloat16 weight1 = query_norm[lane + kHalfDim];
 #pragma unroll
         for (uint32_t index = 0; index < 4; ++index) {
-            __nv_bfloat16* row = query + (token * kQHeads + warp * 4 + index) * kHeadDim;
+            const __nv_bfloat16* row = query + token * query_token_stride + (warp * 4 + index) * kHeadDim;
+            __nv_bfloat16* row_out = query_out + (token * kQHeads + warp * 4 + index) * kHeadDim;
             __nv_bfloat16 out0, out1;
             norm_rope(__bfloat162float(row[lane]), __bfloat162float(row[lane + kHalfDim]), weight0, weight1,
                       sin_value, cos_value, eps, out0, out1);
-            row[lane] = out0;
-            row[lane + kHalfDim] = out1;
+            row_out[lane] = out0;
+            row_out[lane + kHalfDim] = out1;
         }
     } else {
         const __nv_bfloat16 weight0 = key_norm[lane];
@@ -100,7 +104,7 @@ qk_norm_rope_kv_write_decode_kernel(__nv_bfloat16* __restrict__ query, const __n
 #pragma unroll
         for (uint32_t index = 0; index < 4; ++index) {
             const uint32_t head = (warp - 8) * 4 + index;
-            const size_t source = (token * kKvHeads + head) * kHeadDim;
+            const size_t source = token * kv_token_stride + head * kHeadDim;
             const size_t destination = ((page * kKvHeads + head) * kPageSize + offset) * kHeadDim;
             __nv_bfloat16 out0, out1;
             norm_rope(__bfloat162float(key[source + lane]), __bfloat162float(key[source + lane + kHalfDim]), weight0,
@@ -126,8 +130,9 @@ cudaError_t launch_kv_cache_write(cudaStream_t stream, const void* key, const vo
 
 cudaError_t launch_qk_norm_rope_kv_write_decode(cudaStream_t stream, const QkPostprocessArgs& args) {
     return launch_kernel(qk_norm_rope_kv_write_decode_kernel, static_cast<unsigned int>(args.num_tokens), kPostWarps * 32, 0, stream, 1, 
-        static_cast<__nv_bfloat16*>(args.query), static_cast<const __nv_bfloat16*>(args.key),
-        static_cast<const __nv_bfloat16*>(args.value), static_cast<const __nv_bfloat16*>(args.query_norm),
+        static_cast<const __nv_bfloat16*>(args.query), static_cast<__nv_bfloat16*>(args.query_out),
+        static_cast<const __nv_bfloat16*>(args.key), static_cast<const __nv_bfloat16*>(args.value),
+        args.query_token_stride, args.kv_token_stride, static_cast<const __nv_bfloat16*>(args.query_norm),
         static_cast<const __nv_bfloat16*>(args.key_norm), args.inv_freq, args.position_ids, args.slot_mapping,
         static_cast<__nv_bfloat16*>(args.key_cache), static_cast<__nv_bfloat16*>(args.value_cache), args.num_tokens,
         args.num_pages, args.eps);

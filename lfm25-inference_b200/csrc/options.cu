@@ -23,7 +23,7 @@ struct Entry {
 
 Entry g_options[kOptCount] = {
     {"pdl", "LFM25_PDL", 1, 0, 1},
-    {"fused_append", "LFM25_FUSED_APPEND", 1, 0, 1},
+    {"fused_append", "LFM25_FUSED_APPEND", 2, 0, 2},
     {"fused_silu", "LFM25_FUSED_SILU", 1, 0, 1},
     {"fused_silu_bf16", "LFM25_FUSED_SILU_BF16", 0, 0, 1},
     {"kv_evict_first", "LFM25_KV_EVICT_FIRST", 1, 0, 1},

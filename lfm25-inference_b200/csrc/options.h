@@ -4,7 +4,9 @@
 //
 //   name                 values                                default   meaning
 //   pdl                  0 | 1                                 1         programmatic dependent launch on every kernel
-//   fused_append         0 | 1                                 1         decode layers: QK-norm + RoPE + append inside attention
+//   fused_append         0 two launches | 1 one kernel | 2 auto  2       decode layers: QK-norm + RoPE + append as a kernel
+//                                                                        of their own, or inside attention; auto = by
+//                                                                        lfm25_decode_one_kernel_preferred()
 //   fused_silu           0 | 1                                 1         E4M3 Gate/Up: SiLU(gate) * up in the GEMM epilogue
 //   fused_silu_bf16      0 | 1                                 0         the same for a Gate/Up site that stays in BF16
 //   kv_evict_first       0 | 1                                 1         L2 evict-first hint on the KV page stream

@@ -120,6 +120,11 @@ def splitk_decode_splits(num_tokens: int, maximum_context_tokens: int, page_size
     return int(library().lfm25_splitk_decode_splits(num_tokens, maximum_context_tokens, page_size))
 
 
+def decode_one_kernel_preferred(page_size: int, context_tokens: int, batch_size: int) -> bool:
+    """Reference: should_use_mok_one_kernel (src/ops/mok_dispatch.rs:7-27), with thresholds measured on a B200."""
+    return bool(library().lfm25_decode_one_kernel_preferred(page_size, context_tokens, batch_size))
+
+
 def paged_attention_fast_lfm2_bf16_into(query, key_cache, value_cache, block_table, position_ids, output,
                                         page_size: int = 16) -> None:
     """One sequence (reference: src/ops/attention_async_fast.rs:49-83)."""

@@ -148,6 +148,37 @@ def test_workspace_and_split_policy():
             assert splits(tokens, context, 16) in (1, 2, 4, 8)
 
 
+def test_one_kernel_dispatch_and_options():
+    """The one-kernel / two-launch choice (the reference's table: src/ops/mok_dispatch.rs:7-27, tests :29-54) and
+    the option table: unknown names and values out of range are refused, a set value reads back."""
+    library = _abi.library()
+    prefers = library.lfm25_decode_one_kernel_preferred
+    assert library.lfm25_set_option(b"pdl", 1) == _abi.OK
+    assert prefers(16, 64, 16) == 1 and prefers(16, 128, 32) == 1 and prefers(16, 4096, 32) == 1
+    assert prefers(16, 4096, 128) == 1               # a long maximum context in a large batch: a ragged batch
+    assert prefers(16, 40, 1) == 0                   # the dependent launch hides the boundary: two launches
+    assert prefers(16, 16, 128) == 0 and prefers(16, 2048, 128) == 0 and prefers(16, 4096, 64) == 0
+    assert prefers(16, 512, 16) == 0 and prefers(16, 64, 8) == 0
+    assert prefers(32, 16, 8) == 0 and prefers(16, 16, 0) == 0
+    try:
+        assert library.lfm25_set_option(b"pdl", 0) == _abi.OK
+        # without it, the reference's own thresholds
+        assert prefers(16, 16, 128) == 1 and prefers(16, 32, 32) == 1 and prefers(16, 64, 8) == 1
+        assert prefers(16, 32, 33) == 0 and prefers(16, 64, 9) == 0 and prefers(16, 65, 1) == 0
+    finally:
+        assert library.lfm25_set_option(b"pdl", 1) == _abi.OK
+    value = ctypes.c_int64(-1)
+    assert library.lfm25_get_option(b"fused_append", ctypes.byref(value)) == _abi.OK and value.value == 2
+    assert library.lfm25_set_option(b"fused_append", 3) == _abi.ERR_INVALID_ARGUMENT
+    assert library.lfm25_set_option(b"no_such_switch", 1) == _abi.ERR_INVALID_ARGUMENT
+    assert library.lfm25_get_option(b"no_such_switch", ctypes.byref(value)) == _abi.ERR_INVALID_ARGUMENT
+    assert library.lfm25_set_option(None, 1) == _abi.ERR_NULL_POINTER
+    assert library.lfm25_set_option(b"decode_splits", 4) == _abi.OK
+    assert library.lfm25_splitk_decode_splits(128, 4096, 16) == 4
+    assert library.lfm25_set_option(b"decode_splits", 0) == _abi.OK
+    assert library.lfm25_splitk_decode_splits(128, 4096, 16) == 1
+
+
 def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_abi, "_library", None)
     monkeypatch.setattr(_abi, "LIBRARY_PATH", str(tmp_path / "absent.so"))

@@ -20,9 +20,13 @@ def small_batch(device, seed, tokens, pages, steps):
     return batch, token_ids
 
 
+@pytest.mark.parametrize("route", [0, 1], ids=["two_launches", "one_kernel"])
 @pytest.mark.parametrize("pack_qkv", [True, False])
 @pytest.mark.parametrize("use_fp8", [False, True])
-def test_one_step_against_the_oracle(device, use_fp8, pack_qkv):
+def test_one_step_against_the_oracle(device, library_option, use_fp8, pack_qkv, route):
+    """Both routes of an attention layer (QK-norm + RoPE + append as a kernel of their own, or inside attention),
+    with the three projections packed into one GEMM or apart."""
+    library_option("fused_append", route)
     tokens, pages = 3, 32
     model = lfm_model.RandomModel(3, device, pages, 4, pack_qkv=pack_qkv)
     model.fill_caches(4)
