@@ -77,6 +77,10 @@ def parse_arguments():
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     parser.add_argument("--skip-gemm", action="store_true", help="step workload: omit the gemm_roofline table")
     parser.add_argument("--gemm-dtype", default="all", choices=["all", "e4m3", "bf16"], help="gemm workload: which sites")
+    parser.add_argument("--gemm-sites", nargs="*", default=None,
+                        help="gemm workload: only these sites (gate_up down lm_head qkv proj conv_in); a profiling aid")
+    parser.add_argument("--gemm-batches", nargs="*", type=int, default=None, help="gemm workload: only these M")
+    parser.add_argument("--no-cublaslt", action="store_true", help="gemm workload: leave the cuBLASLt columns out")
     parser.add_argument("--requests", type=int, default=192, help="serving workload: requests in the trace")
     parser.add_argument("--rate", type=float, default=32.0, help="serving workload: Poisson arrival rate, requests/s")
     parser.add_argument("--skip-reference-kernels", action="store_true",
@@ -891,9 +895,13 @@ def run_gemm_arm(arguments, rank, world):
     start = time.perf_counter()
     with ClockSampler(0) as sampler:
         if arguments.gemm_dtype in ("all", "e4m3"):
-            rows += gemm_sweep.sweep_fp8(ops, device, hbm_peak, fp8_peak, iterations=arguments.steps, with_quantise=True)
+            rows += gemm_sweep.sweep_fp8(ops, device, hbm_peak, fp8_peak, iterations=arguments.steps, with_quantise=True,
+                                         batches=arguments.gemm_batches, sites=arguments.gemm_sites,
+                                         with_library=not arguments.no_cublaslt)
         if arguments.gemm_dtype in ("all", "bf16"):
-            rows += gemm_sweep.sweep_bf16(ops, device, hbm_peak, bf16_peak, iterations=arguments.steps)
+            rows += gemm_sweep.sweep_bf16(ops, device, hbm_peak, bf16_peak, iterations=arguments.steps,
+                                          batches=arguments.gemm_batches, sites=arguments.gemm_sites,
+                                          with_library=not arguments.no_cublaslt)
     clocks = sampler.summary()
     if ops.device_status()[0] != 0:
         raise RuntimeError("a bounded wait ran out inside the benchmark")
