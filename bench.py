@@ -815,8 +815,12 @@ def run_step_arm(arguments, rank, world):
             "kv_gbs": kv_bytes / attention_seconds / 1e9,
             "regions_eager_ms_per_step": {name: ms / profile_steps for name, (ms, _) in regions.items()},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_source": peak_kind,
-                         "kernel": "ragged_decode_attention_kernel + merge_splitk_kernel (one attention layer)",
+                         "frac": achieved / hbm_peak, "traffic": ATTENTION_TRAFFIC_FACTOR * (kv_bytes + other_bytes),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 16-sequence launch = "
+                                           "1.001 x its algorithmic bytes, scaled by the keys read "
+                                           "(profiles/ragged_decode_attention_config1.md)",
+                         "peak_source": peak_kind,
+                         "kernel": "ragged_decode_attention_kernel, unsplit at 128 sequences (one attention layer)",
                          "algorithmic_bytes_per_launch": kv_bytes + other_bytes},
             "cpu_baseline": {"value": cpu_tokens, "unit": "tok/s", "cores": threads, "kind": "port",
                              "sample": cpu_description},
