@@ -81,6 +81,10 @@ def parse_arguments():
                         help="gemm workload: only these sites (gate_up down lm_head qkv proj conv_in); a profiling aid")
     parser.add_argument("--gemm-batches", nargs="*", type=int, default=None, help="gemm workload: only these M")
     parser.add_argument("--no-cublaslt", action="store_true", help="gemm workload: leave the cuBLASLt columns out")
+    parser.add_argument("--dispatch", action="store_true",
+                        help="serving workload: ONE trace for all replicas, handed out request by request by a front "
+                             "(a thread of rank 0) through the library's dispatcher; --requests and --rate are then "
+                             "per replica and are multiplied by the number of replicas")
     parser.add_argument("--requests", type=int, default=192, help="serving workload: requests in the trace")
     parser.add_argument("--rate", type=float, default=32.0, help="serving workload: Poisson arrival rate, requests/s")
     parser.add_argument("--skip-reference-kernels", action="store_true",
@@ -1122,6 +1126,127 @@ def serving_trace(seed, count, rate_per_s):
     return requests
 
 
+def run_dispatched_serving_arm(arguments, rank, world):
+    """Config 4 over replicas: one engine per GPU, one trace for the whole job, a front on rank 0 that assigns every
+    request at its arrival time with the library's dispatcher (prefix-hash affinity, bounded imbalance).  The only
+    channel between the processes is a host key-value store; no GPU collective runs.  `value` = tokens generated by
+    all replicas / time from the start of the trace until the last replica drained."""
+    import threading
+    import torch
+    import torch.distributed as dist
+
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("gloo")                 # host-side control plane only: barrier, store, gather
+        store = dist.PrefixStore("lfm25-serving/", dist.distributed_c10d._get_default_store())
+    else:
+        store = dist.HashStore()
+    entry.load_package()
+    from lfm25_inference_b200 import model as lfm_model
+    from lfm25_inference_b200 import serving
+
+    slots, max_sequence = 64, 8192 + 512 + 16
+    pages = slots * ((max_sequence + 15) // 16) // 2 + 4096
+    stream = torch.cuda.Stream(device=device)
+    with torch.cuda.stream(stream):
+        model = lfm_model.RandomModel(4, device, pages, slots)          # replicas hold the same weights
+        engine = serving.ServingEngine(model, device, max_slots=slots, max_sequence_tokens=max_sequence,
+                                       max_prefill_tokens=512, radix_pages=4096, checkpoint_capacity=128,
+                                       use_fp8=not arguments.no_fp8, admission_control=arguments.admission_control)
+        engine.calibrate()
+        for _ in range(max(arguments.warmup, 1)):
+            serving.run_trace(engine, serving_trace(100 + rank, 8, 1000.0))
+        before = engine.snapshot()
+        trace = serving_trace(4, arguments.requests * world, arguments.rate * world)     # the same on every rank
+        if world > 1:
+            dist.barrier()
+        if rank == 0:
+            store.set("origin", repr(time.time() + 0.25))
+        origin = float(store.get("origin").decode())
+        front_result = {}
+        front = None
+        if rank == 0:
+            front = threading.Thread(target=lambda: front_result.update(serving.run_front(store, world, trace, origin)))
+            front.start()
+        with ClockSampler(local_rank) as sampler:
+            result = serving.run_replica(engine, store, rank, trace, origin)
+        clocks = sampler.summary()
+        if front is not None:
+            front.join()
+        after = engine.snapshot()
+    result["stats"] = {name: after["stats"][name] - before["stats"][name] for name in before["stats"]}
+    result["prefix_cache"] = {name: after["prefix_cache"][name] - before["prefix_cache"][name]
+                              for name in ("hits", "misses")}
+    result["clocks"] = clocks
+    gathered = [result]
+    if world > 1:
+        gathered = [None] * world if rank == 0 else None
+        dist.gather_object(result, gathered, dst=0)
+    if rank == 0:
+        print(json.dumps(dispatched_serving_line(arguments, world, trace, gathered, front_result)), flush=True)
+    engine.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def dispatched_serving_line(arguments, world, trace, gathered, front_result):
+    """The JSON line of the dispatched serving run from the replicas' records (host arithmetic only)."""
+    records = [record for replica in gathered for record in replica["requests"]]
+    finished = [record for record in records if not record["rejected"] and record["generated"] > 0]
+    rejected = [record for record in records if record["rejected"]]
+    makespan_ms = max(replica["drained_us"] for replica in gathered) / 1e3
+    generated = sum(record["generated"] for record in finished)
+    prompt_tokens = sum(record["prompt_len"] for record in finished)
+    ttft = np.array([record["ttft_us"] for record in finished]) / 1e3
+    tpot = np.array([record["tpot_us"] for record in finished if record["tpot_us"] > 0]) / 1e3
+    hits = sum(replica["prefix_cache"]["hits"] for replica in gathered)
+    misses = sum(replica["prefix_cache"]["misses"] for replica in gathered)
+    reused = sum(replica["stats"]["reused_prompt_tokens"] for replica in gathered)
+    steps = sum(replica["stats"]["steps"] for replica in gathered)
+    value = generated / (makespan_ms * 1e-3)
+    per_replica = []
+    for replica in gathered:
+        mine = [record for record in replica["requests"] if not record["rejected"]]
+        per_replica.append({
+            "replica": replica["replica"], "requests": len(replica["requests"]),
+            "generated_tokens": sum(record["generated"] for record in mine),
+            "drained_ms": replica["drained_us"] / 1e3, "steps": replica["stats"]["steps"],
+            "mixed_steps": replica["stats"]["mixed_steps"],
+            "gpu_busy_frac": replica["stats"]["gpu_ms"] / max(replica["drained_us"] / 1e3, 1e-9),
+            "prefix_hits": replica["prefix_cache"]["hits"], "prefix_misses": replica["prefix_cache"]["misses"],
+            "sm_mhz": replica["clocks"].get("sm_mhz"), "clock_reasons": replica["clocks"].get("reasons")})
+    return {
+        "metric": SERVING_METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": 1,
+        "warmup": arguments.warmup, "ms_per_step": makespan_ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16" if arguments.no_fp8 else "bf16+e4m3", "data": "synthetic",
+        "config": {"workload": SERVING_WORKLOAD + "-dispatched", "requests": len(trace),
+                   "rate_per_s": arguments.rate * world, "request_slots_per_replica": 64,
+                   "maximum_prefill_tokens": 512, "page_size": 16, "prompt_sigma": 1.0, "replicas": world,
+                   "dispatch": "one trace, front on rank 0, lfm25_dispatcher_assign_bounded (prefix hash of the first "
+                               "256 prompt tokens, slack 8192 tokens), host key-value store, no collective",
+                   "step": "native engine loop per replica, one host sync per step"},
+        "requests_per_s": len(finished) / (makespan_ms * 1e-3),
+        "admission_control": bool(arguments.admission_control), "rejected_requests": len(rejected),
+        "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+        "ttft_p50_ms": float(np.percentile(ttft, 50)), "ttft_p95_ms": float(np.percentile(ttft, 95)),
+        "tpot_p50_ms": float(np.percentile(tpot, 50)), "tpot_p95_ms": float(np.percentile(tpot, 95)),
+        "engine_steps": steps,
+        "prefix_cache": {"hits": hits, "misses": misses, "hit_rate": hits / max(hits + misses, 1),
+                         "reused_prompt_tokens": reused, "reused_frac": reused / max(prompt_tokens, 1)},
+        "per_replica": per_replica,
+        "front": {"handed": front_result.get("handed"),
+                  "outstanding_tokens_at_end": front_result.get("outstanding_tokens")},
+        "roofline": None, "cpu_baseline": None,
+        "e2e": {"value": value, "unit": "tok/s",
+                "h2d_bytes_per_step": 4 * (prompt_tokens + generated) * 3 // max(steps, 1),
+                "d2h_bytes_per_step": 4 * 64, "steps": steps},
+        "gpu_launches": None, "clocks": gathered[0]["clocks"],
+    }
+
+
 def run_serving_arm(arguments, rank, world):
     """One "step" = the whole trace.  `value` = generated tokens / makespan, measured end to end through the serving
     loop (token ids in host memory in, sampled ids in host memory out, every step synchronised), so `e2e` is the same
@@ -1218,7 +1343,10 @@ def main():
     if arguments.workload == "serving":
         if arguments.impl == "reference":
             raise SystemExit("--impl reference times the decode workloads")
-        run_serving_arm(arguments, rank, world)
+        if arguments.dispatch:
+            run_dispatched_serving_arm(arguments, rank, world)
+        else:
+            run_serving_arm(arguments, rank, world)
         return
     if arguments.workload == "prefill":
         if arguments.impl == "reference":

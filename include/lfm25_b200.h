@@ -792,6 +792,10 @@ int32_t lfm25_dispatcher_create(size_t replicas, lfm25_dispatcher** out);
 void lfm25_dispatcher_destroy(lfm25_dispatcher* dispatcher);
 int32_t lfm25_dispatcher_assign(lfm25_dispatcher* dispatcher, uint64_t prefix_hash, uint32_t has_prefix,
                                 uint64_t estimated_tokens); /* replica index, or a negative error */
+/* The same with bounded imbalance: the prefix's home replica takes the request only while its outstanding tokens
+ * exceed those of the least-loaded live replica by at most slack_tokens; otherwise the least-loaded replica does. */
+int32_t lfm25_dispatcher_assign_bounded(lfm25_dispatcher* dispatcher, uint64_t prefix_hash, uint32_t has_prefix,
+                                        uint64_t estimated_tokens, uint64_t slack_tokens);
 void lfm25_dispatcher_complete(lfm25_dispatcher* dispatcher, size_t replica, uint64_t tokens);
 void lfm25_dispatcher_mark_failed(lfm25_dispatcher* dispatcher, size_t replica);
 uint64_t lfm25_dispatcher_load(const lfm25_dispatcher* dispatcher, size_t replica);

@@ -334,6 +334,8 @@ PROTOTYPES = {
     "lfm25_dispatcher_create": (ctypes.c_int32, [_size, _P(ctypes.c_void_p)]),
     "lfm25_dispatcher_destroy": (None, [ctypes.c_void_p]),
     "lfm25_dispatcher_assign": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32, ctypes.c_uint64]),
+    "lfm25_dispatcher_assign_bounded": (ctypes.c_int32, [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32,
+                                                         ctypes.c_uint64, ctypes.c_uint64]),
     "lfm25_dispatcher_complete": (None, [ctypes.c_void_p, _size, ctypes.c_uint64]),
     "lfm25_dispatcher_mark_failed": (None, [ctypes.c_void_p, _size]),
     "lfm25_dispatcher_load": (ctypes.c_uint64, [ctypes.c_void_p, _size]),

@@ -123,9 +123,16 @@ class Dispatcher:
         self._handle = ctypes.c_void_p()
         check(library().lfm25_dispatcher_create(replicas, ctypes.byref(self._handle)))
 
-    def assign(self, estimated_tokens: int, prefix_hash: int | None = None) -> int:
-        replica = library().lfm25_dispatcher_assign(self._handle, prefix_hash or 0, int(prefix_hash is not None),
-                                                    estimated_tokens)
+    def assign(self, estimated_tokens: int, prefix_hash: int | None = None, slack_tokens: int | None = None) -> int:
+        """`slack_tokens`: the prefix's home replica may be at most this many outstanding tokens busier than the
+        idlest replica, else the request spills to the idlest one (None = the home always takes it)."""
+        if slack_tokens is None:
+            replica = library().lfm25_dispatcher_assign(self._handle, prefix_hash or 0, int(prefix_hash is not None),
+                                                        estimated_tokens)
+        else:
+            replica = library().lfm25_dispatcher_assign_bounded(self._handle, prefix_hash or 0,
+                                                                int(prefix_hash is not None), estimated_tokens,
+                                                                slack_tokens)
         check(min(replica, 0))
         return int(replica)
 

@@ -264,6 +264,31 @@ int32_t lfm25_dispatcher_assign(lfm25_dispatcher* self, uint64_t prefix_hash, ui
     return static_cast<int32_t>(best);
 }
 
+int32_t lfm25_dispatcher_assign_bounded(lfm25_dispatcher* self, uint64_t prefix_hash, uint32_t has_prefix,
+                                        uint64_t estimated_tokens, uint64_t slack_tokens) {
+    const size_t count = self->replicas.size();
+    size_t least = count;
+    for (size_t index = 0; index < count; ++index) {
+        if (self->replicas[index].alive && (least == count || self->replicas[index].load < self->replicas[least].load)) {
+            least = index;
+        }
+    }
+    if (least == count) {
+        return lfm25::report_error(LFM25_ERR_INVALID_ARGUMENT, "no live replica");
+    }
+    size_t best = least;
+    if (has_prefix) {
+        // the prefix's home keeps the request while it is not more than `slack_tokens` busier than the idlest
+        // replica; past that the request spills there (and that replica's prefix cache learns the prefix)
+        const size_t home = static_cast<size_t>(prefix_hash % count);
+        if (self->replicas[home].alive && self->replicas[home].load - self->replicas[least].load <= slack_tokens) {
+            best = home;
+        }
+    }
+    self->replicas[best].load += estimated_tokens;
+    return static_cast<int32_t>(best);
+}
+
 void lfm25_dispatcher_complete(lfm25_dispatcher* self, size_t replica, uint64_t tokens) {
     if (replica < self->replicas.size()) {
         uint64_t& load = self->replicas[replica].load;

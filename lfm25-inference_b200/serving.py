@@ -10,6 +10,7 @@ the caller built.
 from __future__ import annotations
 
 import ctypes
+import hashlib
 import time
 from dataclasses import dataclass
 
@@ -154,3 +155,117 @@ def run_trace(engine: ServingEngine, requests: list[Request]) -> dict:
     stats = {name: after["stats"][name] - before[name] for name in before}
     return {"makespan_us": makespan_us, "wall_s": time.perf_counter() - origin, "requests": finished, "stats": stats,
             "prefix_cache": after["prefix_cache"], "pool": after["pool"]}
+
+
+# ------------------------------------------------------------------------------ one trace over several replicas
+#
+# One process per GPU, each with its own engine; one front (a thread of rank 0) that walks a single trace in real
+# time and hands every request, at its arrival time, to a replica chosen by the library's dispatcher (least
+# outstanding tokens, prefix-hash affinity with bounded imbalance).  Requests travel as indices into the trace, which
+# every process builds from the same seed; the channel is a key-value store of the host (torch.distributed's store:
+# no GPU collective anywhere).  Keys: "n/<replica>" = requests handed to the replica so far, "q/<replica>/<k>" = index
+# of the k-th of them, "done/<replica>" = tokens the replica has finished with (prompt + generated of completed or
+# rejected requests), "closed" = set once the last request is handed out.
+
+PREFIX_HASH_TOKENS = 256
+
+
+def prefix_hash(prompt: np.ndarray, tokens: int = PREFIX_HASH_TOKENS):
+    """64-bit digest of the first `tokens` prompt ids; None for a shorter prompt (nothing worth an affinity)."""
+    if len(prompt) < tokens:
+        return None
+    data = np.ascontiguousarray(prompt[:tokens], dtype=np.uint32).tobytes()
+    return int.from_bytes(hashlib.blake2b(data, digest_size=8).digest(), "little")
+
+
+def estimated_tokens(request: Request) -> int:
+    return int(len(request.prompt) + request.max_new_tokens)
+
+
+def run_front(store, replicas: int, requests: list[Request], origin_s: float, slack_tokens: int = 8192,
+              clock=time.time, sleep=time.sleep) -> dict:
+    """Hands out `requests` in arrival order, each at origin_s + arrival, and returns the assignment
+    {request_id: replica} with the dispatcher's view of the loads at the end."""
+    from .cache import Dispatcher
+    dispatcher = Dispatcher(replicas)
+    seen_done = [0] * replicas
+    handed = [0] * replicas
+    assignment = {}
+    hashes = [prefix_hash(request.prompt) for request in requests]
+    order = sorted(range(len(requests)), key=lambda index: requests[index].arrival_us)
+    for index in order:
+        request = requests[index]
+        wait = origin_s + request.arrival_us * 1e-6 - clock()
+        if wait > 0:
+            sleep(wait)
+        for replica in range(replicas):                       # completions reported since the last look
+            done = int(store.add(f"done/{replica}", 0))
+            if done > seen_done[replica]:
+                dispatcher.complete(replica, done - seen_done[replica])
+                seen_done[replica] = done
+        replica = dispatcher.assign(estimated_tokens(request), prefix_hash=hashes[index], slack_tokens=slack_tokens)
+        store.set(f"q/{replica}/{handed[replica]}", str(index))
+        handed[replica] += 1
+        store.add(f"n/{replica}", 1)
+        assignment[request.request_id] = replica
+    store.set("closed", "1")
+    return {"assignment": assignment, "handed": handed,
+            "outstanding_tokens": [dispatcher.load(replica) for replica in range(replicas)]}
+
+
+def run_replica(engine, store, replica: int, requests: list[Request], origin_s: float, clock=time.time,
+                idle_sleep_s: float = 0.0002) -> dict:
+    """The loop of one replica: takes the requests the front has handed to it, steps its engine in real time and
+    reports finished tokens back.  `engine` needs submit / step / active / queued (a ServingEngine)."""
+    records = {}
+    taken = 0
+    closed = False
+    first_step_us = None
+    while True:
+        count = int(store.add(f"n/{replica}", 0))
+        while taken < count:
+            request = requests[int(store.get(f"q/{replica}/{taken}"))]
+            taken += 1
+            records[request.request_id] = {"request_id": request.request_id, "prompt_len": len(request.prompt),
+                                           "arrival_us": request.arrival_us, "times_us": [], "tokens": 0,
+                                           "reused_tokens": 0, "rejected": None, "replica": replica,
+                                           "estimated_tokens": estimated_tokens(request)}
+            engine.submit(request)
+        if not engine.queued() and not engine.active():
+            if closed:
+                # one more look at the queue after seeing "closed": the front sets it after its last hand-out
+                if int(store.add(f"n/{replica}", 0)) == taken:
+                    break
+                continue
+            closed = store.check(["closed"])
+            time.sleep(idle_sleep_s)
+            continue
+        now_us = int((clock() - origin_s) * 1e6)
+        if first_step_us is None:
+            first_step_us = now_us
+        events, _ = engine.step(now_us)
+        finished_tokens = 0
+        for request_id, _, finished, time_us, reused, rejected in events:
+            record = records[request_id]
+            if rejected:
+                record["rejected"] = REJECT_REASONS.get(rejected, str(rejected))
+                finished_tokens += record["estimated_tokens"]
+                continue
+            record["times_us"].append(time_us)
+            record["tokens"] += 1
+            record["reused_tokens"] = reused
+            if finished:
+                finished_tokens += record["estimated_tokens"]
+        if finished_tokens:
+            store.add(f"done/{replica}", finished_tokens)
+    last_us = int((clock() - origin_s) * 1e6)
+    out = []
+    for record in records.values():
+        times = record.pop("times_us")
+        gaps = np.diff(times) if len(times) > 1 else np.array([])
+        record["generated"] = record.pop("tokens")
+        record["ttft_us"] = int(times[0] - record["arrival_us"]) if times else None
+        record["last_token_us"] = int(times[-1]) if times else None
+        record["tpot_us"] = float(gaps.mean()) if gaps.size else 0.0
+        out.append(record)
+    return {"replica": replica, "requests": out, "first_step_us": first_step_us, "drained_us": last_us}

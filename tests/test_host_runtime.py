@@ -157,3 +157,19 @@ def test_dispatcher_balances_and_survives_a_replica_failure():
         dispatcher.mark_failed(replica)
     with pytest.raises(Lfm25Error, match="no live replica"):
         dispatcher.assign(1)
+
+
+def test_dispatcher_bounded_affinity_spills_to_the_idlest_replica():
+    """lfm25_dispatcher_assign_bounded: the prefix's home keeps a request while it is at most `slack` tokens busier
+    than the idlest replica, then the idlest one takes it; requests without a prefix go to the idlest replica."""
+    dispatcher = Dispatcher(4)
+    home = 1234567 % 4
+    placed = [dispatcher.assign(100, prefix_hash=1234567, slack_tokens=250) for _ in range(3)]
+    assert placed == [home] * 3 and dispatcher.load(home) == 300
+    spilled = dispatcher.assign(100, prefix_hash=1234567, slack_tokens=250)
+    assert spilled != home and dispatcher.load(spilled) == 100
+    assert dispatcher.assign(10, slack_tokens=250) not in (home, spilled)
+    dispatcher.complete(home, 300)
+    assert dispatcher.assign(100, prefix_hash=1234567, slack_tokens=250) == home
+    dispatcher.mark_failed(home)
+    assert dispatcher.assign(100, prefix_hash=1234567, slack_tokens=250) != home

@@ -41,3 +41,113 @@ def test_single_replica_needs_no_process_group():
     import bench
     assert bench.max_over_ranks([3.0, 4.0], torch.device("cpu"), 1) == [3.0, 4.0]
     assert bench.aggregate_throughput(64, 1, 2.0) == pytest.approx(32000.0)
+
+
+class _FakeEngine:
+    """The engine's interface with no GPU behind it: every active request yields one token per step."""
+
+    def __init__(self):
+        self.waiting, self.running = [], {}
+
+    def submit(self, request):
+        self.waiting.append(request)
+
+    def queued(self):
+        return len(self.waiting)
+
+    def active(self):
+        return len(self.running)
+
+    def step(self, now_us):
+        for request in self.waiting:
+            self.running[request.request_id] = [request, 0]
+        self.waiting = []
+        events = []
+        for request_id in list(self.running):
+            request, produced = self.running[request_id]
+            produced += 1
+            finished = produced == request.max_new_tokens
+            events.append((request_id, 7, finished, now_us, 0, 0))
+            if finished:
+                del self.running[request_id]
+            else:
+                self.running[request_id][1] = produced
+        return events, 0.0
+
+
+def _dispatch_trace():
+    import numpy as np
+    from lfm25_inference_b200 import serving
+    rng = np.random.default_rng(11)
+    shared = rng.integers(0, 65536, size=256).astype(np.uint32)
+    requests = []
+    for index in range(24):
+        prompt = rng.integers(0, 65536, size=int(rng.integers(16, 600))).astype(np.uint32)
+        if index % 2 == 0:
+            prompt = np.concatenate([shared, prompt])
+        requests.append(serving.Request(index, prompt, int(rng.integers(2, 9)), index * 4000))
+    return requests
+
+
+def _dispatch_rank_main(rank, world, port, results):
+    import threading
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from lfm25_inference_b200 import serving
+    store = dist.PrefixStore("trace/", dist.distributed_c10d._get_default_store())
+    trace = _dispatch_trace()
+    dist.barrier()
+    if rank == 0:
+        store.set("origin", repr(time.time() + 0.05))
+    origin = float(store.get("origin").decode())
+    front_result = {}
+    front = None
+    if rank == 0:
+        front = threading.Thread(target=lambda: front_result.update(serving.run_front(store, world, trace, origin,
+                                                                                      slack_tokens=1500)))
+        front.start()
+    mine = serving.run_replica(_FakeEngine(), store, rank, trace, origin)
+    if front is not None:
+        front.join()
+    dist.barrier()
+    done = [int(store.add(f"done/{replica}", 0)) for replica in range(world)]
+    results[rank] = (mine, dict(front_result), done)
+    dist.destroy_process_group()
+
+
+def test_one_trace_is_dispatched_over_two_replicas():
+    """The front on rank 0 hands a single trace out over two replica processes through the host store: every request
+    is served exactly once, on the replica the front chose, each replica reports back what it finished, and the
+    requests that share a prefix stay together until their home replica is too far ahead of the other."""
+    sys.path.insert(0, ROOT)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from lfm25_inference_b200 import serving
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    port = 31500 + os.getpid() % 2000
+    mp.spawn(_dispatch_rank_main, args=(world, port, results), nprocs=world, join=True)
+    trace = _dispatch_trace()
+    front = results[0][1]
+    served = {}
+    for rank in range(world):
+        mine, _, done = results[rank]
+        assert mine["replica"] == rank
+        for record in mine["requests"]:
+            assert record["request_id"] not in served
+            served[record["request_id"]] = rank
+            request = trace[record["request_id"]]
+            assert record["generated"] == request.max_new_tokens and record["rejected"] is None
+            assert record["ttft_us"] is not None and record["ttft_us"] >= 0
+        assert done[rank] == sum(serving.estimated_tokens(trace[record["request_id"]]) for record in mine["requests"])
+    assert served == front["assignment"] and len(served) == len(trace)
+    assert front["handed"] == [sum(1 for rank in served.values() if rank == replica) for replica in range(world)]
+    assert min(front["handed"]) >= 4                               # both replicas worked
+    shared_home = serving.prefix_hash(trace[0].prompt) % world
+    shared_placed = [served[index] for index in range(0, len(trace), 2)]
+    assert shared_placed.count(shared_home) > len(shared_placed) // 2
