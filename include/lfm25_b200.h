@@ -197,8 +197,13 @@ int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream, const lfm25_
  * device looks up the array's device address; make that call before any stream capture begins.  All calls
  * share the one array and it keeps whatever the last call wrote, so calls must not overlap on the GPU: keep
  * them ordered on one stream.  Nothing needs clearing between calls: each call writes every record it later
- * reads.  This entry point has no counterpart in the reference, whose split-K path always takes a
- * caller-allocated `partials` tensor. */
+ * combines into an output row.  A token that has no result (request slot outside the block tables, position
+ * outside its row, unassigned page, a wait that ran out -- the last one also shows in lfm25_device_status) keeps
+ * the output row the caller passed in, in this entry point and in the one with a caller workspace alike: its
+ * records carry a "no result" mark, so values of an earlier call never reach the output.  If a call fails with
+ * LFM25_ERR_CUDA the cached device address is dropped and looked up again by the next call (a host that reset
+ * the device gets a valid address again).  This entry point has no counterpart in the reference, whose split-K
+ * path always takes a caller-allocated `partials` tensor. */
 int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(void* stream,
                                                              const lfm25_fast_ragged_attention_launch* launch,
                                                              size_t num_splits);
@@ -326,15 +331,19 @@ typedef struct lfm25_fp8_linear_config {
 
 /* Replaces BlasLt::linear_fp8_scaled (src/cuda/blaslt/mod.rs:212-298, cuBLASLt descriptor
  * src/cuda/blaslt/fp8.rs:312-353): out[M,N] = bf16(output_scale * x[M,K] * weight[N,K]^T), E4M3 codes in,
- * fp32 accumulation.  No plan cache and no workspace are needed.  Kernel choice: M <= 8 weight-streaming
- * mma.sync kernel, 9..256 tcgen05/TMEM kernel, other shapes a generic kernel; the environment variable
- * LFM25_FP8_GEMM_PATH=stream|umma|generic overrides it for measurements. */
+ * fp32 accumulation.  No plan cache and no workspace are needed.  Kernel choice without a handle: M <= 8
+ * weight-streaming mma.sync kernel, 9..256 tcgen05/TMEM kernel, other shapes a generic kernel; the switch
+ * fp8_gemm_path (lfm25_set_option) overrides it for measurements. */
 int32_t lfm25_linear_fp8_scaled(void* stream, lfm25_slice x, lfm25_slice weight, lfm25_slice out,
                                 const lfm25_fp8_linear_config* config);
 
 /* Replaces the `BlasLt` object (src/cuda/blaslt/mod.rs:30-70): bound to one stream, owns the 32 MiB device
- * workspace that cuBLASLt uses for the BF16 linears, allocated once at creation.  The FP8 linear through the
- * handle is the stateless one on the handle's stream. */
+ * workspace that cuBLASLt uses for the BF16 linears and the exchange buffer through which the tcgen05 kernels
+ * combine the partial sums of a split K axis, both allocated once at creation.  A handle serves ONE stream at a
+ * time: two launches through the same handle must not overlap on the GPU (different streams, or graphs replayed
+ * concurrently), because they would share the workspace and the exchange buffer; give every stream its own handle.
+ * If a bounded wait runs out in one CTA of a split-K cluster, the whole cluster stores nothing (the CTA publishes
+ * the event to its partners before the cluster barrier) and lfm25_device_status reports it. */
 typedef struct lfm25_blaslt lfm25_blaslt;
 int32_t lfm25_blaslt_create(void* stream, lfm25_blaslt** out);
 void lfm25_blaslt_destroy(lfm25_blaslt* handle);
@@ -641,6 +650,12 @@ int32_t lfm25_kv_allocator_pin_cached_pages(lfm25_kv_allocator* allocator, const
 int32_t lfm25_kv_allocator_retain_pages(lfm25_kv_allocator* allocator, const uint32_t* pages, size_t count);
 int64_t lfm25_kv_allocator_grow_sequence(lfm25_kv_allocator* allocator, size_t current_tokens, size_t target_tokens,
                                          uint32_t* block_table, size_t block_table_len);
+/* How many physical pages are missing for growing `sequences` sequences from current_tokens[i] to target_tokens[i]
+ * all together (0 = every one of them fits); nothing is allocated.  A step that grows several sequences asks this
+ * first, so that a shortage is reported before any block-table row has been changed.  No counterpart in the
+ * reference, which grows the sequences of a step one by one (src/model/lfm2_base.rs:215-260). */
+int64_t lfm25_kv_allocator_pages_short(const lfm25_kv_allocator* allocator, const size_t* current_tokens,
+                                       const size_t* target_tokens, size_t sequences);
 void lfm25_kv_allocator_release_sequence(lfm25_kv_allocator* allocator, size_t tokens, uint32_t* block_table,
                                          size_t block_table_len);
 void lfm25_kv_allocator_snapshot(const lfm25_kv_allocator* allocator, lfm25_kv_pool_snapshot* out);

@@ -278,6 +278,7 @@ PROTOTYPES = {
     "lfm25_kv_allocator_pin_cached_pages": (ctypes.c_int32, [ctypes.c_void_p, _P(ctypes.c_uint32), _size]),
     "lfm25_kv_allocator_retain_pages": (ctypes.c_int32, [ctypes.c_void_p, _P(ctypes.c_uint32), _size]),
     "lfm25_kv_allocator_grow_sequence": (ctypes.c_int64, [ctypes.c_void_p, _size, _size, _P(ctypes.c_uint32), _size]),
+    "lfm25_kv_allocator_pages_short": (ctypes.c_int64, [ctypes.c_void_p, _P(_size), _P(_size), _size]),
     "lfm25_kv_allocator_release_sequence": (None, [ctypes.c_void_p, _size, _P(ctypes.c_uint32), _size]),
     "lfm25_kv_allocator_snapshot": (None, [ctypes.c_void_p, _P(KvPoolSnapshot)]),
     "lfm25_block_tables_create": (ctypes.c_int32, [_size, _size, _P(ctypes.c_void_p)]),

@@ -62,6 +62,12 @@ class KvPageAllocator:
         return _count(library().lfm25_kv_allocator_grow_sequence(self._handle, current_tokens, target_tokens,
                                                                  _table_pointer(block_table), block_table.size))
 
+    def pages_short(self, current_tokens, target_tokens) -> int:
+        """Pages missing for growing all the given sequences together (0 = they fit); allocates nothing."""
+        current = (ctypes.c_size_t * len(current_tokens))(*current_tokens)
+        target = (ctypes.c_size_t * len(target_tokens))(*target_tokens)
+        return _count(library().lfm25_kv_allocator_pages_short(self._handle, current, target, len(current_tokens)))
+
     def release_sequence(self, tokens: int, block_table: np.ndarray) -> None:
         library().lfm25_kv_allocator_release_sequence(self._handle, tokens, _table_pointer(block_table),
                                                       block_table.size)

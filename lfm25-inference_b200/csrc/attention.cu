@@ -70,6 +70,21 @@ struct AttentionParams {
     const uint32_t* token_order;  // optional permutation: which token the r-th group of CTAs takes
 };
 
+// A CTA that has no result for its token (request slot outside the block tables, position outside the row, an
+// unassigned page, an append slot that contradicts the block table, a wait that ran out) returns without touching the
+// output.  With the KV axis split, it first marks its four records: a negative sum tells the merge kernel that the
+// token has no result, and the merge then leaves the token's output row as it was -- whatever an earlier launch left
+// in the records is never combined into an output.
+__device__ __forceinline__ void mark_no_result(const AttentionParams& p, uint32_t token, uint32_t kv_head,
+                                               uint32_t split) {
+    if (p.num_splits > 1 && threadIdx.x < kQPerKv) {
+        const size_t q_index = static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + threadIdx.x;
+        float* record = p.partials + (q_index * p.num_splits + split) * kPartialStride;
+        record[0] = -INFINITY;
+        record[1] = -1.0f;
+    }
+}
+
 // FUSED == false: the query is already normalised and rotated and the newest K/V row is already in the cache.
 // FUSED == true : the kernel takes the raw Q/K/V projections of the step (the reference's one-kernel decode,
 //   kernels/attention_fused.cu:89-348): every CTA normalises and rotates its four query heads in registers, and
@@ -103,11 +118,13 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     if (p.request_slots != nullptr) {
         table_row = p.request_slots[token];
         if (table_row >= p.block_table_rows) {
+            mark_no_result(p, token, kv_head, split);
             return;
         }
     }
     const uint32_t position = p.position_ids[token];
     if (static_cast<uint64_t>(position) >= p.block_table_stride * kPageSize) {
+        mark_no_result(p, token, kv_head, split);
         return;
     }
     const uint32_t* __restrict__ table = p.block_tables + table_row * p.block_table_stride;
@@ -125,11 +142,13 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         const uint32_t current_page = table[total_pages - 1];
         const int64_t slot_value = p.slot_mapping[token];
         if (current_page >= p.num_pages || slot_value < 0) {
+            mark_no_result(p, token, kv_head, split);
             return;
         }
         new_row_offset = position % kPageSize;
         if (static_cast<uint64_t>(slot_value) / kPageSize != current_page ||
             static_cast<uint64_t>(slot_value) % kPageSize != new_row_offset) {
+            mark_no_result(p, token, kv_head, split);
             return;
         }
     }
@@ -459,6 +478,7 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     }
     __syncthreads();
     if (*bad_flag != 0) {
+        mark_no_result(p, token, kv_head, split);
         return;
     }
 
@@ -514,8 +534,13 @@ merge_splitk_kernel(const float* __restrict__ partials, __nv_bfloat16* __restric
     const size_t q_index = static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + head;
     const float* records = partials + q_index * num_splits * kPartialStride;
     float maximum = -INFINITY;
+    bool no_result = false;
     for (uint32_t split = 0; split < num_splits; ++split) {
         maximum = fmaxf(maximum, records[split * kPartialStride]);
+        no_result = no_result || records[split * kPartialStride + 1] < 0.0f;
+    }
+    if (no_result) {
+        return;   // a CTA of this token gave up (see mark_no_result): the output row stays as it was
     }
     float denominator = 0.0f;
     float out0 = 0.0f;
@@ -523,10 +548,12 @@ merge_splitk_kernel(const float* __restrict__ partials, __nv_bfloat16* __restric
     for (uint32_t split = 0; split < num_splits; ++split) {
         const float* record = records + split * kPartialStride;
         const float part_sum = record[1];
-        const float scale = part_sum == 0.0f ? 0.0f : fast_exp2((record[0] - maximum) * kLog2e);
-        denominator = fmaf(part_sum, scale, denominator);
-        out0 = fmaf(record[2 + lane], scale, out0);
-        out1 = fmaf(record[2 + lane + 32], scale, out1);
+        if (part_sum != 0.0f) {     // a split without pages wrote (-inf, 0) and nothing else
+            const float scale = fast_exp2((record[0] - maximum) * kLog2e);
+            denominator = fmaf(part_sum, scale, denominator);
+            out0 = fmaf(record[2 + lane], scale, out0);
+            out1 = fmaf(record[2 + lane + 32], scale, out1);
+        }
     }
     __nv_bfloat16* out_row = output + q_index * kHeadDim;
     out_row[lane] = __float2bfloat16_rn(out0 / denominator);

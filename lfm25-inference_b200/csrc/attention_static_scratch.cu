@@ -56,6 +56,14 @@ cudaError_t static_scratch_address(float** address) {
     return cudaSuccess;
 }
 
+void forget_static_scratch_address() {
+    int device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess && device >= 0 && device < kMaxDevices) {
+        std::lock_guard<std::mutex> guard(g_scratch_mutex);
+        g_scratch_address[device] = nullptr;
+    }
+}
+
 }  // namespace
 
 extern "C" int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(
@@ -77,8 +85,13 @@ extern "C" int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(
     if (status != cudaSuccess) {
         return lfm25::report_error(LFM25_ERR_CUDA, "static split-K scratch is not reachable on this device");
     }
-    // Every record that the merge reads for a valid token is written by this same call, so nothing
-    // in the array has to be cleared first; what an earlier call left behind is never read.
+    // Nothing in the array has to be cleared first.  Every record that the merge combines into an output row was
+    // written by this same call: a valid token's CTAs write all of its records, and a token that a CTA gave up on
+    // (request slot outside the block tables, position outside its row, unassigned page, a wait that ran out) gets a
+    // "no result" mark in place of the record, on which the merge leaves that token's output row as the caller
+    // passed it in.  Records of an earlier call are therefore never turned into output.  The one input that can
+    // leave a token without any record is a `token_order` that is not a permutation of the batch; the order arrays
+    // that lfm25_context_order_desc writes always are.
     lfm25_splitk_ragged_attention_launch full;
     full.page_size = launch->page_size;
     full.query = launch->query;
@@ -95,5 +108,11 @@ extern "C" int32_t lfm25_paged_ragged_attention_splitk_static_lfm2_bf16(
     full.block_table_stride = launch->block_table_stride;
     full.num_splits = num_splits;
     full.token_order = launch->token_order;
-    return lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &full);
+    const int32_t result = lfm25_paged_ragged_attention_splitk_lfm2_bf16(stream, &full);
+    if (result == LFM25_ERR_CUDA) {
+        // The context may have been torn down and rebuilt since the address was resolved (cudaDeviceReset in the
+        // host): forget it, so that the next call asks the runtime again.
+        forget_static_scratch_address();
+    }
+    return result;
 }

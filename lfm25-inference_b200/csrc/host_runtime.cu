@@ -143,6 +143,18 @@ int64_t lfm25_kv_allocator_grow_sequence(lfm25_kv_allocator* self, size_t curren
     return static_cast<int64_t>(needed);
 }
 
+int64_t lfm25_kv_allocator_pages_short(const lfm25_kv_allocator* self, const size_t* current_tokens,
+                                       const size_t* target_tokens, size_t sequences) {
+    size_t needed = 0;
+    for (size_t index = 0; index < sequences; ++index) {
+        if (target_tokens[index] < current_tokens[index]) {
+            return LFM25_KV_SEQUENCE_CAPACITY_EXCEEDED;
+        }
+        needed += div_ceil(target_tokens[index], self->page_size) - div_ceil(current_tokens[index], self->page_size);
+    }
+    return needed > self->free_pages.size() ? static_cast<int64_t>(needed - self->free_pages.size()) : 0;
+}
+
 void lfm25_kv_allocator_release_sequence(lfm25_kv_allocator* self, size_t tokens, uint32_t* block_table,
                                          size_t block_table_len) {
     const size_t pages = std::min(div_ceil(tokens, self->page_size), block_table_len);

@@ -73,6 +73,8 @@ struct lfm25_engine {
     lfm25_block_tables* tables = nullptr;
     lfm25_radix_cache* radix = nullptr;
     lfm25_conv_checkpoints* checkpoints = nullptr;
+    std::vector<size_t> grow_from;       // per work item of the step being built: tokens cached before ...
+    std::vector<size_t> grow_to;         // ... and after it
     lfm25_cost_model* cost = nullptr;
     lfm25_decode_executor* executor = nullptr;
     std::vector<uint32_t> conv_layers;   // indices of the gated-convolution layers in the model
@@ -615,6 +617,8 @@ int32_t lfm25_engine_step(lfm25_engine* self, uint64_t now_us, lfm25_engine_even
     }
 
     StepShape shape;
+    self->grow_from.clear();
+    self->grow_to.clear();
     for (size_t index = 0; index < plan.work_count; ++index) {
         lfm25_scheduled_work& item = self->work[index];
         Slot& slot = self->slots[item.slot];
@@ -635,14 +639,27 @@ int32_t lfm25_engine_step(lfm25_engine* self, uint64_t now_us, lfm25_engine_even
             shape.token_ids.push_back(slot.tokens.back());
         }
         item.tokens = count;
-        const int64_t grown = lfm25_kv_allocator_grow_sequence(self->allocator, slot.cached_tokens, begin + count,
-                                                               lfm25_block_tables_slot(self->tables, item.slot),
-                                                               self->pages_per_slot);
-        if (grown < 0) return lfm25::report_error(static_cast<int32_t>(grown), "KV pages exhausted inside a reservation");
-        if (grown > 0) self->tables_dirty = true;
+        self->grow_from.push_back(slot.cached_tokens);
+        self->grow_to.push_back(begin + count);
         shape.prefixes.push_back(begin);
         shape.chunks.push_back(count);
         shape.segment_slots.push_back(item.slot);
+    }
+    // All the sequences of the step grow or none does: a shortage found half way would leave rows of the block
+    // tables pointing at pages that their slots do not account for yet.
+    const int64_t short_by = lfm25_kv_allocator_pages_short(self->allocator, self->grow_from.data(), self->grow_to.data(),
+                                                            plan.work_count);
+    if (short_by != 0) {
+        return lfm25::report_error(short_by < 0 ? static_cast<int32_t>(short_by) : LFM25_KV_PHYSICAL_PAGES_EXHAUSTED,
+                                   "KV pages exhausted inside a reservation");
+    }
+    for (size_t index = 0; index < plan.work_count; ++index) {
+        const lfm25_scheduled_work& item = self->work[index];
+        const int64_t grown = lfm25_kv_allocator_grow_sequence(self->allocator, self->grow_from[index], self->grow_to[index],
+                                                               lfm25_block_tables_slot(self->tables, item.slot),
+                                                               self->pages_per_slot);
+        if (grown != 0) self->tables_dirty = true;        // also on an error: rows may have changed
+        if (grown < 0) return lfm25::report_error(static_cast<int32_t>(grown), "KV pages exhausted inside a reservation");
     }
     if (self->tables_dirty) {
         ENGINE_TRY(upload_tables(self, lfm25_block_tables_data(self->tables)));

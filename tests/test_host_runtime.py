@@ -173,3 +173,25 @@ def test_dispatcher_bounded_affinity_spills_to_the_idlest_replica():
     assert dispatcher.assign(100, prefix_hash=1234567, slack_tokens=250) == home
     dispatcher.mark_failed(home)
     assert dispatcher.assign(100, prefix_hash=1234567, slack_tokens=250) != home
+
+
+def test_pages_short_reports_a_shortage_before_any_row_changes():
+    """A pool too small for a whole step: lfm25_kv_allocator_pages_short names the shortage while the block tables
+    and the pool are untouched; growing the sequences one by one instead would have changed the first rows before
+    failing on a later one.  (The serving engine asks this before it grows the sequences of a step.)"""
+    allocator = KvPageAllocator(6, 16)
+    tables = FixedBlockTables(3, 4)
+    current, target = [0, 0, 0], [33, 33, 33]                # 3 pages each: 9 > 6
+    assert allocator.pages_short(current, target) == 3
+    assert allocator.snapshot()["free_pages"] == 6
+    assert (tables.as_array() == 0xFFFFFFFF).all()
+    assert allocator.pages_short(current[:2], target[:2]) == 0
+    assert allocator.pages_short([16], [17]) == 0 and allocator.pages_short([16], [16]) == 0
+    with pytest.raises(KvAllocationError):
+        allocator.pages_short([32], [16])                    # a target below the current length
+    # one by one: the first two rows grow, the third fails -- the state the engine's pre-check avoids
+    assert allocator.grow_sequence(0, 33, tables.slot(0)) == 3
+    assert allocator.grow_sequence(0, 33, tables.slot(1)) == 3
+    with pytest.raises(KvAllocationError):
+        allocator.grow_sequence(0, 33, tables.slot(2))
+    assert allocator.pages_short([33, 33, 0], [33, 34, 16]) == 1

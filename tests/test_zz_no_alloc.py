@@ -65,3 +65,35 @@ def test_static_scratch_limits(device):
         position_ids=torch.zeros(too_many, dtype=torch.int32, device=device))
     with pytest.raises(Lfm25Error, match="at most 128 tokens"):
         ops.paged_ragged_attention_splitk_static_lfm2_bf16_into(big, 4, torch.zeros_like(big.query))
+
+
+def test_token_without_result_keeps_its_output_row(device):
+    """A valid call, then the same batch with one request slot outside the block tables (a documented no-op, not a
+    fault: the CTAs of that token return after marking their records).  The other rows are bit-identical to the
+    valid call, the row of the bad token keeps what the caller passed in -- not the first call's values, which the
+    shared array still holds -- and no bounded wait has run out.  The entry point with a caller workspace behaves
+    the same."""
+    case = cases.random_ragged_case(32, 9, 16, 1024, 4096)
+    inputs = upload(case, device)
+    tokens = inputs.query.shape[0]
+    good = torch.zeros_like(inputs.query)
+    ops.paged_ragged_attention_splitk_static_lfm2_bf16_into(inputs, 4, good)
+    bad_token = 4
+    slots = case["request_slots"].copy()
+    slots[bad_token] = case["block_tables"].shape[0] + 3
+    broken = ops.FastRaggedAttentionInput(
+        query=inputs.query, arena=inputs.arena, block_tables=inputs.block_tables,
+        block_table_stride=inputs.block_table_stride, request_slots=to_u32(slots, device),
+        position_ids=inputs.position_ids)
+    sentinel = torch.full_like(inputs.query, 3.0)
+    ops.paged_ragged_attention_splitk_static_lfm2_bf16_into(broken, 4, sentinel)
+    workspace = torch.zeros((ops.splitk_workspace_elements(tokens),), dtype=torch.float32, device=device)
+    with_workspace = torch.full_like(inputs.query, 3.0)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(broken, workspace, 4, with_workspace)
+    torch.cuda.synchronize()
+    good_bits, got_bits, workspace_bits = bits_of(good), bits_of(sentinel), bits_of(with_workspace)
+    keep = np.arange(tokens) != bad_token
+    assert np.array_equal(got_bits[keep], good_bits[keep])
+    assert np.array_equal(got_bits[bad_token], bits_of(torch.full((32, 64), 3.0, dtype=torch.bfloat16)))
+    assert np.array_equal(workspace_bits, got_bits)
+    assert ops.device_status()[0] == 0
