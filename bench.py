@@ -741,6 +741,11 @@ def run_step_arm(arguments, rank, world):
         host_sampled = torch.empty(STEP_SEQUENCES, dtype=torch.int32).pin_memory()
         h2d_bytes = host_block.numel() * host_block.element_size()
         d2h_bytes = host_sampled.numel() * host_sampled.element_size()
+        # the same contexts as the timed region: the host owns the positions here, so the served steps start where the
+        # timed steps started (the clock-sampling and profiling steps in between moved the device's positions on by
+        # several hundred tokens, which would make every served step read that much more KV than a timed one)
+        host_meta["positions"].copy_(torch.from_numpy(
+            (batch.positions(0).astype(np.int64) + max(warmup, 3) - 2).astype(np.int32)))   # 3 untimed served steps follow
 
         def served_step():
             # upload of the metadata block, replay of the captured step, download of the ids and the synchronisation

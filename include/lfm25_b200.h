@@ -63,7 +63,7 @@ int32_t lfm25_device_status(void* stream, uint32_t out[4]);
  * (LFM25_* variables read in src/model/lfm2_base.rs and src/engine/serving/radix_owner.rs).  Each switch has a
  * default, may be preset by the environment variable LFM25_<NAME> (read once) and changed at run time here; a
  * change applies to launches issued afterwards and is not recorded in CUDA graphs that are already captured.
- *   pdl, fused_silu, kv_evict_first, engine_graph                      0 | 1 (default 1)
+ *   pdl, fused_silu, kv_evict_first, weights_evict_first, engine_graph 0 | 1 (default 1)
  *   fused_append           0 two launches | 1 one kernel | 2 auto (default): how the decode executor runs an
  *                          attention layer -- QK-norm + RoPE + append as a kernel of their own before the attention
  *                          kernel, or inside it; auto asks lfm25_decode_one_kernel_preferred()

@@ -68,6 +68,7 @@ struct UmmaParams {
     float alpha;
     uint32_t drop_block;     // self-test: the copy of this K block is armed but never issued
     uint64_t wait_limit_ns;  // limit of every mbarrier wait
+    uint32_t weights_evict_first;   // nonzero: the weight tiles carry the L2 evict-first hint (each is read once)
     // Gated mode (packed Gate/Up weights [2 * intermediate, K], gate rows first): a tile is 64 gate rows and the 64
     // up rows that belong to them, and the epilogue writes act = bf16(silu(bf16(gate)) * bf16(up)) -- as E4M3 codes
     // of act * gated_scale when gated_e4m3 is set -- instead of the two projections.  0 = plain GEMM.
@@ -158,13 +159,22 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __grid_co
     const bool gated = p.intermediate != 0;
     const int32_t tile_row = static_cast<int32_t>(tile * (gated ? kTileN / 2 : kTileN));
     // the weight tile of one K block: one 128-row box, or in gated mode two 64-row boxes (gate rows, up rows)
+    // Every weight byte is read once per launch, by one CTA: with the evict-first hint the stream does not push the
+    // activations and the output (which the next kernels read) out of the L2.
+    const uint64_t weight_policy = l2_evict_first_policy();
+    auto load_weight_box = [&](uint32_t dst, uint32_t bar, int32_t k_offset, int32_t row) {
+        if (p.weights_evict_first != 0) {
+            tma_load_2d_hint(dst, &weight_map, bar, k_offset, row, weight_policy);
+        } else {
+            tma_load_2d(dst, &weight_map, bar, k_offset, row);
+        }
+    };
     auto load_weights = [&](uint32_t dst, uint32_t bar, int32_t k_offset) {
         if (gated) {
-            tma_load_2d(dst, &weight_map, bar, k_offset, tile_row);
-            tma_load_2d(dst + kWeightTileBytes / 2, &weight_map, bar, k_offset,
-                        tile_row + static_cast<int32_t>(p.intermediate));
+            load_weight_box(dst, bar, k_offset, tile_row);
+            load_weight_box(dst + kWeightTileBytes / 2, bar, k_offset, tile_row + static_cast<int32_t>(p.intermediate));
         } else {
-            tma_load_2d(dst, &weight_map, bar, k_offset, tile_row);
+            load_weight_box(dst, bar, k_offset, tile_row);
         }
     };
     if (threadIdx.x == 0) {
@@ -590,6 +600,7 @@ cudaError_t launch_umma(cudaStream_t stream, const void* x, const void* weight, 
     params.alpha = alpha;
     params.drop_block = wait_selftest_drop() ? 0u : 0xffffffffu;
     params.wait_limit_ns = wait_limit_ns();
+    params.weights_evict_first = weights_evict_first() ? 1u : 0u;
     params.intermediate = gated != nullptr ? static_cast<uint32_t>(n / 2) : 0;
     params.gated_e4m3 = gated != nullptr && gated->e4m3 ? 1u : 0u;
     params.gated_scale = gated != nullptr ? gated->code_scale : 1.0f;

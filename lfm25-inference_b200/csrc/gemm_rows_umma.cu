@@ -65,6 +65,7 @@ struct RowsParams {
     float* exchange;          // split-K partial tiles [tile][slice][split][a_tiles * 128 batch rows][n_tile] fp32
     unsigned int* status;
     uint64_t wait_limit_ns;
+    uint32_t weights_evict_first;   // nonzero: the weight tiles carry the L2 evict-first hint
     uint32_t m;
     uint32_t n;               // output features (plain) or the intermediate width (gated)
     uint32_t n_tile;          // weight rows per CTA = UMMA N
@@ -228,16 +229,25 @@ gemm_rows_umma_kernel(const __grid_constant__ CUtensorMap weight_map, const __gr
     const uint32_t half = p.n_tile / 2;
     const int32_t weight_row = static_cast<int32_t>(tile * (p.gated ? half : p.n_tile));
     const uint32_t ahead = k_count < p.stages ? k_count : p.stages;
+    const uint64_t weight_policy = l2_evict_first_policy();
     // a ring slot: [activation tile(s)][weight tile]
     auto load_weights = [&](uint32_t block, uint32_t stage) {
         const uint32_t bar = bar_full + 8 * stage;
         const uint32_t dst = ring + stage * p.stage_bytes + x_bytes;
         const int32_t k_offset = static_cast<int32_t>((k_block0 + block) * kBlockK);
-        if (p.gated) {
-            tma_load_2d(dst, &weight_map, bar, k_offset, weight_row);
-            tma_load_2d(dst + half * kBlockK, &weight_map, bar, k_offset, weight_row + static_cast<int32_t>(p.n));
+        // every weight byte is read once per launch: with the evict-first hint the stream leaves the activations
+        // and the output in the L2 for the kernels that read them next
+        if (p.weights_evict_first != 0) {
+            tma_load_2d_hint(dst, &weight_map, bar, k_offset, weight_row, weight_policy);
+            if (p.gated) {
+                tma_load_2d_hint(dst + half * kBlockK, &weight_map, bar, k_offset,
+                                 weight_row + static_cast<int32_t>(p.n), weight_policy);
+            }
         } else {
             tma_load_2d(dst, &weight_map, bar, k_offset, weight_row);
+            if (p.gated) {
+                tma_load_2d(dst + half * kBlockK, &weight_map, bar, k_offset, weight_row + static_cast<int32_t>(p.n));
+            }
         }
     };
     auto load_activations = [&](uint32_t block, uint32_t stage) {
@@ -758,6 +768,7 @@ cudaError_t launch_rows(cudaStream_t stream, const void* x, const void* weight, 
     params.exchange = static_cast<float*>(exchange);
     params.status = status;
     params.wait_limit_ns = wait_limit_ns();
+    params.weights_evict_first = weights_evict_first() ? 1u : 0u;
     params.m = static_cast<uint32_t>(m);
     params.n = static_cast<uint32_t>(n);
     params.n_tile = plan.n_tile;

@@ -242,28 +242,108 @@ __device__ __forceinline__ uint32_t argmax_key(uint16_t bits, uint32_t column) {
     return (static_cast<uint32_t>(ordered) << 16) | ((0xffu - (column & 0xffu)) << 8) | (0xffu - (column >> 8));
 }
 
+// Greedy sampling over one row per CTA, in two passes so that the per-element work is one packed instruction each:
+// pass 1 finds the row's largest value with bf16x2 maxima (NaN never wins: maxNum semantics), pass 2 forms the
+// tie-ordered key only for the few elements that equal it.  A row of 8 * kArgmaxThreads * kArgmaxBatch values
+// (65536: the model's vocabulary) is loaded once, all loads in flight together, and stays in registers for pass 2;
+// other lengths re-read the row in pass 2.
 constexpr uint32_t kArgmaxThreads = 1024;
+constexpr uint32_t kArgmaxBatch = 8;
+
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t word) {
+    return *reinterpret_cast<const __nv_bfloat162*>(&word);
+}
+
+__device__ __forceinline__ __nv_bfloat162 max_of_vector(const uint4& raw, __nv_bfloat162 running) {
+    running = __hmax2(running, as_bf162(raw.x));
+    running = __hmax2(running, as_bf162(raw.y));
+    running = __hmax2(running, as_bf162(raw.z));
+    return __hmax2(running, as_bf162(raw.w));
+}
+
+// keys of the elements of one 8-value vector that equal `wanted` (both halves hold the row maximum)
+__device__ __forceinline__ uint32_t keys_of_matches(const uint4& raw, size_t vector, __nv_bfloat162 wanted,
+                                                    uint32_t best) {
+    const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (uint32_t pair = 0; pair < 4; ++pair) {
+        const unsigned mask = __heq2_mask(as_bf162(words[pair]), wanted);
+        if (mask != 0u) {
+            const uint32_t column = static_cast<uint32_t>(vector) * 8 + pair * 2;
+            if (mask & 0xffffu) {
+                best = max(best, argmax_key(static_cast<uint16_t>(words[pair] & 0xffffu), column));
+            }
+            if (mask >> 16) {
+                best = max(best, argmax_key(static_cast<uint16_t>(words[pair] >> 16), column + 1));
+            }
+        }
+    }
+    return best;
+}
+
 __global__ void __launch_bounds__(kArgmaxThreads)
 argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, uint32_t* __restrict__ sampled, size_t rows,
                    size_t vocab) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ uint32_t warp_best[32];
+    __shared__ uint32_t warp_max[32];
     const size_t row = blockIdx.x;
     if (row >= rows) {
         return;
     }
     const uint16_t* row_bits = reinterpret_cast<const uint16_t*>(logits) + row * vocab;
+    const uint32_t lane = threadIdx.x & 31;
+    const uint32_t warp = threadIdx.x >> 5;
+    const uint32_t warps = blockDim.x >> 5;
     uint32_t best = 0;
     if (vocab % 8 == 0) {
-        for (size_t vector = threadIdx.x; vector < vocab / 8; vector += blockDim.x) {
-            const uint4 raw = __ldg(reinterpret_cast<const uint4*>(row_bits) + vector);
-            const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        const uint4* vectors = reinterpret_cast<const uint4*>(row_bits);
+        const size_t count = vocab / 8;
+        const bool resident = count == static_cast<size_t>(kArgmaxBatch) * blockDim.x;
+        const __nv_bfloat16 lowest = __ushort_as_bfloat16(static_cast<unsigned short>(0xff80u));   // -inf
+        __nv_bfloat162 running = __halves2bfloat162(lowest, lowest);
+        uint4 raw[kArgmaxBatch];
+        if (resident) {
 #pragma unroll
-            for (uint32_t pair = 0; pair < 4; ++pair) {
-                const uint32_t column = static_cast<uint32_t>(vector) * 8 + pair * 2;
-                best = max(best, argmax_key(static_cast<uint16_t>(words[pair] & 0xffffu), column));
-                best = max(best, argmax_key(static_cast<uint16_t>(words[pair] >> 16), column + 1));
+            for (uint32_t index = 0; index < kArgmaxBatch; ++index) {
+                raw[index] = __ldg(vectors + threadIdx.x + index * blockDim.x);
+            }
+#pragma unroll
+            for (uint32_t index = 0; index < kArgmaxBatch; ++index) {
+                running = max_of_vector(raw[index], running);
+            }
+        } else {
+            for (size_t vector = threadIdx.x; vector < count; vector += blockDim.x) {
+                running = max_of_vector(__ldg(vectors + vector), running);
+            }
+        }
+        // the row's maximum: thread -> warp -> CTA
+        __nv_bfloat16 top = __hmax(__low2bfloat16(running), __high2bfloat16(running));
+#pragma unroll
+        for (uint32_t delta = 16; delta > 0; delta >>= 1) {
+            const unsigned short other = __shfl_xor_sync(0xffffffffu, __bfloat16_as_ushort(top), delta);
+            top = __hmax(top, __ushort_as_bfloat16(other));
+        }
+        if (lane == 0) {
+            warp_max[warp] = __bfloat16_as_ushort(top);
+        }
+        __syncthreads();
+        top = __ushort_as_bfloat16(static_cast<unsigned short>(warp_max[lane < warps ? lane : 0]));
+#pragma unroll
+        for (uint32_t delta = 16; delta > 0; delta >>= 1) {
+            const unsigned short other = __shfl_xor_sync(0xffffffffu, __bfloat16_as_ushort(top), delta);
+            top = __hmax(top, __ushort_as_bfloat16(other));
+        }
+        const __nv_bfloat162 wanted = __halves2bfloat162(top, top);
+        if (resident) {
+#pragma unroll
+            for (uint32_t index = 0; index < kArgmaxBatch; ++index) {
+                best = keys_of_matches(raw[index], threadIdx.x + index * blockDim.x, wanted, best);
+            }
+        } else {
+            for (size_t vector = threadIdx.x; vector < count; vector += blockDim.x) {
+                best = keys_of_matches(__ldg(vectors + vector), vector, wanted, best);
             }
         }
     } else {
@@ -275,12 +355,12 @@ argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, uint32_t* __restric
     for (uint32_t delta = 16; delta > 0; delta >>= 1) {
         best = max(best, __shfl_xor_sync(0xffffffffu, best, delta));
     }
-    if ((threadIdx.x & 31) == 0) {
-        warp_best[threadIdx.x >> 5] = best;
+    if (lane == 0) {
+        warp_best[warp] = best;
     }
     __syncthreads();
     if (threadIdx.x < 32) {
-        best = threadIdx.x < (blockDim.x >> 5) ? warp_best[threadIdx.x] : 0u;
+        best = threadIdx.x < warps ? warp_best[threadIdx.x] : 0u;
 #pragma unroll
         for (uint32_t delta = 16; delta > 0; delta >>= 1) {
             best = max(best, __shfl_xor_sync(0xffffffffu, best, delta));

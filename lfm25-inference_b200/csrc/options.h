@@ -10,6 +10,7 @@
 //   fused_silu           0 | 1                                 1         E4M3 Gate/Up: SiLU(gate) * up in the GEMM epilogue
 //   fused_silu_bf16      0 | 1                                 0         the same for a Gate/Up site that stays in BF16
 //   kv_evict_first       0 | 1                                 1         L2 evict-first hint on the KV page stream
+//   weights_evict_first  0 | 1                                 1         the same hint on the weight stream of the tcgen05 GEMMs
 //   engine_graph         0 | 1                                 1         serving engine replays captured decode steps
 //   hybrid_attention     0 auto | 1 umma | 2 mma               0         kernel of the mixed-step attention
 //   fp8_gemm_path        0 auto | 1 stream | 2 umma | 3 generic | 4 rows   0   kernel of the E4M3 linear
@@ -32,6 +33,7 @@ enum Option : int {
     kOptFusedSilu,
     kOptFusedSiluBf16,
     kOptKvEvictFirst,
+    kOptWeightsEvictFirst,
     kOptEngineGraph,
     kOptHybridAttention,
     kOptFp8GemmPath,
@@ -52,6 +54,7 @@ bool set_option_by_name(const char* name, int64_t value);
 bool get_option_by_name(const char* name, int64_t* value);
 
 inline uint64_t wait_limit_ns() { return static_cast<uint64_t>(option(kOptWaitLimitNs)); }
+inline bool weights_evict_first() { return option(kOptWeightsEvictFirst) != 0; }
 inline bool wait_selftest_drop() { return option(kOptWaitSelftestDrop) != 0; }
 
 }  // namespace lfm25

@@ -128,6 +128,10 @@ def test_argmax_tie_order(device):
     rows.append(row)
     row = oracle.f32_to_bf16(np.full(vocab, -3.0e38, dtype=np.float32))                         # all equal, very negative
     rows.append(row)
+    row = np.where(np.arange(vocab) % 2 == 0, 0x7FC0, 0xFF80).astype(np.uint16)                 # only NaN and -inf
+    rows.append(row)
+    row = np.full(vocab, 0xFFC0, dtype=np.uint16); row[40000] = 0xC2C8                          # one finite value among NaN
+    rows.append(row)
     logits = np.stack(rows)
     sampled = torch.zeros(len(rows), dtype=torch.int32, device=device)
     ops.argmax_rows_bf16_into(to_bf16(logits, device), sampled)
@@ -135,6 +139,12 @@ def test_argmax_tie_order(device):
     want = oracle.argmax_rows_bf16(logits)
     assert np.array_equal(got, want)
     assert want[1] == 0 and want[2] == 0 and want[3] == 0 and want[5] == 100 and want[6] == 0
+    assert want[7] == 0 and want[8] == 40000
+    # a vocabulary that is a multiple of 8 but not the register-resident length: the row is read twice
+    short = oracle.f32_to_bf16(rng.integers(-2, 3, size=(5, 4096)).astype(np.float32))
+    sampled = torch.zeros(5, dtype=torch.int32, device=device)
+    ops.argmax_rows_bf16_into(to_bf16(short, device), sampled)
+    assert np.array_equal(sampled.cpu().numpy().view(np.uint32), oracle.argmax_rows_bf16(short))
     odd = workloads.bf16_normal(rng, (3, 1001))
     sampled = torch.zeros(3, dtype=torch.int32, device=device)
     ops.argmax_rows_bf16_into(to_bf16(odd, device), sampled)
