@@ -77,6 +77,10 @@ def parse_arguments():
     parser.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline (profiling runs)")
     parser.add_argument("--skip-gemm", action="store_true", help="step workload: omit the gemm_roofline table")
     parser.add_argument("--gemm-dtype", default="all", choices=["all", "e4m3", "bf16"], help="gemm workload: which sites")
+    parser.add_argument("--timeline", action="store_true",
+                        help="step workload: add `graph_timeline` to the line -- per kernel of the replayed step its "
+                             "launches, duration and the time during which no earlier kernel was still running, from "
+                             "CUPTI activity records (torch.profiler) of a few extra replays after the timed region")
     parser.add_argument("--gemm-sites", nargs="*", default=None,
                         help="gemm workload: only these sites (gate_up down lm_head qkv proj conv_in); a profiling aid")
     parser.add_argument("--gemm-batches", nargs="*", type=int, default=None, help="gemm workload: only these M")
@@ -795,6 +799,10 @@ def run_step_arm(arguments, rank, world):
             except Exception as error:       # optional comparison; the metric does not depend on it
                 reference_kernels = {"error": str(error)[:120]}
 
+        graph_timeline = None
+        if rank == 0 and arguments.timeline:
+            graph_timeline = step_timeline(executor, model, device_batch, stream, use_fp8)
+
         # ---- end to end: host metadata in, sampled ids out, every step ----
         host_block = device_batch.step_metadata.cpu().pin_memory()       # token ids | positions | request slots
         host_meta = {"token_ids": host_block[:STEP_SEQUENCES],
@@ -904,6 +912,7 @@ def run_step_arm(arguments, rank, world):
             "gpu_launches": launches * steps, "cublaslt_launches": library_launches * steps,
             "reference_kernels_same_gpu": reference_kernels,
             "gemm_roofline": gemm_table,
+            "graph_timeline": graph_timeline,
             "replicas": {"tok_s_sum_of_replicas": sum(STEP_SEQUENCES / (ms * 1e-3) for ms, _ in per_rank),
                          "tok_s_from_slowest_replica": STEP_SEQUENCES * steps * world / (total_ms * 1e-3),
                          "ms_per_step_per_rank": [round(ms, 4) for ms, _ in per_rank],
@@ -917,6 +926,42 @@ def run_step_arm(arguments, rank, world):
     blaslt.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def step_timeline(executor, model, device_batch, stream, use_fp8, replays=6):
+    """Per-kernel picture of the replayed step from CUPTI activity records: for every kernel name its launches per
+    step, its summed duration and its exclusive time (the part of it during which no earlier kernel of the step was
+    still running; the dependent launches overlap a kernel's start with its predecessor's end).  A diagnostic: the
+    records are taken on extra replays after the timed region, never on the timed ones."""
+    import re
+    import torch
+    with torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CUDA]) as profile:
+        for _ in range(replays):
+            executor.step_graph(model, device_batch, use_fp8=use_fp8, advance=True)
+        stream.synchronize()
+    records = sorted((event.time_range.start, event.time_range.end, event.name) for event in profile.events()
+                     if event.device_type == torch.autograd.DeviceType.CUDA)
+    starts = [index for index, record in enumerate(records) if "decode_metadata" in record[2]]
+    if len(starts) < 3:
+        return {"error": "no kernel records"}
+    first, last = starts[1], starts[-1]                      # whole steps only, the first one left out
+    steps = len(starts) - 2
+    table = {}
+    frontier = records[first][0]
+    for begin, end, name in records[first:last]:
+        short = re.sub(r"\(.*", "", name)
+        for prefix in ("void ", "lfm25::", "(anonymous namespace)::"):
+            short = short.replace(prefix, "")
+        entry_ = table.setdefault(short[:48], [0, 0.0, 0.0])
+        entry_[0] += 1
+        entry_[1] += end - begin
+        entry_[2] += max(0.0, end - max(begin, frontier))
+        frontier = max(frontier, end)
+    span = (records[last][0] - records[first][0]) / steps
+    kernels = [{"kernel": name, "launches_per_step": count / steps, "us_per_step": round(duration / steps, 2),
+                "exclusive_us_per_step": round(exclusive / steps, 2)}
+               for name, (count, duration, exclusive) in sorted(table.items(), key=lambda item: -item[1][2])]
+    return {"steps": steps, "us_per_step": round(span, 2), "kernels": kernels}
 
 
 def reference_kernel_step(model, device_batch, stream, use_fp8, repeats=16):
