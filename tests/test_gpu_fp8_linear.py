@@ -93,6 +93,25 @@ def test_paths_agree_bit_for_bit_on_exact_sums(device, library_option):
     assert np.array_equal(results[0], oracle.linear_fp8(x, w, 0.25))
 
 
+@pytest.mark.parametrize("path", ["umma", "rows"])
+def test_weight_stream_hint_does_not_change_a_bit(device, library_option, path):
+    """The L2 evict-first hint on the weight tiles (switch `weights_evict_first`) is a cache policy: the same launch
+    with and without it returns identical bits, through a handle (K split over a cluster) and without one."""
+    library_option("fp8_gemm_path", FP8_GEMM_PATHS[path])
+    _, x_codes, w_codes, (_, xd), (_, wd) = quantised_problem(77, 96, 2048, 4096)
+    x_t, w_t = codes_tensor(x_codes, device), codes_tensor(w_codes, device)
+    blaslt = ops.BlasLt()
+    results = []
+    for hint in (1, 0):
+        library_option("weights_evict_first", hint)
+        out = torch.zeros((96, 2048), dtype=torch.bfloat16, device=device)
+        blaslt.linear_fp8_scaled(x_t, w_t, out, xd * wd)
+        results.append((bits_of(out), run_linear(x_codes, w_codes, xd * wd, device)))
+    assert np.array_equal(results[0][0], results[1][0]) and np.array_equal(results[0][1], results[1][1])
+    assert ops.device_status()[0] == 0
+    blaslt.close()
+
+
 @pytest.mark.parametrize("m", [1, 8, 16, 100, 128, 256])
 @pytest.mark.parametrize("n,k", [(2048, 8192), (256, 4096), (16384, 2048), (6144, 2048)])
 def test_blaslt_handle_split_k(device, m, n, k):
