@@ -165,7 +165,12 @@ def run_trace(engine: ServingEngine, requests: list[Request]) -> dict:
 # every process builds from the same seed; the channel is a key-value store of the host (torch.distributed's store:
 # no GPU collective anywhere).  Keys: "n/<replica>" = requests handed to the replica so far, "q/<replica>/<k>" = index
 # of the k-th of them, "done/<replica>" = tokens the replica has finished with (prompt + generated of completed or
-# rejected requests), "closed" = set once the last request is handed out.
+# rejected requests), "beat/<replica>" = wall-clock time of the replica's last sign of life, "closed" = set once the
+# last request is handed out.  A replica whose last sign of life is older than the front's timeout is marked failed
+# in the dispatcher (lfm25_dispatcher_mark_failed) and gets no further requests; what it had been handed and not
+# finished is reported as lost.
+
+HEARTBEAT_PERIOD_S = 0.1
 
 PREFIX_HASH_TOKENS = 256
 
@@ -183,13 +188,15 @@ def estimated_tokens(request: Request) -> int:
 
 
 def run_front(store, replicas: int, requests: list[Request], origin_s: float, slack_tokens: int = 8192,
-              clock=time.time, sleep=time.sleep) -> dict:
+              clock=time.time, sleep=time.sleep, failure_timeout_s: float = 5.0) -> dict:
     """Hands out `requests` in arrival order, each at origin_s + arrival, and returns the assignment
-    {request_id: replica} with the dispatcher's view of the loads at the end."""
+    {request_id: replica} with the dispatcher's view of the loads at the end.  A replica that has given no sign of
+    life for `failure_timeout_s` is marked failed and left out from then on."""
     from .cache import Dispatcher
     dispatcher = Dispatcher(replicas)
     seen_done = [0] * replicas
     handed = [0] * replicas
+    failed = []
     assignment = {}
     hashes = [prefix_hash(request.prompt) for request in requests]
     order = sorted(range(len(requests)), key=lambda index: requests[index].arrival_us)
@@ -198,18 +205,28 @@ def run_front(store, replicas: int, requests: list[Request], origin_s: float, sl
         wait = origin_s + request.arrival_us * 1e-6 - clock()
         if wait > 0:
             sleep(wait)
+        now = clock()
         for replica in range(replicas):                       # completions reported since the last look
+            if replica in failed:
+                continue
             done = int(store.add(f"done/{replica}", 0))
             if done > seen_done[replica]:
                 dispatcher.complete(replica, done - seen_done[replica])
                 seen_done[replica] = done
+            if store.check([f"beat/{replica}"]):
+                last_beat = float(store.get(f"beat/{replica}").decode())
+            else:
+                last_beat = origin_s                             # a replica that never reported counts from the start
+            if now - last_beat > failure_timeout_s and len(failed) + 1 < replicas:
+                dispatcher.mark_failed(replica)
+                failed.append(replica)
         replica = dispatcher.assign(estimated_tokens(request), prefix_hash=hashes[index], slack_tokens=slack_tokens)
         store.set(f"q/{replica}/{handed[replica]}", str(index))
         handed[replica] += 1
         store.add(f"n/{replica}", 1)
         assignment[request.request_id] = replica
     store.set("closed", "1")
-    return {"assignment": assignment, "handed": handed,
+    return {"assignment": assignment, "handed": handed, "failed_replicas": failed,
             "outstanding_tokens": [dispatcher.load(replica) for replica in range(replicas)]}
 
 
@@ -221,7 +238,11 @@ def run_replica(engine, store, replica: int, requests: list[Request], origin_s: 
     taken = 0
     closed = False
     first_step_us = None
+    last_beat = 0.0
     while True:
+        if clock() - last_beat >= HEARTBEAT_PERIOD_S:
+            last_beat = clock()
+            store.set(f"beat/{replica}", repr(last_beat))
         count = int(store.add(f"n/{replica}", 0))
         while taken < count:
             request = requests[int(store.get(f"q/{replica}/{taken}"))]

@@ -46,8 +46,8 @@ def test_single_replica_needs_no_process_group():
 class _FakeEngine:
     """The engine's interface with no GPU behind it: every active request yields one token per step."""
 
-    def __init__(self):
-        self.waiting, self.running = [], {}
+    def __init__(self, step_seconds=0.0):
+        self.waiting, self.running, self.step_seconds = [], {}, step_seconds
 
     def submit(self, request):
         self.waiting.append(request)
@@ -59,6 +59,9 @@ class _FakeEngine:
         return len(self.running)
 
     def step(self, now_us):
+        if self.step_seconds:
+            import time
+            time.sleep(self.step_seconds)
         for request in self.waiting:
             self.running[request.request_id] = [request, 0]
         self.waiting = []
@@ -151,3 +154,86 @@ def test_one_trace_is_dispatched_over_two_replicas():
     shared_home = serving.prefix_hash(trace[0].prompt) % world
     shared_placed = [served[index] for index in range(0, len(trace), 2)]
     assert shared_placed.count(shared_home) > len(shared_placed) // 2
+
+
+class _ReplicaGone(Exception):
+    pass
+
+
+class _DyingEngine(_FakeEngine):
+    """Serves a few steps, then fails for good (the host-side stand-in for a replica that is lost)."""
+
+    def __init__(self, steps_before_failure, step_seconds):
+        super().__init__(step_seconds)
+        self.remaining = steps_before_failure
+
+    def step(self, now_us):
+        if self.remaining == 0:
+            raise _ReplicaGone()
+        self.remaining -= 1
+        return super().step(now_us)
+
+
+def _failure_trace():
+    import numpy as np
+    from lfm25_inference_b200 import serving
+    rng = np.random.default_rng(12)
+    return [serving.Request(index, rng.integers(0, 65536, size=int(rng.integers(16, 200))).astype(np.uint32), 30,
+                            index * 25000) for index in range(40)]
+
+
+def _failure_rank_main(rank, world, port, results):
+    import threading
+    import time
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import __graft_entry__ as entry
+    entry.load_package()
+    from lfm25_inference_b200 import serving
+    store = dist.PrefixStore("failure/", dist.distributed_c10d._get_default_store())
+    trace = _failure_trace()
+    dist.barrier()
+    if rank == 0:
+        store.set("origin", repr(time.time() + 0.05))
+    origin = float(store.get("origin").decode())
+    front_result = {}
+    front = None
+    if rank == 0:
+        front = threading.Thread(target=lambda: front_result.update(
+            serving.run_front(store, world, trace, origin, failure_timeout_s=0.3)))
+        front.start()
+    engine = _FakeEngine(0.004) if rank == 0 else _DyingEngine(20, 0.004)      # replica 1 lives for 80 ms
+    mine = None
+    try:
+        mine = serving.run_replica(engine, store, rank, trace, origin)
+    except _ReplicaGone:
+        pass                                # the replica is gone: no more signs of life, nothing reported
+    if front is not None:
+        front.join()
+    results[rank] = (mine, dict(front_result))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_front_stops_using_a_replica_that_gives_no_sign_of_life():
+    """Failure detection on the host, no GPU involved: replica 1 fails after a few steps (an exception in its loop),
+    its heartbeat in the store goes stale, the front marks it failed in the dispatcher after the timeout and hands
+    every later request to the surviving replica, which serves all of them."""
+    sys.path.insert(0, ROOT)
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    port = 33500 + os.getpid() % 2000
+    mp.spawn(_failure_rank_main, args=(world, port, results), nprocs=world, join=True)
+    trace = _failure_trace()
+    survivor, front = results[0]
+    assert results[1][0] is None
+    assert front["failed_replicas"] == [1]
+    assignment = front["assignment"]
+    handed_to_lost = sorted(request_id for request_id, replica in assignment.items() if replica == 1)
+    assert handed_to_lost and max(handed_to_lost) < len(trace) - 10          # nothing late went to the lost replica
+    assert all(assignment[request.request_id] == 0 for request in trace[-10:])
+    served = {record["request_id"] for record in survivor["requests"] if record["generated"] == 30}
+    assert served == {request_id for request_id, replica in assignment.items() if replica == 0}
+    assert len(served) + len(handed_to_lost) == len(trace)
