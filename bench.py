@@ -816,12 +816,16 @@ def run_step_arm(arguments, rank, world):
         host_meta["positions"].copy_(torch.from_numpy(
             (batch.positions(0).astype(np.int64) + max(warmup, 3) - 2).astype(np.int32)))   # 3 untimed served steps follow
 
+        # the host's bookkeeping between steps on numpy views of the pinned buffers (a few hundred bytes)
+        host_ids, host_positions = host_meta["token_ids"].numpy(), host_meta["positions"].numpy()
+        sampled_view = host_sampled.numpy()
+
         def served_step():
             # upload of the metadata block, replay of the captured step, download of the ids and the synchronisation
             # the serving loop needs (EOS, streaming) before it goes on: one call into the library
             executor.serve_step(model, device_batch, host_block, host_sampled, use_fp8=use_fp8)
-            host_meta["token_ids"].copy_(host_sampled)
-            host_meta["positions"] += 1
+            host_ids[:] = sampled_view
+            host_positions += 1
 
         for _ in range(3):
             served_step()
