@@ -825,7 +825,7 @@ def run_step_arm(arguments, rank, world):
             # the serving loop needs (EOS, streaming) before it goes on: one call into the library
             executor.serve_step(model, device_batch, host_block, host_sampled, use_fp8=use_fp8)
             host_ids[:] = sampled_view
-            host_positions += 1
+            np.add(host_positions, 1, out=host_positions)
 
         for _ in range(3):
             served_step()
