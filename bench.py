@@ -953,9 +953,10 @@ def step_timeline(executor, model, device_batch, stream, use_fp8, replays=6):
     table = {}
     frontier = records[first][0]
     for begin, end, name in records[first:last]:
-        short = re.sub(r"\(.*", "", name)
+        short = name
         for prefix in ("void ", "lfm25::", "(anonymous namespace)::"):
             short = short.replace(prefix, "")
+        short = re.sub(r"\(.*", "", short)
         entry_ = table.setdefault(short[:48], [0, 0.0, 0.0])
         entry_[0] += 1
         entry_[1] += end - begin
@@ -965,7 +966,11 @@ def step_timeline(executor, model, device_batch, stream, use_fp8, replays=6):
     kernels = [{"kernel": name, "launches_per_step": count / steps, "us_per_step": round(duration / steps, 2),
                 "exclusive_us_per_step": round(exclusive / steps, 2)}
                for name, (count, duration, exclusive) in sorted(table.items(), key=lambda item: -item[1][2])]
-    return {"steps": steps, "us_per_step": round(span, 2), "kernels": kernels}
+    mean_context = float(device_batch.positions.cpu().numpy().view(np.uint32).mean()) + 1.0
+    return {"steps": steps, "us_per_step": round(span, 2), "mean_context_tokens_after": round(mean_context, 1),
+            "note": "taken after the timed, clock-sampling and profiling steps: the contexts are longer here than in "
+                    "the timed region, by one token per step run since",
+            "kernels": kernels}
 
 
 def reference_kernel_step(model, device_batch, stream, use_fp8, repeats=16):
