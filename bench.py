@@ -875,11 +875,11 @@ def run_step_arm(arguments, rank, world):
             cpu_tokens, _, cpu_description, threads = step_cpu_sample(model, batch, token_ids, use_fp8,
                                                                       arguments.cpu_sequences or STEP_SEQUENCES, 1)
         per_step = {name: ops_count // profile_steps for name, (_, ops_count) in regions.items()}
-        # GPU kernels per step, counted from the captured graph; the BF16 GEMMs of batches above 32 rows are
+        # GPU kernels per step, counted from the captured graph; the BF16 GEMMs of the larger batches are
         # cuBLASLt's kernels (one per call), everything else is this library's
         graph_kernels = executor.graph_kernels()
         forced = ops.get_option("bf16_gemm")          # 0 auto | 1 umma | 2 cublaslt | 3 rows
-        through_library = forced == 2 or (forced == 0 and STEP_SEQUENCES > 32)
+        through_library = forced == 2 or (forced == 0 and STEP_SEQUENCES > ops.bf16_own_kernel_max_rows())
         library_launches = per_step["bf16_linear"] if through_library else 0
         launches = graph_kernels - library_launches
         line = {

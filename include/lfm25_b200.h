@@ -372,6 +372,10 @@ int32_t lfm25_blaslt_linear_fp8_silu_mul(lfm25_blaslt* handle, lfm25_slice x, lf
  * sites that are not promoted to FP8. */
 int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slice weight, lfm25_slice out, size_t m,
                                  size_t n, size_t k);
+/* The largest batch (rows of x) that lfm25_blaslt_linear_bf16 sends to this library's own tensor-core kernel when
+ * nothing forces a route; larger batches go through cuBLASLt.  The value is measured on the whole decode step (the
+ * figures are in the definition).  No counterpart in the reference, which always calls cuBLASLt. */
+size_t lfm25_bf16_own_kernel_max_rows(void);
 /* The BF16 packed Gate/Up linear with the gated activation in its epilogue, for the layers whose Gate/Up site is
  * not promoted to FP8: linear_decode_into + silu_mul_packed_bf16_into (or ..._to_e4m3_into when `e4m3_output` is
  * set, for an FP8 Down site) of the decode step in one launch (src/model/decode_executor.rs:378-402,

@@ -660,6 +660,13 @@ size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_toke
     return splits;
 }
 
+size_t lfm25_bf16_own_kernel_max_rows(void) {
+    // Whole decode step, every BF16 site on the weight-major tcgen05 kernel against every one through cuBLASLt
+    // (ms per step on a B200): 32 sequences 1.023 / 1.046, 40: 0.882 / 0.918, 48: 0.918 / 0.941, 64: 1.012 / 1.012,
+    // 80: 1.166 / 1.120, 128: 1.415 / 1.322.
+    return 48;
+}
+
 int32_t lfm25_decode_one_kernel_preferred(size_t page_size, size_t context_tokens, size_t batch_size) {
     if (page_size != 16 || batch_size == 0) {
         return 0;
@@ -1007,8 +1014,8 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
     LFM25_ENSURE(out.len >= out_required, LFM25_ERR_BUFFER_TOO_SMALL, "linear output storage too small");
     LFM25_ENSURE(x.ptr && weight.ptr && out.ptr, LFM25_ERR_NULL_POINTER, "linear received a null device pointer");
     // Which kernel: this library's tcgen05 kernels where they measured ahead of cuBLASLt on the step (the
-    // weight-major one up to 32 rows where N % 128 == 0 and K % 64 == 0, the batch-major one where
-    // bf16_rows_preferred says so), cuBLASLt otherwise, as the reference does.  The option bf16_gemm (or the
+    // weight-major one up to lfm25_bf16_own_kernel_max_rows() rows where N % 128 == 0 and K % 64 == 0, the
+    // batch-major one where bf16_rows_preferred says so), cuBLASLt otherwise, as the reference does.  The option bf16_gemm (or the
     // handle's tuning) = umma | cublaslt | rows forces one.
     const bool aligned = ((reinterpret_cast<uintptr_t>(x.ptr) | reinterpret_cast<uintptr_t>(weight.ptr) |
                            reinterpret_cast<uintptr_t>(out.ptr)) &
@@ -1018,7 +1025,7 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
     enum { kLibrary, kUmma, kRows } path = kLibrary;
     if (rows_ok && lfm25::bf16_rows_preferred(m, n, k)) {
         path = kRows;
-    } else if (umma_ok && m <= 32) {
+    } else if (umma_ok && m <= lfm25_bf16_own_kernel_max_rows()) {
         path = kUmma;
     }
     int64_t forced = lfm25::option(lfm25::kOptBf16Gemm);

@@ -720,7 +720,7 @@ GemmRowsPlan gemm_rows_plan(size_t m, size_t n, size_t k_bytes, bool gated, size
 }
 
 // Where this kernel measured ahead of the library's other routes (bench.py --workload gemm: HBM-cold, same process,
-// next to cuBLASLt).  Plain linears: nowhere yet -- the weight-major kernel is ahead up to 32 rows and level above,
+// next to cuBLASLt).  Plain linears: nowhere yet -- the weight-major kernel is ahead up to 48 rows and level above,
 // cuBLASLt is ahead on the 2048- to 6144-row BF16 sites from 33 rows on.  The gated Gate/Up linear (SiLU * Up in
 // the epilogue straight from the accumulator registers) from 64 rows on: 11.9 against 13.7 us at 128 rows, 16.7
 // against 20.0 at 256 (E4M3).

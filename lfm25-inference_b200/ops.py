@@ -120,6 +120,11 @@ def splitk_decode_splits(num_tokens: int, maximum_context_tokens: int, page_size
     return int(library().lfm25_splitk_decode_splits(num_tokens, maximum_context_tokens, page_size))
 
 
+def bf16_own_kernel_max_rows() -> int:
+    """Largest batch that the BF16 linear runs on the library's own tensor-core kernel (cuBLASLt above)."""
+    return int(library().lfm25_bf16_own_kernel_max_rows())
+
+
 def decode_one_kernel_preferred(page_size: int, context_tokens: int, batch_size: int) -> bool:
     """Reference: should_use_mok_one_kernel (src/ops/mok_dispatch.rs:7-27), with thresholds measured on a B200."""
     return bool(library().lfm25_decode_one_kernel_preferred(page_size, context_tokens, batch_size))
