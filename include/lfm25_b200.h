@@ -178,7 +178,9 @@ typedef struct lfm25_splitk_ragged_attention_launch {
     lfm25_slice block_tables;
     lfm25_slice request_slots;
     lfm25_slice position_ids;
-    lfm25_slice partials;      /* f32, >= num_tokens * 32 * num_splits * 66, written */
+    lfm25_slice partials;      /* f32, >= num_tokens * 32 * num_splits * 66, written; or {NULL, 0}: no records are
+                                * written, the splits of a token run as one thread-block cluster and merge through
+                                * distributed shared memory (num_splits 2, 4 or 8; same output bits) */
     lfm25_slice output;
     size_t num_tokens;
     size_t num_pages;

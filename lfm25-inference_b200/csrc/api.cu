@@ -430,9 +430,17 @@ int32_t lfm25_paged_ragged_attention_splitk_lfm2_bf16(void* stream,
                      checked_mul(partial_required, l.num_splits, &partial_required) &&
                      checked_mul(partial_required, 66, &partial_required),
                  LFM25_ERR_OVERFLOW, "split-K partial workspace size overflow");
-    LFM25_ENSURE(l.partials.len >= partial_required, LFM25_ERR_BUFFER_TOO_SMALL,
-                 "split-K partial workspace too small: need %zu, have %zu", partial_required, l.partials.len);
-    LFM25_ENSURE(l.partials.ptr != nullptr, LFM25_ERR_NULL_POINTER, "split-K partial workspace is null");
+    // No workspace at all (null pointer, zero length): the splits of a token merge inside the kernel, as one
+    // thread-block cluster per (token, KV head), and no records are written.
+    const bool in_kernel_merge = l.partials.ptr == nullptr && l.partials.len == 0;
+    if (in_kernel_merge) {
+        LFM25_ENSURE(l.num_splits == 2 || l.num_splits == 4 || l.num_splits == 8, LFM25_ERR_INVALID_ARGUMENT,
+                     "split-K ragged attention without a workspace takes 2, 4 or 8 splits");
+    } else {
+        LFM25_ENSURE(l.partials.len >= partial_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                     "split-K partial workspace too small: need %zu, have %zu", partial_required, l.partials.len);
+        LFM25_ENSURE(l.partials.ptr != nullptr, LFM25_ERR_NULL_POINTER, "split-K partial workspace is null");
+    }
     lfm25::AttentionLaunch args = {};
     args.query = l.query.ptr;
     args.key_cache = l.key_cache.ptr;
@@ -499,8 +507,14 @@ int32_t lfm25_fused_ragged_paged_attention_decode_lfm2_bf16(void* stream,
                          checked_mul(partial_required, splits, &partial_required) &&
                          checked_mul(partial_required, 66, &partial_required),
                      LFM25_ERR_OVERFLOW, "split-K partial workspace size overflow");
-        LFM25_ENSURE(l.partials.ptr != nullptr && l.partials.len >= partial_required, LFM25_ERR_BUFFER_TOO_SMALL,
-                     "split-K partial workspace too small: need %zu, have %zu", partial_required, l.partials.len);
+        if (l.partials.ptr == nullptr && l.partials.len == 0) {
+            // no workspace: the splits merge inside the kernel (one cluster per token and KV head)
+            LFM25_ENSURE(splits == 2 || splits == 4 || splits == 8, LFM25_ERR_INVALID_ARGUMENT,
+                         "fused decode attention without a workspace takes 1, 2, 4 or 8 splits");
+        } else {
+            LFM25_ENSURE(l.partials.ptr != nullptr && l.partials.len >= partial_required, LFM25_ERR_BUFFER_TOO_SMALL,
+                         "split-K partial workspace too small: need %zu, have %zu", partial_required, l.partials.len);
+        }
     }
     lfm25::AttentionLaunch args = {};
     args.query = l.query_raw.ptr;

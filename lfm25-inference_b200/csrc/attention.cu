@@ -36,7 +36,9 @@ constexpr uint32_t kStages = 4;                        // ring depth per warp
 constexpr uint32_t kStageBytes = 2 * kPageTileBytes;   // K tile then V tile
 constexpr uint32_t kRingBytes = kStages * kStageBytes; // per warp
 constexpr uint32_t kMergeFloats = kWarps * kQPerKv * kPartialStride;
-constexpr uint32_t kSmemBytes = kWarps * kRingBytes + kMergeFloats * 4 + kWarps * kStages * 8 + 16;
+constexpr uint32_t kClusterRecordFloats = kQPerKv * kPartialStride;   // this CTA's four split records, for its cluster
+constexpr uint32_t kSmemBytes = kWarps * kRingBytes + kMergeFloats * 4 + kWarps * kStages * 8 + 16 +
+                                kClusterRecordFloats * 4;
 constexpr uint32_t kSmemAlloc = kSmemBytes + 1024;     // room to align the rings to 1 KiB
 
 struct AttentionParams {
@@ -52,6 +54,8 @@ struct AttentionParams {
     uint32_t num_tokens;
     uint32_t num_pages;
     uint32_t num_splits;  // 1: write normalised output; >1: write split records
+    uint32_t cluster_merge;   // with num_splits > 1: the splits of a (token, KV head) are one thread-block cluster and
+                              // merge through distributed shared memory -- no records in global memory, no merge kernel
     uint32_t query_token_stride;  // elements between tokens of `query` (2048 when dense)
     uint32_t kv_token_stride;     // elements between tokens of key_raw / value_raw (512 when dense)
     // fused mode only: the raw projections of the step and what is needed to turn them into the new cache row
@@ -70,6 +74,20 @@ struct AttentionParams {
     const uint32_t* token_order;  // optional permutation: which token the r-th group of CTAs takes
 };
 
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// a float of the same shared-memory offset in the CTA of rank `rank` of this cluster
+__device__ __forceinline__ float load_from_cluster_cta(uint32_t local_address, uint32_t rank) {
+    uint32_t remote;
+    float value;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    return value;
+}
+
 // A CTA that has no result for its token (request slot outside the block tables, position outside the row, an
 // unassigned page, an append slot that contradicts the block table, a wait that ran out) returns without touching the
 // output.  With the KV axis split, it first marks its four records: a negative sum tells the merge kernel that the
@@ -77,7 +95,7 @@ struct AttentionParams {
 // in the records is never combined into an output.
 __device__ __forceinline__ void mark_no_result(const AttentionParams& p, uint32_t token, uint32_t kv_head,
                                                uint32_t split) {
-    if (p.num_splits > 1 && threadIdx.x < kQPerKv) {
+    if (p.num_splits > 1 && p.cluster_merge == 0 && threadIdx.x < kQPerKv) {
         const size_t q_index = static_cast<size_t>(token) * kQHeads + kv_head * kQPerKv + threadIdx.x;
         float* record = p.partials + (q_index * p.num_splits + split) * kPartialStride;
         record[0] = -INFINITY;
@@ -163,6 +181,8 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
     float* merge = reinterpret_cast<float*>(smem + kWarps * kRingBytes);
     const uint32_t bars = smem_u32(smem + kWarps * kRingBytes + kMergeFloats * 4) + warp * kStages * 8;
     uint32_t* bad_flag = reinterpret_cast<uint32_t*>(smem + kWarps * kRingBytes + kMergeFloats * 4 + kWarps * kStages * 8);
+    float* cluster_records =
+        reinterpret_cast<float*>(smem + kWarps * kRingBytes + kMergeFloats * 4 + kWarps * kStages * 8 + 16);
 
     if (threadIdx.x == 0) {
         *bad_flag = 0;
@@ -477,10 +497,13 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         }
     }
     __syncthreads();
-    if (*bad_flag != 0) {
+    const bool failed = *bad_flag != 0;
+    if (failed && p.cluster_merge == 0) {
         mark_no_result(p, token, kv_head, split);
         return;
     }
+    // (in a cluster a failed CTA goes on: its partners wait for it at the cluster barrier, and its record says
+    // "no result")
 
     // ---- combine the 4 warps: thread = (head, dims lane and lane + 32) ----
     const uint32_t head = warp;
@@ -506,7 +529,7 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         __nv_bfloat16* out_row = p.output + q_index * kHeadDim;
         out_row[lane] = __float2bfloat16_rn(out0 / denominator);
         out_row[lane + 32] = __float2bfloat16_rn(out1 / denominator);
-    } else {
+    } else if (p.cluster_merge == 0) {
         float* record = p.partials + (q_index * splits + split) * kPartialStride;
         if (lane == 0) {
             record[0] = maximum;
@@ -514,6 +537,45 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         }
         record[2 + lane] = out0;
         record[2 + lane + 32] = out1;
+    } else {
+        // The `splits` CTAs of this (token, KV head) are one cluster, in split order.  Each leaves its four records in
+        // its own shared memory; after the cluster barrier the first CTA reads them through distributed shared memory
+        // and merges them with the arithmetic of merge_splitk_kernel, in the same order, so the bits are the same.
+        float* mine = cluster_records + head * kPartialStride;
+        if (lane == 0) {
+            mine[0] = failed ? -INFINITY : maximum;
+            mine[1] = failed ? -1.0f : denominator;     // a negative sum: this CTA has no result
+        }
+        mine[2 + lane] = out0;
+        mine[2 + lane + 32] = out1;
+        cluster_barrier();
+        if (split == 0) {
+            const uint32_t local = smem_u32(mine);
+            float top = -INFINITY;
+            bool no_result = false;
+            for (uint32_t other = 0; other < splits; ++other) {
+                top = fmaxf(top, load_from_cluster_cta(local, other));
+                no_result = no_result || load_from_cluster_cta(local + 4, other) < 0.0f;
+            }
+            if (!no_result) {
+                float total = 0.0f;
+                float merged0 = 0.0f;
+                float merged1 = 0.0f;
+                for (uint32_t other = 0; other < splits; ++other) {
+                    const float part_sum = load_from_cluster_cta(local + 4, other);
+                    if (part_sum != 0.0f) {
+                        const float scale = fast_exp2((load_from_cluster_cta(local, other) - top) * kLog2e);
+                        total = fmaf(part_sum, scale, total);
+                        merged0 = fmaf(load_from_cluster_cta(local + (2 + lane) * 4, other), scale, merged0);
+                        merged1 = fmaf(load_from_cluster_cta(local + (2 + lane + 32) * 4, other), scale, merged1);
+                    }
+                }
+                __nv_bfloat16* out_row = p.output + q_index * kHeadDim;
+                out_row[lane] = __float2bfloat16_rn(merged0 / total);
+                out_row[lane + 32] = __float2bfloat16_rn(merged1 / total);
+            }
+        }
+        cluster_barrier();     // nobody leaves while the first CTA may still be reading its records
     }
 }
 
@@ -597,6 +659,14 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.num_tokens = static_cast<uint32_t>(launch.num_tokens);
     params.num_pages = static_cast<uint32_t>(launch.num_pages);
     params.num_splits = launch.num_splits;
+    // No workspace for the split records: the splits of a (token, KV head) run as one thread-block cluster and merge
+    // through distributed shared memory (cluster sizes 2, 4 and 8; the callers ask for nothing else without a
+    // workspace).
+    const bool cluster_merge = launch.num_splits > 1 && launch.partials == nullptr;
+    if (cluster_merge && launch.num_splits != 2 && launch.num_splits != 4 && launch.num_splits != 8) {
+        return cudaErrorInvalidValue;
+    }
+    params.cluster_merge = cluster_merge ? 1u : 0u;
     params.query_token_stride = static_cast<uint32_t>(launch.query_token_stride);
     params.kv_token_stride = static_cast<uint32_t>(launch.kv_token_stride);
     params.key_raw = static_cast<const __nv_bfloat16*>(launch.key_raw);
@@ -613,9 +683,9 @@ cudaError_t launch_ragged_decode_attention(cudaStream_t stream, const AttentionL
     params.selftest_drop = wait_selftest_drop() ? 1 : 0;
     params.token_order = launch.token_order;
     const uint64_t blocks = static_cast<uint64_t>(launch.num_tokens) * kKvHeads * launch.num_splits;
-    cudaError_t status = launch_kernel(kernel, static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream, 1,
-                                       key_map, value_map, params);
-    if (status != cudaSuccess || launch.num_splits == 1) {
+    cudaError_t status = launch_kernel(kernel, static_cast<unsigned int>(blocks), kThreads, kSmemAlloc, stream,
+                                       cluster_merge ? launch.num_splits : 1u, key_map, value_map, params);
+    if (status != cudaSuccess || launch.num_splits == 1 || cluster_merge) {
         return status;
     }
     return launch_kernel(merge_splitk_kernel, static_cast<unsigned int>(launch.num_tokens * kKvHeads), kThreads, 0,

@@ -302,6 +302,10 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             post.num_pages = model->num_pages;
             post.eps = model->norm_eps;
             const size_t splits = lfm25_splitk_decode_splits(tokens, batch->max_context_tokens, 16);
+            // the splits of a token merge inside the attention kernel (a cluster per token and KV head) instead of
+            // through records in global memory and a merge kernel
+            const bool in_kernel_merge = lfm25::option(lfm25::kOptSplitkClusterMerge) != 0 &&
+                                         (splits == 2 || splits == 4 || splits == 8);
             if (fused_append) {
                 // one launch: QK-norm + RoPE + paged append + attention (+ merge when split)
                 RegionTimer timer(self, LFM25_REGION_ATTENTION);
@@ -324,7 +328,9 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
                 fused.block_tables = slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
                 fused.request_slots = slice_of(batch->request_slots, tokens);
                 fused.block_table_stride = batch->block_table_stride;
-                fused.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
+                fused.partials = in_kernel_merge
+                                     ? slice_of(static_cast<float*>(nullptr), 0)
+                                     : slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
                 fused.num_splits = splits;
                 fused.query_token_stride = 0;
                 fused.kv_token_stride = 0;
@@ -377,7 +383,9 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             attention.block_tables = slice_of(batch->block_tables, batch->block_table_stride * batch->block_table_rows);
             attention.request_slots = slice_of(batch->request_slots, tokens);
             attention.position_ids = post.position_ids;
-            attention.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
+            attention.partials = in_kernel_merge
+                                     ? slice_of(static_cast<float*>(nullptr), 0)
+                                     : slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
             attention.output = slice_of(self->post_operator, tokens * kHidden);
             attention.num_tokens = tokens;
             attention.num_pages = model->num_pages;

@@ -28,6 +28,7 @@ Entry g_options[kOptCount] = {
     {"fused_silu_bf16", "LFM25_FUSED_SILU_BF16", 0, 0, 1},
     {"kv_evict_first", "LFM25_KV_EVICT_FIRST", 1, 0, 1},
     {"weights_evict_first", "LFM25_WEIGHTS_EVICT_FIRST", 1, 0, 1},
+    {"splitk_cluster_merge", "LFM25_SPLITK_CLUSTER_MERGE", 1, 0, 1},
     {"engine_graph", "LFM25_ENGINE_GRAPH", 1, 0, 1},
     {"hybrid_attention", "LFM25_HYBRID_ATTENTION", 0, 0, 2},
     {"fp8_gemm_path", "LFM25_FP8_GEMM_PATH", 0, 0, 4},

@@ -11,6 +11,9 @@
 //   fused_silu_bf16      0 | 1                                 0         the same for a Gate/Up site that stays in BF16
 //   kv_evict_first       0 | 1                                 1         L2 evict-first hint on the KV page stream
 //   weights_evict_first  0 | 1                                 1         the same hint on the weight stream of the tcgen05 GEMMs
+//   splitk_cluster_merge 0 | 1                                 1         decode executor: the KV splits of a token merge inside
+//                                                                        the attention kernel (one cluster per token and KV
+//                                                                        head) instead of through records and a merge kernel
 //   engine_graph         0 | 1                                 1         serving engine replays captured decode steps
 //   hybrid_attention     0 auto | 1 umma | 2 mma               0         kernel of the mixed-step attention
 //   fp8_gemm_path        0 auto | 1 stream | 2 umma | 3 generic | 4 rows   0   kernel of the E4M3 linear
@@ -34,6 +37,7 @@ enum Option : int {
     kOptFusedSiluBf16,
     kOptKvEvictFirst,
     kOptWeightsEvictFirst,
+    kOptSplitkClusterMerge,
     kOptEngineGraph,
     kOptHybridAttention,
     kOptFp8GemmPath,

@@ -182,14 +182,16 @@ def paged_ragged_attention_fast_lfm2_bf16(inputs: FastRaggedAttentionInput) -> t
     return output
 
 
-def paged_ragged_attention_splitk_lfm2_bf16_into(inputs: FastRaggedAttentionInput, partials: torch.Tensor,
-                                                 num_splits: int, output: torch.Tensor, token_order=None) -> None:
-    """Reference: src/ops/attention_async_fast.rs:154-197."""
+def paged_ragged_attention_splitk_lfm2_bf16_into(inputs: FastRaggedAttentionInput, partials, num_splits: int,
+                                                 output: torch.Tensor, token_order=None) -> None:
+    """Reference: src/ops/attention_async_fast.rs:154-197.  `partials` None (no counterpart in the reference): no
+    workspace and no records; the splits of a token merge inside the kernel (2, 4 or 8 splits)."""
     _ensure(2 <= num_splits <= SPLITK_MAX_SPLITS, f"split-K attention requires 2..={SPLITK_MAX_SPLITS} splits")
     num_tokens = _validate_ragged_input(inputs)
     launch = _abi.SplitKRaggedAttentionLaunch(
         inputs.arena.page_size, _slice(inputs.query), _slice(inputs.arena.key), _slice(inputs.arena.value),
-        _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids), _slice(partials),
+        _slice(inputs.block_tables), _slice(inputs.request_slots), _slice(inputs.position_ids),
+        _slice(partials) if partials is not None else Slice(None, 0),
         _slice(output), num_tokens, inputs.arena.num_pages, inputs.block_table_stride, num_splits,
         _order_slice(token_order, num_tokens))
     check(library().lfm25_paged_ragged_attention_splitk_lfm2_bf16(_stream(), launch))

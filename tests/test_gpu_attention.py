@@ -286,3 +286,55 @@ def test_token_order_changes_no_result(device):
     with pytest.raises(Lfm25Error):
         ops.paged_ragged_attention_fast_lfm2_bf16_into(inputs, output, token_order=shuffled[:tokens - 1])
     assert ops.device_status()[0] == 0
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+@pytest.mark.parametrize("sequences,low,high", [(1, 3000, 3000), (9, 1, 700), (24, 16, 4096), (70, 100, 2048)])
+def test_merge_inside_the_kernel_gives_the_bits_of_the_merge_kernel(device, splits, sequences, low, high):
+    """Without a workspace the splits of a token run as one thread-block cluster and merge through distributed shared
+    memory; the output must be bit-identical to records + merge kernel, with short contexts (empty splits) in the
+    batch, with and without a token order."""
+    case = cases.random_ragged_case(50 + sequences, sequences, low, high, 8192)
+    inputs = upload(case, device)
+    tokens = case["query"].shape[0]
+    workspace = torch.empty((ops.splitk_workspace_elements(tokens),), dtype=torch.float32, device=device)
+    expected = torch.zeros_like(inputs.query)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, workspace, splits, expected)
+    got = torch.zeros_like(inputs.query)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, None, splits, got)
+    assert np.array_equal(bits_of(got), bits_of(expected))
+    order = torch.zeros(tokens, dtype=torch.int32, device=device)
+    ops.context_order_desc_into(inputs.position_ids, order)
+    ordered = torch.zeros_like(inputs.query)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, None, splits, ordered, token_order=order)
+    assert np.array_equal(bits_of(ordered), bits_of(expected))
+    assert ops.device_status()[0] == 0
+
+
+def test_merge_inside_the_kernel_leaves_a_token_without_result_alone(device):
+    """One request slot outside the block tables (every CTA of that token's clusters returns at once) and one
+    unassigned page in the middle of another sequence (only the split that meets it gives up; its partners still
+    pass the cluster barrier): both rows keep what the caller passed in, the others match the valid run."""
+    case = cases.random_ragged_case(61, 12, 600, 2000, 4096)
+    inputs = upload(case, device)
+    tokens = case["query"].shape[0]
+    good = torch.zeros_like(inputs.query)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, None, 4, good)
+    slots = case["request_slots"].copy()
+    slots[3] = case["block_tables"].shape[0] + 5
+    tables = case["block_tables"].copy()
+    tables[int(case["request_slots"][7]), 20] = 0xFFFFFFFF
+    broken = ops.FastRaggedAttentionInput(
+        query=inputs.query, arena=inputs.arena, block_tables=to_u32(tables, device),
+        block_table_stride=inputs.block_table_stride, request_slots=to_u32(slots, device),
+        position_ids=inputs.position_ids)
+    output = torch.full_like(inputs.query, 5.0)
+    ops.paged_ragged_attention_splitk_lfm2_bf16_into(broken, None, 4, output)
+    got, want = bits_of(output), bits_of(good)
+    fill = bits_of(torch.full((32, 64), 5.0, dtype=torch.bfloat16))
+    assert np.array_equal(got[3], fill) and np.array_equal(got[7], fill)
+    keep = ~np.isin(np.arange(tokens), [3, 7])
+    assert np.array_equal(got[keep], want[keep])
+    with pytest.raises(Lfm25Error, match="2, 4 or 8 splits"):
+        ops.paged_ragged_attention_splitk_lfm2_bf16_into(inputs, None, 3, output)
+    assert ops.device_status()[0] == 0

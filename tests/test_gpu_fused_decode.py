@@ -45,7 +45,7 @@ def run_two_kernels(case, device, splits):
     return bits_of(output), bits_of(arena.key), bits_of(arena.value), bits_of(query)
 
 
-def run_fused(case, device, splits, slots=None, sentinel=None, packed=False):
+def run_fused(case, device, splits, slots=None, sentinel=None, packed=False, in_kernel_merge=False):
     arena = ops.PagedKvArena(to_bf16(case["key_cache"], device), to_bf16(case["value_cache"], device))
     query = to_bf16(case["query"], device)
     key, value = to_bf16(case["key"], device), to_bf16(case["value"], device)
@@ -60,7 +60,8 @@ def run_fused(case, device, splits, slots=None, sentinel=None, packed=False):
     output = torch.zeros_like(query)
     if sentinel is not None:
         output = torch.zeros(query.shape, dtype=torch.int16, device=device).fill_(sentinel).view(torch.bfloat16)
-    partials = torch.empty(ops.splitk_workspace_elements(query.shape[0]), dtype=torch.float32, device=device)
+    partials = None if in_kernel_merge else \
+        torch.empty(ops.splitk_workspace_elements(query.shape[0]), dtype=torch.float32, device=device)
     ops.fused_ragged_paged_attention_decode_lfm2_bf16_into(
         query, key, value, to_bf16(case["query_norm"], device),
         to_bf16(case["key_norm"], device), torch.from_numpy(case["inv_freq"]).to(device),
@@ -86,6 +87,19 @@ def test_fused_equals_two_kernel_route(device, seed, sequences, low, high, pages
         _, exact = oracle.paged_ragged_attention(rotated_query, want_key, want_value, case["batch"].block_tables,
                                                  case["batch"].request_slots, case["positions"], want_exact=True)
         assert_within_oracle(got_output, exact)
+
+
+@pytest.mark.parametrize("splits", [2, 4, 8])
+@pytest.mark.parametrize("packed", [False, True])
+def test_fused_with_the_merge_inside_the_kernel(device, splits, packed):
+    """No workspace: the splits of a token are one cluster and merge through distributed shared memory.  Output and
+    the appended cache rows are bit-identical to the route through records and the merge kernel."""
+    case = build_case(25, 41, 3, 3000, 8192)
+    want = run_fused(case, device, splits, packed=packed)
+    got = run_fused(case, device, splits, packed=packed, in_kernel_merge=True)
+    for a, b in zip(got, want):
+        assert np.array_equal(a, b)
+    assert ops.device_status()[0] == 0
 
 
 @pytest.mark.parametrize("splits", [1, 4])
