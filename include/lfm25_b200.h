@@ -64,6 +64,8 @@ int32_t lfm25_device_status(void* stream, uint32_t out[4]);
  * default, may be preset by the environment variable LFM25_<NAME> (read once) and changed at run time here; a
  * change applies to launches issued afterwards and is not recorded in CUDA graphs that are already captured.
  *   pdl, fused_silu, kv_evict_first, weights_evict_first, engine_graph 0 | 1 (default 1)
+ *   splitk_cluster_merge   0 | 1 (default 1): the decode executor merges the KV splits of a token inside the attention
+ *                          kernel (a cluster per token and KV head) where that measured faster, else never
  *   fused_append           0 two launches | 1 one kernel | 2 auto (default): how the decode executor runs an
  *                          attention layer -- QK-norm + RoPE + append as a kernel of their own before the attention
  *                          kernel, or inside it; auto asks lfm25_decode_one_kernel_preferred()

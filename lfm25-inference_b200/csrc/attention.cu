@@ -84,7 +84,7 @@ __device__ __forceinline__ float load_from_cluster_cta(uint32_t local_address, u
     uint32_t remote;
     float value;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_address), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote));
     return value;
 }
 
@@ -550,24 +550,42 @@ ragged_decode_attention_kernel(const __grid_constant__ CUtensorMap key_map,
         mine[2 + lane + 32] = out1;
         cluster_barrier();
         if (split == 0) {
+            // all remote loads first (up to 8 splits x 4 values per thread in flight), the arithmetic after them
+            constexpr uint32_t kMaxSplits = 8;
             const uint32_t local = smem_u32(mine);
+            float peak[kMaxSplits];
+            float sum[kMaxSplits];
+            float low[kMaxSplits];
+            float high[kMaxSplits];
+#pragma unroll
+            for (uint32_t other = 0; other < kMaxSplits; ++other) {
+                if (other < splits) {
+                    peak[other] = load_from_cluster_cta(local, other);
+                    sum[other] = load_from_cluster_cta(local + 4, other);
+                    low[other] = load_from_cluster_cta(local + (2 + lane) * 4, other);
+                    high[other] = load_from_cluster_cta(local + (2 + lane + 32) * 4, other);
+                }
+            }
             float top = -INFINITY;
             bool no_result = false;
-            for (uint32_t other = 0; other < splits; ++other) {
-                top = fmaxf(top, load_from_cluster_cta(local, other));
-                no_result = no_result || load_from_cluster_cta(local + 4, other) < 0.0f;
+#pragma unroll
+            for (uint32_t other = 0; other < kMaxSplits; ++other) {
+                if (other < splits) {
+                    top = fmaxf(top, peak[other]);
+                    no_result = no_result || sum[other] < 0.0f;
+                }
             }
             if (!no_result) {
                 float total = 0.0f;
                 float merged0 = 0.0f;
                 float merged1 = 0.0f;
-                for (uint32_t other = 0; other < splits; ++other) {
-                    const float part_sum = load_from_cluster_cta(local + 4, other);
-                    if (part_sum != 0.0f) {
-                        const float scale = fast_exp2((load_from_cluster_cta(local, other) - top) * kLog2e);
-                        total = fmaf(part_sum, scale, total);
-                        merged0 = fmaf(load_from_cluster_cta(local + (2 + lane) * 4, other), scale, merged0);
-                        merged1 = fmaf(load_from_cluster_cta(local + (2 + lane + 32) * 4, other), scale, merged1);
+#pragma unroll
+                for (uint32_t other = 0; other < kMaxSplits; ++other) {
+                    if (other < splits && sum[other] != 0.0f) {
+                        const float scale = fast_exp2((peak[other] - top) * kLog2e);
+                        total = fmaf(sum[other], scale, total);
+                        merged0 = fmaf(low[other], scale, merged0);
+                        merged1 = fmaf(high[other], scale, merged1);
                     }
                 }
                 __nv_bfloat16* out_row = p.output + q_index * kHeadDim;

@@ -229,6 +229,20 @@ int32_t linear_decode(lfm25_decode_executor* self, const lfm25_linear_weights& w
                                     rows, weights.n, weights.k);
 }
 
+// Whether the KV splits of a token should merge inside the attention kernel (one cluster per token and KV head,
+// no records, no merge kernel) or through records and the merge kernel.  The cluster saves a launch, but its CTAs
+// leave their SM only together, which costs once the grid runs in several waves.  Whole decode step on a B200, ms per
+// step without / with the in-kernel merge (sequences, splits): 1 (8) 0.662 / 0.644, 4 (8) 0.675 / 0.655,
+// 8 (8) 0.693 / 0.688, 12 (4) 0.709 / 0.701, 16 (4) 0.715 / 0.726, 24 (4) 0.757 / 0.758, 28 (2) 0.783 / 0.774,
+// 48 (2) 0.915 / 0.900, 64 (2) 1.012 / 1.026.
+bool merge_in_kernel_preferred(size_t tokens, size_t splits) {
+    const size_t ctas = tokens * 8 * splits;
+    if (splits == 8) return ctas <= 512;
+    if (splits == 4) return ctas <= 384;
+    if (splits == 2) return ctas <= 768;
+    return false;
+}
+
 int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm25_decode_batch* batch, bool use_fp8,
                 bool advance) {
     cudaStream_t stream = self->blaslt->stream;
@@ -305,7 +319,7 @@ int32_t forward(lfm25_decode_executor* self, const lfm25_model* model, const lfm
             // the splits of a token merge inside the attention kernel (a cluster per token and KV head) instead of
             // through records in global memory and a merge kernel
             const bool in_kernel_merge = lfm25::option(lfm25::kOptSplitkClusterMerge) != 0 &&
-                                         (splits == 2 || splits == 4 || splits == 8);
+                                         merge_in_kernel_preferred(tokens, splits);
             if (fused_append) {
                 // one launch: QK-norm + RoPE + paged append + attention (+ merge when split)
                 RegionTimer timer(self, LFM25_REGION_ATTENTION);
