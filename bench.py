@@ -688,8 +688,10 @@ def run_step_arm(arguments, rank, world):
 
         # ---- instrumented eager pass: CUDA events around every op, for the per-kernel roofline ----
         executor.profile(True)
+        library_calls_before = ops.library_calls()
         for _ in range(profile_steps):
             executor.forward(model, device_batch, use_fp8=use_fp8, advance=True)
+        library_launches = (ops.library_calls() - library_calls_before) // profile_steps    # cuBLASLt matmuls per step
         regions = executor.profile(False, collect=True)
         contexts_profiled = positions_now + 1 + (profile_steps + 1) / 2.0      # mean context during the pass
         attention_ms, attention_ops = regions["attention"]
@@ -875,12 +877,9 @@ def run_step_arm(arguments, rank, world):
             cpu_tokens, _, cpu_description, threads = step_cpu_sample(model, batch, token_ids, use_fp8,
                                                                       arguments.cpu_sequences or STEP_SEQUENCES, 1)
         per_step = {name: ops_count // profile_steps for name, (_, ops_count) in regions.items()}
-        # GPU kernels per step, counted from the captured graph; the BF16 GEMMs of the larger batches are
-        # cuBLASLt's kernels (one per call), everything else is this library's
+        # GPU kernels per step, counted from the captured graph; the matmuls that the library handed to cuBLASLt
+        # during an eager step (one kernel each) are cuBLASLt's, everything else is this library's
         graph_kernels = executor.graph_kernels()
-        forced = ops.get_option("bf16_gemm")          # 0 auto | 1 umma | 2 cublaslt | 3 rows
-        through_library = forced == 2 or (forced == 0 and STEP_SEQUENCES > ops.bf16_own_kernel_max_rows())
-        library_launches = per_step["bf16_linear"] if through_library else 0
         launches = graph_kernels - library_launches
         line = {
             "metric": STEP_METRIC, "value": STEP_SEQUENCES * steps * world / (total_ms * 1e-3), "unit": "tok/s",

@@ -15,6 +15,7 @@ CublasLtBf16* cublaslt_bf16_create(void* workspace, size_t workspace_bytes);
 void cublaslt_bf16_destroy(CublasLtBf16* self);
 cudaError_t cublaslt_bf16_linear(CublasLtBf16* self, cudaStream_t stream, const void* x, const void* weight,
                                  void* out, size_t m, size_t n, size_t k);
+uint64_t cublaslt_bf16_calls();   // matmuls handed to cuBLASLt by this process so far
 }  // namespace lfm25
 
 struct lfm25_blaslt {

@@ -8,6 +8,8 @@
 #include <cublasLt.h>
 #include <dlfcn.h>
 
+#include <atomic>
+
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -61,6 +63,8 @@ Api& api() {
     }();
     return instance;
 }
+
+std::atomic<uint64_t> g_library_calls{0};   // matmuls handed to cuBLASLt so far (also while a stream is captured)
 
 struct Plan {
     cublasLtMatmulDesc_t desc = nullptr;
@@ -146,10 +150,13 @@ cudaError_t cublaslt_bf16_linear(CublasLtBf16* self, cudaStream_t stream, const 
     }
     const float alpha = 1.0f;
     const float beta = 0.0f;
+    g_library_calls.fetch_add(1, std::memory_order_relaxed);
     const cublasStatus_t status =
         api().matmul(self->handle, plan->desc, &alpha, weight, plan->a, x, plan->b, &beta, out, plan->c, out, plan->c,
                      &plan->algo, self->workspace, self->workspace_bytes, stream);
     return status == CUBLAS_STATUS_SUCCESS ? cudaSuccess : cudaErrorUnknown;
 }
+
+uint64_t cublaslt_bf16_calls() { return g_library_calls.load(std::memory_order_relaxed); }
 
 }  // namespace lfm25

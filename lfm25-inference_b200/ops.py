@@ -125,6 +125,15 @@ def bf16_own_kernel_max_rows() -> int:
     return int(library().lfm25_bf16_own_kernel_max_rows())
 
 
+def bf16_own_kernel_preferred(m: int, n: int, k: int) -> bool:
+    return bool(library().lfm25_bf16_own_kernel_preferred(m, n, k))
+
+
+def library_calls() -> int:
+    """Matmuls this process has handed to cuBLASLt so far (not counting replays of captured graphs)."""
+    return int(library().lfm25_blaslt_library_calls())
+
+
 def decode_one_kernel_preferred(page_size: int, context_tokens: int, batch_size: int) -> bool:
     """Reference: should_use_mok_one_kernel (src/ops/mok_dispatch.rs:7-27), with thresholds measured on a B200."""
     return bool(library().lfm25_decode_one_kernel_preferred(page_size, context_tokens, batch_size))
