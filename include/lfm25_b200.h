@@ -380,10 +380,6 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
  * nothing forces a route; larger batches go through cuBLASLt.  The value is measured on the whole decode step (the
  * figures are in the definition).  No counterpart in the reference, which always calls cuBLASLt. */
 size_t lfm25_bf16_own_kernel_max_rows(void);
-/* The same choice for one problem: above lfm25_bf16_own_kernel_max_rows() rows the long weight streams (Down,
- * Gate/Up) stay on the own kernel a while longer, the sites with few weight tiles go to cuBLASLt (measurements in
- * the definition).  1 = own kernel, 0 = cuBLASLt. */
-int32_t lfm25_bf16_own_kernel_preferred(size_t m, size_t n, size_t k);
 /* How many matmuls this process has handed to cuBLASLt so far (calls made while a stream is being captured count
  * once, replays of the captured graph do not): the benchmark's account of library launches per step. */
 uint64_t lfm25_blaslt_library_calls(void);

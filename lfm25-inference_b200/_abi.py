@@ -217,7 +217,6 @@ PROTOTYPES = {
     "lfm25_splitk_decode_splits": (_size, [_size, _size, _size]),
     "lfm25_decode_one_kernel_preferred": (ctypes.c_int32, [_size, _size, _size]),
     "lfm25_bf16_own_kernel_max_rows": (_size, []),
-    "lfm25_bf16_own_kernel_preferred": (ctypes.c_int32, [_size, _size, _size]),
     "lfm25_blaslt_library_calls": (ctypes.c_uint64, []),
     "lfm25_quantize_bf16_e4m3": (ctypes.c_int32, [_stream, Slice, Slice, _size, ctypes.c_float]),
     "lfm25_silu_mul_packed_bf16": (ctypes.c_int32, [_stream, Slice, Slice, _size, _size]),

@@ -677,24 +677,11 @@ size_t lfm25_splitk_decode_splits(size_t num_tokens, size_t maximum_context_toke
 size_t lfm25_bf16_own_kernel_max_rows(void) {
     // Whole decode step, every BF16 site on the weight-major tcgen05 kernel against every one through cuBLASLt
     // (ms per step on a B200): 32 sequences 1.023 / 1.046, 40: 0.882 / 0.918, 48: 0.918 / 0.941, 64: 1.012 / 1.012,
-    // 80: 1.166 / 1.120, 128: 1.415 / 1.322.
+    // 80: 1.166 / 1.120, 128: 1.415 / 1.322.  A choice per site above 48 rows (own kernel for Down up to 96 rows and
+    // Gate/Up up to 112, where its kernel time inside an all-own step is the shorter one; cuBLASLt for the sites with
+    // few weight tiles) was measured too: 64 sequences 1.009, 80 1.138 (cuBLASLt for all: 1.120), 96 1.186 (1.189) --
+    // an own kernel between two library kernels loses the overlap with its neighbours that makes it faster.
     return 48;
-}
-
-int32_t lfm25_bf16_own_kernel_preferred(size_t m, size_t n, size_t k) {
-    if (m <= lfm25_bf16_own_kernel_max_rows()) {
-        return 1;
-    }
-    // Above that the sites differ.  Time of the kernel inside the replayed decode step (CUPTI records; exclusive
-    // microseconds, own weight-major kernel / cuBLASLt):
-    //   rows   Down 2048 x 8192   Gate/Up 16384 x 2048   in-proj 6144 x 2048   2048 x 2048
-    //    64      11.1 / 13.3         14.9 / 15.0            10.0 / 7.1          5.4 / 5.6
-    //    96      13.0 / 13.4         15.6 / 17.6            11.6 / 8.4          7.1 / 5.8
-    //   128      14.4 / 13.6         16.1 / 14.1-16.9       11.9 / 7.6          8.2 / 5.7
-    // The two long streams stay on the own kernel a while longer; the sites with few weight tiles go to cuBLASLt.
-    if (k >= 8192) return m <= 96 ? 1 : 0;
-    if (n >= 16384) return m <= 112 ? 1 : 0;
-    return 0;
 }
 
 uint64_t lfm25_blaslt_library_calls(void) { return lfm25::cublaslt_bf16_calls(); }
@@ -1057,7 +1044,7 @@ int32_t lfm25_blaslt_linear_bf16(lfm25_blaslt* handle, lfm25_slice x, lfm25_slic
     enum { kLibrary, kUmma, kRows } path = kLibrary;
     if (rows_ok && lfm25::bf16_rows_preferred(m, n, k)) {
         path = kRows;
-    } else if (umma_ok && lfm25_bf16_own_kernel_preferred(m, n, k) != 0) {
+    } else if (umma_ok && m <= lfm25_bf16_own_kernel_max_rows()) {
         path = kUmma;
     }
     int64_t forced = lfm25::option(lfm25::kOptBf16Gemm);

@@ -125,10 +125,6 @@ def bf16_own_kernel_max_rows() -> int:
     return int(library().lfm25_bf16_own_kernel_max_rows())
 
 
-def bf16_own_kernel_preferred(m: int, n: int, k: int) -> bool:
-    return bool(library().lfm25_bf16_own_kernel_preferred(m, n, k))
-
-
 def library_calls() -> int:
     """Matmuls this process has handed to cuBLASLt so far (not counting replays of captured graphs)."""
     return int(library().lfm25_blaslt_library_calls())
