@@ -1362,7 +1362,10 @@ def dispatched_serving_line(arguments, world, trace, gathered, front_result):
                          "reused_prompt_tokens": reused, "reused_frac": reused / max(prompt_tokens, 1)},
         "per_replica": per_replica,
         "front": {"handed": front_result.get("handed"),
-                  "outstanding_tokens_at_end": front_result.get("outstanding_tokens")},
+                  "outstanding_tokens_at_end": front_result.get("outstanding_tokens"),
+                  "failed_replicas": front_result.get("failed_replicas"),
+                  "redispatched_requests": len(front_result.get("redispatched_requests") or []),
+                  "unfinished_requests": len(front_result.get("unfinished_requests") or [])},
         "roofline": None, "cpu_baseline": None,
         "e2e": {"value": value, "unit": "tok/s",
                 "h2d_bytes_per_step": 4 * (prompt_tokens + generated) * 3 // max(steps, 1),

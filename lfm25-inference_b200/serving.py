@@ -165,10 +165,11 @@ def run_trace(engine: ServingEngine, requests: list[Request]) -> dict:
 # every process builds from the same seed; the channel is a key-value store of the host (torch.distributed's store:
 # no GPU collective anywhere).  Keys: "n/<replica>" = requests handed to the replica so far, "q/<replica>/<k>" = index
 # of the k-th of them, "done/<replica>" = tokens the replica has finished with (prompt + generated of completed or
-# rejected requests), "beat/<replica>" = wall-clock time of the replica's last sign of life, "closed" = set once the
-# last request is handed out.  A replica whose last sign of life is older than the front's timeout is marked failed
-# in the dispatcher (lfm25_dispatcher_mark_failed) and gets no further requests; what it had been handed and not
-# finished is reported as lost.
+# rejected requests), "fin/<replica>" and "f/<replica>/<k>" = how many requests it has finished and which,
+# "beat/<replica>" = wall-clock time of the replica's last sign of life, "closed" = set by the front once every
+# request of the trace is finished.  A replica whose last sign of life is older than the front's timeout is marked
+# failed in the dispatcher (lfm25_dispatcher_mark_failed) and gets no further requests; what it had been handed and
+# has not reported finished is handed out again to the others.
 
 HEARTBEAT_PERIOD_S = 0.1
 
@@ -188,45 +189,80 @@ def estimated_tokens(request: Request) -> int:
 
 
 def run_front(store, replicas: int, requests: list[Request], origin_s: float, slack_tokens: int = 8192,
-              clock=time.time, sleep=time.sleep, failure_timeout_s: float = 5.0) -> dict:
-    """Hands out `requests` in arrival order, each at origin_s + arrival, and returns the assignment
-    {request_id: replica} with the dispatcher's view of the loads at the end.  A replica that has given no sign of
-    life for `failure_timeout_s` is marked failed and left out from then on."""
+              clock=time.time, sleep=time.sleep, failure_timeout_s: float = 5.0, watch_period_s: float = 0.02) -> dict:
+    """Hands out `requests` in arrival order, each at origin_s + arrival, keeps watching until every request is
+    finished, and returns the assignment {request_id: replica} with the dispatcher's view of the loads at the end.
+    A replica that has given no sign of life for `failure_timeout_s` is marked failed and left out from then on;
+    what it had been handed and has not reported finished is handed out again to the replicas that live (the
+    request starts over there; its arrival time stays)."""
     from .cache import Dispatcher
     dispatcher = Dispatcher(replicas)
     seen_done = [0] * replicas
-    handed = [0] * replicas
+    seen_finished = [0] * replicas
+    handed = [[] for _ in range(replicas)]          # request indices per replica, in hand-out order
+    finished = set()
     failed = []
+    redispatched = []
     assignment = {}
     hashes = [prefix_hash(request.prompt) for request in requests]
-    order = sorted(range(len(requests)), key=lambda index: requests[index].arrival_us)
-    for index in order:
+    state = {"nobody_left": False}
+
+    def hand_out(index: int) -> None:
         request = requests[index]
-        wait = origin_s + request.arrival_us * 1e-6 - clock()
-        if wait > 0:
-            sleep(wait)
+        replica = dispatcher.assign(estimated_tokens(request), prefix_hash=hashes[index], slack_tokens=slack_tokens)
+        store.set(f"q/{replica}/{len(handed[replica])}", str(index))
+        handed[replica].append(index)
+        store.add(f"n/{replica}", 1)
+        assignment[request.request_id] = replica
+
+    def look() -> None:
+        """Completions and signs of life reported since the last look; failures found are handled here."""
         now = clock()
-        for replica in range(replicas):                       # completions reported since the last look
+        for replica in range(replicas):
             if replica in failed:
                 continue
             done = int(store.add(f"done/{replica}", 0))
             if done > seen_done[replica]:
                 dispatcher.complete(replica, done - seen_done[replica])
                 seen_done[replica] = done
+            count = int(store.add(f"fin/{replica}", 0))
+            while seen_finished[replica] < count:
+                finished.add(int(store.get(f"f/{replica}/{seen_finished[replica]}")))
+                seen_finished[replica] += 1
             if store.check([f"beat/{replica}"]):
                 last_beat = float(store.get(f"beat/{replica}").decode())
             else:
                 last_beat = origin_s                             # a replica that never reported counts from the start
-            if now - last_beat > failure_timeout_s and len(failed) + 1 < replicas:
+            if now - last_beat > failure_timeout_s:
+                if len(failed) + 1 == replicas:
+                    state["nobody_left"] = True                  # the last replica is gone too: nothing to hand to
+                    continue
                 dispatcher.mark_failed(replica)
                 failed.append(replica)
-        replica = dispatcher.assign(estimated_tokens(request), prefix_hash=hashes[index], slack_tokens=slack_tokens)
-        store.set(f"q/{replica}/{handed[replica]}", str(index))
-        handed[replica] += 1
-        store.add(f"n/{replica}", 1)
-        assignment[request.request_id] = replica
+                for index in handed[replica]:
+                    if index not in finished:
+                        redispatched.append(requests[index].request_id)
+                        hand_out(index)
+
+    order = sorted(range(len(requests)), key=lambda index: requests[index].arrival_us)
+    for index in order:
+        wait = origin_s + requests[index].arrival_us * 1e-6 - clock()
+        while wait > 0:                                          # keep looking while waiting for the next arrival
+            sleep(min(wait, watch_period_s))
+            look()
+            wait = origin_s + requests[index].arrival_us * 1e-6 - clock()
+        look()
+        if state["nobody_left"]:
+            break
+        hand_out(index)
+    while len(finished) < len(requests) and not state["nobody_left"]:     # all handed out: wait for the results
+        sleep(watch_period_s)
+        look()
     store.set("closed", "1")
-    return {"assignment": assignment, "handed": handed, "failed_replicas": failed,
+    return {"assignment": assignment, "handed": [len(indices) for indices in handed], "failed_replicas": failed,
+            "redispatched_requests": redispatched,
+            "unfinished_requests": sorted(requests[index].request_id for index in range(len(requests))
+                                          if index not in finished),
             "outstanding_tokens": [dispatcher.load(replica) for replica in range(replicas)]}
 
 
@@ -236,8 +272,10 @@ def run_replica(engine, store, replica: int, requests: list[Request], origin_s: 
     reports finished tokens back.  `engine` needs submit / step / active / queued (a ServingEngine)."""
     records = {}
     taken = 0
+    reported = 0
     closed = False
     first_step_us = None
+    busy_until_us = 0
     last_beat = 0.0
     while True:
         if clock() - last_beat >= HEARTBEAT_PERIOD_S:
@@ -245,9 +283,11 @@ def run_replica(engine, store, replica: int, requests: list[Request], origin_s: 
             store.set(f"beat/{replica}", repr(last_beat))
         count = int(store.add(f"n/{replica}", 0))
         while taken < count:
-            request = requests[int(store.get(f"q/{replica}/{taken}"))]
+            index = int(store.get(f"q/{replica}/{taken}"))
+            request = requests[index]
             taken += 1
-            records[request.request_id] = {"request_id": request.request_id, "prompt_len": len(request.prompt),
+            records[request.request_id] = {"request_id": request.request_id, "index": index,
+                                           "prompt_len": len(request.prompt),
                                            "arrival_us": request.arrival_us, "times_us": [], "tokens": 0,
                                            "reused_tokens": 0, "rejected": None, "replica": replica,
                                            "estimated_tokens": estimated_tokens(request)}
@@ -265,21 +305,31 @@ def run_replica(engine, store, replica: int, requests: list[Request], origin_s: 
         if first_step_us is None:
             first_step_us = now_us
         events, _ = engine.step(now_us)
+        if events:
+            busy_until_us = int((clock() - origin_s) * 1e6)
         finished_tokens = 0
+        finished_now = []
         for request_id, _, finished, time_us, reused, rejected in events:
             record = records[request_id]
             if rejected:
                 record["rejected"] = REJECT_REASONS.get(rejected, str(rejected))
                 finished_tokens += record["estimated_tokens"]
+                finished_now.append(record["index"])
                 continue
             record["times_us"].append(time_us)
             record["tokens"] += 1
             record["reused_tokens"] = reused
             if finished:
                 finished_tokens += record["estimated_tokens"]
+                finished_now.append(record["index"])
         if finished_tokens:
             store.add(f"done/{replica}", finished_tokens)
-    last_us = int((clock() - origin_s) * 1e6)
+        for index in finished_now:                      # which requests are finished: what the front re-dispatches by
+            store.set(f"f/{replica}/{reported}", str(index))
+            reported += 1
+        if finished_now:
+            store.add(f"fin/{replica}", len(finished_now))
+    last_us = busy_until_us          # when this replica produced its last token (it then idles until the trace closes)
     out = []
     for record in records.values():
         times = record.pop("times_us")
