@@ -651,7 +651,11 @@ int32_t forward_ragged(lfm25_decode_executor* self, const lfm25_model* model, co
                 decode.block_tables = tables_slice;
                 decode.request_slots = slice_of(batch->request_slots, decode_tokens);
                 decode.position_ids = slice_of(batch->positions, decode_tokens);
-                decode.partials = slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
+                const bool in_kernel_merge = lfm25::option(lfm25::kOptSplitkClusterMerge) != 0 &&
+                                             merge_in_kernel_preferred(decode_tokens, splits);
+                decode.partials = in_kernel_merge
+                                      ? slice_of(static_cast<float*>(nullptr), 0)
+                                      : slice_of(self->partials, lfm25_splitk_workspace_elements(self->maximum_rows));
                 decode.output = slice_of(self->post_operator, decode_tokens * kHidden);
                 decode.num_tokens = decode_tokens;
                 decode.num_pages = model->num_pages;
