@@ -2,7 +2,7 @@
  * lfm25_b200 -- C ABI of the B200-native decode path of the LFM2.5-1.2B runtime.
  *
  * This is the drop-in boundary: one entry point per launch method of the reference's
- * `src/cuda/kernels/*.rs` wrappers and `src/cuda/blaslt` calls that lie on the decode path.
+ * `src/cuda/kernels/` wrappers (one .rs file per kernel family) and `src/cuda/blaslt` calls that lie on the decode path.
  * Each `*_launch` struct has the fields of the Rust `XLaunch<'_>` struct it replaces, in the
  * same order, with every `&CudaSlice<T>` turned into (device pointer, element count).
  * A Rust host binds these with `#[repr(C)]` structs and an `extern "C"` block.
