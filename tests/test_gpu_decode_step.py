@@ -348,3 +348,53 @@ def test_changed_batch_buffers_capture_again(device):
         executor.close()
         reference.close()
         blaslt.close()
+
+
+@pytest.mark.parametrize("rows,low,high", [(8, 1500, 3000), (40, 600, 2500)])
+def test_split_merge_inside_the_kernel_changes_no_bit_of_a_step(device, library_option, rows, low, high):
+    """Small batches of long contexts split the KV axis (8 splits at 8 rows, 2 at 40); the executor then merges the
+    splits inside the attention kernel (a cluster per token and KV head) instead of through records and the merge
+    kernel.  Two self-feeding steps, eagerly and from the graph, with the switch on and off: sampled ids, logits and
+    caches bit for bit."""
+    steps = 2
+    pages = 8192
+    batch = workloads.ragged_decode_batch(41, rows, low, high, pages, steps + 1)
+    token_ids = np.random.default_rng(41).integers(0, lfm_model.VOCAB, size=rows).astype(np.uint32)
+    assert ops.splitk_decode_splits(rows, int(batch.contexts.max()) + steps + 1, 16) in (2, 4, 8)
+
+    def run(in_kernel, use_graph):
+        library_option("splitk_cluster_merge", in_kernel)
+        with torch.cuda.stream(torch.cuda.Stream()):
+            model = lfm_model.RandomModel(23, device, pages, rows)
+            model.fill_caches(24)
+            blaslt = ops.BlasLt()
+            executor = lfm_model.DecodeExecutor(blaslt, rows)
+            device_batch = lfm_model.DecodeBatch(device, batch.block_tables, batch.request_slots, batch.positions(0),
+                                                 token_ids, int(batch.contexts.max()) + steps + 1)
+            executor.forward(model, device_batch, use_fp8=True, advance=False)
+            history = [executor.sampled(rows)]
+            for _ in range(steps):
+                if use_graph:
+                    executor.step_graph(model, device_batch, use_fp8=True)
+                else:
+                    executor.forward(model, device_batch, use_fp8=True, advance=True)
+                history.append(executor.sampled(rows))
+            state = [executor.logits(rows)]
+            state += [bits_of(layer.tensors["key_cache" if layer.is_attention else "conv_state"])
+                      for layer in model.layers]
+            kernels = executor.graph_kernels()
+            torch.cuda.current_stream().synchronize()
+            executor.close()
+            blaslt.close()
+            return history, state, kernels
+
+    want_history, want_state, _ = run(0, False)
+    for in_kernel, use_graph in ((1, False), (1, True), (0, True)):
+        history, state, kernels = run(in_kernel, use_graph)
+        assert all(np.array_equal(a, b) for a, b in zip(history, want_history))
+        assert all(np.array_equal(a, b) for a, b in zip(state, want_state))
+        if use_graph and in_kernel:
+            merged_inside = kernels
+        if use_graph and not in_kernel:
+            assert merged_inside == kernels - 6          # one merge kernel per attention layer fewer
+    assert ops.device_status()[0] == 0
