@@ -606,6 +606,20 @@ GemmRowsPlan gemm_rows_plan(size_t m, size_t n, size_t k_bytes, bool gated, size
     uint32_t ctas_per_sm = tuning.ctas_per_sm;
     const bool can_split = !gated && exchange_bytes > 0;
     const bool few_rows = tiles_of(64) * slices < 148;
+    // The gated Gate/Up of the decode step at 64..128 rows: one wave of 112-row tiles (8192 features: 147 CTAs on 148
+    // SMs), six ring slots in the whole shared memory of an SM and two issuing warps.  Measured inside the step
+    // against the general rule below (which picks 64-row tiles, two CTAs per SM): 64 sequences 1.010 -> 1.000 ms,
+    // 80: 1.124 -> 1.113, 96: 1.189 -> 1.179, 112: level, 128: 1.307 -> 1.304.
+    uint32_t preset_stages = 0;
+    uint32_t preset_issuers = 0;
+    if (gated && n_tile == 0 && tuning.stages == 0 && tuning.issuers == 0 && tuning.smem_bytes == 0 &&
+        ctas_per_sm == 0 && slices == 1 && m >= 64 && m <= 128 && tiles_of(112) > 120 && tiles_of(112) <= 148) {
+        n_tile = 112;
+        ctas_per_sm = 1;
+        budget = kSmemLimit;
+        preset_stages = 6;
+        preset_issuers = 2;
+    }
     if (n_tile == 0) {
         if (few_rows && can_split && splits != 1) {
             n_tile = rows < 128 ? round_up(rows, 16) : 128;
@@ -666,7 +680,7 @@ GemmRowsPlan gemm_rows_plan(size_t m, size_t n, size_t k_bytes, bool gated, size
     }
     const uint32_t stage_bytes = n_tile * kBlockK + x_bytes;
     const uint32_t k_least = k_blocks / splits;
-    uint32_t stages = tuning.stages != 0 ? tuning.stages : slots(n_tile);
+    uint32_t stages = tuning.stages != 0 ? tuning.stages : (preset_stages != 0 ? preset_stages : slots(n_tile));
     if (stages < 3 && tuning.stages == 0) {
         stages = 3;   // fewer than three slots cannot keep the stream going: take what three need
     }
@@ -680,7 +694,7 @@ GemmRowsPlan gemm_rows_plan(size_t m, size_t n, size_t k_bytes, bool gated, size
     // most one phase behind).  A slot count in between is rounded down if four or more slots remain, else up.
     const uint32_t accumulator_columns = round_up(n_tile, 32);
     auto fits_twice = [&](uint32_t count) { return 2 * (count * stage_bytes + fixed + 1024) <= 227 * 1024; };
-    uint32_t issuers = tuning.issuers != 0 ? tuning.issuers : kMaxIssuers;
+    uint32_t issuers = tuning.issuers != 0 ? tuning.issuers : (preset_issuers != 0 ? preset_issuers : kMaxIssuers);
     if (issuers == 3) issuers = 2;
     if (issuers > kMaxIssuers) issuers = kMaxIssuers;
     while (issuers > 1 && (issuers * a_tiles * accumulator_columns > 512 || issuers > k_least)) issuers /= 2;
