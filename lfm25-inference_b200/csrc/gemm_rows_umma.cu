@@ -606,13 +606,15 @@ GemmRowsPlan gemm_rows_plan(size_t m, size_t n, size_t k_bytes, bool gated, size
     uint32_t ctas_per_sm = tuning.ctas_per_sm;
     const bool can_split = !gated && exchange_bytes > 0;
     const bool few_rows = tiles_of(64) * slices < 148;
-    // The gated Gate/Up of the decode step at 64..128 rows: one wave of 112-row tiles (8192 features: 147 CTAs on 148
+    // The Gate/Up of the decode step at 64..128 rows: one wave of 112-row tiles (8192 features: 147 CTAs on 148
     // SMs), six ring slots in the whole shared memory of an SM and two issuing warps.  Measured inside the step
-    // against the general rule below (which picks 64-row tiles, two CTAs per SM): 64 sequences 1.010 -> 1.000 ms,
-    // 80: 1.124 -> 1.113, 96: 1.189 -> 1.179, 112: level, 128: 1.307 -> 1.304.
+    // for the gated form against the general rule below (which picks 64-row tiles, two CTAs per SM): 64 sequences
+    // 1.010 -> 1.000 ms, 80: 1.124 -> 1.113, 96: 1.189 -> 1.179, 112: level, 128: 1.307 -> 1.304.  The plain form
+    // of the same shape takes the same plan, so that both split the K blocks over the issuing warps alike and the
+    // gated launch keeps giving the bits of the plain launch followed by the SiLU * Up kernel.
     uint32_t preset_stages = 0;
     uint32_t preset_issuers = 0;
-    if (gated && n_tile == 0 && tuning.stages == 0 && tuning.issuers == 0 && tuning.smem_bytes == 0 &&
+    if (n_tile == 0 && tuning.stages == 0 && tuning.issuers == 0 && tuning.smem_bytes == 0 &&
         ctas_per_sm == 0 && slices == 1 && m >= 64 && m <= 128 && tiles_of(112) > 120 && tiles_of(112) <= 148) {
         n_tile = 112;
         ctas_per_sm = 1;
