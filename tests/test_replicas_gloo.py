@@ -240,3 +240,40 @@ def test_front_stops_using_a_replica_that_gives_no_sign_of_life():
     served = {record["request_id"] for record in survivor["requests"] if record["generated"] == 30}
     assert served == {request.request_id for request in trace}
     assert set(front["redispatched_requests"]) <= served
+
+
+def test_dispatched_serving_line_adds_up_the_replicas():
+    """The line of the dispatched serving run from the replicas' records (host arithmetic only): tokens and requests
+    are summed over the replicas, the makespan is the slowest replica's, percentiles are taken over all requests."""
+    sys.path.insert(0, ROOT)
+    import argparse
+    import numpy as np
+    import bench
+    from lfm25_inference_b200 import serving
+
+    def record(request_id, replica, generated, ttft_us, tpot_us, rejected=None):
+        return {"request_id": request_id, "prompt_len": 100, "arrival_us": 0, "generated": generated,
+                "ttft_us": ttft_us, "tpot_us": tpot_us, "last_token_us": 0, "reused_tokens": 0, "rejected": rejected,
+                "replica": replica}
+
+    clocks = {"sm_mhz": 1965.0, "sm_max_mhz": 1965.0, "reasons": []}
+    stats = {"steps": 10, "mixed_steps": 4, "decode_steps": 6, "gpu_ms": 900.0, "reused_prompt_tokens": 256,
+             "generated_tokens": 0, "prefill_tokens": 0}
+    gathered = [
+        {"replica": 0, "requests": [record(0, 0, 10, 1000, 2000.0), record(1, 0, 30, 3000, 4000.0)],
+         "drained_us": 1_000_000, "stats": dict(stats), "prefix_cache": {"hits": 1, "misses": 1}, "clocks": clocks},
+        {"replica": 1, "requests": [record(2, 1, 20, 2000, 3000.0), record(3, 1, 0, None, 0.0, rejected="slots")],
+         "drained_us": 2_000_000, "stats": dict(stats), "prefix_cache": {"hits": 0, "misses": 2}, "clocks": clocks},
+    ]
+    trace = [serving.Request(index, np.zeros(100, dtype=np.uint32), 30, 0) for index in range(4)]
+    arguments = argparse.Namespace(warmup=1, rate=2.0, no_fp8=False, admission_control=True)
+    front = {"handed": [2, 2], "outstanding_tokens": [0, 0], "failed_replicas": [], "redispatched_requests": [],
+             "unfinished_requests": []}
+    line = bench.dispatched_serving_line(arguments, 2, trace, gathered, front)
+    assert line["n_gpus"] == 2 and line["ms_per_step"] == 2000.0
+    assert line["generated_tokens"] == 60 and line["value"] == pytest.approx(30.0)        # 60 tokens in 2 s
+    assert line["rejected_requests"] == 1 and line["requests_per_s"] == pytest.approx(1.5)
+    assert line["ttft_p50_ms"] == pytest.approx(2.0) and line["tpot_p50_ms"] == pytest.approx(3.0)
+    assert line["prefix_cache"]["hits"] == 1 and line["prefix_cache"]["misses"] == 3
+    assert [entry["requests"] for entry in line["per_replica"]] == [2, 2]
+    assert line["front"]["redispatched_requests"] == 0 and line["config"]["replicas"] == 2
